@@ -1,0 +1,104 @@
+"""ctypes loader for the plain-C oracle (TEST INFRASTRUCTURE ONLY).
+
+Builds ``liblucid_oracle.so`` next to the source on first use when it is missing
+(gcc only; see ``oracle/Makefile``)."""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_DIR = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_DIR, "liblucid_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    src = os.path.join(_DIR, "lucid_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _DIR, "-B", "liblucid_oracle.so"],
+                              stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _params(scale, zp, rows, cols):
+    s = np.ascontiguousarray(np.asarray(scale, dtype=np.float32).reshape(-1))
+    z = np.ascontiguousarray(np.broadcast_to(np.asarray(zp, dtype=np.float32).reshape(-1), s.shape))
+    return s, z
+
+
+def quantize(x, scale, zp, ch_mode, qmin, qmax, storage=np.int8):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    s, z = _params(scale, zp, rows, cols)
+    out = np.empty((rows, cols), dtype=storage)
+    fn = lib().lo_quantize_f32_s8 if storage == np.int8 else lib().lo_quantize_f32_s16
+    fn(_p(x), C.c_size_t(rows), C.c_size_t(cols), _p(s), _p(z), C.c_int(ch_mode),
+       C.c_int(qmin), C.c_int(qmax), _p(out))
+    return out
+
+
+def dequantize(q, scale, zp, ch_mode):
+    q = np.ascontiguousarray(q)
+    rows, cols = q.shape
+    s, z = _params(scale, zp, rows, cols)
+    out = np.empty((rows, cols), dtype=np.float32)
+    fn = lib().lo_dequantize_s8_f32 if q.dtype == np.int8 else lib().lo_dequantize_s16_f32
+    fn(_p(q), C.c_size_t(rows), C.c_size_t(cols), _p(s), _p(z), C.c_int(ch_mode), _p(out))
+    return out
+
+
+def fake_quantize(x, scale, zp, ch_mode, qmin, qmax):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    s, z = _params(scale, zp, rows, cols)
+    out = np.empty((rows, cols), dtype=np.float32)
+    lib().lo_fake_quantize_f32(_p(x), C.c_size_t(rows), C.c_size_t(cols), _p(s), _p(z),
+                               C.c_int(ch_mode), C.c_int(qmin), C.c_int(qmax), _p(out))
+    return out
+
+
+def minmax_rows(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    mn = np.empty(rows, dtype=np.float32)
+    mx = np.empty(rows, dtype=np.float32)
+    lib().lo_minmax_rows_f32(_p(x), C.c_size_t(rows), C.c_size_t(cols), _p(mn), _p(mx))
+    return mn, mx
+
+
+def calculate_qparams(mn, mx, symmetric, signed, qmin, qmax, eps=1e-8):
+    mn = np.ascontiguousarray(np.asarray(mn, dtype=np.float32).reshape(-1))
+    mx = np.ascontiguousarray(np.asarray(mx, dtype=np.float32).reshape(-1))
+    s = np.empty_like(mn)
+    z = np.empty_like(mn)
+    lib().lo_calculate_qparams(_p(mn), _p(mx), C.c_size_t(mn.size), C.c_int(int(symmetric)),
+                               C.c_int(int(signed)), C.c_int(qmin), C.c_int(qmax),
+                               C.c_float(eps), _p(s), _p(z))
+    return s, z
+
+
+def gemm_i8(a, w):
+    a = np.ascontiguousarray(a)
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    assert a.dtype in (np.int8, np.uint8)
+    m, k = a.shape
+    n = w.shape[0]
+    acc = np.empty((m, n), dtype=np.int32)
+    lib().lo_gemm_i8_i32(_p(a), C.c_int(int(a.dtype == np.int8)), _p(w), C.c_size_t(m),
+                         C.c_size_t(n), C.c_size_t(k), _p(acc))
+    return acc
