@@ -1,0 +1,184 @@
+/*
+ * lucid_b200 -- C ABI of the B200 (sm_100a) quantized-inference kernels.
+ *
+ * Drop-in boundary for Lucid's quantization hot path.  Every entry point takes
+ * plain device pointers and sizes; the caller owns all memory (inputs, outputs
+ * and workspaces); nothing is retained after the call returns.  All work is
+ * enqueued on the given CUDA stream (a cudaStream_t passed as void*; NULL is
+ * the legacy default stream) and the functions return without synchronising.
+ *
+ * Return value: 0 on success, otherwise one of the LQ_ERR_* codes; the text of
+ * the last failure on the calling thread is available from lq_last_error().
+ * Codes map onto the reference's error taxonomy (lucid/_C/core/Error.h:63-495):
+ * SHAPE -> ShapeMismatch, DTYPE -> DtypeMismatch, DEVICE -> DeviceMismatch,
+ * UNSUPPORTED -> NotImplementedError, others -> LucidError.
+ *
+ * Arithmetic contract (bit-exact with the reference's CPU path): every step is
+ * one IEEE binary32 operation in the reference's order, division is a true
+ * divide, rounding is ties-to-even.
+ */
+#ifndef LUCID_B200_H_
+#define LUCID_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LQ_VERSION 100
+
+enum lq_status {
+  LQ_OK = 0,
+  LQ_ERR_SHAPE = 1,        /* sizes inconsistent or zero where not allowed            */
+  LQ_ERR_DTYPE = 2,        /* dtype code not valid for this argument                  */
+  LQ_ERR_DEVICE = 3,       /* null pointer where a device pointer is required         */
+  LQ_ERR_ALIGNMENT = 4,    /* pointer / leading dimension violates a stated alignment */
+  LQ_ERR_UNSUPPORTED = 5,  /* valid request this build does not implement             */
+  LQ_ERR_WORKSPACE = 6,    /* workspace too small                                     */
+  LQ_ERR_CUDA = 7,         /* CUDA runtime / driver error (text in lq_last_error)     */
+  LQ_ERR_TIMEOUT = 8       /* a bounded device-side wait ran out                      */
+};
+
+enum lq_dtype {
+  LQ_F32 = 0,
+  LQ_BF16 = 1,
+  LQ_S8 = 2,
+  LQ_U8 = 3,
+  LQ_S16 = 4, /* storage of the reference's quint8 codes (lucid/quantization/_qscheme.py:243) */
+  LQ_S32 = 5
+};
+
+/* How scale / zero_point broadcast over a (rows, cols) view. */
+enum lq_ch_mode {
+  LQ_PER_TENSOR = 0, /* one value                                             */
+  LQ_PER_ROW = 1,    /* one value per row    (ch_axis = 0; per-token)         */
+  LQ_PER_COL = 2     /* one value per column (ch_axis = last)                 */
+};
+
+int lq_version(void);
+/* Copies the calling thread's last error text (NUL terminated) into buf. */
+int lq_last_error(char* buf, size_t n);
+
+/* ---- calibration ------------------------------------------------------- */
+
+/* Bytes of workspace lq_minmax needs for the per-tensor mode.  The workspace
+ * must be zero-filled once before its first use; the kernel leaves it zeroed
+ * again, so it can be reused by later calls on the same stream. */
+size_t lq_minmax_workspace_bytes(void);
+
+/* Running-range reduction.
+ * Replaces MinMaxObserver.forward (lucid/quantization/observer.py:364-370; the
+ * x.min()/x.max() pair of lucid/nn/quantized/dynamic/linear.py:87-89) for
+ * mode = LQ_PER_TENSOR and PerChannelMinMaxObserver.forward
+ * (lucid/quantization/observer.py:635-648) for mode = LQ_PER_ROW.
+ * x: (rows, cols) row-major, in_dtype LQ_F32 or LQ_BF16.
+ * out_min / out_max: 1 float (per tensor) or rows floats. */
+int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, int mode, float* out_min,
+              float* out_max, void* workspace, size_t workspace_bytes, void* stream);
+
+/* (scale, zero_point) from observed ranges, on device.
+ * Replaces calculate_qparams (lucid/quantization/_qparams.py:190-215). */
+int lq_calculate_qparams(const float* min_val, const float* max_val, size_t n, int symmetric,
+                         int is_signed, int qmin, int qmax, float eps, float* scale,
+                         float* zero_point, void* stream);
+
+/* ---- affine encode / decode ------------------------------------------- */
+
+/* q = clip(rint(x / s) + z, qmin, qmax) cast to out_dtype.
+ * Replaces quantize (lucid/quantization/_functional.py:164-182).
+ * scale / zero_point are device pointers (1, rows or cols floats according to
+ * ch_mode); when scale is NULL the host scalars scale_value / zp_value are used
+ * (ch_mode must be LQ_PER_TENSOR).  in_dtype LQ_F32 | LQ_BF16; out_dtype LQ_S8 |
+ * LQ_U8 | LQ_S16. */
+int lq_quantize(const void* x, int in_dtype, size_t rows, size_t cols, const float* scale,
+                const float* zero_point, float scale_value, float zp_value, int ch_mode, int qmin,
+                int qmax, void* out, int out_dtype, void* stream);
+
+/* x = (f32(q) - z) * s.  Replaces dequantize
+ * (lucid/quantization/_functional.py:269-281).  q_dtype LQ_S8 | LQ_U8 | LQ_S16;
+ * out_dtype LQ_F32 | LQ_BF16 (bf16 = the f32 result rounded once). */
+int lq_dequantize(const void* q, int q_dtype, size_t rows, size_t cols, const float* scale,
+                  const float* zero_point, float scale_value, float zp_value, int ch_mode,
+                  void* out, int out_dtype, void* stream);
+
+/* (clip(rint(x / s) + z, qmin, qmax) - z) * s, forward only.  Replaces
+ * _FakeQuantizeAffine.forward (lucid/quantization/_functional.py:299-313).
+ * When mask is non-NULL the straight-through saturation mask
+ * (lucid/quantization/_functional.py:315-317) is written as f32 0/1. */
+int lq_fake_quantize(const float* x, size_t rows, size_t cols, const float* scale,
+                     const float* zero_point, float scale_value, float zp_value, int ch_mode,
+                     int qmin, int qmax, float* out, float* mask, void* stream);
+
+/* Per-token symmetric activation encode in one pass over HBM: row abs-max ->
+ * scale = max(absmax / ((qmax - qmin) / 2), eps) -> codes.  Equals
+ * PerChannelMinMaxObserver(ch_axis=0) -> calculate_qparams(symmetric, signed)
+ * -> quantize(ch_axis=0) (lucid/quantization/observer.py:635-648,
+ * _qparams.py:203-207, _functional.py:180-182).  in_dtype LQ_F32 | LQ_BF16
+ * (bf16 is upcast to f32 first).  out: int8 (rows, cols); out_scale: rows. */
+int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, size_t cols, int qmin, int qmax,
+                          float eps, int8_t* out, float* out_scale, void* stream);
+
+/* ---- contraction -------------------------------------------------------- */
+
+enum lq_activation { LQ_ACT_NONE = 0, LQ_ACT_RELU = 1, LQ_ACT_SILU_GATE = 2 };
+
+/* Epilogue applied to the exact int32 accumulator acc[m,n] = sum_k a[m,k]*b[n,k]:
+ *
+ *   t = acc - a_zp * b_rowsum[n]                       (exact, int32)
+ *   out_dtype LQ_S32:  out = t
+ *   otherwise:         y = f32(t) * (a_scale[m] * b_scale[n])
+ *                      y = y + bias[n]                  (if bias)
+ *                      y = max(y, 0)                    (LQ_ACT_RELU)
+ *     LQ_F32 / LQ_BF16: out = y (bf16: rounded once)
+ *     LQ_S8 / LQ_U8:    out = clip(rint(y / out_scale) + out_zp, qmin, qmax)
+ *
+ * Every float step is a separate binary32 operation (no FMA contraction).
+ * LQ_ACT_SILU_GATE: b holds [gate; up] interleaved in blocks of 128 rows; the
+ * output has N/2 columns: silu(y_gate) * y_up.
+ *
+ * This is the integer form of nn.quantized.Linear.forward
+ * (lucid/nn/quantized/linear.py:199-215) and dynamic.Linear.forward
+ * (lucid/nn/quantized/dynamic/linear.py:84-99), which the reference evaluates
+ * as dequantize -> float GEMM -> fake_quantize. */
+typedef struct lq_epilogue {
+  int32_t out_dtype;       /* lq_dtype of out                                     */
+  int32_t act;             /* lq_activation                                       */
+  int32_t a_scale_mode;    /* LQ_PER_TENSOR (1 float) or LQ_PER_ROW (M floats)    */
+  int32_t qmin, qmax;      /* requantisation grid (LQ_S8 / LQ_U8 outputs)         */
+  int32_t reserved;
+  const float* a_scale;    /* device                                              */
+  const float* a_zp;       /* device, 1 float holding an integer value, or NULL   */
+  const int32_t* b_rowsum; /* device, N ints: sum_k b[n,k]; required with a_zp    */
+  const float* b_scale;    /* device, N floats                                    */
+  const float* bias;       /* device, N floats, or NULL                           */
+  const float* out_scale;  /* device, 1 float (requantising outputs)              */
+  const float* out_zp;     /* device, 1 float                                     */
+} lq_epilogue_t;
+
+/* out(M, N) = epilogue(a(M, K) . b(N, K)^T); a and b are K-contiguous 8-bit
+ * codes (a signed or unsigned, b signed); K % 16 == 0 and a, b 16-byte aligned
+ * (TMA), ldo in elements of out.  Needs no workspace.
+ * `status` (device, 1 int32, may be NULL) receives LQ_ERR_TIMEOUT if a bounded
+ * device-side wait ran out; it is left untouched otherwise. */
+int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+               const lq_epilogue_t* ep, void* out, size_t ldo, int32_t* status, void* stream);
+
+/* sum_k b[n,k] for the zero-point correction term (N ints). */
+int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream);
+
+/* NHWC implicit-GEMM convolution on 8-bit codes with KRSC signed weights:
+ * out[n,p,q,k] = epilogue(sum_{r,s,c} x[n, p*stride+r-pad, q*stride+s-pad, c] * w[k,r,s,c]).
+ * Out-of-image taps read code 0, which is exact when the activation zero point
+ * is 0 (symmetric or post-ReLU grids).  Integer form of
+ * nn.quantized.Conv2d.forward (lucid/nn/quantized/conv.py:168-184).
+ * C % 16 == 0; ep->a_zp must be NULL. */
+int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H, size_t W,
+                      size_t C, size_t K, size_t R, size_t S, size_t stride, size_t pad,
+                      const lq_epilogue_t* ep, void* out, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUCID_B200_H_ */

@@ -1,0 +1,188 @@
+"""ctypes binding of ``liblucid_b200.so`` (the C ABI in ``include/lucid_b200.h``).
+
+This is the thin shim that sits where the reference registers its
+``engine.quantized`` ops (lucid/_C/bindings/bind_quantized.cpp:18-30): raw
+device pointers in, status code out.  There is no CPU fallback: a missing
+library or a non-CUDA tensor raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "liblucid_b200.so")
+
+# dtype / mode codes of include/lucid_b200.h
+F32, BF16, S8, U8, S16, S32 = 0, 1, 2, 3, 4, 5
+PER_TENSOR, PER_ROW, PER_COL = 0, 1, 2
+ACT_NONE, ACT_RELU, ACT_SILU_GATE = 0, 1, 2
+ERR_TIMEOUT = 8
+
+_TORCH_CODE = {
+    torch.float32: F32, torch.bfloat16: BF16, torch.int8: S8, torch.uint8: U8,
+    torch.int16: S16, torch.int32: S32,
+}
+
+
+# ---- error taxonomy, named after the reference's (lucid/_C/core/Error.h:63-495)
+class LucidError(RuntimeError):
+    pass
+
+
+class ShapeMismatch(LucidError):
+    pass
+
+
+class DtypeMismatch(LucidError):
+    pass
+
+
+class DeviceMismatch(LucidError):
+    pass
+
+
+class EngineUnavailable(LucidError):
+    pass
+
+
+_STATUS_EXC = {1: ShapeMismatch, 2: DtypeMismatch, 3: DeviceMismatch, 4: ShapeMismatch,
+               5: NotImplementedError, 6: LucidError, 7: LucidError, 8: TimeoutError}
+
+
+class Epilogue(C.Structure):
+    _fields_ = [
+        ("out_dtype", C.c_int32), ("act", C.c_int32), ("a_scale_mode", C.c_int32),
+        ("qmin", C.c_int32), ("qmax", C.c_int32), ("reserved", C.c_int32),
+        ("a_scale", C.c_void_p), ("a_zp", C.c_void_p), ("b_rowsum", C.c_void_p),
+        ("b_scale", C.c_void_p), ("bias", C.c_void_p), ("out_scale", C.c_void_p),
+        ("out_zp", C.c_void_p),
+    ]
+
+
+_SIGNATURES = {
+    "lq_version": (C.c_int, []),
+    "lq_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
+    "lq_minmax_workspace_bytes": (C.c_size_t, []),
+    "lq_minmax": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p,
+                            C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lq_calculate_qparams": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
+                                       C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
+                                       C.c_void_p]),
+    "lq_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                              C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                              C.c_void_p]),
+    "lq_dequantize": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_void_p,
+                                C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p, C.c_int,
+                                C.c_void_p]),
+    "lq_fake_quantize": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                                   C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]),
+    "lq_quantize_per_token": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int,
+                                        C.c_int, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_gemm_s8": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                             C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "lq_rowsum_s8": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "lq_conv2d_nhwc_s8": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p] + [C.c_size_t] * 9 +
+                          [C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+
+
+def library_present() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def load():
+    """Load the shared library (no GPU needed) and declare every signature."""
+    global _lib
+    if _lib is None:
+        if not library_present():
+            raise EngineUnavailable(
+                f"{LIB_PATH} is missing: build it with `python -m lucid_b200.csrc.build` "
+                "(there is no CPU fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def is_available() -> bool:
+    """True when the kernels can run: library built and a CUDA device visible."""
+    return library_present() and torch.cuda.is_available()
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    load().lq_last_error(buf, 512)
+    return buf.value.decode(errors="replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise _STATUS_EXC.get(rc, LucidError)(f"lucid_b200 [{rc}]: {last_error()}")
+
+
+def code_of(dt: torch.dtype) -> int:
+    try:
+        return _TORCH_CODE[dt]
+    except KeyError:
+        raise DtypeMismatch(f"dtype {dt} is not supported by the B200 quantized engine") from None
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{what} must be a tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise DeviceMismatch(
+            f"{what} lives on {t.device}; the B200 quantized engine only runs on CUDA tensors "
+            "(no CPU fallback)")
+
+
+def ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device=None):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# per-(device, stream) zero-initialised workspace for the per-tensor range reduction
+_minmax_ws: dict = {}
+
+
+def minmax_workspace(device: torch.device) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _minmax_ws.get(key)
+    if ws is None:
+        n = int(load().lq_minmax_workspace_bytes())
+        ws = torch.zeros(n, dtype=torch.uint8, device=device)
+        _minmax_ws[key] = ws
+    return ws
+
+
+# per-device word the GEMM writes LQ_ERR_TIMEOUT into when a bounded wait ran out
+_status_words: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    w = _status_words.get(device.index)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device.index] = w
+    return w
+
+
+def check_device_status(device: torch.device) -> None:
+    """Synchronising check of the timeout word (tests and debugging)."""
+    w = _status_words.get(device.index)
+    if w is not None and int(w.item()) != 0:
+        code = int(w.item())
+        w.zero_()
+        raise _STATUS_EXC.get(code, LucidError)(f"lucid_b200: device-side status {code}")

@@ -1,0 +1,34 @@
+// Error plumbing and version query of the C ABI.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace lq {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return LQ_OK;
+  g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+  return LQ_ERR_CUDA;
+}
+
+}  // namespace lq
+
+extern "C" int lq_version(void) { return LQ_VERSION; }
+
+extern "C" int lq_last_error(char* buf, size_t n) {
+  if (!buf || n == 0) return LQ_ERR_DEVICE;
+  const std::string& s = lq::g_last_error;
+  size_t k = s.size() < n - 1 ? s.size() : n - 1;
+  memcpy(buf, s.data(), k);
+  buf[k] = '\0';
+  return LQ_OK;
+}

@@ -1,0 +1,716 @@
+// s8 x s8 -> s32 contraction on the 5th-generation tensor cores (sm_100a):
+//   TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring ->
+//   tcgen05.mma kind::i8 issued by one thread -> int32 accumulators in TMEM ->
+//   epilogue warps read TMEM (tcgen05.ld), apply scales / bias / activation /
+//   requantisation in registers and store.
+//
+// One persistent CTA per SM; 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer
+// and TMEM owner, warps 2..5 = epilogue (one TMEM lane quadrant each).  Two
+// accumulator stages in TMEM let the epilogue of tile i overlap the mainloop of
+// tile i+1.  The same mainloop serves the Linear GEMM and the NHWC implicit-GEMM
+// convolution (the producer walks filter taps with shifted 4-D TMA boxes whose
+// out-of-image elements are zero-filled, which is the padding).
+//
+// Every wait on an mbarrier is bounded: when the budget runs out the CTA raises
+// an abort flag, reports LQ_ERR_TIMEOUT through the status word, drains and
+// frees its TMEM before returning, so the context stays usable.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lq {
+namespace {
+
+constexpr int BM = 128;       // rows of the CTA tile == TMEM lanes
+constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128B swizzle atom
+constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
+constexpr int kGemmThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kABytes = BM * BK;
+  static constexpr int kBBytes = BN * BK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  // ring + 1 KB alignment slack + barriers (512 B) + per-warp epilogue staging (4 x 3 KB)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + 4 * 3072;
+};
+
+struct Geometry {
+  // GEMM: rows = M.  Conv: output pixels arranged as (img, P, Q).
+  int conv;            // 0 GEMM, 1 implicit-GEMM conv
+  int M, N, K;         // GEMM extents (conv: M = imgs*P*Q, K = R*S*C)
+  int tiles_m, tiles_n, num_kb;
+  // conv only
+  int P, Q, C, R, S, pad;
+  int tile_h, tile_w, tiles_p, tiles_q;
+  int cblocks;         // ceil(C / BK)
+};
+
+struct Epi {
+  int out_dtype, act, a_scale_mode, qmin, qmax;
+  const float* a_scale;
+  const float* a_zp;
+  const int32_t* b_rowsum;
+  const float* b_scale;
+  const float* bias;
+  const float* out_scale;
+  const float* out_zp;
+  void* out;
+  long long ldo;  // elements
+  int n_out;      // columns of out (N, or N/2 for the gated epilogue)
+  int vec_ok;     // 16-byte vector stores allowed
+  int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the CTA is aborting or the budget ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tm), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, int c0, int c1,
+                                            int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows are 128 B, eight
+// rows form a 1024 B swizzle atom (stride-byte-offset), leading-byte-offset is 1
+// (ignored for swizzled K-major), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::i8: D = s32, A = u8|s8, B = s8, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int a_signed, int bn) {
+  return (2u << 4) | ((uint32_t)(a_signed ? 1 : 0) << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---- epilogue helpers -------------------------------------------------------------
+__device__ __forceinline__ float silu_f32(float x) {
+  return __fmul_rn(x, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
+}
+
+// y for accumulator `acc` of tile-local column n (params staged in shared memory).
+__device__ __forceinline__ float dequant_acc(int acc, int zpa, float sa, const int32_t* s_rowsum,
+                                             const float* s_bscale, const float* s_bias,
+                                             bool has_bias, int n) {
+  const int t = acc - zpa * s_rowsum[n];
+  float y = __fmul_rn((float)t, __fmul_rn(sa, s_bscale[n]));
+  if (has_bias) y = __fadd_rn(y, s_bias[n]);
+  return y;
+}
+
+// `words` holds 32 elements of type T packed little-endian; every index below is
+// a compile-time constant so the array stays in registers.
+template <typename T>
+__device__ __forceinline__ T extract_elem(const uint32_t* words, int j);
+template <>
+__device__ __forceinline__ int32_t extract_elem<int32_t>(const uint32_t* w, int j) { return (int32_t)w[j]; }
+template <>
+__device__ __forceinline__ float extract_elem<float>(const uint32_t* w, int j) { return __uint_as_float(w[j]); }
+template <>
+__device__ __forceinline__ uint16_t extract_elem<uint16_t>(const uint32_t* w, int j) {
+  return (uint16_t)(w[j >> 1] >> (16 * (j & 1)));
+}
+template <>
+__device__ __forceinline__ uint8_t extract_elem<uint8_t>(const uint32_t* w, int j) {
+  return (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+}
+
+template <typename T, int NWORDS>
+__device__ __forceinline__ void store_vals(T* dst, const uint32_t (&words)[32], int valid_elems,
+                                           bool vec) {
+  if (vec && valid_elems == 32) {
+#pragma unroll
+    for (int i = 0; i < NWORDS / 4; ++i)
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + 16 * i) =
+          make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid_elems) dst[j] = extract_elem<T>(words, j);
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const Geometry g, const Epi ep, const uint32_t idesc) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + C::kStages * C::kABytes;
+  uint8_t* tail = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);  // full[S], empty[S], tfull[2], tempty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 260);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, kEpiThreads / 32);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = g.tiles_m * g.tiles_n;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int tm_idx = tile % g.tiles_m;
+        const int n0 = (tile / g.tiles_m) * BN;
+        int m0 = tm_idx * BM, img = 0, p0 = 0, q0 = 0;
+        if (g.conv) {
+          const int per_img = g.tiles_p * g.tiles_q;
+          img = tm_idx / per_img;
+          const int rem = tm_idx - img * per_img;
+          p0 = (rem / g.tiles_q) * g.tile_h;
+          q0 = (rem % g.tiles_q) * g.tile_w;
+        }
+        const uint32_t a_bytes = g.conv ? (uint32_t)(BK * g.tile_w * g.tile_h) : (uint32_t)C::kABytes;
+        for (int kb = 0; kb < g.num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, a_bytes + (uint32_t)C::kBBytes);
+          const uint32_t a_dst = smem_u32(smem_a + stage * C::kABytes);
+          const uint32_t b_dst = smem_u32(smem_b + stage * C::kBBytes);
+          if (g.conv) {
+            const int tap = kb / g.cblocks;
+            const int cb = kb - tap * g.cblocks;
+            const int r = tap / g.S, s = tap - r * g.S;
+            tma_load_4d(a_dst, &tm_a, cb * BK, q0 + s - g.pad, p0 + r - g.pad, img, full);
+            tma_load_2d(b_dst, &tm_b, tap * g.C + cb * BK, n0, full);
+          } else {
+            tma_load_2d(a_dst, &tm_a, kb * BK, m0, full);
+            tma_load_2d(b_dst, &tm_b, kb * BK, n0, full);
+          }
+          if (++stage == C::kStages) stage = 0, phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < g.num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
+          const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K inside the swizzle atom = advancing the start address
+            tc_mma_i8(d_tmem, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
+                      idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);  // frees the stage once the MMAs have read it
+          if (++stage == C::kStages) stage = 0, phase ^= 1u;
+        }
+        if (!ok) break;
+        tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+        if (++acc == 2) acc = 0, acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;       // tile-local row == TMEM lane
+    // per-warp copy of the tile's per-column parameters (no cross-warp barrier)
+    uint8_t* stage_base = tail + 512 + (warp - 2) * 3072;
+    float* s_bscale = reinterpret_cast<float*>(stage_base);              // [256]
+    float* s_bias = reinterpret_cast<float*>(stage_base + 1024);         // [256]
+    int32_t* s_rowsum = reinterpret_cast<int32_t*>(stage_base + 2048);   // [256]
+    const bool has_bias = ep.bias != nullptr;
+    const bool gated = ep.act == LQ_ACT_SILU_GATE;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int tm_idx = tile % g.tiles_m;
+      const int n0 = (tile / g.tiles_m) * BN;
+      // stage the per-column parameters of this tile
+      __syncwarp();  // previous tile's readers are done
+      for (int j = lane; j < BN; j += 32) {
+        const int n = n0 + j;
+        const bool v = n < g.N;
+        s_bscale[j] = (v && ep.b_scale) ? ep.b_scale[n] : 1.0f;
+        s_bias[j] = (v && has_bias) ? ep.bias[n] : 0.0f;
+        s_rowsum[j] = (v && ep.b_rowsum) ? ep.b_rowsum[n] : 0;
+      }
+      __syncwarp();
+
+      // output row of this thread
+      bool row_ok;
+      long long out_row;
+      int m_global;
+      if (g.conv) {
+        const int per_img = g.tiles_p * g.tiles_q;
+        const int img = tm_idx / per_img;
+        const int rem = tm_idx - img * per_img;
+        const int ph = row / g.tile_w, qw = row - ph * g.tile_w;
+        const int p = (rem / g.tiles_q) * g.tile_h + ph;
+        const int q = (rem % g.tiles_q) * g.tile_w + qw;
+        row_ok = ph < g.tile_h && p < g.P && q < g.Q;
+        m_global = (img * g.P + p) * g.Q + q;
+      } else {
+        m_global = tm_idx * BM + row;
+        row_ok = m_global < g.M;
+      }
+      out_row = (long long)m_global * ep.ldo;
+      float sa = 1.0f;
+      if (ep.a_scale) sa = ep.a_scale_mode == LQ_PER_ROW ? (row_ok ? ep.a_scale[m_global] : 1.0f) : ep.a_scale[0];
+      const int zpa = ep.a_zp ? (int)ep.a_zp[0] : 0;
+      float so = 1.0f, zo = 0.0f;
+      if (ep.out_scale) so = ep.out_scale[0];
+      if (ep.out_zp) zo = ep.out_zp[0];
+      const float fqmin = (float)ep.qmin, fqmax = (float)ep.qmax;
+
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+
+      if (!gated) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          __syncwarp();  // tcgen05.ld is warp-aligned: reconverge after the divergent skip below
+          tc_ld32(taddr + c * 32, r);
+          tc_wait_ld();
+          const int ncol0 = n0 + c * 32;
+          const int valid = row_ok ? min(32, g.N - ncol0) : 0;
+          if (valid <= 0) continue;
+          const int32_t* rs = s_rowsum + c * 32;
+          const float* bs = s_bscale + c * 32;
+          const float* bb = s_bias + c * 32;
+          if (ep.out_dtype == LQ_S32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = (uint32_t)((int)r[j] - zpa * rs[j]);
+            store_vals<int32_t, 32>(reinterpret_cast<int32_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
+          } else {
+            float y[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              y[j] = dequant_acc((int)r[j], zpa, sa, rs, bs, bb, has_bias, j);
+              if (ep.act == LQ_ACT_RELU) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
+            }
+            if (ep.out_dtype == LQ_F32) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(y[j]);
+              store_vals<float, 32>(reinterpret_cast<float*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
+            } else if (ep.out_dtype == LQ_BF16) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                r[j] = f32_to_bf16_bits(y[2 * j]) | (f32_to_bf16_bits(y[2 * j + 1]) << 16);
+              store_vals<uint16_t, 16>(reinterpret_cast<uint16_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
+            } else {  // LQ_S8 / LQ_U8: requantise
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                  w |= ((uint32_t)(int)code_f32(y[4 * j + b], so, zo, fqmin, fqmax) & 0xffu) << (8 * b);
+                r[j] = w;
+              }
+              store_vals<uint8_t, 8>(reinterpret_cast<uint8_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
+            }
+          }
+        }
+      } else {
+        // gated: tile columns [0,BN/2) are gate, [BN/2,BN) the matching up columns
+        const int on0 = (tile / g.tiles_m) * (BN / 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          __syncwarp();
+          tc_ld32(taddr + c * 32, rg);
+          tc_ld32(taddr + BN / 2 + c * 32, ru);
+          tc_wait_ld();
+          const int ocol0 = on0 + c * 32;
+          const int valid = row_ok ? min(32, ep.n_out - ocol0) : 0;
+          if (valid <= 0) continue;
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float yg = dequant_acc((int)rg[j], zpa, sa, s_rowsum, s_bscale, s_bias, has_bias, c * 32 + j);
+            const float yu = dequant_acc((int)ru[j], zpa, sa, s_rowsum, s_bscale, s_bias, has_bias,
+                                         BN / 2 + c * 32 + j);
+            y[j] = __fmul_rn(silu_f32(yg), yu);
+          }
+          if (ep.out_dtype == LQ_F32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) rg[j] = __float_as_uint(y[j]);
+            store_vals<float, 32>(reinterpret_cast<float*>(ep.out) + out_row + ocol0, rg, valid, ep.vec_ok);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              rg[j] = f32_to_bf16_bits(y[2 * j]) | (f32_to_bf16_bits(y[2 * j + 1]) << 16);
+            store_vals<uint16_t, 16>(reinterpret_cast<uint16_t*>(ep.out) + out_row + ocol0, rg, valid, ep.vec_ok);
+          }
+        }
+      }
+      // hand the accumulator stage back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (++acc == 2) acc = 0, acc_phase ^= 1u;
+    }
+  }
+
+  // ===== teardown (every role falls through to here) =====
+  __syncwarp();
+  if (*abort_flag) {
+    // give copies / MMAs still in flight time to land before the CTA's shared
+    // memory and TMEM are released
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+    if (threadIdx.x == 0 && ep.status) atomicExch(ep.status, (int)LQ_ERR_TIMEOUT);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+int encode_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k, uint64_t row_stride,
+              uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {row_stride};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (2-D) failed: " + std::to_string((int)r));
+  return LQ_OK;
+}
+
+int encode_nhwc(CUtensorMap* tm, const void* base, uint64_t n, uint64_t h, uint64_t w, uint64_t c,
+                uint32_t box_w, uint32_t box_h) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[4] = {c, w, h, n};
+  cuuint64_t strides[3] = {c, c * w, c * w * h};
+  cuuint32_t box[4] = {(cuuint32_t)BK, box_w, box_h, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed: " + std::to_string((int)r));
+  return LQ_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMs;
+  }
+  return n;
+}
+
+int check_epilogue(const lq_epilogue_t* e, size_t N, const char* who, bool allow_gate) {
+  const std::string w(who);
+  if (!e) return fail(LQ_ERR_DEVICE, w + ": epilogue descriptor is null");
+  switch (e->out_dtype) {
+    case LQ_S32: case LQ_F32: case LQ_BF16: case LQ_S8: case LQ_U8: break;
+    default: return fail(LQ_ERR_DTYPE, w + ": out_dtype must be s32|f32|bf16|s8|u8");
+  }
+  if (e->act < LQ_ACT_NONE || e->act > LQ_ACT_SILU_GATE) return fail(LQ_ERR_UNSUPPORTED, w + ": unknown activation");
+  if (e->act == LQ_ACT_SILU_GATE) {
+    if (!allow_gate) return fail(LQ_ERR_UNSUPPORTED, w + ": gated epilogue is GEMM-only");
+    if (e->out_dtype != LQ_F32 && e->out_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, w + ": gated epilogue writes f32|bf16");
+    if (N % 256 != 0) return fail(LQ_ERR_SHAPE, w + ": gated epilogue needs N % 256 == 0 ([gate;up] in blocks of 128 rows)");
+  }
+  if (e->out_dtype != LQ_S32) {
+    if (!e->a_scale || !e->b_scale) return fail(LQ_ERR_DEVICE, w + ": a_scale and b_scale are required for scaled outputs");
+    if (e->a_scale_mode != LQ_PER_TENSOR && e->a_scale_mode != LQ_PER_ROW) return fail(LQ_ERR_SHAPE, w + ": a_scale_mode");
+  }
+  if (e->a_zp && !e->b_rowsum) return fail(LQ_ERR_DEVICE, w + ": a_zp needs b_rowsum");
+  if (e->out_dtype == LQ_S8 || e->out_dtype == LQ_U8) {
+    if (!e->out_scale || !e->out_zp) return fail(LQ_ERR_DEVICE, w + ": requantising outputs need out_scale/out_zp");
+    const int lo = e->out_dtype == LQ_S8 ? -128 : 0, hi = e->out_dtype == LQ_S8 ? 127 : 255;
+    if (e->qmin < lo || e->qmax > hi || e->qmin >= e->qmax) return fail(LQ_ERR_SHAPE, w + ": qmin/qmax outside the output dtype");
+  }
+  return LQ_OK;
+}
+
+size_t dtype_size(int dt) {
+  switch (dt) {
+    case LQ_S32: case LQ_F32: return 4;
+    case LQ_BF16: case LQ_S16: return 2;
+    default: return 1;
+  }
+}
+
+void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_out, int32_t* status) {
+  d->out_dtype = e->out_dtype, d->act = e->act, d->a_scale_mode = e->a_scale_mode;
+  d->qmin = e->qmin, d->qmax = e->qmax;
+  d->a_scale = e->a_scale, d->a_zp = e->a_zp, d->b_rowsum = e->b_rowsum, d->b_scale = e->b_scale;
+  d->bias = e->bias, d->out_scale = e->out_scale, d->out_zp = e->out_zp;
+  d->out = out, d->ldo = (long long)ldo, d->n_out = (int)n_out, d->status = status;
+  const size_t esz = dtype_size(e->out_dtype);
+  d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
+}
+
+template <int BN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep,
+           uint32_t idesc, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_s8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg<BN>::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
+  const int total = g.tiles_m * g.tiles_n;
+  const int grid = total < sm_count() ? total : sm_count();
+  gemm_s8_kernel<BN><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, st>>>(ta, tb, g, ep, idesc);
+  return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
+}
+
+}  // namespace
+}  // namespace lq
+
+using namespace lq;
+
+extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                          const lq_epilogue_t* e, void* out, size_t ldo, int32_t* status,
+                          void* stream) {
+  if (M == 0 || N == 0) return LQ_OK;
+  if (!a || !b || !out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8: null pointer");
+  if (K == 0) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: K must be positive");
+  if (K % 16 != 0) return fail(LQ_ERR_ALIGNMENT, "lq_gemm_s8: K must be a multiple of 16 (pad with zero codes)");
+  if (!aligned16(a) || !aligned16(b)) return fail(LQ_ERR_ALIGNMENT, "lq_gemm_s8: a and b must be 16-byte aligned");
+  if (M > 0x7fffffffu || N > 0x7fffffffu || K > 0x7fffffffu) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: extent too large");
+  int rc = check_epilogue(e, N, "lq_gemm_s8", true);
+  if (rc) return rc;
+  const size_t n_out = e->act == LQ_ACT_SILU_GATE ? N / 2 : N;
+  if (ldo < n_out) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: ldo smaller than the output width");
+
+  const bool wide = N > 128 || e->act == LQ_ACT_SILU_GATE;
+  const int bn = wide ? 256 : 128;
+  Geometry g = {};
+  g.conv = 0, g.M = (int)M, g.N = (int)N, g.K = (int)K;
+  g.tiles_m = (int)((M + BM - 1) / BM), g.tiles_n = (int)((N + bn - 1) / bn);
+  g.num_kb = (int)((K + BK - 1) / BK);
+  CUtensorMap ta, tb;
+  if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
+  if ((rc = encode_2d(&tb, b, N, K, K, (uint32_t)bn))) return rc;
+  Epi ep;
+  fill_epi(&ep, e, out, ldo, n_out, status);
+  const uint32_t idesc = make_idesc(a_signed, bn);
+  return wide ? launch<256>(ta, tb, g, ep, idesc, (cudaStream_t)stream)
+              : launch<128>(ta, tb, g, ep, idesc, (cudaStream_t)stream);
+}
+
+extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H,
+                                 size_t W, size_t C, size_t K, size_t R, size_t S, size_t stride,
+                                 size_t pad, const lq_epilogue_t* e, void* out, int32_t* status,
+                                 void* stream) {
+  if (N == 0 || K == 0) return LQ_OK;
+  if (!x || !w || !out) return fail(LQ_ERR_DEVICE, "lq_conv2d_nhwc_s8: null pointer");
+  if (H == 0 || W == 0 || C == 0 || R == 0 || S == 0) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: zero extent");
+  if (stride != 1) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: only stride 1 is implemented");
+  if (C % 16 != 0) return fail(LQ_ERR_ALIGNMENT, "lq_conv2d_nhwc_s8: C must be a multiple of 16");
+  if (!aligned16(x) || !aligned16(w)) return fail(LQ_ERR_ALIGNMENT, "lq_conv2d_nhwc_s8: x and w must be 16-byte aligned");
+  if (H + 2 * pad < R || W + 2 * pad < S) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: filter larger than padded input");
+  int rc = check_epilogue(e, K, "lq_conv2d_nhwc_s8", false);
+  if (rc) return rc;
+  if (e->a_zp) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: activation zero point must be 0 (padding reads code 0)");
+  if (e->a_scale_mode != LQ_PER_TENSOR && e->out_dtype != LQ_S32) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: per-tensor activation scale only");
+  const size_t P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
+  if (N * P * Q > 0x7fffffffu) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: too many output pixels");
+
+  if (R == 1 && S == 1 && pad == 0) {
+    // a 1x1 convolution over NHWC pixels is a plain GEMM with M = N*H*W
+    return lq_gemm_s8(x, x_signed, w, N * H * W, K, C, e, out, K, status, stream);
+  }
+  Geometry g = {};
+  g.conv = 1;
+  g.P = (int)P, g.Q = (int)Q, g.C = (int)C, g.R = (int)R, g.S = (int)S, g.pad = (int)pad;
+  g.tile_w = (int)(Q < (size_t)BM ? Q : BM);
+  g.tile_h = BM / g.tile_w;
+  if ((size_t)g.tile_h > P) g.tile_h = (int)P;
+  g.tiles_q = (int)((Q + g.tile_w - 1) / g.tile_w);
+  g.tiles_p = (int)((P + g.tile_h - 1) / g.tile_h);
+  const bool wide = K > 128;
+  const int bn = wide ? 256 : 128;
+  g.M = (int)(N * P * Q), g.N = (int)K, g.K = (int)(R * S * C);
+  g.tiles_m = (int)N * g.tiles_p * g.tiles_q;
+  g.tiles_n = (int)((K + bn - 1) / bn);
+  g.cblocks = (int)((C + BK - 1) / BK);
+  g.num_kb = (int)(R * S) * g.cblocks;
+  CUtensorMap ta, tb;
+  if ((rc = encode_nhwc(&ta, x, N, H, W, C, (uint32_t)g.tile_w, (uint32_t)g.tile_h))) return rc;
+  if ((rc = encode_2d(&tb, w, K, R * S * C, R * S * C, (uint32_t)bn))) return rc;
+  Epi ep;
+  fill_epi(&ep, e, out, K, K, status);
+  const uint32_t idesc = make_idesc(x_signed, bn);
+  return wide ? launch<256>(ta, tb, g, ep, idesc, (cudaStream_t)stream)
+              : launch<128>(ta, tb, g, ep, idesc, (cudaStream_t)stream);
+}

@@ -1,0 +1,62 @@
+"""Shared helpers of the quantized modules (lucid/nn/quantized/_utils.py:27-113)."""
+
+from __future__ import annotations
+
+import warnings
+from dataclasses import dataclass
+
+import torch
+
+from ...quantization import (PerChannelMinMaxObserver, QDtype, per_channel_symmetric, qint8,
+                             quantize)
+
+
+@dataclass
+class QCodes:
+    """Integer codes riding along a fake-quantized float tensor, so that the
+    next quantized module can consume them without re-encoding."""
+
+    codes: torch.Tensor       # int8 or uint8, same shape as the float tensor (NHWC for conv)
+    scale: torch.Tensor       # 0-d f32
+    zero_point: torch.Tensor  # 0-d f32
+    layout: str = "rowmajor"  # "rowmajor" | "nhwc"
+    zp_is_zero: bool | None = None  # known on the host without a sync, when not None
+
+
+def tag(t: torch.Tensor, qc: QCodes) -> torch.Tensor:
+    t._lq_codes = qc
+    return t
+
+
+def codes_of(t: torch.Tensor):
+    return getattr(t, "_lq_codes", None)
+
+
+def quantize_weight(mod) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
+    """(codes, scale, zero_point, ch_axis) of a float module's weight.
+
+    A module with a ``qconfig`` uses its weight observer factory; otherwise the
+    default per-output-channel symmetric qint8 observer."""
+    weight = mod.weight.detach()
+    qconfig = getattr(mod, "qconfig", None)
+    wobs = qconfig.weight() if qconfig is not None and hasattr(qconfig, "weight") else \
+        PerChannelMinMaxObserver(ch_axis=0, qscheme=per_channel_symmetric, qdtype=qint8)
+    wobs(weight)
+    scale, zero_point = wobs.calculate_qparams()
+    ch_axis = wobs.ch_axis
+    codes = quantize(weight, scale, zero_point, wobs.qdtype, ch_axis=ch_axis)
+    return codes, scale, zero_point, (ch_axis if ch_axis is not None else 0)
+
+
+def activation_qparams(mod) -> tuple[torch.Tensor, torch.Tensor, QDtype]:
+    """Output (scale, zero_point, qdtype) from the module's calibrated observer."""
+    obs = mod.activation_post_process
+    min_val = getattr(obs, "min_val", None)
+    if min_val is not None and bool(torch.isinf(min_val).any().item()):
+        warnings.warn(
+            f"Quantizing {type(mod).__name__} whose activation observer never saw data -- "
+            "calibrate the prepared model before converting, or the quantized output "
+            "collapses to a near-zero grid.", stacklevel=3)
+    scale, zero_point = obs.calculate_qparams()
+    dev = mod.weight.device if hasattr(mod, "weight") else scale.device
+    return scale.to(dev), zero_point.to(dev), obs.qdtype

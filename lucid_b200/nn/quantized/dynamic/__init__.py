@@ -1,0 +1,3 @@
+"""Dynamically quantized modules (lucid/nn/quantized/dynamic/__init__.py)."""
+
+from .linear import GatedMLP, Linear, PerTokenLinear, interleave_gate_up  # noqa: F401

@@ -1,0 +1,130 @@
+"""Integer contraction entry points (tensor-level wrappers over the C ABI).
+
+``gemm_s8`` / ``conv2d_nhwc_s8`` compute exact int32 accumulators on the
+tcgen05 tensor cores and apply the fused epilogue documented in
+``include/lucid_b200.h``.  They are what the quantized modules call in place of
+the reference's dequantize -> float GEMM -> fake-quantize sequence
+(lucid/nn/quantized/linear.py:199-215, lucid/nn/quantized/conv.py:168-184).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ... import _lib
+
+_OUT_CODE = {torch.int32: _lib.S32, torch.float32: _lib.F32, torch.bfloat16: _lib.BF16,
+             torch.int8: _lib.S8, torch.uint8: _lib.U8}
+
+
+def _f32(t, dev, what):
+    if t is None:
+        return None
+    if not isinstance(t, torch.Tensor):
+        t = torch.tensor(float(t), dtype=torch.float32, device=dev)
+    if t.device != dev:
+        t = t.to(dev)
+    if t.dtype != torch.float32:
+        t = t.to(torch.float32)
+    return t.contiguous()
+
+
+def _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
+              qmin, qmax, keep):
+    if out_dtype not in _OUT_CODE:
+        raise _lib.DtypeMismatch(f"unsupported GEMM output dtype {out_dtype}")
+    a_scale = _f32(a_scale, dev, "a_scale")
+    a_zp = _f32(a_zp, dev, "a_zp")
+    b_scale = _f32(b_scale, dev, "b_scale")
+    bias = _f32(bias, dev, "bias")
+    out_scale = _f32(out_scale, dev, "out_scale")
+    out_zp = _f32(out_zp, dev, "out_zp")
+    if b_rowsum is not None:
+        b_rowsum = b_rowsum.to(device=dev, dtype=torch.int32).contiguous()
+    keep.extend([a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp])
+    e = _lib.Epilogue()
+    e.out_dtype = _OUT_CODE[out_dtype]
+    e.act = act
+    e.a_scale_mode = _lib.PER_ROW if (a_scale is not None and a_scale.numel() > 1) else _lib.PER_TENSOR
+    e.qmin, e.qmax = int(qmin), int(qmax)
+    e.a_scale = _lib.ptr(a_scale)
+    e.a_zp = _lib.ptr(a_zp)
+    e.b_rowsum = _lib.ptr(b_rowsum)
+    e.b_scale = _lib.ptr(b_scale)
+    e.bias = _lib.ptr(bias)
+    e.out_scale = _lib.ptr(out_scale)
+    e.out_zp = _lib.ptr(out_zp)
+    return e
+
+
+def rowsum_s8(b: torch.Tensor) -> torch.Tensor:
+    """``sum_k b[n, k]`` as int32: the zero-point correction vector."""
+    _lib.require_cuda(b, "weight codes")
+    if b.dtype != torch.int8:
+        raise _lib.DtypeMismatch("weight codes must be int8")
+    b2 = b.contiguous().reshape(b.shape[0], -1)
+    out = torch.empty(b2.shape[0], dtype=torch.int32, device=b.device)
+    with torch.cuda.device(b.device):
+        _lib.check(_lib.load().lq_rowsum_s8(_lib.ptr(b2), b2.shape[0], b2.shape[1], _lib.ptr(out),
+                                            _lib.stream_ptr(b.device)))
+    return out
+
+
+def gemm_s8(a, b, *, out_dtype=torch.int32, a_scale=None, a_zp=None, b_rowsum=None, b_scale=None,
+            bias=None, act=_lib.ACT_NONE, out_scale=None, out_zp=None, qmin=0, qmax=0, out=None):
+    """``epilogue(a @ b.T)`` for 8-bit codes ``a (M, K)`` (int8 or uint8) and
+    ``b (N, K)`` (int8).  ``a_scale`` scalar (per tensor) or ``M`` values (per
+    token)."""
+    _lib.require_cuda(a, "activation codes")
+    _lib.require_cuda(b, "weight codes")
+    if a.dtype not in (torch.int8, torch.uint8) or b.dtype != torch.int8:
+        raise _lib.DtypeMismatch("gemm_s8 takes int8/uint8 activations and int8 weights")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise _lib.ShapeMismatch(f"gemm_s8 shapes {tuple(a.shape)} x {tuple(b.shape)}^T")
+    a = a.contiguous()
+    b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    n_out = n // 2 if act == _lib.ACT_SILU_GATE else n
+    dev = a.device
+    if out is None:
+        out = torch.empty((m, n_out), dtype=out_dtype, device=dev)
+    keep: list = []
+    e = _epilogue(dev, out.dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
+                  qmin, qmax, keep)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().lq_gemm_s8(
+            _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e),
+            _lib.ptr(out), out.stride(0), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+    return out
+
+
+def conv2d_nhwc_s8(x, w_krsc, *, pad=0, stride=1, out_dtype=torch.int32, a_scale=None,
+                   b_scale=None, bias=None, act=_lib.ACT_NONE, out_scale=None, out_zp=None,
+                   qmin=0, qmax=0):
+    """NHWC implicit-GEMM convolution on codes: ``x (N, H, W, C)`` int8/uint8
+    with zero point 0, ``w_krsc (K, R, S, C)`` int8.  Returns ``(N, P, Q, K)``."""
+    _lib.require_cuda(x, "activation codes")
+    _lib.require_cuda(w_krsc, "weight codes")
+    if x.dtype not in (torch.int8, torch.uint8) or w_krsc.dtype != torch.int8:
+        raise _lib.DtypeMismatch("conv2d_nhwc_s8 takes int8/uint8 activations and int8 weights")
+    if x.dim() != 4 or w_krsc.dim() != 4 or x.shape[3] != w_krsc.shape[3]:
+        raise _lib.ShapeMismatch(f"conv2d_nhwc_s8 shapes {tuple(x.shape)} * {tuple(w_krsc.shape)}")
+    x = x.contiguous()
+    w_krsc = w_krsc.contiguous()
+    n, h, w, c = x.shape
+    k, r, s, _ = w_krsc.shape
+    p = (h + 2 * pad - r) // stride + 1
+    q = (w + 2 * pad - s) // stride + 1
+    dev = x.device
+    out = torch.empty((n, p, q, k), dtype=out_dtype, device=dev)
+    keep: list = []
+    e = _epilogue(dev, out_dtype, act, a_scale, None, None, b_scale, bias, out_scale, out_zp,
+                  qmin, qmax, keep)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().lq_conv2d_nhwc_s8(
+            _lib.ptr(x), int(x.dtype == torch.int8), _lib.ptr(w_krsc), n, h, w, c, k, r, s, stride,
+            pad, C.byref(e), _lib.ptr(out), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+    return out

@@ -1,0 +1,90 @@
+"""Output-channel (N) sharded W8A8 linear for one box of GPUs.
+
+Rank ``r`` of ``w`` owns the contiguous rows ``[r*N/w, (r+1)*N/w)`` of the
+``(N, K)`` weight with their scales and bias.  Activations (and their per-token
+scales) are replicated, every rank's integer GEMM is independent, and one
+exchange step -- an all-gather of the ``(M, N/w)`` output shards -- rebuilds the
+``(M, N)`` result on every rank.  Sharding changes no number: each output
+column is produced by exactly one rank with the 1-GPU arithmetic.
+
+The reference has no distributed code; this module is new surface.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ... import _lib
+from ...quantization import qint8, quantize_per_token
+from . import functional as QF
+
+
+def shard_bounds(n: int, world: int, rank: int, multiple: int = 1) -> tuple[int, int]:
+    """Row range of ``rank``: equal contiguous shards; ``n`` must divide evenly
+    into ``world`` shards that are multiples of ``multiple``."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    if n % (world * multiple) != 0:
+        raise _lib.ShapeMismatch(f"N={n} does not split into {world} shards of a multiple of {multiple}")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather ``(M, n_local)`` column shards into ``(M, world * n_local)``.
+
+    The collective lands shards as ``(world, M, n_local)``; one strided copy puts
+    them side by side.  Works on any backend (NCCL on GPUs, gloo on CPU)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return local
+    m, n_local = local.shape
+    stage = torch.empty((world * m, n_local), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(stage, local.contiguous(), group=group)
+    stage = stage.view(world, m, n_local)
+    if out is None:
+        out = torch.empty((m, world * n_local), dtype=local.dtype, device=local.device)
+    out.view(m, world, n_local).copy_(stage.permute(1, 0, 2))
+    return out
+
+
+class ColumnShardedLinear(torch.nn.Module):
+    """This rank's shard of a per-token W8A8 linear plus the output all-gather."""
+
+    def __init__(self, in_features: int, out_features: int, world: int, rank: int,
+                 bias: bool = False, group=None) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.world, self.rank, self.group = world, rank, group
+        self.n0, self.n1 = shard_bounds(out_features, world, rank)
+        n_local = self.n1 - self.n0
+        self.register_buffer("weight_int8", torch.zeros((n_local, in_features), dtype=torch.int8))
+        self.register_buffer("weight_scale", torch.ones(n_local))
+        if bias:
+            self.register_buffer("bias", torch.zeros(n_local))
+        else:
+            self.bias = None
+
+    @classmethod
+    def from_full(cls, weight_int8: torch.Tensor, weight_scale: torch.Tensor, bias, world: int,
+                  rank: int, group=None) -> "ColumnShardedLinear":
+        n, k = weight_int8.shape
+        m = cls(k, n, world, rank, bias is not None, group)
+        m.weight_int8 = weight_int8[m.n0:m.n1].contiguous()
+        m.weight_scale = weight_scale[m.n0:m.n1].contiguous()
+        if bias is not None:
+            m.bias = bias[m.n0:m.n1].contiguous()
+        return m.to(weight_int8.device)
+
+    def forward_codes(self, a: torch.Tensor, a_scale: torch.Tensor, out_dtype=torch.bfloat16,
+                      gather: bool = True) -> torch.Tensor:
+        local = QF.gemm_s8(a, self.weight_int8, out_dtype=out_dtype, a_scale=a_scale,
+                           b_scale=self.weight_scale, bias=self.bias)
+        return gather_columns(local, self.group) if gather and self.world > 1 else local
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lead = x.shape[:-1]
+        a, s = quantize_per_token(x.reshape(-1, self.in_features), qint8)
+        y = self.forward_codes(a, s, x.dtype)
+        return y.reshape(*lead, y.shape[-1])

@@ -1,0 +1,146 @@
+"""CPU-only checks of the drop-in boundary: the C-ABI library loads and exports
+every declared symbol, the Python surface mirrors the reference's names, and
+argument errors are raised before any device work."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import lucid_b200
+import lucid_b200.nn.quantized as nnq
+import lucid_b200.quantization as Q
+from lucid_b200 import _lib
+from lucid_b200.quantization import _functional as QFn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "lucid_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_symbols()
+    assert {"lq_quantize", "lq_dequantize", "lq_gemm_s8", "lq_conv2d_nhwc_s8", "lq_minmax"} <= set(names)
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/lucid_b200.h but not exported"
+    # the shim binds exactly the declared set
+    assert sorted(_lib._SIGNATURES) == names
+    assert _lib.load().lq_version() == 100
+
+
+def test_host_side_argument_errors_need_no_gpu():
+    lib = _lib.load()
+    e = _lib.Epilogue()
+    assert lib.lq_quantize(None, 0, 4, 4, None, None, 1.0, 0.0, 0, -128, 127, None, 2, None) == 3
+    assert "null" in _lib.last_error()
+    assert lib.lq_quantize(None, 0, 0, 4, None, None, 1.0, 0.0, 0, -128, 127, None, 2, None) == 0  # empty
+    one = ctypes.c_void_p(16)
+    assert lib.lq_gemm_s8(one, 1, one, 8, 8, 24, ctypes.byref(e), one, 8, None, None) == 4  # K % 16
+    assert lib.lq_gemm_s8(one, 1, one, 8, 8, 32, None, one, 8, None, None) == 3
+    e.out_dtype = 99
+    assert lib.lq_gemm_s8(one, 1, one, 8, 8, 32, ctypes.byref(e), one, 8, None, None) == 2
+    e.out_dtype = _lib.F32
+    assert lib.lq_gemm_s8(one, 1, one, 8, 8, 32, ctypes.byref(e), one, 8, None, None) == 3  # scales missing
+    assert lib.lq_minmax(one, 0, 0, 4, 0, one, one, one, 1 << 20, None) == 1  # empty has no range
+    assert lib.lq_minmax(one, 0, 4, 4, 0, one, one, one, 8, None) == 6  # workspace too small
+    assert lib.lq_conv2d_nhwc_s8(one, 1, one, 1, 8, 8, 16, 16, 3, 3, 2, 1, ctypes.byref(e), one, None, None) == 5
+
+
+def test_cpu_tensors_are_rejected_not_emulated():
+    x = torch.randn(4, 16)
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        Q.quantize(x, 0.1, 0.0, Q.qint8)
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        Q.dequantize(torch.zeros(4, dtype=torch.int8), 0.1, 0.0)
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        Q.MinMaxObserver()(x)
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        nnq.dynamic.Linear(16, 8)(x)
+
+
+def test_surface_matches_reference_names():
+    assert (Q.qint8.quant_min, Q.qint8.quant_max, Q.qint8.storage) == (-128, 127, "int8")
+    assert (Q.quint8.quant_min, Q.quint8.quant_max, Q.quint8.storage) == (0, 255, "int16")
+    assert (Q.qint4.quant_min, Q.qint4.quant_max) == (-8, 7)
+    assert Q.qint32.storage == "int32" and Q.qint8.signed and not Q.quint8.signed
+    assert repr(Q.qint8) == "lucid.quantization.qint8"
+    assert Q.per_channel_symmetric.is_per_channel and not Q.per_tensor_affine.is_per_channel
+    assert Q.per_tensor_symmetric.is_symmetric and not Q.per_channel_affine.is_symmetric
+    lin = nnq.Linear(32, 16)
+    assert list(lin.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point", "bias",
+                                      "scale", "zero_point"]
+    assert lin.weight_int8.dtype == torch.int8 and lin.out_qdtype is Q.quint8
+    assert "qdtype=quint8" in repr(lin)
+    conv = nnq.Conv2d(16, 32, 3, padding=1)
+    assert tuple(conv.weight_int8.shape) == (32, 16, 3, 3)
+    assert list(conv.state_dict()) == list(lin.state_dict())
+    dyn = nnq.dynamic.Linear(32, 16, bias=False)
+    assert list(dyn.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point"]
+    assert "dynamic=True" in repr(dyn)
+
+
+def test_engine_switch():
+    b = lucid_b200.backends.quantized
+    assert b.engine == "auto" and b.use_int8()
+    with pytest.raises(ValueError):
+        b.engine = "fastest"
+    b.engine = "reference"
+    assert not b.use_int8()
+    b.engine = "mlx_group"
+    with pytest.raises(lucid_b200.EngineUnavailable):
+        b.use_int8()
+    b.engine = "auto"
+    assert lucid_b200.device("cuda:0").type == "cuda"
+    with pytest.raises(RuntimeError):
+        lucid_b200.device("metal")
+    with pytest.raises(ValueError):
+        lucid_b200.device("tpu")
+
+
+def test_view2d_and_param_broadcast():
+    x = torch.empty(6, 32, 16)
+    assert QFn._view2d(x, 0, True) == (6, 512, _lib.PER_ROW, 1)
+    assert QFn._view2d(x, 2, True) == (192, 16, _lib.PER_COL, 1)
+    assert QFn._view2d(x, -1, True) == (192, 16, _lib.PER_COL, 1)
+    assert QFn._view2d(x, 1, True) == (192, 16, _lib.PER_ROW, 6)
+    assert QFn._view2d(x, None, False) == (192, 16, _lib.PER_TENSOR, 1)
+    rows, cols, mode, s, z, sv, zv = QFn._prepare_params(x, 0.5, 3, None)
+    assert (s, z, sv, zv, mode) == (None, None, 0.5, 3.0, _lib.PER_TENSOR)
+    sc = torch.arange(32, dtype=torch.float32)
+    rows, cols, mode, s, z, _, _ = QFn._prepare_params(x, sc, 0.0, 1)
+    assert mode == _lib.PER_ROW and s.numel() == 192 and torch.equal(s[:32], sc) and torch.equal(s[32:64], sc)
+    assert z.numel() == 192 and float(z.abs().sum()) == 0.0
+    with pytest.raises(lucid_b200.ShapeMismatch):
+        QFn._prepare_params(x, torch.ones(5), 0.0, 1)
+    with pytest.raises(lucid_b200.ShapeMismatch):
+        QFn._prepare_params(x, torch.ones(5), 0.0, None)
+
+
+def test_gate_up_interleave_layout():
+    g = torch.arange(256).reshape(256, 1)
+    u = g + 1000
+    w = nnq.dynamic.interleave_gate_up(g, u)
+    assert w.shape == (512, 1)
+    assert w[:128, 0].tolist() == list(range(128)) and w[128:256, 0].tolist() == list(range(1000, 1128))
+    assert w[256:384, 0].tolist() == list(range(128, 256))
+    with pytest.raises(lucid_b200.ShapeMismatch):
+        nnq.dynamic.interleave_gate_up(g[:100], u[:100])
+
+
+def test_shard_bounds():
+    from lucid_b200.nn.quantized.sharded import shard_bounds
+
+    assert [shard_bounds(28672, 8, r) for r in (0, 7)] == [(0, 3584), (25088, 28672)]
+    assert shard_bounds(10240, 8, 3) == (3840, 5120)
+    with pytest.raises(lucid_b200.ShapeMismatch):
+        shard_bounds(10, 4, 0)
+    with pytest.raises(ValueError):
+        shard_bounds(16, 4, 4)
