@@ -1,0 +1,494 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (config.workload = "llama2_70b_linears_m4096"): one decoder layer's
+int8-weight / int8-activation linears at M = 4096 tokens, d_model 8192, ffn
+28672, 64 heads with 8 KV heads: QKV (N = 10240), O, gate+up (one GEMM with the
+SiLU-gate epilogue) and down.  A step = per-token encode of each bf16
+activation (fused abs-max + quantize) and the four integer GEMMs with fused
+dequantise epilogues; 7.01e12 integer ops.  Weights (856 MB of codes) exceed
+L2, so every step streams them from HBM again.  Synthetic data: seeded normal
+activations, N(0, 0.02^2) weights quantized per output channel.
+
+With N > 1 every weight is sharded over output channels (N/w rows per rank) and
+each GEMM is followed by an all-gather of the bf16 output shards (strong
+scaling: the total work is fixed).
+
+`value` is whole-job TOPS with inputs resident in HBM.  `e2e` is the same
+metric through the public module API with pinned HOST activations copied in and
+the result copied out inside the timed region.  `--impl reference` times the
+NumPy transcription of the reference's float path (dequantize weight -> f32
+GEMM) on the host cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+D_MODEL, D_FF, M_TOKENS = 8192, 28672, 4096
+N_QKV = 8192 + 2 * 8 * 128  # 64 query heads + 2 x 8 KV heads of 128
+PROJ = {  # name: (N, K)
+    "qkv": (N_QKV, D_MODEL), "o": (D_MODEL, D_MODEL), "gate": (D_FF, D_MODEL),
+    "up": (D_FF, D_MODEL), "down": (D_MODEL, D_FF),
+}
+OPS_PER_STEP = sum(2 * M_TOKENS * n * k for n, k in PROJ.values())
+WORKLOAD = "llama2_70b_linears_m4096"
+METRIC = "quantized Linear int8 TOPS (% tcgen05 i8 peak); quant/dequant HBM GB/s"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"],
+                "bf16_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2])), power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the observed power range
+        lim = (max(power) + min(power)) / 2 if power else 0
+        loaded = [s for s, p in zip(sm, power) if p >= lim] or sm
+        return {"sm_mhz": float(np.median(loaded)), "sm_max_mhz": float(max(mx)),
+                "power_w_max": float(max(power)), "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------
+# CPU arm: NumPy transcription of the reference's float path on a bounded sample
+# ---------------------------------------------------------------------------------
+def cpu_reference_step(sample, rng_state):
+    """One pass over the sampled workload with the reference's op sequence:
+    per-token fake-quantize of the activation, dequantize the int8 weight
+    (re-done every forward, lucid/nn/quantized/linear.py:202-207), f32 GEMM."""
+    from oracle import lucid_oracle as O
+
+    ops = 0
+    for name, (xa, wq, ws) in sample.items():
+        mn, mx = O.per_channel_minmax_observe(xa, 0)
+        s, z = O.calculate_qparams(mn, mx, True, O.QINT8)
+        xq = O.fake_quantize(xa, s, z, -128, 127, ch_axis=0)
+        w = O.dequantize(wq, ws, np.zeros_like(ws), ch_axis=0)
+        y = O.linear_f32(xq, w, None)
+        ops += 2 * xa.shape[0] * w.shape[0] * w.shape[1]
+        del y
+    return ops
+
+
+def make_cpu_sample(tokens=128, row_fraction=8, seed=0):
+    rng = np.random.default_rng(seed)
+    sample = {}
+    for name, (n, k) in PROJ.items():
+        ns = n // row_fraction
+        xa = rng.standard_normal((tokens, k)).astype(np.float32)
+        wq = rng.integers(-127, 128, (ns, k)).astype(np.int8)
+        ws = (np.abs(rng.standard_normal(ns)) * 1e-3 + 1e-4).astype(np.float32)
+        sample[name] = (xa, wq, ws)
+    desc = (f"{tokens} of {M_TOKENS} tokens x 1/{row_fraction} of every projection's output "
+            f"channels (all five projections, full K)")
+    return sample, desc
+
+
+def cpu_threads():
+    try:
+        from threadpoolctl import threadpool_info
+
+        n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
+        return max(n) if n else (os.cpu_count() or 1)
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    sample, desc = make_cpu_sample()
+    for _ in range(max(args.warmup, 1)):
+        cpu_reference_step(sample, None)
+    t0 = time.perf_counter()
+    ops = 0
+    for _ in range(args.steps):
+        ops += cpu_reference_step(sample, None)
+    dt = time.perf_counter() - t0
+    tops = ops / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tops, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens": M_TOKENS, "d_model": D_MODEL, "d_ff": D_FF,
+                   "sharding": "none (host cores)"},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+                         "sample": desc + "; NumPy transcription of the reference float path "
+                         "(the Accelerate engine cannot build on Linux)"},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------
+# B200 arm
+# ---------------------------------------------------------------------------------
+def run_b200_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import lucid_b200.nn.quantized as nnq
+    import lucid_b200.quantization as Q
+    from lucid_b200 import _lib
+    from lucid_b200.nn.quantized import functional as QF
+    from lucid_b200.nn.quantized.sharded import gather_columns, shard_bounds
+
+    if not _lib.is_available():
+        raise SystemExit("bench.py: the CUDA extension or a CUDA device is missing (no CPU fallback)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    # ---- synthetic weights: codes + per-channel scales, this rank's output-channel shard
+    g = torch.Generator(device=dev).manual_seed(1234)
+
+    def make_weight(n, k, multiple=1):
+        n0, n1 = shard_bounds(n, world, rank, multiple)
+        wq = torch.randint(-127, 128, (n1 - n0, k), dtype=torch.int8, device=dev, generator=g)
+        ws = torch.rand(n1 - n0, device=dev, generator=g) * 1e-3 + 1e-4
+        return wq, ws
+
+    w_qkv, s_qkv = make_weight(*PROJ["qkv"])
+    w_o, s_o = make_weight(*PROJ["o"])
+    w_g, s_g = make_weight(*PROJ["gate"], multiple=128)
+    w_u, s_u = make_weight(*PROJ["up"], multiple=128)
+    w_gu = nnq.dynamic.interleave_gate_up(w_g, w_u)
+    s_gu = nnq.dynamic.interleave_gate_up(s_g, s_u)
+    del w_g, w_u
+    w_d, s_d = make_weight(*PROJ["down"])
+    ff_local = w_gu.shape[0] // 2
+
+    gh = torch.Generator().manual_seed(99)
+    host_x = [torch.randn(M_TOKENS, D_MODEL, generator=gh).to(torch.bfloat16).pin_memory()
+              for _ in range(3)]  # layer input, attention output, MLP input
+    x_dev = [h.to(dev) for h in host_x]
+    out_qkv = torch.empty((M_TOKENS, w_qkv.shape[0]), dtype=torch.bfloat16, device=dev)
+    out_o = torch.empty((M_TOKENS, w_o.shape[0]), dtype=torch.bfloat16, device=dev)
+    out_h = torch.empty((M_TOKENS, ff_local), dtype=torch.bfloat16, device=dev)
+    out_d = torch.empty((M_TOKENS, w_d.shape[0]), dtype=torch.bfloat16, device=dev)
+    host_out = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
+
+    gemm_events: list = []
+
+    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False):
+        if record:
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+        QF.gemm_s8(a, w, a_scale=a_s, b_scale=w_s, act=act, out=out)
+        if record:
+            e1.record()
+            gemm_events.append((e0, e1))
+
+    def step(xs, record=False):
+        """One pass of the hot path; returns the down-projection output."""
+        a, s = Q.quantize_per_token(xs[0], Q.qint8)
+        gemm(a, s, w_qkv, s_qkv, out_qkv, record=record)
+        qkv = gather_columns(out_qkv) if world > 1 else out_qkv
+        a, s = Q.quantize_per_token(xs[1], Q.qint8)
+        gemm(a, s, w_o, s_o, out_o, record=record)
+        o = gather_columns(out_o) if world > 1 else out_o
+        a, s = Q.quantize_per_token(xs[2], Q.qint8)
+        gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record)
+        h = gather_columns(out_h) if world > 1 else out_h
+        a, s = Q.quantize_per_token(h, Q.qint8)
+        # the down projection contracts over the full ffn width: K is not sharded
+        gemm(a, s, w_d, s_d, out_d, record=record)
+        d = gather_columns(out_d) if world > 1 else out_d
+        return qkv, o, d
+
+    launches_per_step = 8  # 4 per-token encodes + 4 GEMMs (library collectives not counted)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step(x_dev)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step(x_dev, record=True)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
+    n_gemm = len(gemm_events)
+    t = torch.tensor([ms_total, gemm_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, gemm_ms = float(t[0]), float(t[1])
+    ms_per_step = ms_total / args.steps
+    tops = OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+    _lib.check_device_status(dev)
+
+    # ---- end to end: pinned host activations in, result out, public API --------------
+    def e2e_step():
+        xs = [h.to(dev, non_blocking=True) for h in host_x]
+        _, _, d = step(xs)
+        host_out.copy_(d, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    t = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t[0]) / args.steps
+    e2e_tops = OPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
+    h2d = sum(h.numel() * h.element_size() for h in host_x)
+    d2h = host_out.numel() * host_out.element_size()
+
+    # ---- HBM streams on config 1 (rank 0, one GPU): rotating buffers larger than L2 ----
+    streams = None
+    if rank == 0:
+        streams = bench_streams(torch, Q, _lib, dev, peaks)
+
+    # ---- CPU baseline on a bounded sample (rank 0, N = 1 only) ------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample, desc = make_cpu_sample()
+        cpu_reference_step(sample, None)
+        t0 = time.perf_counter()
+        reps, ops = 0, 0
+        while time.perf_counter() - t0 < 12.0 or reps < 2:
+            ops += cpu_reference_step(sample, None)
+            reps += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": ops / dt / 1e12, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+               "sample": desc + f"; {reps} passes in {dt:.1f} s; NumPy transcription of the "
+               "reference float path (its Accelerate engine cannot build on Linux)"}
+
+    if rank == 0:
+        gemm_ops_per_launch = OPS_PER_STEP / 4 / world
+        avg_launch_s = gemm_ms * 1e-3 / max(n_gemm, 1)
+        achieved = gemm_ops_per_launch / avg_launch_s / 1e12
+        peak = 2.0 * peaks["bf16_sustained"]
+        line = {
+            "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8 x s8 -> s32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens": M_TOKENS, "d_model": D_MODEL, "d_ff": D_FF,
+                       "n_qkv": N_QKV, "sharding": f"N-sharded x{world}" if world > 1 else "none",
+                       "l2": "weights (856 MB of codes) exceed L2; streamed from HBM every step"},
+            "roofline": {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS",
+                "frac": achieved / peak, "traffic": None,
+                "kernel": "gemm_s8_kernel<256>",
+                "peak_note": f"2 x cuBLAS bf16 sustained ({peaks['source']}); nominal dense int8 "
+                             "is 4500 TOPS",
+                "frac_of_nominal_4500": achieved / 4500.0,
+            },
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "streams": streams,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
+    """quantize / dequantize / min-max on the (4096, 4096) f32 tensor of config 1,
+    timed as CUDA-graph replays over 6 rotating buffer sets (480 MB > L2)."""
+    n = 4096
+    sets = 6
+    xs = [torch.randn(n, n, device=dev) for _ in range(sets)]
+    qs = [torch.empty(n, n, dtype=torch.int8, device=dev) for _ in range(sets)]
+    lib = _lib.load()
+    ws = _lib.minmax_workspace(dev)
+    mn = torch.empty(1, device=dev)
+    mx = torch.empty(1, device=dev)
+
+    def graph_time(fn):
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for j in range(sets):
+                fn(j)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph):
+            for j in range(sets):
+                fn(j)
+        gph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(iters):
+            gph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (iters * sets) * 1e-3  # seconds per launch
+
+    def f_quant(j):
+        _lib.check(lib.lq_quantize(_lib.ptr(xs[j]), _lib.F32, n, n, None, None, 0.03, 0.0, 0, -127,
+                                   127, _lib.ptr(qs[j]), _lib.S8, _lib.stream_ptr(dev)))
+
+    def f_dequant(j):
+        _lib.check(lib.lq_dequantize(_lib.ptr(qs[j]), _lib.S8, n, n, None, None, 0.03, 0.0, 0,
+                                     _lib.ptr(xs[j]), _lib.F32, _lib.stream_ptr(dev)))
+
+    def f_minmax(j):
+        _lib.check(lib.lq_minmax(_lib.ptr(xs[j]), _lib.F32, 1, n * n, 0, _lib.ptr(mn), _lib.ptr(mx),
+                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+
+    out = {}
+    elems = n * n
+    for name, fn, bytes_per_elem in (("quantize_f32_s8", f_quant, 5), ("dequantize_s8_f32", f_dequant, 5),
+                                     ("minmax_f32", f_minmax, 4)):
+        sec = graph_time(fn)
+        gbs = elems * bytes_per_elem / sec / 1e9
+        out[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                     "frac_of_nominal_8000": gbs / 8000.0}
+    out["workload"] = "config 1: (4096, 4096) f32, 6 rotating buffer sets, CUDA-graph replays"
+    return out
+
+
+def run_single_kernel_case(args):
+    """Small single-kernel runs for profiler captures: `--case gemm` launches one
+    integer GEMM shape (operands larger than L2), `--case streams` the config-1
+    quantize / dequantize / min-max kernels."""
+    import torch
+
+    import lucid_b200.quantization as Q
+    from lucid_b200 import _lib
+    from lucid_b200.nn.quantized import functional as QF
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    if args.case == "streams":
+        print(json.dumps({"case": "streams", "streams": bench_streams(torch, Q, _lib, dev, peaks, iters=args.steps)}))
+        return 0
+    m, n, k = (int(v) for v in args.shape.split(","))
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev)
+    b = torch.randint(-128, 128, (n, k), dtype=torch.int8, device=dev)
+    sa = torch.rand(m, device=dev)
+    sb = torch.rand(n, device=dev)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    for _ in range(args.warmup):
+        QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    e0.record()
+    for _ in range(args.steps):
+        QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    _lib.check_device_status(dev)
+    print(json.dumps({"case": "gemm", "shape": [m, n, k], "ms": ms, "TOPS": 2 * m * n * k / ms / 1e9}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams"])
+    ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    if args.case != "full":
+        return run_single_kernel_case(args)
+    return run_b200_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
