@@ -16,6 +16,9 @@
 // frees its TMEM before returning, so the context stays usable.
 #include <cuda.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -31,11 +34,14 @@ constexpr int kEpiThreads = 128;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s
 
-template <int BN>
+template <int BN, bool PAIR>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  // PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2); each
+  // CTA stages its own 128 rows of A and half of the B rows.
+  static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : 6);
   static constexpr int kABytes = BM * BK;
-  static constexpr int kBBytes = BN * BK;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;
+  static constexpr int kBBytes = kBRows * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   // ring + 1 KB alignment slack + barriers (512 B) + per-warp epilogue staging (4 x 3 KB)
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + 4 * 3072;
@@ -160,6 +166,61 @@ __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- cta_group::2 (CTA pair) variants -----------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+// The pair's loads complete on the leader CTA's barrier (no multicast: each CTA fetches
+// its own rows).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tm), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tm, int c0, int c1,
+                                                 int c2, int c3, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(cluster_bar)
+      : "memory");
+}
+// commit that arrives on the same barrier offset in both CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // K-major operand tile in shared memory, 128-byte swizzle: rows are 128 B, eight
 // rows form a 1024 B swizzle atom (stride-byte-offset), leading-byte-offset is 1
 // (ignored for swizzled K-major), descriptor version 1, layout type 2.
@@ -174,9 +235,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 }
 
 // Instruction descriptor for kind::i8: D = s32, A = u8|s8, B = s8, both K-major.
-__host__ __device__ constexpr uint32_t make_idesc(int a_signed, int bn) {
+__host__ __device__ constexpr uint32_t make_idesc(int a_signed, int bn, int mma_m = BM) {
   return (2u << 4) | ((uint32_t)(a_signed ? 1 : 0) << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) |
-         ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(mma_m >> 4) << 24);
 }
 
 // ---- epilogue helpers -------------------------------------------------------------
@@ -227,11 +288,11 @@ __device__ __forceinline__ void store_vals(T* dst, const uint32_t (&words)[32], 
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const Geometry g, const Epi ep, const uint32_t idesc) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -249,6 +310,15 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
   const uint32_t bar_tempty = bar_tfull + 16;
 
+  // PAIR: CTA `rank` of the 2-CTA cluster owns M sub-tile 2*pair_m + rank and B rows
+  // [rank*BN/2, (rank+1)*BN/2) of the tile; the leader (rank 0) issues the MMAs.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int tiles_mw = PAIR ? (g.tiles_m + 1) / 2 : g.tiles_m;  // M tiles per worker
+  const int total_tiles = tiles_mw * g.tiles_n;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -256,7 +326,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, kEpiThreads / 32);
+      mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * (kEpiThreads / 32));
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -264,67 +334,84 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = g.tiles_m * g.tiles_n;
-
   if (warp == 0) {
-    // ===== TMA producer =====
+    // ===== TMA producer (one per CTA) =====
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int tm_idx = tile % g.tiles_m;
-        const int n0 = (tile / g.tiles_m) * BN;
+      for (int tile = worker; tile < total_tiles && ok; tile += num_workers) {
+        const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
+        const int n0 = (tile / tiles_mw) * BN + (int)rank * C::kBRows;
         int m0 = tm_idx * BM, img = 0, p0 = 0, q0 = 0;
         if (g.conv) {
           const int per_img = g.tiles_p * g.tiles_q;
-          img = tm_idx / per_img;
+          img = tm_idx / per_img;  // >= number of images for the padding sub-tile: zero-filled
           const int rem = tm_idx - img * per_img;
           p0 = (rem / g.tiles_q) * g.tile_h;
           q0 = (rem % g.tiles_q) * g.tile_w;
         }
         const uint32_t a_bytes = g.conv ? (uint32_t)(BK * g.tile_w * g.tile_h) : (uint32_t)C::kABytes;
+        const uint32_t stage_tx = (a_bytes + (uint32_t)C::kBBytes) * (PAIR ? 2u : 1u);
         for (int kb = 0; kb < g.num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, a_bytes + (uint32_t)C::kBBytes);
           const uint32_t a_dst = smem_u32(smem_a + stage * C::kABytes);
           const uint32_t b_dst = smem_u32(smem_b + stage * C::kBBytes);
+          int ax = kb * BK, bx = kb * BK, r = 0, sft = 0;
           if (g.conv) {
             const int tap = kb / g.cblocks;
             const int cb = kb - tap * g.cblocks;
-            const int r = tap / g.S, s = tap - r * g.S;
-            tma_load_4d(a_dst, &tm_a, cb * BK, q0 + s - g.pad, p0 + r - g.pad, img, full);
-            tma_load_2d(b_dst, &tm_b, tap * g.C + cb * BK, n0, full);
+            r = tap / g.S, sft = tap - r * g.S;
+            ax = cb * BK, bx = tap * g.C + cb * BK;
+          }
+          if (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier
+            const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
+            if (leader) mbar_expect_tx(bar_full + 8 * stage, stage_tx);
+            if (g.conv) tma_load_4d_pair(a_dst, &tm_a, ax, q0 + sft - g.pad, p0 + r - g.pad, img, full);
+            else tma_load_2d_pair(a_dst, &tm_a, ax, m0, full);
+            tma_load_2d_pair(b_dst, &tm_b, bx, n0, full);
           } else {
-            tma_load_2d(a_dst, &tm_a, kb * BK, m0, full);
-            tma_load_2d(b_dst, &tm_b, kb * BK, n0, full);
+            const uint32_t full = bar_full + 8 * stage;
+            mbar_expect_tx(full, stage_tx);
+            if (g.conv) tma_load_4d(a_dst, &tm_a, ax, q0 + sft - g.pad, p0 + r - g.pad, img, full);
+            else tma_load_2d(a_dst, &tm_a, ax, m0, full);
+            tma_load_2d(b_dst, &tm_b, bx, n0, full);
           }
           if (++stage == C::kStages) stage = 0, phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    // ===== MMA issuer =====
-    if (lane == 0) {
+    // ===== MMA issuer (leader CTA only when paired) =====
+    if (lane == 0 && leader) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < total_tiles && ok; tile += num_workers) {
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -339,14 +426,19 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K inside the swizzle atom = advancing the start address
-            tc_mma_i8(d_tmem, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)),
-                      idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t koff = (uint64_t)(k * (UMMA_K >> 4));
+            if (PAIR) tc_mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * stage);  // frees the stage once the MMAs have read it
+          // frees the stage (in both CTAs when paired) once the MMAs have read it
+          if (PAIR) tc_commit_pair(bar_empty + 8 * stage);
+          else tc_commit(bar_empty + 8 * stage);
           if (++stage == C::kStages) stage = 0, phase ^= 1u;
         }
         if (!ok) break;
-        tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+        // accumulator complete
+        if (PAIR) tc_commit_pair(bar_tfull + 8 * acc);
+        else tc_commit(bar_tfull + 8 * acc);
         if (++acc == 2) acc = 0, acc_phase ^= 1u;
       }
     }
@@ -364,9 +456,10 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int tm_idx = tile % g.tiles_m;
-      const int n0 = (tile / g.tiles_m) * BN;
+    const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
+    for (int tile = worker; tile < total_tiles; tile += num_workers) {
+      const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
+      const int n0 = (tile / tiles_mw) * BN;
       // stage the per-column parameters of this tile
       __syncwarp();  // previous tile's readers are done
       for (int j = lane; j < BN; j += 32) {
@@ -389,7 +482,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int ph = row / g.tile_w, qw = row - ph * g.tile_w;
         const int p = (rem / g.tiles_q) * g.tile_h + ph;
         const int q = (rem % g.tiles_q) * g.tile_w + qw;
-        row_ok = ph < g.tile_h && p < g.P && q < g.Q;
+        row_ok = tm_idx < g.tiles_m && ph < g.tile_h && p < g.P && q < g.Q;
         m_global = (img * g.P + p) * g.Q + q;
       } else {
         m_global = tm_idx * BM + row;
@@ -456,7 +549,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
       } else {
         // gated: tile columns [0,BN/2) are gate, [BN/2,BN) the matching up columns
-        const int on0 = (tile / g.tiles_m) * (BN / 2);
+        const int on0 = (tile / tiles_mw) * (BN / 2);
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           uint32_t rg[32], ru[32];
@@ -490,7 +583,10 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       // hand the accumulator stage back to the MMA issuer
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(tempty_target + 8 * acc);
+        else mbar_arrive(bar_tempty + 8 * acc);
+      }
       if (++acc == 2) acc = 0, acc_phase ^= 1u;
     }
   }
@@ -505,11 +601,17 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer may still signal this CTA's barriers / read its tiles
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(kTmemCols)
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(kTmemCols)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(kTmemCols)
+                   : "memory");
   }
 }
 
@@ -617,20 +719,78 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
   d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep,
            uint32_t idesc, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_s8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    Cfg<BN>::kSmemBytes);
+  static int max_clusters = 0;
+  auto kernel = gemm_s8_kernel<BN, PAIR>;
+  constexpr int smem = Cfg<BN, PAIR>::kSmemBytes;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (PAIR && attr_err == cudaSuccess) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(2 * sm_count(), 1, 1);
+      probe.blockDim = dim3(kGemmThreads, 1, 1);
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+      probe.attrs = at, probe.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &probe) != cudaSuccess || max_clusters <= 0) {
+        cudaGetLastError();
+        max_clusters = sm_count() / 2;
+      }
+    }
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
-  const int total = g.tiles_m * g.tiles_n;
-  const int grid = total < sm_count() ? total : sm_count();
-  gemm_s8_kernel<BN><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, st>>>(ta, tb, g, ep, idesc);
-  return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
+  const int tiles_mw = PAIR ? (g.tiles_m + 1) / 2 : g.tiles_m;
+  const int total = tiles_mw * g.tiles_n;
+  if (!PAIR) {
+    const int grid = total < sm_count() ? total : sm_count();
+    kernel<<<grid, kGemmThreads, smem, st>>>(ta, tb, g, ep, idesc);
+    return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
+  }
+  const int clusters = total < max_clusters ? total : max_clusters;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+  cfg.attrs = at, cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, ep, idesc), "gemm_s8_kernel (paired) launch");
+}
+
+// Tile shape policy: CTA pairs (256 x 256 tiles, cta_group::2) when there is enough work to
+// fill the clusters; single CTAs (128 x 256, or 128 x 128 for narrow outputs) otherwise.
+enum class Shape { kPair256, kSingle256, kSingle128 };
+
+Shape pick_shape(size_t m_subtiles, size_t N, bool gated) {
+  const char* force = getenv("LQ_GEMM_SHAPE");
+  if (force) {
+    if (!strcmp(force, "pair")) return Shape::kPair256;
+    if (!strcmp(force, "single256")) return Shape::kSingle256;
+    if (!strcmp(force, "single128") && !gated) return Shape::kSingle128;
+  }
+  if (N <= 128 && !gated) return Shape::kSingle128;
+  const size_t tiles_n = (N + 255) / 256;
+  const size_t pair_tiles = ((m_subtiles + 1) / 2) * tiles_n;
+  // a pair tile on a half-empty M pair wastes a CTA; need at least ~one wave of clusters
+  if (m_subtiles >= 2 && pair_tiles >= (size_t)(sm_count() / 2)) return Shape::kPair256;
+  return Shape::kSingle256;
+}
+
+int dispatch(Shape sh, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,
+             int a_signed, cudaStream_t st) {
+  switch (sh) {
+    case Shape::kPair256: return launch<256, true>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st);
+    case Shape::kSingle256: return launch<256, false>(ta, tb, g, ep, make_idesc(a_signed, 256), st);
+    default: return launch<128, false>(ta, tb, g, ep, make_idesc(a_signed, 128), st);
+  }
 }
 
 }  // namespace
@@ -652,20 +812,19 @@ extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M
   const size_t n_out = e->act == LQ_ACT_SILU_GATE ? N / 2 : N;
   if (ldo < n_out) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: ldo smaller than the output width");
 
-  const bool wide = N > 128 || e->act == LQ_ACT_SILU_GATE;
-  const int bn = wide ? 256 : 128;
   Geometry g = {};
   g.conv = 0, g.M = (int)M, g.N = (int)N, g.K = (int)K;
-  g.tiles_m = (int)((M + BM - 1) / BM), g.tiles_n = (int)((N + bn - 1) / bn);
+  g.tiles_m = (int)((M + BM - 1) / BM);
+  const Shape sh = pick_shape((size_t)g.tiles_m, N, e->act == LQ_ACT_SILU_GATE);
+  const int bn = sh == Shape::kSingle128 ? 128 : 256;
+  g.tiles_n = (int)((N + bn - 1) / bn);
   g.num_kb = (int)((K + BK - 1) / BK);
   CUtensorMap ta, tb;
   if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
-  if ((rc = encode_2d(&tb, b, N, K, K, (uint32_t)bn))) return rc;
+  if ((rc = encode_2d(&tb, b, N, K, K, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
   Epi ep;
   fill_epi(&ep, e, out, ldo, n_out, status);
-  const uint32_t idesc = make_idesc(a_signed, bn);
-  return wide ? launch<256>(ta, tb, g, ep, idesc, (cudaStream_t)stream)
-              : launch<128>(ta, tb, g, ep, idesc, (cudaStream_t)stream);
+  return dispatch(sh, ta, tb, g, ep, a_signed, (cudaStream_t)stream);
 }
 
 extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H,
@@ -698,19 +857,17 @@ extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, s
   if ((size_t)g.tile_h > P) g.tile_h = (int)P;
   g.tiles_q = (int)((Q + g.tile_w - 1) / g.tile_w);
   g.tiles_p = (int)((P + g.tile_h - 1) / g.tile_h);
-  const bool wide = K > 128;
-  const int bn = wide ? 256 : 128;
   g.M = (int)(N * P * Q), g.N = (int)K, g.K = (int)(R * S * C);
   g.tiles_m = (int)N * g.tiles_p * g.tiles_q;
+  const Shape sh = pick_shape((size_t)g.tiles_m, K, false);
+  const int bn = sh == Shape::kSingle128 ? 128 : 256;
   g.tiles_n = (int)((K + bn - 1) / bn);
   g.cblocks = (int)((C + BK - 1) / BK);
   g.num_kb = (int)(R * S) * g.cblocks;
   CUtensorMap ta, tb;
   if ((rc = encode_nhwc(&ta, x, N, H, W, C, (uint32_t)g.tile_w, (uint32_t)g.tile_h))) return rc;
-  if ((rc = encode_2d(&tb, w, K, R * S * C, R * S * C, (uint32_t)bn))) return rc;
+  if ((rc = encode_2d(&tb, w, K, R * S * C, R * S * C, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
   Epi ep;
   fill_epi(&ep, e, out, K, K, status);
-  const uint32_t idesc = make_idesc(x_signed, bn);
-  return wide ? launch<256>(ta, tb, g, ep, idesc, (cudaStream_t)stream)
-              : launch<128>(ta, tb, g, ep, idesc, (cudaStream_t)stream);
+  return dispatch(sh, ta, tb, g, ep, x_signed, (cudaStream_t)stream);
 }

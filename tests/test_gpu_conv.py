@@ -30,9 +30,16 @@ CASES = [  # n, h, w, c, k, r, pad
 ]
 
 
+@pytest.fixture(params=["auto", "pair", "single256"])
+def tile_shape(request, monkeypatch):
+    if request.param != "auto":
+        monkeypatch.setenv("LQ_GEMM_SHAPE", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("n,h,w,c,k,r,pad", CASES)
 @pytest.mark.parametrize("signed", [False, True])
-def test_conv_accumulators_exact(n, h, w, c, k, r, pad, signed):
+def test_conv_accumulators_exact(n, h, w, c, k, r, pad, signed, tile_shape):
     rng = np.random.default_rng(n + h + c + k + r)
     x = rng.integers(-128 if signed else 0, 128 if signed else 256, (n, h, w, c)).astype(
         np.int8 if signed else np.uint8)
@@ -42,7 +49,7 @@ def test_conv_accumulators_exact(n, h, w, c, k, r, pad, signed):
     assert np.array_equal(host(acc), O.int_conv2d_nhwc_exact(x, wt, 1, pad))
 
 
-def test_conv_stack_resnet_stage3_reduced():
+def test_conv_stack_resnet_stage3_reduced(tile_shape):
     """Config-4 chain at batch 4: codes between layers bit-exact against the
     kernel-order epilogue on exact accumulators."""
     rng = np.random.default_rng(3)

@@ -36,9 +36,17 @@ SHAPES = [(128, 128, 128), (128, 256, 128), (256, 512, 256), (1, 16, 16), (130, 
           (77, 129, 4096), (384, 640, 1040), (512, 1024, 2048), (128, 96, 32), (300, 257, 48)]
 
 
+@pytest.fixture(params=["auto", "pair", "single256", "single128"])
+def tile_shape(request, monkeypatch):
+    """Forces the GEMM's tile policy (CTA pair 256x256 / single 128x256 / single 128x128)."""
+    if request.param != "auto":
+        monkeypatch.setenv("LQ_GEMM_SHAPE", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("m,n,k", SHAPES)
 @pytest.mark.parametrize("a_signed", [True, False])
-def test_accumulators_exact(m, n, k, a_signed):
+def test_accumulators_exact(m, n, k, a_signed, tile_shape):
     rng = np.random.default_rng(m * 7 + n * 3 + k)
     a = _codes(rng, (m, k), a_signed)
     b = _codes(rng, (n, k), True)
@@ -60,10 +68,11 @@ def test_accumulator_extremes():
     _sync_status()
 
 
-def test_many_tiles_persistent_schedule():
-    # more tiles than SMs, several K blocks: exercises both TMEM stages and ring wrap-around
+@pytest.mark.parametrize("m,n,k", [(2048, 3072, 1024), (4096, 4864, 512), (2176, 5120, 384)])
+def test_many_tiles_persistent_schedule(m, n, k, tile_shape):
+    # more tiles than SMs / clusters, several K blocks: exercises both TMEM stages, the ring
+    # wrap-around and (paired) an odd number of M sub-tiles
     rng = np.random.default_rng(11)
-    m, n, k = 2048, 3072, 1024
     a, b = _codes(rng, (m, k)), _codes(rng, (n, k))
     acc = QF.gemm_s8(dev(a), dev(b), out_dtype=torch.int32)
     _sync_status()
@@ -132,7 +141,7 @@ def test_per_token_epilogue(out_dtype):
 
 
 @pytest.mark.parametrize("unsigned_out,relu", [(True, True), (True, False), (False, False), (False, True)])
-def test_requantising_epilogue_bit_exact(unsigned_out, relu):
+def test_requantising_epilogue_bit_exact(unsigned_out, relu, tile_shape):
     x, w, b = _c2_like(300, 256, 520, seed=7)
     wq, ws, _ = O.quantize_weight_per_channel(w)
     xs, xz = O.calculate_qparams(x.min(), x.max(), False, O.QUINT8)
@@ -186,7 +195,9 @@ def test_static_linear_module_vs_reference_float_form(golden):
     assert (d2 > 0).mean() < 1e-3 and d2.max() <= s * 1.001
 
 
-def test_gated_epilogue():
+def test_gated_epilogue(tile_shape):
+    if tile_shape == "single128":
+        pytest.skip("gated tiles are 256 wide")
     rng = np.random.default_rng(13)
     m, k, f = 200, 256, 384
     x = rng.standard_normal((m, k)).astype(np.float32)
