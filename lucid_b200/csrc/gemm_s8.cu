@@ -16,6 +16,7 @@
 // frees its TMEM before returning, so the context stays usable.
 #include <cuda.h>
 
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -56,6 +57,7 @@ struct Geometry {
   int P, Q, C, R, S, pad;
   int tile_h, tile_w, tiles_p, tiles_q;
   int cblocks;         // ceil(C / BK)
+  int debug;           // timing probes: 1 no loads, 2 no MMAs, 4 epilogue skips TMEM reads and stores, 8 epilogue skips stores
 };
 
 struct Epi {
@@ -113,6 +115,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+// Warp-uniform wait: every lane polls, the warp agrees on the outcome.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+// One lane of a converged warp.  The surrounding control flow stays warp-uniform so that
+// loop state and descriptors can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
                                             uint32_t bar) {
@@ -356,11 +373,11 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   if (warp == 0) {
     // ===== TMA producer (one per CTA) =====
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = worker; tile < total_tiles && ok; tile += num_workers) {
+      for (int tile = worker; tile < total_tiles && ok && !(g.debug & 1); tile += num_workers) {
         const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
         const int n0 = (tile / tiles_mw) * BN + (int)rank * C::kBRows;
         int m0 = tm_idx * BM, img = 0, p0 = 0, q0 = 0;
@@ -374,7 +391,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t a_bytes = g.conv ? (uint32_t)(BK * g.tile_w * g.tile_h) : (uint32_t)C::kABytes;
         const uint32_t stage_tx = (a_bytes + (uint32_t)C::kBBytes) * (PAIR ? 2u : 1u);
         for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
@@ -387,7 +404,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             r = tap / g.S, sft = tap - r * g.S;
             ax = cb * BK, bx = tap * g.C + cb * BK;
           }
-          if (PAIR) {
+          if (!elect_one()) {
+          } else if (PAIR) {
             // both CTAs' bytes are counted on the leader's barrier
             const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
             if (leader) mbar_expect_tx(bar_full + 8 * stage, stage_tx);
@@ -407,38 +425,44 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only when paired) =====
-    if (lane == 0 && leader) {
+    if (leader) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = worker; tile < total_tiles && ok; tile += num_workers) {
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
+        if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+          if (!(g.debug & 1) && !mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag)) {
             ok = false;
             break;
           }
-          tc_fence_after();
+          if (!(g.debug & 32)) tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
           const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
+          const bool issuer = elect_one();
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
+          for (int k = 0; k < BK / UMMA_K && !(g.debug & 2) && issuer; ++k) {
             // advancing K inside the swizzle atom = advancing the start address
             const uint64_t koff = (uint64_t)(k * (UMMA_K >> 4));
             if (PAIR) tc_mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
             else tc_mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           // frees the stage (in both CTAs when paired) once the MMAs have read it
-          if (PAIR) tc_commit_pair(bar_empty + 8 * stage);
+          if ((g.debug & 16) || !issuer) {
+          } else if (PAIR) tc_commit_pair(bar_empty + 8 * stage);
           else tc_commit(bar_empty + 8 * stage);
+          __syncwarp();
           if (++stage == C::kStages) stage = 0, phase ^= 1u;
         }
         if (!ok) break;
         // accumulator complete
-        if (PAIR) tc_commit_pair(bar_tfull + 8 * acc);
-        else tc_commit(bar_tfull + 8 * acc);
+        if (elect_one()) {
+          if (PAIR) tc_commit_pair(bar_tfull + 8 * acc);
+          else tc_commit(bar_tfull + 8 * acc);
+        }
+        __syncwarp();
         if (++acc == 2) acc = 0, acc_phase ^= 1u;
       }
     }
@@ -501,7 +525,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
 
-      if (!gated) {
+      if (g.debug & 4) {
+      } else if (!gated) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -509,7 +534,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           tc_ld32(taddr + c * 32, r);
           tc_wait_ld();
           const int ncol0 = n0 + c * 32;
-          const int valid = row_ok ? min(32, g.N - ncol0) : 0;
+          const int valid = (row_ok && !(g.debug & 8)) ? min(32, g.N - ncol0) : 0;
           if (valid <= 0) continue;
           const int32_t* rs = s_rowsum + c * 32;
           const float* bs = s_bscale + c * 32;
@@ -753,6 +778,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
     return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
   }
   const int clusters = total < max_clusters ? total : max_clusters;
+  if (getenv("LQ_GEMM_VERBOSE"))
+    fprintf(stderr, "[lq] paired launch: %d tiles on %d clusters (max active %d)\n", total, clusters, max_clusters);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
@@ -819,6 +846,7 @@ extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M
   const int bn = sh == Shape::kSingle128 ? 128 : 256;
   g.tiles_n = (int)((N + bn - 1) / bn);
   g.num_kb = (int)((K + BK - 1) / BK);
+  if (const char* dbg = getenv("LQ_GEMM_DEBUG")) g.debug = atoi(dbg);
   CUtensorMap ta, tb;
   if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
   if ((rc = encode_2d(&tb, b, N, K, K, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
