@@ -30,8 +30,8 @@ namespace {
 constexpr int BM = 128;       // rows of the CTA tile == TMEM lanes
 constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128B swizzle atom
 constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
-constexpr int kGemmThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpiWarps = 8;        // two per TMEM lane quadrant, each takes half the columns
 constexpr int kTmemCols = 512;
 constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s
 
@@ -44,8 +44,8 @@ struct Cfg {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // ring + 1 KB alignment slack + barriers (512 B) + per-warp epilogue staging (4 x 3 KB)
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + 4 * 3072;
+  // ring + 1 KB alignment slack + barriers (512 B) + per-warp output staging (8 x 4 KB)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kEpiWarps * 4096;
 };
 
 struct Geometry {
@@ -73,6 +73,7 @@ struct Epi {
   long long ldo;  // elements
   int n_out;      // columns of out (N, or N/2 for the gated epilogue)
   int vec_ok;     // 16-byte vector stores allowed
+  int par_vec;    // per-column parameter arrays are 16-byte aligned (vector loads)
   int32_t* status;
 };
 
@@ -179,9 +180,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // ---- cta_group::2 (CTA pair) variants -----------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -262,45 +260,223 @@ __device__ __forceinline__ float silu_f32(float x) {
   return __fmul_rn(x, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
 }
 
-// y for accumulator `acc` of tile-local column n (params staged in shared memory).
-__device__ __forceinline__ float dequant_acc(int acc, int zpa, float sa, const int32_t* s_rowsum,
-                                             const float* s_bscale, const float* s_bias,
-                                             bool has_bias, int n) {
-  const int t = acc - zpa * s_rowsum[n];
-  float y = __fmul_rn((float)t, __fmul_rn(sa, s_bscale[n]));
-  if (has_bias) y = __fadd_rn(y, s_bias[n]);
-  return y;
+// tcgen05.wait::ld that also carries the loaded registers, so that no use of them can be
+// scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                 "+r"(r[31])
+               :
+               : "memory");
 }
 
-// `words` holds 32 elements of type T packed little-endian; every index below is
-// a compile-time constant so the array stays in registers.
-template <typename T>
-__device__ __forceinline__ T extract_elem(const uint32_t* words, int j);
-template <>
-__device__ __forceinline__ int32_t extract_elem<int32_t>(const uint32_t* w, int j) { return (int32_t)w[j]; }
-template <>
-__device__ __forceinline__ float extract_elem<float>(const uint32_t* w, int j) { return __uint_as_float(w[j]); }
-template <>
-__device__ __forceinline__ uint16_t extract_elem<uint16_t>(const uint32_t* w, int j) {
-  return (uint16_t)(w[j >> 1] >> (16 * (j & 1)));
-}
-template <>
-__device__ __forceinline__ uint8_t extract_elem<uint8_t>(const uint32_t* w, int j) {
-  return (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
-}
+enum { KIND_S32 = 0, KIND_F32 = 1, KIND_BF16 = 2, KIND_Q8 = 3 };
+template <int KIND>
+struct KindInfo {
+  static constexpr int kEsz = KIND == KIND_Q8 ? 1 : (KIND == KIND_BF16 ? 2 : 4);
+};
 
-template <typename T, int NWORDS>
-__device__ __forceinline__ void store_vals(T* dst, const uint32_t (&words)[32], int valid_elems,
-                                           bool vec) {
-  if (vec && valid_elems == 32) {
+// Per-thread state of one tile's epilogue.
+struct RowCtx {
+  float sa;          // activation scale of this thread's row
+  int zpa;           // activation zero point
+  float so, zo;      // output grid
+  float fqmin, fqmax;
+  uint32_t row_mask; // valid rows of this warp (bit r = tile row quad*32 + r)
+  long long row0;    // global output row of the warp's first row
+};
+
+// 32 accumulators of one row -> 32 packed outputs (8 * esz words).
+template <int KIND>
+__device__ __forceinline__ void finish32(const float (&y)[32], uint32_t (&w)[32], const RowCtx& rc) {
+  if (KIND == KIND_F32) {
 #pragma unroll
-    for (int i = 0; i < NWORDS / 4; ++i)
-      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + 16 * i) =
-          make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(y[j]);
+  } else if (KIND == KIND_BF16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < valid_elems) dst[j] = extract_elem<T>(words, j);
+    for (int j = 0; j < 8; ++j) {
+      uint32_t v = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        v |= ((uint32_t)(int)code_f32(y[4 * j + b], rc.so, rc.zo, rc.fqmin, rc.fqmax) & 0xffu) << (8 * b);
+      w[j] = v;
+    }
+  }
+}
+
+// Flush the warp's staging buffer (32 rows x 128 B, 16-byte pieces XOR-swizzled by row):
+// eight lanes write one full 128-byte line of a row.
+template <int ESZ>
+__device__ __forceinline__ void flush_group(const uint8_t* stg, int lane, const Epi& ep,
+                                            const RowCtx& rc, int gcol0, int pieces) {
+  constexpr int EPP = 16 / ESZ;  // elements per 16-byte piece
+  const int pc = lane & 7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = k * 4 + (lane >> 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + ((pc ^ (r & 7)) << 4));
+    const int col = gcol0 + pc * EPP;
+    const int nvalid = ep.n_out - col;
+    if (((rc.row_mask >> r) & 1u) && pc < pieces && nvalid > 0) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + ((rc.row0 + r) * ep.ldo + col) * ESZ;
+      if (ep.vec_ok && nvalid >= EPP) {
+        *reinterpret_cast<uint4*>(dst) = v;
+      } else {
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < EPP; ++e) {
+          if (e < nvalid) {
+            if (ESZ == 4) reinterpret_cast<uint32_t*>(dst)[e] = wv[e];
+            else if (ESZ == 2) reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(wv[e >> 1] >> (16 * (e & 1)));
+            else dst[e] = (uint8_t)(wv[e >> 2] >> (8 * (e & 3)));
+          }
+        }
+      }
+    }
+  }
+}
+
+// Parameters of 32 consecutive columns; `fast` = the whole chunk is inside N and the arrays
+// are 16-byte aligned (straight-line vector loads, every lane asks for the same address).
+__device__ __forceinline__ void load_params32(const float* p, int col, int ncols, bool fast,
+                                              float dflt, float (&v)[32]) {
+  if (fast) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(p + col) + q);
+      v[4 * q] = t.x, v[4 * q + 1] = t.y, v[4 * q + 2] = t.z, v[4 * q + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = col + j < ncols ? __ldg(p + col + j) : dflt;
+  }
+}
+
+// y[j] = f32(acc[j] - zpa * rowsum[j]) * (sa * sb[j]) [+ bias[j]]; every float step is a
+// separate binary32 operation.
+__device__ __forceinline__ void dequant32(const Epi& ep, const Geometry& g, const RowCtx& rc,
+                                          const uint32_t (&acc)[32], int col, float (&y)[32]) {
+  const bool fast = ep.par_vec && col + 32 <= g.N;
+  int t[32];
+  if (ep.b_rowsum != nullptr && rc.zpa != 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int rs = col + j < g.N ? __ldg(ep.b_rowsum + col + j) : 0;
+      t[j] = (int)acc[j] - rc.zpa * rs;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) t[j] = (int)acc[j];
+  }
+  float p[32];
+  load_params32(ep.b_scale, col, g.N, fast, 1.0f, p);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) y[j] = __fmul_rn((float)t[j], __fmul_rn(rc.sa, p[j]));
+  if (ep.bias != nullptr) {
+    load_params32(ep.bias, col, g.N, fast, 0.0f, p);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], p[j]);
+  }
+}
+
+// One 32-column chunk of one row: accumulators -> outputs -> this thread's slot of the
+// staging buffer; the warp flushes the buffer when a 128-byte group is complete.
+// `rel` is the chunk's index inside this warp's column range of `count` chunks.
+template <int BN, int KIND, bool GATED>
+__device__ __forceinline__ void process_chunk(const Epi& ep, const Geometry& g, const RowCtx& rc,
+                                              const uint32_t (&acc)[32], const uint32_t (&acc_u)[32],
+                                              int it, int rel, int count, uint8_t* stg, int lane,
+                                              int n0, int on0) {
+  constexpr int ESZ = KindInfo<KIND>::kEsz;
+  constexpr int CPG = 128 / (32 * ESZ);  // chunks per 128-byte group
+  constexpr int PPI = 2 * ESZ;           // 16-byte pieces per chunk
+  const int bc = n0 + it * 32;           // column in the B / parameter space
+  uint32_t w[32];
+  if (KIND == KIND_S32) {
+    if (ep.b_rowsum != nullptr && rc.zpa != 0) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int rs = bc + j < g.N ? __ldg(ep.b_rowsum + bc + j) : 0;
+        w[j] = (uint32_t)((int)acc[j] - rc.zpa * rs);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) w[j] = acc[j];
+    }
+  } else {
+    float y[32];
+    dequant32(ep, g, rc, acc, bc, y);
+    if (GATED) {
+      float u[32];
+      dequant32(ep, g, rc, acc_u, bc + BN / 2, u);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) y[j] = __fmul_rn(silu_f32(y[j]), u[j]);
+    } else if (ep.act == LQ_ACT_RELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
+    }
+    finish32<KIND>(y, w, rc);
+  }
+  // stage: row = lane, 16-byte pieces swizzled by (row & 7)
+  const int cs = rel % CPG;
+#pragma unroll
+  for (int i = 0; i < PPI; ++i) {
+    const int piece = cs * PPI + i;
+    *reinterpret_cast<uint4*>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+        make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  }
+  if (cs == CPG - 1 || rel == count - 1) {
+    __syncwarp();
+    flush_group<ESZ>(stg, lane, ep, rc, on0 + (it - cs) * 32, (cs + 1) * PPI);
+    __syncwarp();
+  }
+}
+
+// Epilogue of one accumulator tile for one warp: 32 TMEM lanes (rows) x half of the tile's
+// columns (`half` selects which).  Two register buffers alternate: the TMEM load of chunk
+// i+1 is in flight while chunk i is processed, and a buffer is only read after the wait
+// that covers its load.
+template <int BN, int KIND, bool GATED>
+__device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, const RowCtx& rc,
+                                              uint32_t taddr, uint8_t* stg, int lane, int half,
+                                              int n0, int on0) {
+  constexpr int NIT = (GATED ? BN / 2 : BN) / 32;  // chunks of 32 output columns in the tile
+  constexpr int CNT = NIT / 2;                     // chunks per warp
+  static_assert(GATED || CNT % 2 == 0, "chunks are processed in pairs");
+  const int it0 = half * CNT;
+  if (GATED) {
+    // two accumulator chunks (gate, up) per step already fill the register budget
+    uint32_t a0[32], u0[32];
+#pragma unroll 1
+    for (int r = 0; r < CNT; ++r) {
+      tc_ld32(taddr + (it0 + r) * 32, a0);
+      tc_ld32(taddr + BN / 2 + (it0 + r) * 32, u0);
+      tc_wait_ld_dep(a0);
+      tc_wait_ld_dep(u0);
+      process_chunk<BN, KIND, GATED>(ep, g, rc, a0, u0, it0 + r, r, CNT, stg, lane, n0, on0);
+    }
+  } else {
+    uint32_t a0[32], a1[32];
+    tc_ld32(taddr + it0 * 32, a0);
+#pragma unroll 1
+    for (int r = 0; r < CNT; r += 2) {
+      tc_wait_ld_dep(a0);
+      tc_ld32(taddr + (it0 + r + 1) * 32, a1);
+      process_chunk<BN, KIND, GATED>(ep, g, rc, a0, a0, it0 + r, r, CNT, stg, lane, n0, on0);
+      tc_wait_ld_dep(a1);
+      if (r + 2 < CNT) tc_ld32(taddr + (it0 + r + 2) * 32, a0);
+      process_chunk<BN, KIND, GATED>(ep, g, rc, a1, a1, it0 + r + 1, r + 1, CNT, stg, lane, n0, on0);
+    }
   }
 }
 
@@ -343,7 +519,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * (kEpiThreads / 32));
+      mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * kEpiWarps);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -468,36 +644,21 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     __syncwarp();
   } else {
-    // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
+    // ===== epilogue: warps 2..9; TMEM lane quadrant = warp % 4, column half = (warp - 2) / 4 =====
     const int quad = warp & 3;
-    const int row = quad * 32 + lane;       // tile-local row == TMEM lane
-    // per-warp copy of the tile's per-column parameters (no cross-warp barrier)
-    uint8_t* stage_base = tail + 512 + (warp - 2) * 3072;
-    float* s_bscale = reinterpret_cast<float*>(stage_base);              // [256]
-    float* s_bias = reinterpret_cast<float*>(stage_base + 1024);         // [256]
-    int32_t* s_rowsum = reinterpret_cast<int32_t*>(stage_base + 2048);   // [256]
-    const bool has_bias = ep.bias != nullptr;
+    const int row = quad * 32 + lane;  // tile-local row == TMEM lane
+    uint8_t* stg = tail + 512 + (warp - 2) * 4096;  // this warp's output staging
+    const int half = (warp - 2) >> 2;
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
     for (int tile = worker; tile < total_tiles; tile += num_workers) {
       const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
-      const int n0 = (tile / tiles_mw) * BN;
-      // stage the per-column parameters of this tile
-      __syncwarp();  // previous tile's readers are done
-      for (int j = lane; j < BN; j += 32) {
-        const int n = n0 + j;
-        const bool v = n < g.N;
-        s_bscale[j] = (v && ep.b_scale) ? ep.b_scale[n] : 1.0f;
-        s_bias[j] = (v && has_bias) ? ep.bias[n] : 0.0f;
-        s_rowsum[j] = (v && ep.b_rowsum) ? ep.b_rowsum[n] : 0;
-      }
-      __syncwarp();
-
-      // output row of this thread
+      const int tn_idx = tile / tiles_mw;
+      // output row of this thread; valid rows of a tile are a prefix and map to
+      // consecutive output rows
       bool row_ok;
-      long long out_row;
       int m_global;
       if (g.conv) {
         const int per_img = g.tiles_p * g.tiles_q;
@@ -512,98 +673,33 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         m_global = tm_idx * BM + row;
         row_ok = m_global < g.M;
       }
-      out_row = (long long)m_global * ep.ldo;
-      float sa = 1.0f;
-      if (ep.a_scale) sa = ep.a_scale_mode == LQ_PER_ROW ? (row_ok ? ep.a_scale[m_global] : 1.0f) : ep.a_scale[0];
-      const int zpa = ep.a_zp ? (int)ep.a_zp[0] : 0;
-      float so = 1.0f, zo = 0.0f;
-      if (ep.out_scale) so = ep.out_scale[0];
-      if (ep.out_zp) zo = ep.out_zp[0];
-      const float fqmin = (float)ep.qmin, fqmax = (float)ep.qmax;
+      RowCtx rc;
+      rc.sa = 1.0f;
+      if (ep.a_scale) rc.sa = ep.a_scale_mode == LQ_PER_ROW ? (row_ok ? __ldg(ep.a_scale + m_global) : 1.0f) : __ldg(ep.a_scale);
+      rc.zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0;
+      rc.so = ep.out_scale ? __ldg(ep.out_scale) : 1.0f;
+      rc.zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
+      rc.fqmin = (float)ep.qmin, rc.fqmax = (float)ep.qmax;
+      rc.row_mask = __ballot_sync(0xffffffffu, row_ok && !(g.debug & 8));
+      rc.row0 = (long long)__shfl_sync(0xffffffffu, m_global, 0);
 
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-
+      const int n0 = tn_idx * BN;
       if (g.debug & 4) {
-      } else if (!gated) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          __syncwarp();  // tcgen05.ld is warp-aligned: reconverge after the divergent skip below
-          tc_ld32(taddr + c * 32, r);
-          tc_wait_ld();
-          const int ncol0 = n0 + c * 32;
-          const int valid = (row_ok && !(g.debug & 8)) ? min(32, g.N - ncol0) : 0;
-          if (valid <= 0) continue;
-          const int32_t* rs = s_rowsum + c * 32;
-          const float* bs = s_bscale + c * 32;
-          const float* bb = s_bias + c * 32;
-          if (ep.out_dtype == LQ_S32) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = (uint32_t)((int)r[j] - zpa * rs[j]);
-            store_vals<int32_t, 32>(reinterpret_cast<int32_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
-          } else {
-            float y[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              y[j] = dequant_acc((int)r[j], zpa, sa, rs, bs, bb, has_bias, j);
-              if (ep.act == LQ_ACT_RELU) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
-            }
-            if (ep.out_dtype == LQ_F32) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(y[j]);
-              store_vals<float, 32>(reinterpret_cast<float*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
-            } else if (ep.out_dtype == LQ_BF16) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                r[j] = f32_to_bf16_bits(y[2 * j]) | (f32_to_bf16_bits(y[2 * j + 1]) << 16);
-              store_vals<uint16_t, 16>(reinterpret_cast<uint16_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
-            } else {  // LQ_S8 / LQ_U8: requantise
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                uint32_t w = 0;
-#pragma unroll
-                for (int b = 0; b < 4; ++b)
-                  w |= ((uint32_t)(int)code_f32(y[4 * j + b], so, zo, fqmin, fqmax) & 0xffu) << (8 * b);
-                r[j] = w;
-              }
-              store_vals<uint8_t, 8>(reinterpret_cast<uint8_t*>(ep.out) + out_row + ncol0, r, valid, ep.vec_ok);
-            }
-          }
-        }
+      } else if (gated) {
+        const int on0 = tn_idx * (BN / 2);
+        if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true>(ep, g, rc, taddr, stg, lane, half, n0, on0);
+        else epilogue_tile<BN, KIND_BF16, true>(ep, g, rc, taddr, stg, lane, half, n0, on0);
+      } else if (ep.out_dtype == LQ_BF16) {
+        epilogue_tile<BN, KIND_BF16, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+      } else if (ep.out_dtype == LQ_F32) {
+        epilogue_tile<BN, KIND_F32, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+      } else if (ep.out_dtype == LQ_S32) {
+        epilogue_tile<BN, KIND_S32, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
       } else {
-        // gated: tile columns [0,BN/2) are gate, [BN/2,BN) the matching up columns
-        const int on0 = (tile / tiles_mw) * (BN / 2);
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t rg[32], ru[32];
-          __syncwarp();
-          tc_ld32(taddr + c * 32, rg);
-          tc_ld32(taddr + BN / 2 + c * 32, ru);
-          tc_wait_ld();
-          const int ocol0 = on0 + c * 32;
-          const int valid = row_ok ? min(32, ep.n_out - ocol0) : 0;
-          if (valid <= 0) continue;
-          float y[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float yg = dequant_acc((int)rg[j], zpa, sa, s_rowsum, s_bscale, s_bias, has_bias, c * 32 + j);
-            const float yu = dequant_acc((int)ru[j], zpa, sa, s_rowsum, s_bscale, s_bias, has_bias,
-                                         BN / 2 + c * 32 + j);
-            y[j] = __fmul_rn(silu_f32(yg), yu);
-          }
-          if (ep.out_dtype == LQ_F32) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) rg[j] = __float_as_uint(y[j]);
-            store_vals<float, 32>(reinterpret_cast<float*>(ep.out) + out_row + ocol0, rg, valid, ep.vec_ok);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              rg[j] = f32_to_bf16_bits(y[2 * j]) | (f32_to_bf16_bits(y[2 * j + 1]) << 16);
-            store_vals<uint16_t, 16>(reinterpret_cast<uint16_t*>(ep.out) + out_row + ocol0, rg, valid, ep.vec_ok);
-          }
-        }
+        epilogue_tile<BN, KIND_Q8, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
       }
       // hand the accumulator stage back to the MMA issuer
       tc_fence_before();
@@ -742,6 +838,7 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
   d->out = out, d->ldo = (long long)ldo, d->n_out = (int)n_out, d->status = status;
   const size_t esz = dtype_size(e->out_dtype);
   d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
+  d->par_vec = aligned16(e->b_scale) && aligned16(e->bias) && aligned16(e->b_rowsum);
 }
 
 template <int BN, bool PAIR>
