@@ -102,11 +102,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait.  Returns false when the CTA is aborting or the budget ran out.
+// Bounded wait.  Returns false when the CTA is aborting or the budget ran out.  SLEEP_NS > 0
+// backs off between polls (long waits by warps that are not on the critical path).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
@@ -118,8 +121,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 // Warp-uniform wait: every lane polls, the warp agrees on the outcome.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+  return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag));
 }
 // One lane of a converged warp.  The surrounding control flow stays warp-uniform so that
 // loop state and descriptors can live in uniform registers.
@@ -683,7 +687,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       rc.row_mask = __ballot_sync(0xffffffffu, row_ok && !(g.debug & 8));
       rc.row0 = (long long)__shfl_sync(0xffffffffu, m_global, 0);
 
-      if (!mbar_wait_warp(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      if (!mbar_wait_warp<200>(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
       const int n0 = tn_idx * BN;
