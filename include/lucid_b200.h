@@ -78,6 +78,29 @@ size_t lq_minmax_workspace_bytes(void);
 int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, int mode, float* out_min,
               float* out_max, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Per-tensor range reduction that allocates nothing and takes no workspace.
+ * (No counterpart in the reference: it exists for callers of this library that
+ * cannot allocate device memory where they need a range -- code inside an arena
+ * or pool owner that forbids nested allocation, latency-critical threads that
+ * must not touch an allocator, and foreign-language hosts that bind only this
+ * header.)  The scratch that lq_minmax takes from its caller lives in a fixed
+ * array of about 10 KB inside the library image; every GPU that loads the
+ * library holds that array until the process exits.
+ *
+ * x: n contiguous elements (LQ_F32 | LQ_BF16); out_min / out_max: 1 float each.
+ * n must not exceed lq_minmax_noalloc_max_elems() (2^30); larger inputs are
+ * rejected with LQ_ERR_SHAPE -- use lq_minmax with a workspace for those.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and caches it; make that
+ * first call outside any stream capture.  All calls on a device share the one
+ * array: the call re-arms it on `stream` before launching, so calls that are
+ * ordered on a stream are safe, while calls that can overlap on the GPU
+ * (different streams, different host threads) race and must be serialised by
+ * the caller.  Results are identical to lq_minmax in per-tensor mode. */
+size_t lq_minmax_noalloc_max_elems(void);
+int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* out_min, float* out_max,
+                      void* stream);
+
 /* (scale, zero_point) from observed ranges, on device.
  * Replaces calculate_qparams (lucid/quantization/_qparams.py:190-215). */
 int lq_calculate_qparams(const float* min_val, const float* max_val, size_t n, int symmetric,

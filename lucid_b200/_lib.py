@@ -69,6 +69,8 @@ _SIGNATURES = {
     "lq_minmax_workspace_bytes": (C.c_size_t, []),
     "lq_minmax": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p,
                             C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lq_minmax_noalloc_max_elems": (C.c_size_t, []),
+    "lq_minmax_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lq_calculate_qparams": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
                                        C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                                        C.c_void_p]),

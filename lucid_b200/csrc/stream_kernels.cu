@@ -5,6 +5,9 @@
 // one IEEE binary32 operation per step (see common.cuh).
 #include <math.h>
 
+#include <mutex>
+#include <string>
+
 #include "common.cuh"
 
 namespace lq {
@@ -608,4 +611,66 @@ extern "C" int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, v
   const bool vec_ok = aligned16(b) && (K % 16 == 0);
   rowsum_kernel<<<grid_for(N * 32), kThreads, 0, (cudaStream_t)stream>>>(b, N, K, vec_ok, out);
   return check_cuda(cudaGetLastError(), "lq_rowsum_s8 launch");
+}
+
+// ---- allocation-free variant of the per-tensor range reduction -------------------------------
+//
+// Some callers must not allocate device memory at the point where they need a range: code
+// running inside a memory-pool or arena owner that forbids nested allocation, a real-time
+// serving thread that may not take the allocator lock, or a host written in another language
+// that binds only this C ABI and has no device allocator of its own.  For them the scratch
+// of the reduction (one partial min/max pair per CTA and the arrival counter) lives in a
+// fixed array inside the library image instead of a caller-supplied workspace.
+namespace lq {
+namespace {
+constexpr size_t kNoAllocMaxElems = size_t(1) << 30;  // 2^30 elements per call
+static __device__ __align__(256) unsigned char g_minmax_scratch[sizeof(MinMaxWorkspace)];
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device.  In host code the array's name
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+int scratch_address(void** out) {
+  int dev = 0;
+  LQ_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(LQ_ERR_UNSUPPORTED, "lq_minmax_noalloc: device index out of range");
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    LQ_CUDA(cudaGetSymbolAddress(&p, g_minmax_scratch));
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return LQ_OK;
+}
+}  // namespace
+}  // namespace lq
+
+extern "C" size_t lq_minmax_noalloc_max_elems(void) { return lq::kNoAllocMaxElems; }
+
+extern "C" int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* out_min,
+                                 float* out_max, void* stream) {
+  if (!x || !out_min || !out_max) return fail(LQ_ERR_DEVICE, "lq_minmax_noalloc: null pointer");
+  if (n == 0) return fail(LQ_ERR_SHAPE, "lq_minmax_noalloc: empty input has no min/max");
+  if (n > kNoAllocMaxElems)
+    return fail(LQ_ERR_SHAPE, "lq_minmax_noalloc: " + std::to_string(n) + " elements exceed the built-in scratch's limit of " +
+                                  std::to_string(kNoAllocMaxElems) + " per call; use lq_minmax with a workspace");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_minmax_noalloc: in_dtype");
+  void* scratch = nullptr;
+  int rc = scratch_address(&scratch);
+  if (rc != LQ_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps whatever the previous call left: re-arm the arrival counter
+  LQ_CUDA(cudaMemsetAsync(scratch, 0, 16, st));
+  const bool vec_ok = aligned16(x);
+  size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
+  int grid = (int)(want < 1 ? 1 : (want > (size_t)(kNumSMs * 4) ? kNumSMs * 4 : want));
+  auto* ws = (MinMaxWorkspace*)scratch;
+  if (in_dtype == LQ_F32)
+    minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max);
+  else
+    minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max);
+  return check_cuda(cudaGetLastError(), "lq_minmax_noalloc launch");
 }
