@@ -30,12 +30,167 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Every step is a separate IEEE binary32 operation; the intrinsics keep the
 // compiler from contracting or approximating them.
 
+// Correctly rounded x / s with the divisor's reciprocal hoisted out of the element loop.
+// q0 = RN(x * y) with y = RN(1 / s) is within 1.5 ulp of x / s; two residual corrections
+// (r = x - s*q exactly, by FMA; q += r*y) give the correctly rounded quotient (Markstein), the
+// same value `__fdiv_rn` returns.  The short form is used only where no intermediate can
+// overflow or lose bits to underflow: |s| in [2^-60, 2^60] and |q| < 2^24; everything else
+// (huge quotients, denormal or huge scales, inf / NaN) takes the full-range division.
+struct Divisor {
+  float s, y;
+  bool fast;
+};
+__device__ __forceinline__ Divisor make_divisor(float s) {
+  Divisor d;
+  const float a = fabsf(s);
+  d.s = s;
+  d.fast = a > 0x1p-60f && a < 0x1p60f;
+  d.y = d.fast ? __frcp_rn(s) : 0.0f;
+  return d;
+}
+__device__ __forceinline__ float div_rn(float x, const Divisor& d) {
+  if (d.fast) {
+    float q = __fmul_rn(x, d.y);
+    if (fabsf(q) < 0x1p24f && fabsf(x) > 0x1p-90f) {
+      float r = __fmaf_rn(-q, d.s, x);
+      q = __fmaf_rn(r, d.y, q);
+      r = __fmaf_rn(-q, d.s, x);
+      return __fmaf_rn(r, d.y, q);
+    }
+    if (x == 0.0f) return q;  // +-0 / s
+  }
+  return __fdiv_rn(x, d.s);
+}
+
+// Four quotients by the same divisor.  The short form runs unconditionally on all four (no
+// per-element branch, so the four dependency chains overlap); the rare elements outside its
+// domain are redone with the full-range division afterwards.
+// Returns true when at least one element took the full division (its quotient is >= `limit`
+// in magnitude, infinite or NaN).
+__device__ __forceinline__ bool div_rn4(const float (&x)[4], const Divisor& d, float (&q)[4],
+                                        float limit = 0x1p24f) {
+  bool any = false;
+  if (d.fast) {
+    bool redo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float q0 = __fmul_rn(x[i], d.y);
+      float r = __fmaf_rn(-q0, d.s, x[i]);
+      const float q1 = __fmaf_rn(r, d.y, q0);
+      r = __fmaf_rn(-q1, d.s, x[i]);
+      q[i] = __fmaf_rn(r, d.y, q1);
+      // Outside |q| < limit (overflowing or NaN quotients included) the full division decides.
+      // Tiny operands need no guard: |s| >= 2^-60 keeps any quotient that lost bits to
+      // underflow far below 1/2, and every caller rounds the quotient to an integer next.
+      redo[i] = !(fabsf(q0) < limit);
+      any |= redo[i];
+    }
+    if (any) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (redo[i]) q[i] = __fdiv_rn(x[i], d.s);
+    }
+  } else {
+    any = true;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = __fdiv_rn(x[i], d.s);
+  }
+  return any;
+}
+
+// clip(rint(x / s) + z, qmin, qmax) for four elements sharing (s, z).
+__device__ __forceinline__ void code4_f32(const float (&x)[4], const Divisor& d, float z, float qmin,
+                                          float qmax, float (&c)[4]) {
+  float q[4];
+  div_rn4(x, d, q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float t = __fadd_rn(rintf(q[i]), z);
+    // max-then-min equals the compare-based clip for every non-NaN t (NaN is out of contract:
+    // the reference's integer cast of it is undefined)
+    c[i] = fminf(fmaxf(t, qmin), qmax);
+  }
+}
+
+// Integer-domain tail of the encode.  For |q| < 2^22, q + 1.5*2^23 rounds q to the nearest
+// integer (ties to even) in the low mantissa bits, so rint, "+ z", the clip and the integer cast
+// collapse into one float add and integer ops, with the same result as the float sequence
+// whenever z is an integer of modest size.  `zofs` = z - bits(1.5*2^23).
+struct IntGrid {
+  int zofs, qmin, qmax;
+  bool fast;   // z integral, |z|, |qmin|, |qmax| < 2^22
+  bool clamp;  // grid narrower than the saturating pack of the storage type
+};
+__device__ __forceinline__ IntGrid make_int_grid(float z, float qmin, float qmax, int store_lo, int store_hi) {
+  IntGrid g;
+  g.fast = z == rintf(z) && fabsf(z) < 0x1p22f && fabsf(qmin) < 0x1p22f && fabsf(qmax) < 0x1p22f;
+  g.zofs = (g.fast ? (int)z : 0) - 0x4B400000;
+  g.qmin = (int)qmin, g.qmax = (int)qmax;
+  g.clamp = !(g.qmin <= store_lo && g.qmax >= store_hi);
+  return g;
+}
+// clip(rint(x / s) + z, qmin, qmax) as integers, four elements sharing (s, z).
+__device__ __forceinline__ void code4_int(const float (&x)[4], const Divisor& d, const IntGrid& g,
+                                          float z, float qmin, float qmax, int (&c)[4]) {
+  float q[4];
+  const bool any = div_rn4(x, d, q, 0x1p22f);
+  if (!any && g.fast) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int v = __float_as_int(__fadd_rn(q[i], 12582912.0f)) + g.zofs;
+      if (g.clamp) v = min(max(v, g.qmin), g.qmax);
+      c[i] = v;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float t = __fadd_rn(rintf(q[i]), z);
+      c[i] = __float2int_rz(t < qmin ? qmin : (t > qmax ? qmax : t));
+    }
+  }
+}
+// four ints -> four packed 8-bit codes (saturating to the storage type)
+__device__ __forceinline__ uint32_t pack4i_s8(const int (&c)[4]) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(c[3]), "r"(c[2]), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(c[1]), "r"(c[0]), "r"(hi));
+  return out;
+}
+__device__ __forceinline__ uint32_t pack4i_u8(const int (&c)[4]) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(c[3]), "r"(c[2]), "r"(0));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(c[1]), "r"(c[0]), "r"(hi));
+  return out;
+}
+
+// Four integral floats (already clipped to the storage range) -> four packed 8-bit codes.
+__device__ __forceinline__ uint32_t pack4_s8(const float (&c)[4]) {
+  const int a = __float2int_rz(c[0]), b = __float2int_rz(c[1]), d = __float2int_rz(c[2]), e = __float2int_rz(c[3]);
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e), "r"(d), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+  return out;
+}
+__device__ __forceinline__ uint32_t pack4_u8(const float (&c)[4]) {
+  const int a = __float2int_rz(c[0]), b = __float2int_rz(c[1]), d = __float2int_rz(c[2]), e = __float2int_rz(c[3]);
+  uint32_t hi, out;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e), "r"(d), "r"(0));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+  return out;
+}
+
 // clip(rint(x / s) + z, qmin, qmax): the reference's quantize, float domain.
-__device__ __forceinline__ float code_f32(float x, float s, float z, float qmin, float qmax) {
-  float t = __fdiv_rn(x, s);
+__device__ __forceinline__ float code_f32(float x, const Divisor& d, float z, float qmin, float qmax) {
+  float t = div_rn(x, d);
   t = rintf(t);  // ties to even
   t = __fadd_rn(t, z);
   // compare-based clip, lower bound first; NaN falls through
+  return t < qmin ? qmin : (t > qmax ? qmax : t);
+}
+__device__ __forceinline__ float code_f32(float x, float s, float z, float qmin, float qmax) {
+  float t = __fdiv_rn(x, s);
+  t = rintf(t);
+  t = __fadd_rn(t, z);
   return t < qmin ? qmin : (t > qmax ? qmax : t);
 }
 
@@ -72,5 +227,50 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+// ---- bulk-copy pipeline pieces (HBM -> shared memory without register staging) ---------------
+namespace pipe {
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// One-dimensional bulk copy global -> shared; `bytes` and both addresses are multiples of 16.
+// The bytes are counted on `bar`, whose single arrival this call also performs.
+__device__ __forceinline__ void load_async(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Orders this thread's earlier generic-proxy reads of shared memory before later
+// asynchronous-proxy writes to it (a slot is refilled after it was read).
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Bounded wait on a phase; false when the poll budget (seconds) ran out.
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+}  // namespace pipe
 
 }  // namespace lq

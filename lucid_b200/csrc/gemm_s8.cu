@@ -288,7 +288,8 @@ struct KindInfo {
 struct RowCtx {
   float sa;          // activation scale of this thread's row
   int zpa;           // activation zero point
-  float so, zo;      // output grid
+  Divisor so;        // output grid: scale (with its hoisted reciprocal)
+  float zo;          // ... and zero point
   float fqmin, fqmax;
   uint32_t row_mask; // valid rows of this warp (bit r = tile row quad*32 + r)
   long long row0;    // global output row of the warp's first row
@@ -309,11 +310,11 @@ __device__ __forceinline__ void finish32(const float (&y)[32], uint32_t (&w)[32]
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      uint32_t v = 0;
-#pragma unroll
-      for (int b = 0; b < 4; ++b)
-        v |= ((uint32_t)(int)code_f32(y[4 * j + b], rc.so, rc.zo, rc.fqmin, rc.fqmax) & 0xffu) << (8 * b);
-      w[j] = v;
+      const float x4[4] = {y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]};
+      float c[4];
+      code4_f32(x4, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
+      // identical byte patterns for both storages once the value is inside its grid
+      w[j] = rc.fqmin < 0.0f ? pack4_s8(c) : pack4_u8(c);
     }
   }
 }
@@ -681,7 +682,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       rc.sa = 1.0f;
       if (ep.a_scale) rc.sa = ep.a_scale_mode == LQ_PER_ROW ? (row_ok ? __ldg(ep.a_scale + m_global) : 1.0f) : __ldg(ep.a_scale);
       rc.zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0;
-      rc.so = ep.out_scale ? __ldg(ep.out_scale) : 1.0f;
+      rc.so = make_divisor(ep.out_scale ? __ldg(ep.out_scale) : 1.0f);
       rc.zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
       rc.fqmin = (float)ep.qmin, rc.fqmax = (float)ep.qmax;
       rc.row_mask = __ballot_sync(0xffffffffu, row_ok && !(g.debug & 8));

@@ -1,9 +1,10 @@
 // HBM-bound streaming kernels: range reduction, qparams, quantize, dequantize,
 // fake-quantize and the fused per-token encode.  All are 128-bit coalesced
-// streams; each thread moves 16 elements per iteration and the grids are sized
+// streams; lanes take consecutive 4-element groups (full-line warp accesses) and the grids are sized
 // in multiples of the SM count.  Arithmetic follows the reference's order with
 // one IEEE binary32 operation per step (see common.cuh).
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <string>
@@ -137,30 +138,122 @@ struct Packet<int16_t> {
   __device__ static void store1(int16_t* p, float v) { *p = (int16_t)(int)v; }
 };
 
-__device__ __forceinline__ void packet_params(const QParamRef& q, size_t row, size_t col0,
-                                              float (&s)[16], float (&z)[16]) {
-  if (q.mode == LQ_PER_COL) {
+// ---- 4-element groups: the unit of the coalesced streams ---------------------------------
+// Consecutive lanes take consecutive groups, so every warp-level access is one contiguous
+// run (512 B of f32, 256 B of bf16 / s16, 128 B of 8-bit codes): full lines, no sector is
+// fetched twice.
+template <typename T>
+struct Quad;
+template <>
+struct Quad<float> {
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const uint4 u = ld_stream_u4(p);
+    v[0] = __uint_as_float(u.x), v[1] = __uint_as_float(u.y), v[2] = __uint_as_float(u.z), v[3] = __uint_as_float(u.w);
+  }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    st_stream_u4(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+  }
+};
+__device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u1(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_u2(void* p, uint2 v) {
+  asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_stream_u1(void* p, uint32_t v) {
+  asm volatile("st.global.L1::no_allocate.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+template <>
+struct Quad<__nv_bfloat16> {
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 u = ld_stream_u2(p);
+    v[0] = bf16_bits_to_f32(u.x & 0xffffu), v[1] = bf16_bits_to_f32(u.x >> 16);
+    v[2] = bf16_bits_to_f32(u.y & 0xffffu), v[3] = bf16_bits_to_f32(u.y >> 16);
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[4]) {
+    st_stream_u2(p, make_uint2(f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16),
+                               f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16)));
+  }
+};
+template <typename T>
+struct Quad8 {
+  __device__ static void load(const T* p, float (&v)[4]) {
+    const uint32_t u = ld_stream_u1(p);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 a = __ldg(reinterpret_cast<const float4*>(q.s + col0) + i);
-      float4 b = __ldg(reinterpret_cast<const float4*>(q.z + col0) + i);
-      s[4 * i] = a.x, s[4 * i + 1] = a.y, s[4 * i + 2] = a.z, s[4 * i + 3] = a.w;
-      z[4 * i] = b.x, z[4 * i + 1] = b.y, z[4 * i + 2] = b.z, z[4 * i + 3] = b.w;
-    }
+    for (int b = 0; b < 4; ++b) v[b] = (float)(T)((u >> (8 * b)) & 0xffu);
+  }
+  __device__ static void store(T* p, const float (&v)[4]) {
+    // values arrive clipped to the grid, which lies inside the storage type
+    st_stream_u1(p, sizeof(T) == 1 && T(-1) < T(0) ? pack4_s8(v) : pack4_u8(v));
+  }
+};
+template <typename T>
+struct StoreRange;
+template <>
+struct StoreRange<int8_t> { static constexpr int lo = -128, hi = 127; };
+template <>
+struct StoreRange<uint8_t> { static constexpr int lo = 0, hi = 255; };
+template <>
+struct StoreRange<int16_t> { static constexpr int lo = -32768, hi = 32767; };
+template <>
+struct StoreRange<float> { static constexpr int lo = 0, hi = 0; };
+template <>
+struct StoreRange<__nv_bfloat16> { static constexpr int lo = 0, hi = 0; };
+// four integer codes -> storage (saturating)
+__device__ __forceinline__ void store_codes(int8_t* p, const int (&c)[4]) { st_stream_u1(p, pack4i_s8(c)); }
+__device__ __forceinline__ void store_codes(uint8_t* p, const int (&c)[4]) { st_stream_u1(p, pack4i_u8(c)); }
+__device__ __forceinline__ void store_codes(int16_t* p, const int (&c)[4]) {
+  uint32_t lo, hi;
+  asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(lo) : "r"(c[1]), "r"(c[0]));
+  asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(hi) : "r"(c[3]), "r"(c[2]));
+  st_stream_u2(p, make_uint2(lo, hi));
+}
+__device__ __forceinline__ void store_codes(float*, const int (&)[4]) {}
+__device__ __forceinline__ void store_codes(__nv_bfloat16*, const int (&)[4]) {}
+template <>
+struct Quad<int8_t> : Quad8<int8_t> {};
+template <>
+struct Quad<uint8_t> : Quad8<uint8_t> {};
+template <>
+struct Quad<int16_t> {
+  __device__ static void load(const int16_t* p, float (&v)[4]) {
+    const uint2 u = ld_stream_u2(p);
+    v[0] = (float)(int16_t)(u.x & 0xffffu), v[1] = (float)(int16_t)(u.x >> 16);
+    v[2] = (float)(int16_t)(u.y & 0xffffu), v[3] = (float)(int16_t)(u.y >> 16);
+  }
+  __device__ static void store(int16_t* p, const float (&v)[4]) {
+    st_stream_u2(p, make_uint2(((uint32_t)(int)v[0] & 0xffffu) | (((uint32_t)(int)v[1] & 0xffffu) << 16),
+                               ((uint32_t)(int)v[2] & 0xffffu) | (((uint32_t)(int)v[3] & 0xffffu) << 16)));
+  }
+};
+
+__device__ __forceinline__ void quad_params(const QParamRef& q, size_t elem, size_t cols,
+                                            float (&s)[4], float (&z)[4]) {
+  if (q.mode == LQ_PER_COL) {
+    const size_t col = elem % cols;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(q.s + col));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(q.z + col));
+    s[0] = a.x, s[1] = a.y, s[2] = a.z, s[3] = a.w;
+    z[0] = b.x, z[1] = b.y, z[2] = b.z, z[3] = b.w;
   } else {
     float sv, zv;
     if (q.mode == LQ_PER_ROW) {
-      sv = __ldg(q.s + row);
-      zv = __ldg(q.z + row);
+      const size_t row = elem / cols;
+      sv = __ldg(q.s + row), zv = __ldg(q.z + row);
     } else if (q.s != nullptr) {
-      sv = __ldg(q.s);
-      zv = __ldg(q.z);
+      sv = __ldg(q.s), zv = __ldg(q.z);
     } else {
-      sv = q.sv;
-      zv = q.zv;
+      sv = q.sv, zv = q.zv;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) s[i] = sv, z[i] = zv;
+    for (int i = 0; i < 4; ++i) s[i] = sv, z[i] = zv;
   }
 }
 
@@ -180,36 +273,99 @@ __device__ __forceinline__ void scalar_params(const QParamRef& q, size_t row, si
 enum class Op { kQuantize, kDequantize, kFakeQuantize };
 
 template <Op OP>
-__device__ __forceinline__ float apply(float x, float s, float z, float qmin, float qmax,
+__device__ __forceinline__ float apply(float x, const Divisor& d, float z, float qmin, float qmax,
                                        float* mask) {
-  if (OP == Op::kQuantize) return code_f32(x, s, z, qmin, qmax);
+  const float s = d.s;
+  if (OP == Op::kQuantize) return code_f32(x, d, z, qmin, qmax);
   if (OP == Op::kDequantize) return __fmul_rn(__fsub_rn(x, z), s);
   // fake-quantize: q_pre, clip, (q - z) * s
-  float q_pre = __fadd_rn(rintf(__fdiv_rn(x, s)), z);
+  float q_pre = __fadd_rn(rintf(div_rn(x, d)), z);
   float q = q_pre < qmin ? qmin : (q_pre > qmax ? qmax : q_pre);
   if (mask) *mask = (q_pre >= qmin ? 1.0f : 0.0f) * (q_pre <= qmax ? 1.0f : 0.0f);
   return __fmul_rn(__fsub_rn(q, z), s);
 }
 
-// Vector kernel: one 16-element packet per thread-iteration, grid-stride.
+// One 4-element group sharing (scale, zero point): branch-free in the common case.
+template <Op OP, bool MASK>
+__device__ __forceinline__ void apply4(float (&v)[4], const Divisor& d, float z, float qmin,
+                                       float qmax, float (&m)[4]) {
+  if (OP == Op::kDequantize) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __fmul_rn(__fsub_rn(v[i], z), d.s);
+  } else if (OP == Op::kQuantize) {
+    float c[4];
+    code4_f32(v, d, z, qmin, qmax, c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = c[i];
+  } else {
+    float q[4];
+    div_rn4(v, d, q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float q_pre = __fadd_rn(rintf(q[i]), z);
+      const float c = q_pre < qmin ? qmin : (q_pre > qmax ? qmax : q_pre);
+      if (MASK) m[i] = (q_pre >= qmin ? 1.0f : 0.0f) * (q_pre <= qmax ? 1.0f : 0.0f);
+      v[i] = __fmul_rn(__fsub_rn(c, z), d.s);
+    }
+  }
+}
+
+// Divisor of a group: hoisted for per-tensor parameters, rebuilt per group otherwise.
+template <Op OP>
+__device__ __forceinline__ Divisor group_divisor(float s) {
+  Divisor d;
+  d.s = s, d.y = 0.0f, d.fast = false;
+  if (OP != Op::kDequantize) d = make_divisor(s);
+  return d;
+}
+
+// Vector kernel: kUnroll coalesced 4-element groups per thread-iteration, grid-stride.
+constexpr int kUnroll = 8;
 template <Op OP, typename In, typename Out, bool MASK>
 __global__ void __launch_bounds__(kThreads)
 affine_vec_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __restrict__ mask,
                   size_t rows, size_t cols, QParamRef q, float qmin, float qmax) {
-  const size_t ppr = cols / 16;
-  const size_t npackets = rows * ppr;
-  const size_t stride = (size_t)gridDim.x * kThreads;
-  for (size_t p = (size_t)blockIdx.x * kThreads + threadIdx.x; p < npackets; p += stride) {
-    const size_t row = p / ppr;
-    const size_t col0 = (p - row * ppr) * 16;
-    const size_t off = row * cols + col0;
-    float v[16], s[16], z[16], m[16];
-    Packet<In>::load(x + off, v);
-    packet_params(q, row, col0, s, z);
+  const size_t ngroups = rows * cols / 4;
+  const size_t span = (size_t)kThreads * kUnroll;
+  Divisor dt = group_divisor<OP>(1.0f);
+  if (q.mode == LQ_PER_TENSOR) dt = group_divisor<OP>(q.s != nullptr ? __ldg(q.s) : q.sv);
+  const IntGrid igt = make_int_grid(q.mode == LQ_PER_TENSOR ? (q.z != nullptr ? __ldg(q.z) : q.zv) : 0.0f, qmin, qmax,
+                                    StoreRange<Out>::lo, StoreRange<Out>::hi);
+  for (size_t base = (size_t)blockIdx.x * span; base < ngroups; base += (size_t)gridDim.x * span) {
+    float v[kUnroll][4];
+    size_t gidx[kUnroll];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = apply<OP>(v[i], s[i], z[i], qmin, qmax, MASK ? &m[i] : nullptr);
-    Packet<Out>::store(out + off, v);
-    if (MASK) Packet<float>::store(mask + off, m);
+    for (int u = 0; u < kUnroll; ++u) {
+      gidx[u] = base + (size_t)u * kThreads + threadIdx.x;
+      if (gidx[u] < ngroups) Quad<In>::load(x + gidx[u] * 4, v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (gidx[u] >= ngroups) continue;
+      float s[4], z[4], m[4];
+      quad_params(q, gidx[u] * 4, cols, s, z);
+      if (q.mode == LQ_PER_COL) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          Divisor d;
+          d.s = s[i], d.y = 0.0f, d.fast = false;
+          if (OP != Op::kDequantize) d = make_divisor(s[i]);
+          v[u][i] = apply<OP>(v[u][i], d, z[i], qmin, qmax, MASK ? &m[i] : nullptr);
+        }
+      } else {
+        const Divisor d = q.mode == LQ_PER_TENSOR ? dt : group_divisor<OP>(s[0]);
+        if (OP == Op::kQuantize) {
+          const IntGrid ig = q.mode == LQ_PER_TENSOR ? igt : make_int_grid(z[0], qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
+          int c[4];
+          code4_int(v[u], d, ig, z[0], qmin, qmax, c);
+          store_codes(out + gidx[u] * 4, c);
+          continue;
+        }
+        apply4<OP, MASK>(v[u], d, z[0], qmin, qmax, m);
+      }
+      Quad<Out>::store(out + gidx[u] * 4, v[u]);
+      if (MASK) Quad<float>::store(mask + gidx[u] * 4, m);
+    }
   }
 }
 
@@ -224,33 +380,19 @@ affine_scalar_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __r
     const size_t row = i / cols, col = i - row * cols;
     float s, z, m;
     scalar_params(q, row, col, s, z);
-    float r = apply<OP>(Packet<In>::load1(x + i), s, z, qmin, qmax, MASK ? &m : nullptr);
+    Divisor d;
+    d.s = s, d.y = 0.0f, d.fast = false;
+    float r = apply<OP>(Packet<In>::load1(x + i), d, z, qmin, qmax, MASK ? &m : nullptr);
     Packet<Out>::store1(out + i, r);
     if (MASK) mask[i] = m;
   }
 }
 
-inline int grid_for(size_t work_items) {
+inline int grid_for(size_t work_items, size_t cap = (size_t)kNumSMs * 64) {
   size_t blocks = (work_items + kThreads - 1) / kThreads;
-  if (blocks > (size_t)kMaxBlocks) blocks = kMaxBlocks;
+  if (blocks > cap) blocks = cap;
   if (blocks == 0) blocks = 1;
   return (int)blocks;
-}
-
-template <Op OP, typename In, typename Out, bool MASK = false>
-int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t cols,
-                  const QParamRef& q, int qmin, int qmax, cudaStream_t st) {
-  const bool vec = (cols % 16 == 0) && aligned16(x) && aligned16(out) &&
-                   (!MASK || aligned16(mask)) &&
-                   (q.mode != LQ_PER_COL || (aligned16(q.s) && aligned16(q.z)));
-  if (vec) {
-    affine_vec_kernel<OP, In, Out, MASK><<<grid_for(rows * (cols / 16)), kThreads, 0, st>>>(
-        (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
-  } else {
-    affine_scalar_kernel<OP, In, Out, MASK><<<grid_for(rows * cols), kThreads, 0, st>>>(
-        (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
-  }
-  return check_cuda(cudaGetLastError(), "affine kernel launch");
 }
 
 int make_params(const float* scale, const float* zp, float sv, float zv, int ch_mode, QParamRef* q) {
@@ -271,31 +413,47 @@ struct MinMaxWorkspace {
   float pmax[kMaxBlocks];
 };
 
+// Elements per 16-byte vector of the input type.
+template <typename In>
+struct VecOf {
+  static constexpr int kElems = 16 / sizeof(In);
+};
+template <typename In>
+__device__ __forceinline__ void vec_minmax(uint4 u, float& mn, float& mx);
+template <>
+__device__ __forceinline__ void vec_minmax<float>(uint4 u, float& mn, float& mx) {
+  const float a = __uint_as_float(u.x), b = __uint_as_float(u.y), c = __uint_as_float(u.z), d = __uint_as_float(u.w);
+  mn = fminf(mn, fminf(fminf(a, b), fminf(c, d)));
+  mx = fmaxf(mx, fmaxf(fmaxf(a, b), fmaxf(c, d)));
+}
+template <>
+__device__ __forceinline__ void vec_minmax<__nv_bfloat16>(uint4 u, float& mn, float& mx) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float a = bf16_bits_to_f32(w[j] & 0xffffu), b = bf16_bits_to_f32(w[j] >> 16);
+    mn = fminf(mn, fminf(a, b));
+    mx = fmaxf(mx, fmaxf(a, b));
+  }
+}
+
+// x[0..n): lane `first` of `stride` cooperating threads.  16-byte vectors, consecutive
+// threads on consecutive vectors, four loads in flight per thread.
 template <typename In>
 __device__ __forceinline__ void minmax_accumulate(const In* x, size_t n, size_t first, size_t stride,
                                                   bool vec_ok, float& mn, float& mx) {
-  // x[0..n): thread `first` of `stride` threads.  16 elements per packet.
-  size_t npk = vec_ok ? n / 16 : 0;
-  size_t p = first;
-  // two packets in flight per iteration
-  for (; p + stride < npk; p += 2 * stride) {
-    float a[16], b[16];
-    Packet<In>::load(x + p * 16, a);
-    Packet<In>::load(x + (p + stride) * 16, b);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      mn = fminf(mn, fminf(a[i], b[i]));
-      mx = fmaxf(mx, fmaxf(a[i], b[i]));
-    }
+  constexpr int E = VecOf<In>::kElems;
+  const size_t nvec = vec_ok ? n / E : 0;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  size_t i = first;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    const uint4 a = ld_stream_u4(xv + i), b = ld_stream_u4(xv + i + stride);
+    const uint4 c = ld_stream_u4(xv + i + 2 * stride), d = ld_stream_u4(xv + i + 3 * stride);
+    vec_minmax<In>(a, mn, mx), vec_minmax<In>(b, mn, mx), vec_minmax<In>(c, mn, mx), vec_minmax<In>(d, mn, mx);
   }
-  for (; p < npk; p += stride) {
-    float a[16];
-    Packet<In>::load(x + p * 16, a);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) mn = fminf(mn, a[i]), mx = fmaxf(mx, a[i]);
-  }
-  for (size_t i = npk * 16 + first; i < n; i += stride) {
-    float v = Packet<In>::load1(x + i);
+  for (; i < nvec; i += stride) vec_minmax<In>(ld_stream_u4(xv + i), mn, mx);
+  for (size_t e = nvec * E + first; e < n; e += stride) {
+    const float v = Packet<In>::load1(x + e);
     mn = fminf(mn, v), mx = fmaxf(mx, v);
   }
 }
@@ -314,15 +472,225 @@ __device__ __forceinline__ void block_minmax(float& mn, float& mx) {
   __syncthreads();
 }
 
+// ---- bulk-copy pipelined variants ---------------------------------------------------------
+// Reads are the long pole of these kernels: with register-staged loads a thread holds a few
+// 16-byte loads in flight and idles until they land.  Here each persistent CTA keeps a ring of
+// shared-memory slots filled by one-dimensional bulk copies (cp.async.bulk, completion counted
+// on an mbarrier): tens of KB per CTA stay in flight with no registers tied up, threads read
+// the slot with conflict-free 16-byte shared loads and write results straight to HBM.
+constexpr uint32_t kRingBytes = 64 * 1024;
+constexpr uint32_t kChunkBytes = 8 * 1024;
+constexpr int kRingHeader = 128;  // mbarriers
+
+// Streams at least this large use the bulk-copy ring (LQ_STREAM_PIPE_MIN overrides, bytes).
+inline size_t pipe_min_bytes() {
+  static const size_t v = [] {
+    const char* e = getenv("LQ_STREAM_PIPE_MIN");
+    return e ? (size_t)strtoull(e, nullptr, 10) : (size_t)256 * 1024;
+  }();
+  return v;
+}
+
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u1(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+// four consecutive elements of type T from a shared-memory slot
+template <typename T>
+__device__ __forceinline__ void lds_quad(uint32_t a, float (&v)[4]);
+template <>
+__device__ __forceinline__ void lds_quad<float>(uint32_t a, float (&v)[4]) {
+  const uint4 u = lds_u4(a);
+  v[0] = __uint_as_float(u.x), v[1] = __uint_as_float(u.y), v[2] = __uint_as_float(u.z), v[3] = __uint_as_float(u.w);
+}
+template <>
+__device__ __forceinline__ void lds_quad<__nv_bfloat16>(uint32_t a, float (&v)[4]) {
+  const uint2 u = lds_u2(a);
+  v[0] = bf16_bits_to_f32(u.x & 0xffffu), v[1] = bf16_bits_to_f32(u.x >> 16);
+  v[2] = bf16_bits_to_f32(u.y & 0xffffu), v[3] = bf16_bits_to_f32(u.y >> 16);
+}
+template <>
+__device__ __forceinline__ void lds_quad<int16_t>(uint32_t a, float (&v)[4]) {
+  const uint2 u = lds_u2(a);
+  v[0] = (float)(int16_t)(u.x & 0xffffu), v[1] = (float)(int16_t)(u.x >> 16);
+  v[2] = (float)(int16_t)(u.y & 0xffffu), v[3] = (float)(int16_t)(u.y >> 16);
+}
+template <>
+__device__ __forceinline__ void lds_quad<int8_t>(uint32_t a, float (&v)[4]) {
+  const uint32_t u = lds_u1(a);
+#pragma unroll
+  for (int b = 0; b < 4; ++b) v[b] = (float)(int8_t)((u >> (8 * b)) & 0xffu);
+}
+template <>
+__device__ __forceinline__ void lds_quad<uint8_t>(uint32_t a, float (&v)[4]) {
+  const uint32_t u = lds_u1(a);
+#pragma unroll
+  for (int b = 0; b < 4; ++b) v[b] = (float)((u >> (8 * b)) & 0xffu);
+}
+
+// Persistent chunk pipeline.  CTA b consumes chunks b, b + G, b + 2G, ... of `chunk_bytes`
+// (the last one may be shorter; all sizes are multiples of 16).  `consume(slot_addr, chunk,
+// bytes)` is called by every thread of the CTA once the chunk has landed.  Returns false if a
+// bounded wait ran out (nothing more is consumed).
+template <typename F>
+__device__ __forceinline__ bool run_chunks(const uint8_t* src, size_t total_bytes, uint32_t chunk_bytes,
+                                           int stages, uint8_t* smem, F&& consume) {
+  const uint32_t bar0 = pipe::smem_addr(smem);
+  const uint32_t buf0 = bar0 + kRingHeader;
+  const size_t nchunks = (total_bytes + chunk_bytes - 1) / chunk_bytes;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) pipe::bar_init(bar0 + 8 * s, 1);
+    pipe::bar_init_fence();
+  }
+  __syncthreads();
+  auto bytes_of = [&](size_t c) {
+    const size_t rem = total_bytes - c * chunk_bytes;
+    return (uint32_t)(rem < chunk_bytes ? rem : chunk_bytes);
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      const size_t c = blockIdx.x + (size_t)s * gridDim.x;
+      if (c < nchunks) pipe::load_async(buf0 + s * chunk_bytes, src + c * chunk_bytes, bytes_of(c), bar0 + 8 * s);
+    }
+  }
+  int s = 0;
+  uint32_t phase = 0;
+  for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    if (!__syncthreads_and(pipe::bar_wait(bar0 + 8 * s, phase) ? 1 : 0)) return false;
+    consume(buf0 + s * chunk_bytes, c, bytes_of(c));
+    pipe::fence_async_smem();  // this thread's reads of the slot precede its refill
+    __syncthreads();
+    const size_t cn = c + (size_t)stages * gridDim.x;
+    if (threadIdx.x == 0 && cn < nchunks)
+      pipe::load_async(buf0 + s * chunk_bytes, src + cn * chunk_bytes, bytes_of(cn), bar0 + 8 * s);
+    if (++s == stages) s = 0, phase ^= 1u;
+  }
+  return true;
+}
+
+// Number of times a pipelined kernel gave up on a bounded wait (never expected; a copy that
+// does not complete means the source range was not readable).
+__device__ unsigned int g_pipe_timeouts = 0;
+
+template <Op OP, typename In, typename Out, bool MASK>
+__global__ void __launch_bounds__(kThreads)
+affine_pipe_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __restrict__ mask,
+                   size_t n, size_t cols, QParamRef q, float qmin, float qmax, int stages) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  // the 16-byte multiple part goes through the ring; at most 15 bytes of elements are left
+  const size_t main_bytes = (n * sizeof(In)) & ~(size_t)15;
+  constexpr uint32_t kChunkElems = kChunkBytes / sizeof(In);
+  Divisor dt = group_divisor<OP>(1.0f);
+  if (q.mode == LQ_PER_TENSOR) dt = group_divisor<OP>(q.s != nullptr ? __ldg(q.s) : q.sv);
+  const IntGrid igt = make_int_grid(q.mode == LQ_PER_TENSOR ? (q.z != nullptr ? __ldg(q.z) : q.zv) : 0.0f, qmin, qmax,
+                                    StoreRange<Out>::lo, StoreRange<Out>::hi);
+  const bool ok = run_chunks(reinterpret_cast<const uint8_t*>(x), main_bytes, kChunkBytes, stages, ring,
+                             [&](uint32_t slot, size_t chunk, uint32_t bytes) {
+    const uint32_t groups = bytes / (4 * sizeof(In));
+    const size_t e0 = chunk * kChunkElems;
+#pragma unroll 2
+    for (uint32_t g = threadIdx.x; g < groups; g += kThreads) {
+      float v[4], s[4], z[4], m[4];
+      lds_quad<In>(slot + g * (4 * sizeof(In)), v);
+      const size_t e = e0 + (size_t)g * 4;
+      quad_params(q, e, cols, s, z);
+      if (q.mode == LQ_PER_COL) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          Divisor d;
+          d.s = s[i], d.y = 0.0f, d.fast = false;
+          if (OP != Op::kDequantize) d = make_divisor(s[i]);
+          v[i] = apply<OP>(v[i], d, z[i], qmin, qmax, MASK ? &m[i] : nullptr);
+        }
+      } else {
+        const Divisor d = q.mode == LQ_PER_TENSOR ? dt : group_divisor<OP>(s[0]);
+        if (OP == Op::kQuantize) {
+          const IntGrid ig = q.mode == LQ_PER_TENSOR ? igt : make_int_grid(z[0], qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
+          int c[4];
+          code4_int(v, d, ig, z[0], qmin, qmax, c);
+          store_codes(out + e, c);
+          continue;
+        }
+        apply4<OP, MASK>(v, d, z[0], qmin, qmax, m);
+      }
+      Quad<Out>::store(out + e, v);
+      if (MASK) Quad<float>::store(mask + e, m);
+    }
+  });
+  if (!ok && threadIdx.x == 0) atomicAdd(&g_pipe_timeouts, 1u);
+  // elements past the last 16-byte boundary (n % 4 == 0, so this is one group at most)
+  const size_t done = main_bytes / sizeof(In);
+  if (blockIdx.x == 0 && done < n) {
+    for (size_t e = done + threadIdx.x; e < n; e += kThreads) {
+      float s1, z1, m1;
+      scalar_params(q, e / cols, e % cols, s1, z1);
+      Divisor d;
+      d.s = s1, d.y = 0.0f, d.fast = false;
+      const float r = apply<OP>(Packet<In>::load1(x + e), d, z1, qmin, qmax, MASK ? &m1 : nullptr);
+      Packet<Out>::store1(out + e, r);
+      if (MASK) mask[e] = m1;
+    }
+  }
+}
+
+template <typename In>
+__device__ __forceinline__ void smem_vec_minmax(uint32_t slot, uint32_t bytes, int first, int stride,
+                                                float& mn, float& mx) {
+  const uint32_t nvec = bytes / 16;
+  for (uint32_t i = first; i < nvec; i += stride) vec_minmax<In>(lds_u4(slot + i * 16), mn, mx);
+}
+
+// Opt a pipelined kernel into its dynamic shared memory once.
+template <typename K>
+cudaError_t enable_ring(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+template <Op OP, typename In, typename Out, bool MASK = false>
+int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t cols,
+                  const QParamRef& q, int qmin, int qmax, cudaStream_t st) {
+  const bool vec = (cols % 4 == 0) && aligned16(x) && aligned16(out) &&
+                   (!MASK || aligned16(mask)) &&
+                   (q.mode != LQ_PER_COL || (aligned16(q.s) && aligned16(q.z)));
+  const size_t n = rows * cols;
+  // Measured on B200: the decode (write-heavy, 4 output bytes per input byte) is faster through
+  // the bulk-copy ring with persistent CTAs; the encodes are issue-bound and faster with
+  // register-staged loads and one CTA per span.
+  if (vec && OP == Op::kDequantize && n * sizeof(In) >= pipe_min_bytes()) {
+    auto kernel = affine_pipe_kernel<OP, In, Out, MASK>;
+    constexpr int stages = kRingBytes / kChunkBytes;
+    constexpr size_t smem = kRingHeader + kRingBytes;
+    static cudaError_t attr = enable_ring(kernel, smem);
+    if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
+    const size_t nchunks = (n * sizeof(In) + kChunkBytes - 1) / kChunkBytes;
+    const int grid = (int)(nchunks < (size_t)(kNumSMs * 3) ? nchunks : (size_t)(kNumSMs * 3));
+    kernel<<<grid, kThreads, smem, st>>>((const In*)x, (Out*)out, mask, n, cols, q, (float)qmin, (float)qmax, stages);
+  } else if (vec) {
+    affine_vec_kernel<OP, In, Out, MASK><<<grid_for((n / 4 + kUnroll - 1) / kUnroll), kThreads, 0, st>>>(
+        (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
+  } else {
+    affine_scalar_kernel<OP, In, Out, MASK><<<grid_for(n), kThreads, 0, st>>>(
+        (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
+  }
+  return check_cuda(cudaGetLastError(), "affine kernel launch");
+}
+
+
 // Per-tensor: per-CTA partials go to the workspace; the CTA that takes the last
 // ticket folds them (min/max are exact in any order) and re-arms the ticket.
-template <typename In>
-__global__ void __launch_bounds__(kThreads)
-minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWorkspace* ws,
-                     float* out_min, float* out_max) {
-  float mn = INFINITY, mx = -INFINITY;
-  minmax_accumulate(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
-                    (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
+__device__ __forceinline__ void finish_tensor_minmax(float mn, float mx, MinMaxWorkspace* ws,
+                                                     float* out_min, float* out_max) {
   block_minmax(mn, mx);
   __shared__ bool is_last;
   if (threadIdx.x == 0) {
@@ -347,6 +715,75 @@ minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWork
     ws->ticket = 0;  // leave the workspace zeroed for the next call
   }
 }
+
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWorkspace* ws,
+                     float* out_min, float* out_max) {
+  float mn = INFINITY, mx = -INFINITY;
+  minmax_accumulate(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
+                    (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
+  finish_tensor_minmax(mn, mx, ws, out_min, out_max);
+}
+
+// Per-tensor range reduction through the ring (same partial / ticket scheme as below).
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+minmax_pipe_kernel(const In* __restrict__ x, size_t n, MinMaxWorkspace* ws, float* out_min,
+                   float* out_max, int stages) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  const size_t main_bytes = (n * sizeof(In)) & ~(size_t)15;
+  float mn = INFINITY, mx = -INFINITY;
+  const bool ok = run_chunks(reinterpret_cast<const uint8_t*>(x), main_bytes, kChunkBytes, stages, ring,
+                             [&](uint32_t slot, size_t, uint32_t bytes) {
+    smem_vec_minmax<In>(slot, bytes, threadIdx.x, kThreads, mn, mx);
+  });
+  if (!ok && threadIdx.x == 0) atomicAdd(&g_pipe_timeouts, 1u);
+  if (blockIdx.x == 0)
+    for (size_t e = main_bytes / sizeof(In) + threadIdx.x; e < n; e += kThreads) {
+      const float v = Packet<In>::load1(x + e);
+      mn = fminf(mn, v), mx = fmaxf(mx, v);
+    }
+  finish_tensor_minmax(mn, mx, ws, out_min, out_max);
+}
+
+// Fused per-token encode with the row held in shared memory: one HBM read per element.
+// A chunk of the ring is one row; rows are prefetched while earlier ones are encoded.
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+per_token_pipe_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps,
+                      float qmin, float qmax, int8_t* __restrict__ out, float* __restrict__ out_scale,
+                      int stages) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ float s_scale;
+  const uint32_t row_bytes = (uint32_t)(cols * sizeof(In));
+  const bool ok = run_chunks(reinterpret_cast<const uint8_t*>(x), rows * (size_t)row_bytes, row_bytes, stages, ring,
+                             [&](uint32_t slot, size_t r, uint32_t) {
+    float mn = INFINITY, mx = -INFINITY;
+    smem_vec_minmax<In>(slot, row_bytes, threadIdx.x, kThreads, mn, mx);
+    block_minmax(mn, mx);
+    if (threadIdx.x == 0) {
+      const float m = fmaxf(fabsf(fminf(mn, 0.0f)), fabsf(fmaxf(mx, 0.0f)));
+      const float sc = fmaxf(__fdiv_rn(m, half), eps);
+      s_scale = sc;
+      out_scale[r] = sc;
+    }
+    __syncthreads();
+    const Divisor d = make_divisor(s_scale);
+    const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    int8_t* outr = out + r * cols;
+    const uint32_t groups = (uint32_t)(cols / 4);
+    for (uint32_t g = threadIdx.x; g < groups; g += kThreads) {
+      float v[4];
+      int c[4];
+      lds_quad<In>(slot + g * (4 * sizeof(In)), v);
+      code4_int(v, d, ig, 0.0f, qmin, qmax, c);
+      store_codes(outr + (size_t)g * 4, c);
+    }
+  });
+  if (!ok && threadIdx.x == 0) atomicAdd(&g_pipe_timeouts, 1u);
+}
+
 
 // Per-row: one CTA per row (grid-stride over rows).
 template <typename In>
@@ -407,7 +844,6 @@ per_token_kernel(const In* __restrict__ x, size_t rows, size_t cols, bool vec_ok
   for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const In* xr = x + r * cols;
     float mn = INFINITY, mx = -INFINITY;
-    const size_t npk = vec_ok ? cols / 16 : 0;
     // first pass: keep the lines in L2 (ld.global.cg through the packet loader's
     // non-allocating L1 policy does that already)
     minmax_accumulate(xr, cols, threadIdx.x, kThreads, vec_ok, mn, mx);
@@ -420,16 +856,18 @@ per_token_kernel(const In* __restrict__ x, size_t rows, size_t cols, bool vec_ok
       out_scale[r] = s;
     }
     __syncthreads();
-    const float s = s_scale;
+    const Divisor s = make_divisor(s_scale);
+    const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
     int8_t* outr = out + r * cols;
-    for (size_t p = threadIdx.x; p < npk; p += kThreads) {
-      float v[16];
-      Packet<In>::load(xr + p * 16, v);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = code_f32(v[i], s, 0.0f, qmin, qmax);
-      Packet<int8_t>::store(outr + p * 16, v);
+    const size_t ngr = vec_ok ? cols / 4 : 0;
+    for (size_t gi = threadIdx.x; gi < ngr; gi += kThreads) {
+      float v[4];
+      int c[4];
+      Quad<In>::load(xr + gi * 4, v);
+      code4_int(v, s, ig, 0.0f, qmin, qmax, c);
+      store_codes(outr + gi * 4, c);
     }
-    for (size_t i = npk * 16 + threadIdx.x; i < cols; i += kThreads)
+    for (size_t i = ngr * 4 + threadIdx.x; i < cols; i += kThreads)
       outr[i] = (int8_t)(int)code_f32(Packet<In>::load1(xr + i), s, 0.0f, qmin, qmax);
     __syncthreads();  // s_scale is rewritten by the next row
   }
@@ -485,7 +923,21 @@ extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, 
     size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
     int grid = (int)(want < 1 ? 1 : (want > (size_t)(kNumSMs * 4) ? kNumSMs * 4 : want));
     auto* ws = (MinMaxWorkspace*)workspace;
-    if (in_dtype == LQ_F32)
+    if (vec_ok && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
+      // bulk-copy ring variant (kept for comparison; the register-staged kernel is faster)
+      constexpr int stages = kRingBytes / kChunkBytes;
+      constexpr size_t smem = kRingHeader + kRingBytes;
+      static cudaError_t a32 = enable_ring(minmax_pipe_kernel<float>, smem);
+      static cudaError_t a16 = enable_ring(minmax_pipe_kernel<__nv_bfloat16>, smem);
+      if (a32 != cudaSuccess || a16 != cudaSuccess)
+        return check_cuda(a32 != cudaSuccess ? a32 : a16, "cudaFuncSetAttribute(ring)");
+      const size_t nchunks = (n * esz + kChunkBytes - 1) / kChunkBytes;
+      const int pgrid = (int)(nchunks < (size_t)(kNumSMs * 3) ? nchunks : (size_t)(kNumSMs * 3));
+      if (in_dtype == LQ_F32)
+        minmax_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, n, ws, out_min, out_max, stages);
+      else
+        minmax_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, n, ws, out_min, out_max, stages);
+    } else if (in_dtype == LQ_F32)
       minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max);
     else
       minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max);
@@ -596,6 +1048,28 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
   const float half = (float)((double)(qmax - qmin) / 2.0);
   const int grid = (int)(rows < (size_t)kMaxBlocks ? rows : kMaxBlocks);
   cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16)
+    return fail(LQ_ERR_DTYPE, "lq_quantize_per_token: in_dtype must be f32|bf16");
+  const size_t row_bytes = cols * esz;
+  constexpr size_t kRowRing = 96 * 1024;
+  if (vec_ok && row_bytes >= 20 * 1024 && row_bytes <= kRowRing && rows * row_bytes >= pipe_min_bytes()) {
+    // rows held in shared memory: one HBM read per element, rows prefetched through the ring
+    int stages = (int)(kRowRing / row_bytes);
+    if (stages > 8) stages = 8;
+    const size_t smem = kRingHeader + (size_t)stages * row_bytes;
+    static cudaError_t a32 = enable_ring(per_token_pipe_kernel<float>, kRingHeader + kRowRing);
+    static cudaError_t a16 = enable_ring(per_token_pipe_kernel<__nv_bfloat16>, kRingHeader + kRowRing);
+    if (a32 != cudaSuccess || a16 != cudaSuccess)
+      return check_cuda(a32 != cudaSuccess ? a32 : a16, "cudaFuncSetAttribute(ring)");
+    const int ctas_per_sm = smem > 64 * 1024 ? 2 : 3;
+    const size_t cap = (size_t)kNumSMs * ctas_per_sm;
+    const int pgrid = (int)(rows < cap ? rows : cap);
+    if (in_dtype == LQ_F32)
+      per_token_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
+    else
+      per_token_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
+    return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
+  }
   if (in_dtype == LQ_F32)
     per_token_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, vec_ok, half, eps, (float)qmin, (float)qmax, out, out_scale);
   else if (in_dtype == LQ_BF16)

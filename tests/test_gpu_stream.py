@@ -223,3 +223,53 @@ def test_cpu_tensor_is_rejected():
 
     with pytest.raises(L.DeviceMismatch):
         Q.quantize(torch.zeros(4), 0.1, 0.0, Q.qint8)
+
+
+def _near_ties(rng, scale, n):
+    """Inputs whose quotient by `scale` sits on or next to a .5 tie."""
+    k = rng.integers(-300, 300, n).astype(np.float32)
+    x = ((k + np.float32(0.5)) * np.float32(scale)).astype(np.float32)
+    lo = np.nextafter(x, np.float32(-np.inf))
+    hi = np.nextafter(x, np.float32(np.inf))
+    return np.concatenate([x, lo, hi, np.nextafter(lo, np.float32(-np.inf)), np.nextafter(hi, np.float32(np.inf))])
+
+
+def test_division_is_correctly_rounded_around_ties():
+    """The kernels divide with a hoisted reciprocal plus residual corrections; the result
+    must be the correctly rounded quotient everywhere, most visibly next to .5 ties."""
+    rng = np.random.default_rng(21)
+    for scale in np.exp(rng.uniform(np.log(1e-6), np.log(1e3), 40)).astype(np.float32):
+        x = np.concatenate([_near_ties(rng, scale, 4096),
+                            (rng.standard_normal(4096) * scale * 100).astype(np.float32)])
+        x = x[: (x.size // 16) * 16].reshape(-1, 16)
+        for qd, oqd, z in ((Q.qint8, O.QINT8, 0.0), (Q.quint8, O.QUINT8, 131.0)):
+            got = host(Q.quantize(dev(x), float(scale), z, qd))
+            assert np.array_equal(got, O.quantize(x, float(scale), z, oqd)), scale
+        fq = host(Q.fake_quantize(dev(x), float(scale), 3.0, -128, 127))
+        assert np.array_equal(fq, O.fake_quantize(x, float(scale), 3.0, -128, 127)), scale
+
+
+def test_division_exact_per_channel_random_scales():
+    rng = np.random.default_rng(22)
+    rows, cols = 512, 1024
+    s_col = np.exp(rng.uniform(np.log(1e-5), np.log(10.0), cols)).astype(np.float32)
+    s_row = np.exp(rng.uniform(np.log(1e-5), np.log(10.0), rows)).astype(np.float32)
+    k = rng.integers(-200, 200, (rows, cols)).astype(np.float32) + np.float32(0.5)
+    for s, axis in ((s_col, 1), (s_row, 0)):
+        sb = s.reshape(1, -1) if axis == 1 else s.reshape(-1, 1)
+        x = (k * sb).astype(np.float32)
+        x[::2] = np.nextafter(x[::2], np.float32(np.inf))
+        x[1::4] = np.nextafter(x[1::4], np.float32(-np.inf))
+        z = np.zeros_like(s)
+        got = host(Q.quantize(dev(x), dev(s), dev(z), Q.qint8, ch_axis=axis))
+        assert np.array_equal(got, O.quantize(x, s, z, O.QINT8, ch_axis=axis))
+
+
+def test_extreme_scales_and_values_take_the_full_division():
+    x = np.array([0.0, -0.0, 1e-45, -1e-40, 1e-30, 3.0e38, -3.0e38, 1.0, -1.0, 123.456, 1e20, -1e-20,
+                  5e-39, 2.5, 3.5, -2.5], np.float32).reshape(1, 16)
+    for scale in (1e-42, 1e-30, 1e-8, 1.0, 1e30, 3e38):
+        got = host(Q.quantize(dev(x), float(scale), 0.0, Q.qint8))
+        with np.errstate(over="ignore", divide="ignore"):
+            ref = O.quantize(x, float(scale), 0.0, O.QINT8)
+        assert np.array_equal(got, ref), scale
