@@ -322,24 +322,33 @@ def run_b200_arm(args):
     _lib.check_device_status(dev)
 
     # ---- end to end: pinned host activations in, result out, public API --------------
-    def e2e_step():
-        xs = [h.to(dev, non_blocking=True) for h in host_x]
-        _, _, d = step(xs)
-        host_out.copy_(d, non_blocking=True)
+    # Every step copies its three activations from pinned host memory and its result back;
+    # lucid_b200.HostPipeline overlaps the copy legs of neighbouring steps with the compute.
+    import lucid_b200
 
+    def layer(x0, x1, x2):
+        return step((x0, x1, x2))[2]
+
+    pipe_e2e = lucid_b200.HostPipeline(layer, x_dev, out_d if world == 1 else
+                                       torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16, device=dev), dev)
     for _ in range(3):
-        e2e_step()
+        pipe_e2e.submit(host_x, host_out)
+    pipe_e2e.drain()
     barrier()
+    t_e2e = time.perf_counter()
     f0, f1 = torch.cuda.Event(True), torch.cuda.Event(True)
-    f0.record()
+    f0.record(pipe_e2e.s_in)
     for _ in range(args.steps):
-        e2e_step()
-    f1.record()
+        pipe_e2e.submit(host_x, host_out)
+    f1.record(pipe_e2e.s_out)
+    pipe_e2e.drain()
     barrier()
-    t = torch.tensor([f0.elapsed_time(f1)], dtype=torch.float64, device=dev)
+    wall_ms = (time.perf_counter() - t_e2e) * 1e3
+    t = torch.tensor([f0.elapsed_time(f1), wall_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0]) / args.steps
+    e2e_wall_ms = float(t[1]) / args.steps
     e2e_tops = OPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
     h2d = sum(h.numel() * h.element_size() for h in host_x)
     d2h = host_out.numel() * host_out.element_size()
@@ -386,7 +395,9 @@ def run_b200_arm(args):
             },
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "wall_ms_per_step": e2e_wall_ms,
+                    "how": "lucid_b200.HostPipeline: H2D / compute / D2H of neighbouring steps overlap"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "streams": streams,

@@ -13,6 +13,7 @@ or a CPU tensor raises.
 
 from . import backends, nn, quantization  # noqa: F401
 from ._device import device  # noqa: F401
+from ._pipeline import HostPipeline  # noqa: F401
 from ._lib import (DeviceMismatch, DtypeMismatch, EngineUnavailable, LucidError,  # noqa: F401
                    ShapeMismatch, is_available)
 
