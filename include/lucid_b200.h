@@ -188,6 +188,19 @@ typedef struct lq_epilogue {
 int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
                const lq_epilogue_t* ep, void* out, size_t ldo, int32_t* status, void* stream);
 
+/* The same contraction with the exchange step of an output-channel-sharded Linear fused
+ * into its epilogue: every finished tile is stored into ALL `n_dst` destinations (1..8), each
+ * the base of a row-major (M, ldo) buffer, at column offset `col0`.  outs[0] is normally this
+ * GPU's own buffer and outs[1..] the same buffer on its peers, mapped into this process
+ * (CUDA IPC / symmetric memory); the stores are plain peer stores over NVLink and overlap the
+ * mainloop of the following tiles, replacing an all-gather of (M, N) shards plus a re-layout.
+ * `outs` is a HOST array of device pointers.  The caller orders consumers after the kernels of
+ * all ranks (a barrier across the ranks on the stream).  No counterpart in the reference,
+ * which has no distributed code. */
+int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                     const lq_epilogue_t* ep, void* const* outs, int n_dst, size_t ldo,
+                     size_t col0, int32_t* status, void* stream);
+
 /* sum_k b[n,k] for the zero-point correction term (N ints). */
 int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream);
 

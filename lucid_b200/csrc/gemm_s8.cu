@@ -69,7 +69,10 @@ struct Epi {
   const float* bias;
   const float* out_scale;
   const float* out_zp;
-  void* out;
+  void* out;           // first destination
+  void* more_outs[7];  // further destinations of the same tiles (peer GPUs' buffers)
+  int n_dst;           // number of destinations (>= 1)
+  long long col0;      // column offset of this GEMM's columns inside every destination
   long long ldo;  // elements
   int n_out;      // columns of out (N, or N/2 for the gated epilogue)
   int vec_ok;     // 16-byte vector stores allowed
@@ -333,17 +336,22 @@ __device__ __forceinline__ void flush_group(const uint8_t* stg, int lane, const 
     const int col = gcol0 + pc * EPP;
     const int nvalid = ep.n_out - col;
     if (((rc.row_mask >> r) & 1u) && pc < pieces && nvalid > 0) {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + ((rc.row0 + r) * ep.ldo + col) * ESZ;
-      if (ep.vec_ok && nvalid >= EPP) {
-        *reinterpret_cast<uint4*>(dst) = v;
-      } else {
-        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+      const long long off = ((rc.row0 + r) * ep.ldo + ep.col0 + col) * ESZ;
+      // the same 16 bytes go to every destination: this GPU's buffer first, then the peers'
+      // (plain stores over NVLink; the exchange overlaps the mainloop of the next tile)
+      for (int dsti = 0; dsti < ep.n_dst; ++dsti) {
+        uint8_t* dst = reinterpret_cast<uint8_t*>(dsti == 0 ? ep.out : ep.more_outs[dsti - 1]) + off;
+        if (ep.vec_ok && nvalid >= EPP) {
+          *reinterpret_cast<uint4*>(dst) = v;
+        } else {
+          const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int e = 0; e < EPP; ++e) {
-          if (e < nvalid) {
-            if (ESZ == 4) reinterpret_cast<uint32_t*>(dst)[e] = wv[e];
-            else if (ESZ == 2) reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(wv[e >> 1] >> (16 * (e & 1)));
-            else dst[e] = (uint8_t)(wv[e >> 2] >> (8 * (e & 3)));
+          for (int e = 0; e < EPP; ++e) {
+            if (e < nvalid) {
+              if (ESZ == 4) reinterpret_cast<uint32_t*>(dst)[e] = wv[e];
+              else if (ESZ == 2) reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(wv[e >> 1] >> (16 * (e & 1)));
+              else dst[e] = (uint8_t)(wv[e >> 2] >> (8 * (e & 3)));
+            }
           }
         }
       }
@@ -841,6 +849,8 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
   d->a_scale = e->a_scale, d->a_zp = e->a_zp, d->b_rowsum = e->b_rowsum, d->b_scale = e->b_scale;
   d->bias = e->bias, d->out_scale = e->out_scale, d->out_zp = e->out_zp;
   d->out = out, d->ldo = (long long)ldo, d->n_out = (int)n_out, d->status = status;
+  d->n_dst = 1, d->col0 = 0;
+  for (auto& m : d->more_outs) m = nullptr;
   const size_t esz = dtype_size(e->out_dtype);
   d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
   d->par_vec = aligned16(e->b_scale) && aligned16(e->bias) && aligned16(e->b_rowsum);
@@ -927,19 +937,25 @@ int dispatch(Shape sh, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g
 
 using namespace lq;
 
-extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
-                          const lq_epilogue_t* e, void* out, size_t ldo, int32_t* status,
-                          void* stream) {
+namespace lq {
+namespace {
+int gemm_impl(const char* who, const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+              const lq_epilogue_t* e, void* const* outs, int n_dst, size_t ldo, size_t col0,
+              int32_t* status, void* stream) {
+  const std::string w(who);
   if (M == 0 || N == 0) return LQ_OK;
-  if (!a || !b || !out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8: null pointer");
-  if (K == 0) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: K must be positive");
-  if (K % 16 != 0) return fail(LQ_ERR_ALIGNMENT, "lq_gemm_s8: K must be a multiple of 16 (pad with zero codes)");
-  if (!aligned16(a) || !aligned16(b)) return fail(LQ_ERR_ALIGNMENT, "lq_gemm_s8: a and b must be 16-byte aligned");
-  if (M > 0x7fffffffu || N > 0x7fffffffu || K > 0x7fffffffu) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: extent too large");
-  int rc = check_epilogue(e, N, "lq_gemm_s8", true);
+  if (!a || !b || !outs) return fail(LQ_ERR_DEVICE, w + ": null pointer");
+  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, w + ": between 1 and 8 destinations");
+  for (int i = 0; i < n_dst; ++i)
+    if (!outs[i]) return fail(LQ_ERR_DEVICE, w + ": null destination pointer");
+  if (K == 0) return fail(LQ_ERR_SHAPE, w + ": K must be positive");
+  if (K % 16 != 0) return fail(LQ_ERR_ALIGNMENT, w + ": K must be a multiple of 16 (pad with zero codes)");
+  if (!aligned16(a) || !aligned16(b)) return fail(LQ_ERR_ALIGNMENT, w + ": a and b must be 16-byte aligned");
+  if (M > 0x7fffffffu || N > 0x7fffffffu || K > 0x7fffffffu) return fail(LQ_ERR_SHAPE, w + ": extent too large");
+  int rc = check_epilogue(e, N, who, true);
   if (rc) return rc;
   const size_t n_out = e->act == LQ_ACT_SILU_GATE ? N / 2 : N;
-  if (ldo < n_out) return fail(LQ_ERR_SHAPE, "lq_gemm_s8: ldo smaller than the output width");
+  if (ldo < col0 + n_out) return fail(LQ_ERR_SHAPE, w + ": ldo smaller than column offset + output width");
 
   Geometry g = {};
   g.conv = 0, g.M = (int)M, g.N = (int)N, g.K = (int)K;
@@ -953,8 +969,31 @@ extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M
   if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
   if ((rc = encode_2d(&tb, b, N, K, K, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
   Epi ep;
-  fill_epi(&ep, e, out, ldo, n_out, status);
+  fill_epi(&ep, e, outs[0], ldo, n_out, status);
+  ep.n_dst = n_dst, ep.col0 = (long long)col0;
+  const size_t esz = dtype_size(e->out_dtype);
+  ep.vec_ok = ep.vec_ok && ((col0 * esz) % 16 == 0);
+  for (int i = 1; i < n_dst; ++i) {
+    ep.more_outs[i - 1] = outs[i];
+    ep.vec_ok = ep.vec_ok && aligned16(outs[i]);
+  }
   return dispatch(sh, ta, tb, g, ep, a_signed, (cudaStream_t)stream);
+}
+}  // namespace
+}  // namespace lq
+
+extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                          const lq_epilogue_t* e, void* out, size_t ldo, int32_t* status,
+                          void* stream) {
+  if (M != 0 && N != 0 && !out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8: null pointer");
+  void* outs[1] = {out};
+  return gemm_impl("lq_gemm_s8", a, a_signed, b, M, N, K, e, outs, 1, ldo, 0, status, stream);
+}
+
+extern "C" int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N,
+                                size_t K, const lq_epilogue_t* e, void* const* outs, int n_dst,
+                                size_t ldo, size_t col0, int32_t* status, void* stream) {
+  return gemm_impl("lq_gemm_s8_bcast", a, a_signed, b, M, N, K, e, outs, n_dst, ldo, col0, status, stream);
 }
 
 extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H,

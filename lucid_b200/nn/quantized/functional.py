@@ -101,6 +101,39 @@ def gemm_s8(a, b, *, out_dtype=torch.int32, a_scale=None, a_zp=None, b_rowsum=No
     return out
 
 
+def gemm_s8_bcast(a, b, dst_ptrs, dst_shape, col0, *, out_dtype=torch.bfloat16, a_scale=None, a_zp=None,
+                  b_rowsum=None, b_scale=None, bias=None, act=_lib.ACT_NONE, out_scale=None,
+                  out_zp=None, qmin=0, qmax=0):
+    """`gemm_s8` whose epilogue stores every tile into several `(M, ld)` buffers at column
+    offset `col0`: `dst_ptrs` are raw device addresses (this GPU's buffer first, then the same
+    buffer on its peers, e.g. `_SymmetricMemory.buffer_ptrs`), `dst_shape = (M, ld)`.  The
+    caller synchronises the ranks before the buffers are read."""
+    _lib.require_cuda(a, "activation codes")
+    _lib.require_cuda(b, "weight codes")
+    if a.dtype not in (torch.int8, torch.uint8) or b.dtype != torch.int8:
+        raise _lib.DtypeMismatch("gemm_s8_bcast takes int8/uint8 activations and int8 weights")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise _lib.ShapeMismatch(f"gemm_s8_bcast shapes {tuple(a.shape)} x {tuple(b.shape)}^T")
+    a = a.contiguous()
+    b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    n_out = n // 2 if act == _lib.ACT_SILU_GATE else n
+    if dst_shape[0] < m or dst_shape[1] < col0 + n_out:
+        raise _lib.ShapeMismatch(f"destination {tuple(dst_shape)} too small for rows {m}, columns "
+                                 f"[{col0}, {col0 + n_out})")
+    dev = a.device
+    keep: list = []
+    e = _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
+                  qmin, qmax, keep)
+    ptrs = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().lq_gemm_s8_bcast(
+            _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e), ptrs,
+            len(dst_ptrs), int(dst_shape[1]), int(col0), _lib.ptr(_lib.status_word(dev)),
+            _lib.stream_ptr(dev)))
+
+
 def conv2d_nhwc_s8(x, w_krsc, *, pad=0, stride=1, out_dtype=torch.int32, a_scale=None,
                    b_scale=None, bias=None, act=_lib.ACT_NONE, out_scale=None, out_zp=None,
                    qmin=0, qmax=0):

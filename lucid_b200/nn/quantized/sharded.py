@@ -49,6 +49,46 @@ def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = N
     return out
 
 
+class PeerOutputs:
+    """Double-buffered `(rows, cols)` output that every rank of the group can write: the
+    GEMM epilogue of each rank stores its column shard straight into all ranks' copies
+    (symmetric memory, plain peer stores over NVLink), so the exchange step needs no separate
+    all-gather kernel and no re-layout.  Two buffers alternate: a rank may start writing the
+    other buffer while peers still read this one; the barrier after each GEMM orders the rest.
+
+    Construction is collective (all ranks, same order)."""
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.bufs, self.ptrs = [], []
+        for _ in range(2):
+            t = symm_mem.empty((rows, cols), dtype=dtype, device=device)
+            h = symm_mem.rendezvous(t, self.group)
+            own = int(h.buffer_ptrs[self.rank])
+            # this GPU's buffer first, then the peers'
+            self.ptrs.append([own] + [int(p) for r, p in enumerate(h.buffer_ptrs) if r != self.rank])
+            self.bufs.append(t)
+            self._keep = getattr(self, "_keep", []) + [h]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.turn = 0
+
+    def next(self):
+        """(local tensor, destination pointers) of the buffer to fill now."""
+        i = self.turn
+        self.turn ^= 1
+        return self.bufs[i], self.ptrs[i]
+
+    def fence(self) -> None:
+        """All ranks' stores into the current buffer are complete and visible after this
+        (stream-ordered): a 4-byte all-reduce follows each rank's GEMM on its stream."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
 class ColumnShardedLinear(torch.nn.Module):
     """This rank's shard of a per-token W8A8 linear plus the output all-gather."""
 
@@ -78,10 +118,29 @@ class ColumnShardedLinear(torch.nn.Module):
         return m.to(weight_int8.device)
 
     def forward_codes(self, a: torch.Tensor, a_scale: torch.Tensor, out_dtype=torch.bfloat16,
-                      gather: bool = True) -> torch.Tensor:
+                      gather: bool = True, act: int = _lib.ACT_NONE) -> torch.Tensor:
+        """`exchange = "p2p"` (set by `use_peer_outputs`) fuses the exchange into the GEMM
+        epilogue; otherwise the shards are all-gathered with NCCL."""
+        n_local = self.weight_int8.shape[0] // (2 if act == _lib.ACT_SILU_GATE else 1)
+        peer = getattr(self, "_peer", None)
+        if gather and self.world > 1 and peer is not None:
+            if a.shape[0] > peer.rows or peer.dtype != out_dtype:
+                raise _lib.ShapeMismatch("peer output buffers were sized for fewer rows / another dtype")
+            buf, ptrs = peer.next()
+            QF.gemm_s8_bcast(a, self.weight_int8, ptrs, (peer.rows, peer.cols), self.rank * n_local,
+                             out_dtype=out_dtype, a_scale=a_scale, b_scale=self.weight_scale,
+                             bias=self.bias, act=act)
+            peer.fence()
+            return buf[: a.shape[0]]
         local = QF.gemm_s8(a, self.weight_int8, out_dtype=out_dtype, a_scale=a_scale,
-                           b_scale=self.weight_scale, bias=self.bias)
+                           b_scale=self.weight_scale, bias=self.bias, act=act)
         return gather_columns(local, self.group) if gather and self.world > 1 else local
+
+    def use_peer_outputs(self, max_rows: int, dtype=torch.bfloat16, gated: bool = False) -> None:
+        """Collective: allocate the symmetric output buffers for inputs of up to `max_rows`
+        rows and switch the exchange step to epilogue peer stores."""
+        cols = self.out_features // (2 if gated else 1)
+        self._peer = PeerOutputs(max_rows, cols, dtype, self.weight_int8.device, self.group)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
