@@ -210,7 +210,7 @@ def run_b200_arm(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=180))
     peaks = load_peaks()
 
     # ---- synthetic weights: codes + per-channel scales, this rank's output-channel shard
@@ -432,18 +432,16 @@ def run_b200_arm(args):
 
 
 def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
-    """quantize / dequantize / min-max on the (4096, 4096) f32 tensor of config 1,
-    timed as CUDA-graph replays over 6 rotating buffer sets (480 MB > L2)."""
-    n = 4096
-    sets = 6
-    xs = [torch.randn(n, n, device=dev) for _ in range(sets)]
-    qs = [torch.empty(n, n, dtype=torch.int8, device=dev) for _ in range(sets)]
+    """quantize / dequantize / min-max timed as CUDA-graph replays over rotating buffer sets
+    larger than L2: at config-1 size ((4096, 4096) f32, 6 sets = 480 MB; a 64 MB launch lasts
+    10-20 us, so launch ramp and tail weigh in) and at (16384, 16384) (2 sets = 2.5 GB), which
+    shows the rate the kernels sustain."""
     lib = _lib.load()
     ws = _lib.minmax_workspace(dev)
     mn = torch.empty(1, device=dev)
     mx = torch.empty(1, device=dev)
 
-    def graph_time(fn):
+    def graph_time(fn, sets, reps):
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -459,33 +457,39 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
         e0.record()
-        for _ in range(iters):
+        for _ in range(reps):
             gph.replay()
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / (iters * sets) * 1e-3  # seconds per launch
-
-    def f_quant(j):
-        _lib.check(lib.lq_quantize(_lib.ptr(xs[j]), _lib.F32, n, n, None, None, 0.03, 0.0, 0, -127,
-                                   127, _lib.ptr(qs[j]), _lib.S8, _lib.stream_ptr(dev)))
-
-    def f_dequant(j):
-        _lib.check(lib.lq_dequantize(_lib.ptr(qs[j]), _lib.S8, n, n, None, None, 0.03, 0.0, 0,
-                                     _lib.ptr(xs[j]), _lib.F32, _lib.stream_ptr(dev)))
-
-    def f_minmax(j):
-        _lib.check(lib.lq_minmax(_lib.ptr(xs[j]), _lib.F32, 1, n * n, 0, _lib.ptr(mn), _lib.ptr(mx),
-                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+        return e0.elapsed_time(e1) / (reps * sets) * 1e-3  # seconds per launch
 
     out = {}
-    elems = n * n
-    for name, fn, bytes_per_elem in (("quantize_f32_s8", f_quant, 5), ("dequantize_s8_f32", f_dequant, 5),
-                                     ("minmax_f32", f_minmax, 4)):
-        sec = graph_time(fn)
-        gbs = elems * bytes_per_elem / sec / 1e9
-        out[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                     "frac_of_nominal_8000": gbs / 8000.0}
-    out["workload"] = "config 1: (4096, 4096) f32, 6 rotating buffer sets, CUDA-graph replays"
+    for label, n, sets, reps in (("config1_4096x4096", 4096, 6, iters), ("large_16384x16384", 16384, 2, max(iters // 4, 5))):
+        xs = [torch.randn(n, n, device=dev) for _ in range(sets)]
+        qs = [torch.empty(n, n, dtype=torch.int8, device=dev) for _ in range(sets)]
+
+        def f_quant(j):
+            _lib.check(lib.lq_quantize(_lib.ptr(xs[j]), _lib.F32, n, n, None, None, 0.03, 0.0, 0, -127,
+                                       127, _lib.ptr(qs[j]), _lib.S8, _lib.stream_ptr(dev)))
+
+        def f_dequant(j):
+            _lib.check(lib.lq_dequantize(_lib.ptr(qs[j]), _lib.S8, n, n, None, None, 0.03, 0.0, 0,
+                                         _lib.ptr(xs[j]), _lib.F32, _lib.stream_ptr(dev)))
+
+        def f_minmax(j):
+            _lib.check(lib.lq_minmax(_lib.ptr(xs[j]), _lib.F32, 1, n * n, 0, _lib.ptr(mn), _lib.ptr(mx),
+                                     _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+
+        block = {}
+        for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("dequantize_s8_f32", f_dequant, 5),
+                              ("minmax_f32", f_minmax, 4)):
+            sec = graph_time(fn, sets, reps)
+            gbs = n * n * bpe / sec / 1e9
+            block[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                           "frac_of_nominal_8000": gbs / 8000.0}
+        out[label] = block
+        del xs, qs
+    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range)"
     return out
 
 
