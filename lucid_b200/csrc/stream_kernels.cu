@@ -874,6 +874,73 @@ per_token_kernel(const In* __restrict__ x, size_t rows, size_t cols, bool vec_ok
   }
 }
 
+// Fused per-token encode for rows of at most 16 KB: the row lives in registers (four 16-byte
+// vectors per thread, consecutive lanes on consecutive vectors), so HBM is read exactly once
+// and nothing is re-read from L2.
+template <typename In>
+__global__ void __launch_bounds__(kThreads, 4)
+per_token_reg_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps,
+                     float qmin, float qmax, int8_t* __restrict__ out, float* __restrict__ out_scale) {
+  constexpr int E = VecOf<In>::kElems;  // elements per 16-byte vector
+  __shared__ float s_part[2][kThreads / 32];
+  const uint32_t nvec = (uint32_t)(cols / E);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  int flip = 0;
+  uint4 v[4], vn[4];
+  auto load_row = [&](size_t r, uint4 (&dst)[4]) {
+    const uint4* xv = reinterpret_cast<const uint4*>(x + r * cols);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t i = threadIdx.x + k * kThreads;
+      dst[k] = i < nvec ? ld_stream_u4(xv + i) : make_uint4(0, 0, 0, 0);  // zeros do not move an abs-max
+    }
+  };
+  if (blockIdx.x < rows) load_row(blockIdx.x, v);
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x, flip ^= 1) {
+    // the next row's loads are in flight while this one is encoded
+    const size_t rn = r + gridDim.x;
+    if (rn < rows) load_row(rn, vn);
+    float mn = 0.0f, mx = 0.0f;  // the range is extended to include 0 anyway
+#pragma unroll
+    for (int k = 0; k < 4; ++k) vec_minmax<In>(v[k], mn, mx);
+    float am = fmaxf(fabsf(mn), fabsf(mx));
+    am = warp_max(am);
+    if (l == 0) s_part[flip][w] = am;
+    __syncthreads();  // the only block barrier per row (partials are double-buffered)
+    float m = s_part[flip][0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, s_part[flip][i]);
+    const float sc = fmaxf(__fdiv_rn(m, half), eps);
+    if (threadIdx.x == 0) out_scale[r] = sc;
+    const Divisor d = make_divisor(sc);
+    const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    int8_t* outr = out + r * cols;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t i = threadIdx.x + k * kThreads;
+      if (i >= nvec) continue;
+      const uint32_t wv[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+      if (E == 4) {
+        const float f[4] = {__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3])};
+        int c[4];
+        code4_int(f, d, ig, 0.0f, qmin, qmax, c);
+        st_stream_u1(outr + (size_t)i * 4, pack4i_s8(c));
+      } else {
+        const float f0[4] = {bf16_bits_to_f32(wv[0] & 0xffffu), bf16_bits_to_f32(wv[0] >> 16),
+                             bf16_bits_to_f32(wv[1] & 0xffffu), bf16_bits_to_f32(wv[1] >> 16)};
+        const float f1[4] = {bf16_bits_to_f32(wv[2] & 0xffffu), bf16_bits_to_f32(wv[2] >> 16),
+                             bf16_bits_to_f32(wv[3] & 0xffffu), bf16_bits_to_f32(wv[3] >> 16)};
+        int c0[4], c1[4];
+        code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
+        code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        st_stream_u2(outr + (size_t)i * 8, make_uint2(pack4i_s8(c0), pack4i_s8(c1)));
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = vn[k];
+  }
+}
+
 // sum_k b[n,k]: one warp per row.
 __global__ void __launch_bounds__(kThreads)
 rowsum_kernel(const int8_t* __restrict__ b, size_t N, size_t K, bool vec_ok,
@@ -1062,13 +1129,22 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     static cudaError_t a16 = enable_ring(per_token_pipe_kernel<__nv_bfloat16>, kRingHeader + kRowRing);
     if (a32 != cudaSuccess || a16 != cudaSuccess)
       return check_cuda(a32 != cudaSuccess ? a32 : a16, "cudaFuncSetAttribute(ring)");
-    const int ctas_per_sm = smem > 64 * 1024 ? 2 : 3;
+    int ctas_per_sm = (int)((200 * 1024) / smem);
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
     const size_t cap = (size_t)kNumSMs * ctas_per_sm;
     const int pgrid = (int)(rows < cap ? rows : cap);
     if (in_dtype == LQ_F32)
       per_token_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
     else
       per_token_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
+    return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
+  }
+  if (vec_ok && row_bytes <= 16 * 1024) {
+    if (in_dtype == LQ_F32)
+      per_token_reg_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale);
+    else
+      per_token_reg_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale);
     return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
   }
   if (in_dtype == LQ_F32)
