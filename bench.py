@@ -349,20 +349,33 @@ def run_b200_arm(args):
     # lucid_b200.HostPipeline overlaps the copy legs of neighbouring steps with the compute.
     import lucid_b200
 
+    # N > 1: the host link is shared by all GPUs of the box, so each rank copies only its 1/w of
+    # the token rows and the ranks all-gather the rest over NVLink; each rank returns its 1/w of
+    # the result rows (the full result reaches the host exactly once).
+    rows_per = M_TOKENS // world
+    r0, r1 = rank * rows_per, (rank + 1) * rows_per
+    host_in = [h[r0:r1] for h in host_x] if world > 1 else host_x
+    host_res = host_out[r0:r1] if world > 1 else host_out
+    full_x = [torch.empty_like(t) for t in x_dev] if world > 1 else None
+
     def layer(x0, x1, x2):
+        if world > 1:
+            for full, shard in zip(full_x, (x0, x1, x2)):
+                dist.all_gather_into_tensor(full, shard)
+            return step(full_x)[2][r0:r1]
         return step((x0, x1, x2))[2]
 
-    pipe_e2e = lucid_b200.HostPipeline(layer, x_dev, out_d if world == 1 else
-                                       torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16, device=dev), dev)
+    pipe_e2e = lucid_b200.HostPipeline(layer, [x[r0:r1] for x in x_dev] if world > 1 else x_dev,
+                                       torch.empty((rows_per, D_MODEL), dtype=torch.bfloat16, device=dev) if world > 1 else out_d, dev)
     for _ in range(3):
-        pipe_e2e.submit(host_x, host_out)
+        pipe_e2e.submit(host_in, host_res)
     pipe_e2e.drain()
     barrier()
     t_e2e = time.perf_counter()
     f0, f1 = torch.cuda.Event(True), torch.cuda.Event(True)
     f0.record(pipe_e2e.s_in)
     for _ in range(args.steps):
-        pipe_e2e.submit(host_x, host_out)
+        pipe_e2e.submit(host_in, host_res)
     f1.record(pipe_e2e.s_out)
     pipe_e2e.drain()
     barrier()
@@ -373,7 +386,7 @@ def run_b200_arm(args):
     e2e_ms = float(t[0]) / args.steps
     e2e_wall_ms = float(t[1]) / args.steps
     e2e_tops = OPS_PER_STEP / (e2e_ms * 1e-3) / 1e12
-    h2d = sum(h.numel() * h.element_size() for h in host_x)
+    h2d = sum(h.numel() * h.element_size() for h in host_x)  # whole job, all ranks together
     d2h = host_out.numel() * host_out.element_size()
 
     # ---- HBM streams on config 1 (rank 0, one GPU): rotating buffers larger than L2 ----
@@ -420,7 +433,9 @@ def run_b200_arm(args):
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "wall_ms_per_step": e2e_wall_ms,
-                    "how": "lucid_b200.HostPipeline: H2D / compute / D2H of neighbouring steps overlap"},
+                    "how": "lucid_b200.HostPipeline: H2D / compute / D2H of neighbouring steps overlap"
+                           + ("; each rank copies 1/w of the token rows in (all-gathered over NVLink) and "
+                              "1/w of the result rows out" if world > 1 else "")},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "streams": streams,
