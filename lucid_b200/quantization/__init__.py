@@ -8,3 +8,5 @@ from ._qparams import QParams, calculate_qparams  # noqa: F401
 from ._qscheme import (QDtype, QScheme, per_channel_affine, per_channel_symmetric,  # noqa: F401
                        per_tensor_affine, per_tensor_symmetric, qint4, qint8, qint32, quint8)
 from .observer import MinMaxObserver, ObserverBase, PerChannelMinMaxObserver, minmax  # noqa: F401
+from ._quantize import DeQuantStub, QuantStub, convert, prepare, quantize_dynamic  # noqa: F401,E402
+from .qconfig import QConfig, get_default_qconfig  # noqa: F401,E402

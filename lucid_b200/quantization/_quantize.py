@@ -1,0 +1,161 @@
+"""Eager-mode workflows: ``prepare`` -> calibrate -> ``convert`` and ``quantize_dynamic``
+(lucid/quantization/_quantize.py:204-419, 429-554, 684-699).
+
+The float model is a ``torch.nn`` model on a CUDA device; the converted model holds the
+quantized modules of ``lucid_b200.nn.quantized``, whose buffers carry the reference's
+``state_dict`` names (``weight_int8`` / ``weight_scale`` / ``weight_zero_point`` / ``bias`` /
+``scale`` / ``zero_point``), so a checkpoint written by either side loads into the other.
+"""
+
+from __future__ import annotations
+
+import copy
+import warnings
+
+import torch
+
+from ._qscheme import QDtype, qint8
+from .qconfig import QConfig, get_default_qconfig
+
+
+class QuantStub(torch.nn.Module):
+    """Marks where float activations enter the quantized region (identity until converted)."""
+
+    def forward(self, x):
+        return x
+
+
+class DeQuantStub(torch.nn.Module):
+    """Marks where activations leave the quantized region (identity)."""
+
+    def forward(self, x):
+        return x
+
+
+def _intrinsic():
+    try:
+        import torch.ao.nn.intrinsic as nni
+
+        return nni
+    except Exception:  # pragma: no cover - torch always ships it
+        return None
+
+
+def _observed_types() -> tuple:
+    nni = _intrinsic()
+    fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
+    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub) + fused
+
+
+def _quant_mapping() -> dict:
+    import lucid_b200.nn.quantized as nnq
+
+    m = {
+        torch.nn.Linear: nnq.Linear.from_float,
+        torch.nn.Conv2d: nnq.Conv2d.from_float,
+        QuantStub: nnq.Quantize.from_float,
+        DeQuantStub: nnq.DeQuantize.from_float,
+    }
+    nni = _intrinsic()
+    if nni is not None:
+        m[nni.LinearReLU] = nnq.LinearReLU.from_float
+        m[nni.ConvReLU2d] = nnq.ConvReLU2d.from_float
+    return m
+
+
+def _make_observer_hook(obs):
+    def hook(module, inputs, output):
+        obs(output.detach().to(torch.float32).contiguous())
+        return None
+
+    return hook
+
+
+def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
+    """Attach an activation observer (forward hook) to every quantizable module; nothing
+    numeric changes.  Fused containers are observed as a unit, not their children."""
+    qcfg = qconfig if qconfig is not None else get_default_qconfig()
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    observed = _observed_types()
+    nni = _intrinsic()
+    fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
+    inside_fused = set()
+    n_matched = 0
+    for name, mod in model.named_modules():
+        if any(name.startswith(p + ".") for p in inside_fused):
+            continue
+        if not isinstance(mod, observed):
+            continue
+        if isinstance(mod, fused):
+            inside_fused.add(name)
+        mod.qconfig = qcfg
+        obs = qcfg.activation()
+        mod.activation_post_process = obs
+        mod._lq_hook = mod.register_forward_hook(_make_observer_hook(obs))
+        n_matched += 1
+    if n_matched == 0:
+        warnings.warn("prepare(): the qconfig matched no quantizable modules -- convert() will "
+                      "leave this model unchanged.", stacklevel=2)
+    return model
+
+
+def _convert_recursive(module, mapping, always) -> None:
+    for name, child in list(module.named_children()):
+        build = mapping.get(type(child))
+        convertible = build is not None and (
+            isinstance(child, always) or hasattr(child, "activation_post_process"))
+        if convertible:
+            hook = getattr(child, "_lq_hook", None)
+            if hook is not None:
+                hook.remove()
+            # assign through _modules to keep the child's position (Sequential order)
+            module._modules[name] = build(child)
+        else:
+            _convert_recursive(child, mapping, always)
+
+
+def convert(model: torch.nn.Module, inplace: bool = False):
+    """Swap every calibrated float module for its quantized counterpart."""
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    mapping = _quant_mapping()
+    always = (DeQuantStub,)
+    build = mapping.get(type(model))
+    if build is not None and hasattr(model, "activation_post_process"):
+        return build(model)
+    _convert_recursive(model, mapping, always)
+    return model
+
+
+def _dynamic_mapping() -> dict:
+    import lucid_b200.nn.quantized as nnq
+
+    return {torch.nn.Linear: nnq.dynamic.Linear.from_float}
+
+
+def _swap_dynamic(module, mapping, types, dtype) -> None:
+    for name, child in list(module.named_children()):
+        build = mapping.get(type(child))
+        if build is not None and type(child) in types:
+            module._modules[name] = build(child, dtype)
+        else:
+            _swap_dynamic(child, mapping, types, dtype)
+
+
+def quantize_dynamic(model: torch.nn.Module, qconfig_spec: set | None = None, dtype: QDtype = qint8,
+                     inplace: bool = False):
+    """int8 weights, activations quantized at run time; no calibration."""
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    mapping = _dynamic_mapping()
+    types = qconfig_spec if qconfig_spec is not None else set(mapping)
+    if not any(type(m) in types for m in model.modules()):
+        warnings.warn("quantize_dynamic(): no module of a targeted type "
+                      f"({', '.join(sorted(t.__name__ for t in types))}) found -- the model is "
+                      "returned unchanged.", stacklevel=2)
+    build = mapping.get(type(model))
+    if build is not None and type(model) in types:
+        return build(model, dtype)
+    _swap_dynamic(model, mapping, types, dtype)
+    return model
