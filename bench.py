@@ -545,9 +545,90 @@ def run_single_kernel_case(args):
     return 0
 
 
+def run_config_cases(args):
+    """Device-resident timings of the other BASELINE configurations (parity-test cases, not
+    bench lines): config 2 dynamic Linear, config 3 gated MLP block, config 4 conv stack."""
+    import torch
+
+    import lucid_b200.nn.quantized as nnq
+    import lucid_b200.quantization as Q
+    from lucid_b200 import _lib
+    from lucid_b200.nn.quantized import functional as QF
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def timed(fn, iters):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    # config 2: dynamic Linear, f32 in/out (range reduction + qparams + encode + GEMM)
+    lin = torch.nn.Linear(4096, 4096).to(dev)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(4096, 4096, device=dev, generator=g) * 0.02)
+        lin.bias.copy_(torch.randn(4096, device=dev, generator=g) * 0.01)
+    qlin = nnq.dynamic.Linear.from_float(lin)
+    x2 = torch.randn(2048, 4096, device=dev, generator=g)
+    ms = timed(lambda: qlin(x2), args.steps)
+    out["config2_dynamic_linear"] = {"ms": ms, "TOPS": 2 * 2048 * 4096 * 4096 / ms / 1e9,
+                                     "note": "module forward: min-max, qparams, u8 encode, GEMM with zero-point correction + bias, f32 out"}
+    # config 3: gated MLP block, bf16
+    d, ff = 4096, 11008
+    mlp = nnq.dynamic.GatedMLP.from_float(torch.randn(ff, d, device=dev, generator=g) * 0.02,
+                                          torch.randn(ff, d, device=dev, generator=g) * 0.02,
+                                          torch.randn(d, ff, device=dev, generator=g) * 0.02)
+    x3 = torch.randn(8, 512, d, device=dev, generator=g).to(torch.bfloat16)
+    ms = timed(lambda: mlp(x3), args.steps)
+    out["config3_gated_mlp"] = {"ms": ms, "TOPS": 3 * 2 * 4096 * d * ff / ms / 1e9,
+                                "note": "2 per-token encodes + gate/up GEMM with SiLU-gate epilogue + down GEMM, bf16"}
+    # config 4: conv stack on codes, fused bias + ReLU + requantise
+    n, h, w = 64, 28, 28
+    a = torch.randint(-127, 128, (n, h, w, 512), dtype=torch.int8, device=dev, generator=g)
+    layers = []
+    for cin, cout, r, pad in ((512, 256, 1, 0), (256, 256, 3, 1), (256, 1024, 1, 0)):
+        wq = torch.randint(-127, 128, (cout, r, r, cin), dtype=torch.int8, device=dev, generator=g)
+        layers.append((wq, torch.rand(cout, device=dev) * 1e-3 + 1e-4, torch.randn(cout, device=dev) * 0.01, pad))
+    one = torch.tensor(0.02, device=dev)
+    zero = torch.tensor(0.0, device=dev)
+
+    def conv_stack():
+        t = a
+        for wq, ws, b, pad in layers:
+            t = QF.conv2d_nhwc_s8(t, wq, pad=pad, out_dtype=torch.uint8, a_scale=one, b_scale=ws, bias=b,
+                                  act=_lib.ACT_RELU, out_scale=one, out_zp=zero, qmin=0, qmax=255)
+        return t
+
+    ms = timed(conv_stack, args.steps)
+    ops = 2 * n * h * w * (512 * 256 + 9 * 256 * 256 + 256 * 1024)
+    out["config4_conv_stack"] = {"ms": ms, "TOPS": ops / ms / 1e9,
+                                 "note": "1x1 512->256, 3x3 256->256, 1x1 256->1024 on NHWC codes, N=64, 28x28"}
+    per = []
+    t = a
+    for wq, ws, b, pad in layers:
+        f = lambda t=t, wq=wq, ws=ws, b=b, pad=pad: QF.conv2d_nhwc_s8(
+            t, wq, pad=pad, out_dtype=torch.uint8, a_scale=one, b_scale=ws, bias=b, act=_lib.ACT_RELU,
+            out_scale=one, out_zp=zero, qmin=0, qmax=255)
+        per.append(timed(f, args.steps) * 1e3)
+        t = f()
+    out["config4_conv_stack"]["layer_us"] = per
+    _lib.check_device_status(dev)
+    print(json.dumps({"case": "configs", "configs": out}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams"])
+    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs"])
     ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -559,6 +640,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.case == "configs":
+        return run_config_cases(args)
     if args.case != "full":
         return run_single_kernel_case(args)
     return run_b200_arm(args)

@@ -119,6 +119,15 @@ int lq_quantize(const void* x, int in_dtype, size_t rows, size_t cols, const flo
                 const float* zero_point, float scale_value, float zp_value, int ch_mode, int qmin,
                 int qmax, void* out, int out_dtype, void* stream);
 
+/* Dynamic per-tensor encode in one call: observed range -> (scale, zero_point) -> codes, all
+ * on the device (no host round trip).  Replaces the x.min() / x.max() -> calculate_qparams ->
+ * fake_quantize prologue of dynamic.Linear.forward (lucid/nn/quantized/dynamic/linear.py:87-92).
+ * workspace as for lq_minmax; out_scale / out_zp: 1 float each; out_minmax: 2 floats. */
+int lq_quantize_dynamic(const void* x, int in_dtype, size_t rows, size_t cols, int symmetric,
+                        int is_signed, int qmin, int qmax, float eps, void* workspace,
+                        size_t workspace_bytes, void* out, int out_dtype, float* out_scale,
+                        float* out_zp, float* out_minmax, void* stream);
+
 /* x = (f32(q) - z) * s.  Replaces dequantize
  * (lucid/quantization/_functional.py:269-281).  q_dtype LQ_S8 | LQ_U8 | LQ_S16;
  * out_dtype LQ_F32 | LQ_BF16 (bf16 = the f32 result rounded once). */

@@ -77,6 +77,9 @@ _SIGNATURES = {
     "lq_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
                               C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
                               C.c_void_p]),
+    "lq_quantize_dynamic": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int,
+                                      C.c_int, C.c_float, C.c_void_p, C.c_size_t, C.c_void_p, C.c_int,
+                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lq_dequantize": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_void_p,
                                 C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p, C.c_int,
                                 C.c_void_p]),

@@ -1225,3 +1225,21 @@ extern "C" int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* o
     minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max);
   return check_cuda(cudaGetLastError(), "lq_minmax_noalloc launch");
 }
+
+// Dynamic per-tensor encode in one call: range reduction -> qparams -> codes (three launches,
+// no host round trip; scale and zero point stay on the device for the GEMM epilogue).
+extern "C" int lq_quantize_dynamic(const void* x, int in_dtype, size_t rows, size_t cols, int symmetric,
+                                   int is_signed, int qmin, int qmax, float eps, void* workspace,
+                                   size_t workspace_bytes, void* out, int out_dtype, float* out_scale,
+                                   float* out_zp, float* out_minmax, void* stream) {
+  if (rows == 0 || cols == 0) return fail(LQ_ERR_SHAPE, "lq_quantize_dynamic: empty input has no range");
+  if (!out_scale || !out_zp || !out_minmax) return fail(LQ_ERR_DEVICE, "lq_quantize_dynamic: null pointer");
+  int rc = lq_minmax(x, in_dtype, 1, rows * cols, LQ_PER_TENSOR, out_minmax, out_minmax + 1, workspace,
+                     workspace_bytes, stream);
+  if (rc != LQ_OK) return rc;
+  rc = lq_calculate_qparams(out_minmax, out_minmax + 1, 1, symmetric, is_signed, qmin, qmax, eps, out_scale,
+                            out_zp, stream);
+  if (rc != LQ_OK) return rc;
+  return lq_quantize(x, in_dtype, rows, cols, out_scale, out_zp, 0.0f, 0.0f, LQ_PER_TENSOR, qmin, qmax, out,
+                     out_dtype, stream);
+}

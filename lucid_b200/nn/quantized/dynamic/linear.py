@@ -19,9 +19,8 @@ from __future__ import annotations
 import torch
 
 from .... import _lib
-from ....quantization import (PerChannelMinMaxObserver, QDtype, calculate_qparams, minmax,
-                              per_channel_symmetric, per_tensor_affine, qint8, quantize,
-                              quantize_per_token, quantize_to, quint8)
+from ....quantization import (PerChannelMinMaxObserver, QDtype, per_channel_symmetric, qint8, quantize,
+                              quantize_dynamic_per_tensor, quantize_per_token, quint8)
 from .. import functional as QF
 from ..linear import _WeightCache
 
@@ -55,11 +54,7 @@ class Linear(torch.nn.Module):
             raise NotImplementedError("dynamic.Linear needs in_features % 16 == 0 on the integer path")
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
-        qd = self.act_qdtype
-        mn, mx = minmax(x2)
-        x_scale, x_zp = calculate_qparams(mn, mx, per_tensor_affine, qd)
-        a = quantize_to(x2, x_scale, x_zp, qd.quant_min, qd.quant_max,
-                        torch.int8 if qd.signed else torch.uint8)
+        a, x_scale, x_zp = quantize_dynamic_per_tensor(x2, self.act_qdtype)
         w = self.weight_int8
         rowsum = self._cache.get(w, "rowsum", lambda: QF.rowsum_s8(w))
         out_dtype = x.dtype if x.dtype in (torch.float32, torch.bfloat16) else torch.float32

@@ -23,8 +23,7 @@ import torch
 import torch.nn.functional as F
 
 from ... import _lib, backends
-from ...quantization import (QDtype, calculate_qparams, dequantize, fake_quantize, minmax,
-                             per_tensor_affine, quantize_to, quint8)
+from ...quantization import QDtype, dequantize, fake_quantize, quantize_dynamic_per_tensor, quint8
 from . import functional as QF
 from ._utils import QCodes, activation_qparams, codes_of, quantize_weight, tag
 
@@ -33,9 +32,7 @@ def encode_activation(x: torch.Tensor):
     """Codes of an activation whose grid is not known: per-tensor affine quint8
     from the live range, exactly the encode dynamic.Linear performs
     (lucid/nn/quantized/dynamic/linear.py:87-92)."""
-    mn, mx = minmax(x)
-    s, z = calculate_qparams(mn, mx, per_tensor_affine, quint8)
-    return quantize_to(x, s, z, 0, 255, torch.uint8), s, z
+    return quantize_dynamic_per_tensor(x, quint8)
 
 
 class _WeightCache:

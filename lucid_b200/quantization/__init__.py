@@ -2,8 +2,8 @@
 (lucid/quantization/__init__.py:58-65): schemes, grids, qparams, the three
 affine primitives and the min/max observers."""
 
-from ._functional import (dequantize, fake_quantize, quantize, quantize_per_token,  # noqa: F401
-                          quantize_to)
+from ._functional import (dequantize, fake_quantize, quantize, quantize_dynamic_per_tensor,  # noqa: F401
+                          quantize_per_token, quantize_to)
 from ._qparams import QParams, calculate_qparams  # noqa: F401
 from ._qscheme import (QDtype, QScheme, per_channel_affine, per_channel_symmetric,  # noqa: F401
                        per_tensor_affine, per_tensor_symmetric, qint4, qint8, qint32, quint8)

@@ -152,6 +152,28 @@ def fake_quantize(x, scale, zero_point, quant_min, quant_max, ch_axis=None) -> t
     return out
 
 
+def quantize_dynamic_per_tensor(x, qdtype: QDtype, symmetric: bool = False, eps: float = 1e-8):
+    """Per-tensor encode on the live range in one native call: min/max -> calculate_qparams ->
+    quantize.  Returns ``(codes (int8 | uint8), scale, zero_point)``, the latter two 0-d device
+    tensors (nothing is synchronised)."""
+    xc = _input(x, "dynamic encode input", (torch.float32, torch.bfloat16))
+    if xc.numel() == 0:
+        raise _lib.ShapeMismatch("cannot observe an empty tensor")
+    dev = xc.device
+    store = torch.int8 if qdtype.signed else torch.uint8
+    out = torch.empty(xc.shape, dtype=store, device=dev)
+    small = torch.empty(4, dtype=torch.float32, device=dev)  # scale, zp, min, max
+    cols = xc.shape[-1] if xc.dim() > 0 else 1
+    with torch.cuda.device(dev):
+        ws = _lib.minmax_workspace(dev)
+        _lib.check(_lib.load().lq_quantize_dynamic(
+            _lib.ptr(xc), _lib.code_of(xc.dtype), xc.numel() // cols, cols, int(symmetric),
+            int(qdtype.signed), qdtype.quant_min, qdtype.quant_max, C.c_float(eps), _lib.ptr(ws),
+            ws.numel(), _lib.ptr(out), _lib.code_of(store), C.c_void_p(small.data_ptr()),
+            C.c_void_p(small.data_ptr() + 4), C.c_void_p(small.data_ptr() + 8), _lib.stream_ptr(dev)))
+    return out, small[0], small[1]
+
+
 def quantize_per_token(x, qdtype: QDtype, eps: float = 1e-8):
     """Per-token (row of the last axis) symmetric encode in one HBM pass.
 
