@@ -527,16 +527,25 @@ def run_single_kernel_case(args):
     m, n, k = (int(v) for v in args.shape.split(","))
     a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev)
     b = torch.randint(-128, 128, (n, k), dtype=torch.int8, device=dev)
-    sa = torch.rand(m, device=dev)
     sb = torch.rand(n, device=dev)
-    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    if args.epi == "u8":  # conv-style epilogue: per-tensor scale, bias, ReLU, requantise to u8
+        sa = torch.tensor(1e-4, device=dev)
+        bias = torch.randn(n, device=dev)
+        so, zo = torch.tensor(0.05, device=dev), torch.tensor(0.0, device=dev)
+        out = torch.empty((m, n), dtype=torch.uint8, device=dev)
+        run = lambda: QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, bias=bias, act=_lib.ACT_RELU, out_scale=so,
+                                 out_zp=zo, qmin=0, qmax=255, out=out)
+    else:
+        sa = torch.rand(m, device=dev)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        run = lambda: QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=out)
     for _ in range(args.warmup):
-        QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=out)
+        run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
     e0.record()
     for _ in range(args.steps):
-        QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=out)
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
@@ -630,6 +639,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs"])
     ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm")
+    ap.add_argument("--epi", default="bf16", choices=["bf16", "u8"], help="epilogue of --case gemm")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

@@ -40,6 +40,9 @@ struct Divisor {
   float s, y;
   bool fast;
 };
+// Full-range IEEE division, kept out of line: it is the rare path, and inlining its
+// expansion at every element bloats the hot loops past the instruction cache.
+static __device__ __noinline__ float div_full(float x, float s) { return __fdiv_rn(x, s); }
 __device__ __forceinline__ Divisor make_divisor(float s) {
   Divisor d;
   const float a = fabsf(s);
@@ -59,7 +62,7 @@ __device__ __forceinline__ float div_rn(float x, const Divisor& d) {
     }
     if (x == 0.0f) return q;  // +-0 / s
   }
-  return __fdiv_rn(x, d.s);
+  return div_full(x, d.s);
 }
 
 // Four quotients by the same divisor.  The short form runs unconditionally on all four (no
@@ -88,12 +91,12 @@ __device__ __forceinline__ bool div_rn4(const float (&x)[4], const Divisor& d, f
     if (any) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        if (redo[i]) q[i] = __fdiv_rn(x[i], d.s);
+        if (redo[i]) q[i] = div_full(x[i], d.s);
     }
   } else {
     any = true;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) q[i] = __fdiv_rn(x[i], d.s);
+    for (int i = 0; i < 4; ++i) q[i] = div_full(x[i], d.s);
   }
   return any;
 }

@@ -30,22 +30,24 @@ namespace {
 constexpr int BM = 128;       // rows of the CTA tile == TMEM lanes
 constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128B swizzle atom
 constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
-constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
-constexpr int kEpiWarps = 8;        // two per TMEM lane quadrant, each takes half the columns
+// Epilogue warps per CTA (EW): 8 when the mainloop of a tile outlasts its epilogue (large K:
+// more ring stages, fewer polling warps), 16 when the epilogue is the long pole (small K).
+constexpr int threads_for(int ew) { return 64 + 32 * ew; }  // producer warp, MMA warp, epilogue warps
 constexpr int kTmemCols = 512;
 constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int EW>
 struct Cfg {
   // PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2); each
   // CTA stages its own 128 rows of A and half of the B rows.
-  static constexpr int kStages = PAIR ? 6 : (BN == 256 ? 4 : 6);
+  // the ring shares the SM's 227 KB with EW x 4 KB of epilogue staging
+  static constexpr int kStages = EW == 16 ? (PAIR ? 5 : (BN == 256 ? 3 : 5)) : (PAIR ? 6 : (BN == 256 ? 4 : 6));
   static constexpr int kABytes = BM * BK;
   static constexpr int kBRows = PAIR ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * BK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // ring + 1 KB alignment slack + barriers (512 B) + per-warp output staging (8 x 4 KB)
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kEpiWarps * 4096;
+  // ring + 1 KB alignment slack + barriers (512 B) + per-warp output staging (EW x 4 KB)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + EW * 4096;
 };
 
 struct Geometry {
@@ -267,6 +269,24 @@ __device__ __forceinline__ float silu_f32(float x) {
   return __fmul_rn(x, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
 }
 
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld_dep16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 // tcgen05.wait::ld that also carries the loaded registers, so that no use of them can be
 // scheduled ahead of the wait.
 __device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&r)[32]) {
@@ -297,30 +317,6 @@ struct RowCtx {
   uint32_t row_mask; // valid rows of this warp (bit r = tile row quad*32 + r)
   long long row0;    // global output row of the warp's first row
 };
-
-// 32 accumulators of one row -> 32 packed outputs (8 * esz words).
-template <int KIND>
-__device__ __forceinline__ void finish32(const float (&y)[32], uint32_t (&w)[32], const RowCtx& rc) {
-  if (KIND == KIND_F32) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(y[j]);
-  } else if (KIND == KIND_BF16) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
-      w[j] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float x4[4] = {y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]};
-      float c[4];
-      code4_f32(x4, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
-      // identical byte patterns for both storages once the value is inside its grid
-      w[j] = rc.fqmin < 0.0f ? pack4_s8(c) : pack4_u8(c);
-    }
-  }
-}
 
 // Flush the warp's staging buffer (32 rows x 128 B, 16-byte pieces XOR-swizzled by row):
 // eight lanes write one full 128-byte line of a row.
@@ -359,146 +355,144 @@ __device__ __forceinline__ void flush_group(const uint8_t* stg, int lane, const 
   }
 }
 
-// Parameters of 32 consecutive columns; `fast` = the whole chunk is inside N and the arrays
-// are 16-byte aligned (straight-line vector loads, every lane asks for the same address).
-__device__ __forceinline__ void load_params32(const float* p, int col, int ncols, bool fast,
-                                              float dflt, float (&v)[32]) {
+// Parameters of 16 consecutive columns; `fast` = the block is inside N and the arrays are
+// 16-byte aligned (straight-line vector loads, every lane asks for the same address).
+__device__ __forceinline__ void load_params16(const float* p, int col, int ncols, bool fast,
+                                              float dflt, float (&v)[16]) {
   if (fast) {
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
+    for (int q = 0; q < 4; ++q) {
       const float4 t = __ldg(reinterpret_cast<const float4*>(p + col) + q);
       v[4 * q] = t.x, v[4 * q + 1] = t.y, v[4 * q + 2] = t.z, v[4 * q + 3] = t.w;
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = col + j < ncols ? __ldg(p + col + j) : dflt;
+    for (int j = 0; j < 16; ++j) v[j] = col + j < ncols ? __ldg(p + col + j) : dflt;
   }
 }
 
-// y[j] = f32(acc[j] - zpa * rowsum[j]) * (sa * sb[j]) [+ bias[j]]; every float step is a
-// separate binary32 operation.
-__device__ __forceinline__ void dequant32(const Epi& ep, const Geometry& g, const RowCtx& rc,
-                                          const uint32_t (&acc)[32], int col, float (&y)[32]) {
-  const bool fast = ep.par_vec && col + 32 <= g.N;
-  int t[32];
+// y[j] = f32(acc[j] - zpa * rowsum[j]) * (sa * sb[j]) [+ bias[j]] for 16 columns; every float
+// step is a separate binary32 operation.
+__device__ __forceinline__ void dequant16(const Epi& ep, const Geometry& g, const RowCtx& rc,
+                                          const uint32_t* acc, int col, float (&y)[16]) {
+  const bool fast = ep.par_vec && col + 16 <= g.N;
+  float p[16];
+  load_params16(ep.b_scale, col, g.N, fast, 1.0f, p);
   if (ep.b_rowsum != nullptr && rc.zpa != 0) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < 16; ++j) {
       const int rs = col + j < g.N ? __ldg(ep.b_rowsum + col + j) : 0;
-      t[j] = (int)acc[j] - rc.zpa * rs;
+      y[j] = __fmul_rn((float)((int)acc[j] - rc.zpa * rs), __fmul_rn(rc.sa, p[j]));
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) t[j] = (int)acc[j];
+    for (int j = 0; j < 16; ++j) y[j] = __fmul_rn((float)(int)acc[j], __fmul_rn(rc.sa, p[j]));
   }
-  float p[32];
-  load_params32(ep.b_scale, col, g.N, fast, 1.0f, p);
-#pragma unroll
-  for (int j = 0; j < 32; ++j) y[j] = __fmul_rn((float)t[j], __fmul_rn(rc.sa, p[j]));
   if (ep.bias != nullptr) {
-    load_params32(ep.bias, col, g.N, fast, 0.0f, p);
+    load_params16(ep.bias, col, g.N, fast, 0.0f, p);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) y[j] = __fadd_rn(y[j], p[j]);
+    for (int j = 0; j < 16; ++j) y[j] = __fadd_rn(y[j], p[j]);
   }
 }
 
-// One 32-column chunk of one row: accumulators -> outputs -> this thread's slot of the
-// staging buffer; the warp flushes the buffer when a 128-byte group is complete.
-// `rel` is the chunk's index inside this warp's column range of `count` chunks.
-template <int BN, int KIND, bool GATED>
-__device__ __forceinline__ void process_chunk(const Epi& ep, const Geometry& g, const RowCtx& rc,
-                                              const uint32_t (&acc)[32], const uint32_t (&acc_u)[32],
-                                              int it, int rel, int count, uint8_t* stg, int lane,
+// 16 outputs of one row -> 4 * esz packed words.
+template <int KIND>
+__device__ __forceinline__ void finish16(const float (&y)[16], uint32_t (&w)[16], const RowCtx& rc) {
+  if (KIND == KIND_F32) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = __float_as_uint(y[j]);
+  } else if (KIND == KIND_BF16) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float x4[4] = {y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]};
+      float c[4];
+      code4_f32(x4, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
+      // identical byte patterns for both storages once the value is inside its grid
+      w[j] = rc.fqmin < 0.0f ? pack4_s8(c) : pack4_u8(c);
+    }
+  }
+}
+
+// Epilogue of one accumulator tile for one warp: 32 TMEM lanes (rows) x 1/PARTS of the
+// tile's output columns (`part` selects which), in blocks of 16 columns: TMEM -> registers ->
+// outputs -> this thread's slot of the staging buffer; the warp flushes the buffer whenever a
+// 128-byte group per row is complete.  Four warps share a lane quadrant, so the TMEM and
+// parameter load latencies of one warp hide behind the arithmetic of the others; the short
+// blocks keep the 16-warp build inside its 96-register budget.
+template <int BN, int KIND, bool GATED, int PARTS>
+__device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, const RowCtx& rc,
+                                              uint32_t taddr, uint8_t* stg, int lane, int part,
                                               int n0, int on0) {
   constexpr int ESZ = KindInfo<KIND>::kEsz;
-  constexpr int CPG = 128 / (32 * ESZ);  // chunks per 128-byte group
-  constexpr int PPI = 2 * ESZ;           // 16-byte pieces per chunk
-  const int bc = n0 + it * 32;           // column in the B / parameter space
-  uint32_t w[32];
-  if (KIND == KIND_S32) {
-    if (ep.b_rowsum != nullptr && rc.zpa != 0) {
+  constexpr int OUTC = GATED ? BN / 2 : BN;   // output columns of the tile
+  constexpr int WCOLS = OUTC / PARTS;         // ... of this warp
+  constexpr int NB = WCOLS / 16;              // 16-column blocks per warp
+  constexpr int BPG = 8 / ESZ;                // blocks per 128-byte group
+  static_assert(NB >= 1, "tile too narrow for this many column parts");
+  const int c0 = part * WCOLS;                // first output column of this warp inside the tile
+#pragma unroll 1
+  for (int blk = 0; blk < NB; ++blk) {
+    const int oc = c0 + blk * 16;             // output column inside the tile
+    uint32_t acc[16], acc_u[16];
+    tc_ld16(taddr + oc, acc);
+    if (GATED) tc_ld16(taddr + BN / 2 + oc, acc_u);
+    tc_wait_ld_dep16(acc);
+    if (GATED) tc_wait_ld_dep16(acc_u);
+    uint32_t w[16];
+    if (KIND == KIND_S32) {
+      if (ep.b_rowsum != nullptr && rc.zpa != 0) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int rs = bc + j < g.N ? __ldg(ep.b_rowsum + bc + j) : 0;
-        w[j] = (uint32_t)((int)acc[j] - rc.zpa * rs);
+        for (int j = 0; j < 16; ++j) {
+          const int col = n0 + oc + j;
+          const int rs = col < g.N ? __ldg(ep.b_rowsum + col) : 0;
+          w[j] = (uint32_t)((int)acc[j] - rc.zpa * rs);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = acc[j];
       }
     } else {
+      float y[16];
+      dequant16(ep, g, rc, acc, n0 + oc, y);
+      if (GATED) {
+        float u[16];
+        dequant16(ep, g, rc, acc_u, n0 + BN / 2 + oc, u);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) w[j] = acc[j];
+        for (int j = 0; j < 16; ++j) y[j] = __fmul_rn(silu_f32(y[j]), u[j]);
+      } else if (ep.act == LQ_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], 0.0f);
+      }
+      finish16<KIND>(y, w, rc);
     }
-  } else {
-    float y[32];
-    dequant32(ep, g, rc, acc, bc, y);
-    if (GATED) {
-      float u[32];
-      dequant32(ep, g, rc, acc_u, bc + BN / 2, u);
+    // stage: row = lane, 16-byte pieces swizzled by (row & 7)
+    const int cs = blk % BPG;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) y[j] = __fmul_rn(silu_f32(y[j]), u[j]);
-    } else if (ep.act == LQ_ACT_RELU) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
+    for (int i = 0; i < ESZ; ++i) {
+      const int piece = cs * ESZ + i;
+      *reinterpret_cast<uint4*>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
+          make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
     }
-    finish32<KIND>(y, w, rc);
-  }
-  // stage: row = lane, 16-byte pieces swizzled by (row & 7)
-  const int cs = rel % CPG;
-#pragma unroll
-  for (int i = 0; i < PPI; ++i) {
-    const int piece = cs * PPI + i;
-    *reinterpret_cast<uint4*>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) =
-        make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-  }
-  if (cs == CPG - 1 || rel == count - 1) {
-    __syncwarp();
-    flush_group<ESZ>(stg, lane, ep, rc, on0 + (it - cs) * 32, (cs + 1) * PPI);
-    __syncwarp();
-  }
-}
-
-// Epilogue of one accumulator tile for one warp: 32 TMEM lanes (rows) x half of the tile's
-// columns (`half` selects which).  Two register buffers alternate: the TMEM load of chunk
-// i+1 is in flight while chunk i is processed, and a buffer is only read after the wait
-// that covers its load.
-template <int BN, int KIND, bool GATED>
-__device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, const RowCtx& rc,
-                                              uint32_t taddr, uint8_t* stg, int lane, int half,
-                                              int n0, int on0) {
-  constexpr int NIT = (GATED ? BN / 2 : BN) / 32;  // chunks of 32 output columns in the tile
-  constexpr int CNT = NIT / 2;                     // chunks per warp
-  static_assert(GATED || CNT % 2 == 0, "chunks are processed in pairs");
-  const int it0 = half * CNT;
-  if (GATED) {
-    // two accumulator chunks (gate, up) per step already fill the register budget
-    uint32_t a0[32], u0[32];
-#pragma unroll 1
-    for (int r = 0; r < CNT; ++r) {
-      tc_ld32(taddr + (it0 + r) * 32, a0);
-      tc_ld32(taddr + BN / 2 + (it0 + r) * 32, u0);
-      tc_wait_ld_dep(a0);
-      tc_wait_ld_dep(u0);
-      process_chunk<BN, KIND, GATED>(ep, g, rc, a0, u0, it0 + r, r, CNT, stg, lane, n0, on0);
-    }
-  } else {
-    uint32_t a0[32], a1[32];
-    tc_ld32(taddr + it0 * 32, a0);
-#pragma unroll 1
-    for (int r = 0; r < CNT; r += 2) {
-      tc_wait_ld_dep(a0);
-      tc_ld32(taddr + (it0 + r + 1) * 32, a1);
-      process_chunk<BN, KIND, GATED>(ep, g, rc, a0, a0, it0 + r, r, CNT, stg, lane, n0, on0);
-      tc_wait_ld_dep(a1);
-      if (r + 2 < CNT) tc_ld32(taddr + (it0 + r + 2) * 32, a0);
-      process_chunk<BN, KIND, GATED>(ep, g, rc, a1, a1, it0 + r + 1, r + 1, CNT, stg, lane, n0, on0);
+    if (cs == BPG - 1 || blk == NB - 1) {
+      __syncwarp();
+      flush_group<ESZ>(stg, lane, ep, rc, on0 + c0 + (blk - cs) * 16, (cs + 1) * ESZ);
+      __syncwarp();
     }
   }
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <int BN, bool PAIR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, bool PAIR, int EW>
+__global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const Geometry g, const Epi ep, const uint32_t idesc) {
-  using C = Cfg<BN, PAIR>;
+  using C = Cfg<BN, PAIR, EW>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -532,7 +526,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * kEpiWarps);
+      mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * EW);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -657,11 +651,12 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     __syncwarp();
   } else {
-    // ===== epilogue: warps 2..9; TMEM lane quadrant = warp % 4, column half = (warp - 2) / 4 =====
+    // ===== epilogue: warps 2..EW+1; TMEM lane quadrant = warp % 4, column part = (warp - 2) / 4 =====
+    constexpr int PARTS = EW / 4;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // tile-local row == TMEM lane
     uint8_t* stg = tail + 512 + (warp - 2) * 4096;  // this warp's output staging
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -703,16 +698,16 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       if (g.debug & 4) {
       } else if (gated) {
         const int on0 = tn_idx * (BN / 2);
-        if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true>(ep, g, rc, taddr, stg, lane, half, n0, on0);
-        else epilogue_tile<BN, KIND_BF16, true>(ep, g, rc, taddr, stg, lane, half, n0, on0);
+        if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0);
+        else epilogue_tile<BN, KIND_BF16, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0);
       } else if (ep.out_dtype == LQ_BF16) {
-        epilogue_tile<BN, KIND_BF16, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+        epilogue_tile<BN, KIND_BF16, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       } else if (ep.out_dtype == LQ_F32) {
-        epilogue_tile<BN, KIND_F32, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+        epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       } else if (ep.out_dtype == LQ_S32) {
-        epilogue_tile<BN, KIND_S32, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+        epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       } else {
-        epilogue_tile<BN, KIND_Q8, false>(ep, g, rc, taddr, stg, lane, half, n0, n0);
+        epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       }
       // hand the accumulator stage back to the MMA issuer
       tc_fence_before();
@@ -856,14 +851,15 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
   d->par_vec = aligned16(e->b_scale) && aligned16(e->bias) && aligned16(e->b_rowsum);
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, int EW>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep,
            uint32_t idesc, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   static int max_clusters = 0;
-  auto kernel = gemm_s8_kernel<BN, PAIR>;
-  constexpr int smem = Cfg<BN, PAIR>::kSmemBytes;
+  auto kernel = gemm_s8_kernel<BN, PAIR, EW>;
+  constexpr int smem = Cfg<BN, PAIR, EW>::kSmemBytes;
+  constexpr int kGemmThreads = threads_for(EW);
   std::call_once(once, [&] {
     attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (PAIR && attr_err == cudaSuccess) {
@@ -925,10 +921,18 @@ Shape pick_shape(size_t m_subtiles, size_t N, bool gated) {
 
 int dispatch(Shape sh, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,
              int a_signed, cudaStream_t st) {
+  // tiles whose mainloop (k-blocks x ~0.28 us) is shorter than their epilogue get 16 epilogue warps
+  bool wide_epi = g.num_kb <= 32;
+  if (const char* f = getenv("LQ_GEMM_EPI_WARPS")) wide_epi = atoi(f) == 16;
   switch (sh) {
-    case Shape::kPair256: return launch<256, true>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st);
-    case Shape::kSingle256: return launch<256, false>(ta, tb, g, ep, make_idesc(a_signed, 256), st);
-    default: return launch<128, false>(ta, tb, g, ep, make_idesc(a_signed, 128), st);
+    case Shape::kPair256:
+      return wide_epi ? launch<256, true, 16>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st)
+                      : launch<256, true, 8>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st);
+    case Shape::kSingle256:
+      return wide_epi ? launch<256, false, 16>(ta, tb, g, ep, make_idesc(a_signed, 256), st)
+                      : launch<256, false, 8>(ta, tb, g, ep, make_idesc(a_signed, 256), st);
+    default:
+      return launch<128, false, 8>(ta, tb, g, ep, make_idesc(a_signed, 128), st);
   }
 }
 

@@ -36,12 +36,17 @@ SHAPES = [(128, 128, 128), (128, 256, 128), (256, 512, 256), (1, 16, 16), (130, 
           (77, 129, 4096), (384, 640, 1040), (512, 1024, 2048), (128, 96, 32), (300, 257, 48)]
 
 
-@pytest.fixture(params=["auto", "pair", "single256", "single128"])
+@pytest.fixture(params=["auto", "pair", "single256", "single128", "pair-epi8", "pair-epi16",
+                        "single256-epi8", "single256-epi16"])
 def tile_shape(request, monkeypatch):
-    """Forces the GEMM's tile policy (CTA pair 256x256 / single 128x256 / single 128x128)."""
-    if request.param != "auto":
-        monkeypatch.setenv("LQ_GEMM_SHAPE", request.param)
-    return request.param
+    """Forces the GEMM's tile policy (CTA pair 256x256 / single 128x256 / single 128x128) and
+    the epilogue build (8 or 16 epilogue warps)."""
+    shape, _, epi = request.param.partition("-epi")
+    if shape != "auto":
+        monkeypatch.setenv("LQ_GEMM_SHAPE", shape)
+    if epi:
+        monkeypatch.setenv("LQ_GEMM_EPI_WARPS", epi)
+    return shape
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
