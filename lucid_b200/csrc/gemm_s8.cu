@@ -279,6 +279,18 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// load and wait in one statement: the registers are defined only once the data has landed
+__device__ __forceinline__ void tc_ld16_sync(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld_dep16(uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
@@ -440,10 +452,14 @@ __device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, 
   for (int blk = 0; blk < NB; ++blk) {
     const int oc = c0 + blk * 16;             // output column inside the tile
     uint32_t acc[16], acc_u[16];
-    tc_ld16(taddr + oc, acc);
-    if (GATED) tc_ld16(taddr + BN / 2 + oc, acc_u);
-    tc_wait_ld_dep16(acc);
-    if (GATED) tc_wait_ld_dep16(acc_u);
+    if (GATED) {
+      tc_ld16(taddr + oc, acc);
+      tc_ld16(taddr + BN / 2 + oc, acc_u);
+      tc_wait_ld_dep16(acc);
+      tc_wait_ld_dep16(acc_u);
+    } else {
+      tc_ld16_sync(taddr + oc, acc);
+    }
     uint32_t w[16];
     if (KIND == KIND_S32) {
       if (ep.b_rowsum != nullptr && rc.zpa != 0) {
