@@ -424,8 +424,8 @@ def run_b200_arm(args):
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS",
                 "frac": achieved / peak,
-                # DRAM bytes per average GEMM launch: the ncu capture of 4096 x 16384 x 8192
-                # (profiles/gemm_s8_pair_4096x16384x8192_ncu_full.md) moved 318.6 MB for 302.0 MB
+                # DRAM bytes per average GEMM launch: an ncu capture of 4096 x 16384 x 8192
+                # (dram__bytes_read.sum + dram__bytes_write.sum) moved 318.6 MB for 302.0 MB
                 # of algorithmic bytes (A + B read once, output written once); the same factor is
                 # applied to this workload's average launch (381.7 MB algorithmic at one GPU)
                 "traffic": 381.7e6 / world * (318.6 / 302.0),

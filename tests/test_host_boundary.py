@@ -144,3 +144,22 @@ def test_shard_bounds():
         shard_bounds(10, 4, 0)
     with pytest.raises(ValueError):
         shard_bounds(16, 4, 4)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No CPU fallback: without the built extension the package raises instead of emulating."""
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "liblucid_b200.so"))
+    assert not _lib.is_available()
+    with pytest.raises(lucid_b200.EngineUnavailable):
+        _lib.load()
+    assert not lucid_b200.backends.quantized.available
+
+
+def test_package_never_imports_the_oracle():
+    import subprocess
+    import sys
+
+    code = ("import sys, lucid_b200, lucid_b200.nn.quantized, lucid_b200.quantization;"
+            "assert not any(m == 'oracle' or m.startswith('oracle.') for m in sys.modules)")
+    subprocess.check_call([sys.executable, "-c", code], cwd=ROOT)
