@@ -453,7 +453,7 @@ def run_b200_arm(args):
 
 
 def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
-    """quantize / dequantize / min-max timed as CUDA-graph replays over rotating buffer sets
+    """quantize / dequantize / min-max / histogram timed as CUDA-graph replays over rotating buffer sets
     larger than L2: at config-1 size ((4096, 4096) f32, 6 sets = 480 MB; a 64 MB launch lasts
     10-20 us, so launch ramp and tail weigh in) and at (16384, 16384) (2 sets = 2.5 GB), which
     shows the rate the kernels sustain."""
@@ -461,6 +461,8 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
     ws = _lib.minmax_workspace(dev)
     mn = torch.empty(1, device=dev)
     mx = torch.empty(1, device=dev)
+    hws = _lib.histc_workspace(dev)
+    hist = torch.zeros(2048, device=dev)
 
     def graph_time(fn, sets, reps):
         side = torch.cuda.Stream(dev)
@@ -501,16 +503,24 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
             _lib.check(lib.lq_minmax(_lib.ptr(xs[j]), _lib.F32, 1, n * n, 0, _lib.ptr(mn), _lib.ptr(mx),
                                      _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
 
+        def f_hist(j):
+            # one batch of the histogram observer: bin on a fixed range, measure the batch's
+            # own range, fold the running histogram
+            _lib.check(lib.lq_histc(_lib.ptr(xs[j]), _lib.F32, n * n, -6.0, 6.0, 2048, _lib.ptr(hist), -6.0,
+                                    6.0, _lib.ptr(hist), _lib.ptr(mn), _lib.ptr(mx), _lib.ptr(hws),
+                                    hws.numel(), _lib.stream_ptr(dev)))
+
         block = {}
-        for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("dequantize_s8_f32", f_dequant, 5),
-                              ("minmax_f32", f_minmax, 4)):
+        # dequantize last: it overwrites the normal samples with 255 grid values
+        for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("minmax_f32", f_minmax, 4),
+                              ("histogram_observe_f32", f_hist, 4), ("dequantize_s8_f32", f_dequant, 5)):
             sec = graph_time(fn, sets, reps)
             gbs = n * n * bpe / sec / 1e9
             block[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                            "frac_of_nominal_8000": gbs / 8000.0}
         out[label] = block
         del xs, qs
-    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range)"
+    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range and histogram)"
     return out
 
 

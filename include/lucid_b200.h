@@ -101,6 +101,31 @@ size_t lq_minmax_noalloc_max_elems(void);
 int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* out_min, float* out_max,
                       void* stream);
 
+/* Bytes of workspace lq_histc needs (zero-filled once before its first use; the kernel
+ * leaves it zeroed again), and the largest bin count it accepts. */
+size_t lq_histc_workspace_bytes(void);
+int lq_histc_max_bins(void);
+
+/* One batch of the histogram observer in one pass over x.
+ * Replaces histc (lucid/_C/ops/composite/Stats.cpp:47-91; counting loop
+ * lucid/_C/backend/cpu/CpuBackend.h:13276-13318) and, around it, what
+ * HistogramObserver.forward does per batch (lucid/quantization/observer.py:819-838): the
+ * x.min() / x.max() pair and the fold of the running histogram, re-binned onto the wider range
+ * when the range grew (HistogramObserver._rebin, observer.py:786-817).
+ *   counts[b] = #{ v in x : lo <= v <= hi, b = min(trunc((double(v) - lo) / ((hi - lo) / bins)), bins - 1) }
+ *   hist_out  = float(counts)                                   prev_hist == NULL
+ *             = float(counts) + prev_hist                       prev range == [lo, hi]
+ *             = float(counts) + rebin(prev_hist onto [lo, hi])  otherwise
+ * The bin index is the reference's binary64 expression bit for bit; NaN elements are skipped
+ * (the reference's cast of NaN to an index is undefined).  lo < hi, both finite: a caller
+ * with an empty range derives one from the data first, as the reference's histc does.
+ * x: n contiguous elements (LQ_F32 | LQ_BF16).  hist_out: bins floats; it may be prev_hist.
+ * out_min / out_max: optional (NULL to skip), 1 float each: the min / max of x from the same
+ * pass, so a caller can bin against its current range and learn whether the range held. */
+int lq_histc(const void* x, int in_dtype, size_t n, double lo, double hi, int bins,
+             const float* prev_hist, double prev_lo, double prev_hi, float* hist_out,
+             float* out_min, float* out_max, void* workspace, size_t workspace_bytes, void* stream);
+
 /* (scale, zero_point) from observed ranges, on device.
  * Replaces calculate_qparams (lucid/quantization/_qparams.py:190-215). */
 int lq_calculate_qparams(const float* min_val, const float* max_val, size_t n, int symmetric,

@@ -71,6 +71,11 @@ _SIGNATURES = {
                             C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "lq_minmax_noalloc_max_elems": (C.c_size_t, []),
     "lq_minmax_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_histc_workspace_bytes": (C.c_size_t, []),
+    "lq_histc_max_bins": (C.c_int, []),
+    "lq_histc": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_double, C.c_double, C.c_int,
+                           C.c_void_p, C.c_double, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p,
+                           C.c_void_p, C.c_size_t, C.c_void_p]),
     "lq_calculate_qparams": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
                                        C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                                        C.c_void_p]),
@@ -172,6 +177,19 @@ def minmax_workspace(device: torch.device) -> torch.Tensor:
         n = int(load().lq_minmax_workspace_bytes())
         ws = torch.zeros(n, dtype=torch.uint8, device=device)
         _minmax_ws[key] = ws
+    return ws
+
+
+_hist_ws: dict = {}
+
+
+def histc_workspace(device: torch.device) -> torch.Tensor:
+    """Zero-initialised workspace of ``lq_histc`` for the current (device, stream)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _hist_ws.get(key)
+    if ws is None:
+        ws = torch.zeros(int(load().lq_histc_workspace_bytes()), dtype=torch.uint8, device=device)
+        _hist_ws[key] = ws
     return ws
 
 

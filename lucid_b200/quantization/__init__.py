@@ -1,12 +1,15 @@
 """B200-native drop-in for the hot part of ``lucid.quantization``
 (lucid/quantization/__init__.py:58-65): schemes, grids, qparams, the three
-affine primitives and the min/max observers."""
+affine primitives and the calibration observers."""
 
 from ._functional import (dequantize, fake_quantize, quantize, quantize_dynamic_per_tensor,  # noqa: F401
                           quantize_per_token, quantize_to)
 from ._qparams import QParams, calculate_qparams  # noqa: F401
 from ._qscheme import (QDtype, QScheme, per_channel_affine, per_channel_symmetric,  # noqa: F401
                        per_tensor_affine, per_tensor_symmetric, qint4, qint8, qint32, quint8)
-from .observer import MinMaxObserver, ObserverBase, PerChannelMinMaxObserver, minmax  # noqa: F401
+from .observer import (FixedQParamsObserver, HistogramObserver, MinMaxObserver,  # noqa: F401
+                       MovingAverageMinMaxObserver, MovingAveragePerChannelMinMaxObserver,
+                       NoopObserver, ObserverBase, PerChannelMinMaxObserver, PlaceholderObserver,
+                       histc, minmax)
 from ._quantize import DeQuantStub, QuantStub, convert, prepare, quantize_dynamic  # noqa: F401,E402
 from .qconfig import QConfig, get_default_qconfig  # noqa: F401,E402

@@ -6,7 +6,7 @@ from __future__ import annotations
 from typing import Callable, NamedTuple
 
 from ._qscheme import per_channel_symmetric, per_tensor_affine, qint8, quint8
-from .observer import MinMaxObserver, PerChannelMinMaxObserver
+from .observer import HistogramObserver, PerChannelMinMaxObserver
 
 
 class QConfig(NamedTuple):
@@ -17,13 +17,10 @@ class QConfig(NamedTuple):
 
 
 def get_default_qconfig() -> QConfig:
-    """Per-tensor affine quint8 activations, per-output-channel symmetric qint8 weights.
-
-    The reference's default activation observer is its histogram observer
-    (lucid/quantization/qconfig.py:180-192); this build calibrates activations with the
-    running min/max observer (same scheme and grid, no tail clipping)."""
+    """Per-tensor affine quint8 activations calibrated by the histogram observer,
+    per-output-channel symmetric qint8 weights (lucid/quantization/qconfig.py:180-192)."""
     return QConfig(
-        activation=MinMaxObserver.with_args(qscheme=per_tensor_affine, qdtype=quint8),
+        activation=HistogramObserver.with_args(qscheme=per_tensor_affine, qdtype=quint8),
         weight=PerChannelMinMaxObserver.with_args(ch_axis=0, qscheme=per_channel_symmetric,
                                                   qdtype=qint8),
     )

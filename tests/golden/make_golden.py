@@ -124,6 +124,12 @@ class Tensor:
     def any(self):
         return Tensor(np.asarray(self.a.any()))
 
+    def all(self):
+        return Tensor(np.asarray(self.a.all()))
+
+    def tolist(self):
+        return self.a.tolist()
+
     # -- scalar promotion: a Python number becomes a 0-d constant of the
     #    tensor's dtype when the tensor is floating, else float32 / int64.
     def _other(self, o):
@@ -245,6 +251,45 @@ def isinf(t):
     return Tensor(np.isinf(t.a))
 
 
+def where(c, a, b):
+    return Tensor(np.where(_t(c), _t(a), _t(b)))
+
+
+def arange(n, device=None):
+    return Tensor(np.arange(n, dtype=np.int64))
+
+
+def scatter_add(out, dim, index, src):
+    """Adds ``src[i]`` into ``out[index[i]]``, sources visited in order."""
+    assert dim == 0
+    r = out.a.copy()
+    for i, d in enumerate(index.a.tolist()):
+        r[d] = r[d] + src.a[i]
+    return Tensor(r)
+
+
+def histc(t, bins=100, min=0, max=0):  # noqa: A002
+    """Stand-in for the engine's histc, which is C++ and cannot be executed here: a
+    restatement of lucid/_C/ops/composite/Stats.cpp:47-91 over the counting loop of
+    lucid/_C/backend/cpu/CpuBackend.h:13276-13318, written element by element."""
+    lo, hi = float(min), float(max)
+    flat = t.a.astype(np.float64).ravel()
+    if lo == hi:
+        lo, hi = float(flat.min()), float(flat.max())
+        if lo == hi:
+            hi = lo + 1.0
+    step = (hi - lo) / float(bins)
+    counts = np.zeros(bins, dtype=np.float64)
+    for v in flat.tolist():
+        if v < lo or v > hi:
+            continue
+        b = int((v - lo) / step)
+        if b >= bins:
+            b = bins - 1
+        counts[b] += 1.0
+    return Tensor(counts.astype(t.a.dtype))
+
+
 # -- autograd stand-in (forward only)
 class FunctionCtx:
     def save_for_backward(self, *ts):
@@ -336,6 +381,7 @@ def install(reference_root):
         Tensor=Tensor, tensor=tensor, zeros=zeros, ones=ones, zeros_like=zeros_like,
         full_like=full_like, minimum=minimum, maximum=maximum, abs=_abs, round=_round,
         clip=clip, moveaxis=moveaxis, amin=amin, amax=amax, isinf=isinf, dtype=dtype,
+        where=where, arange=arange, scatter_add=scatter_add, histc=histc,
         device=device, float32=float32, float64=float64, int8=int8, int16=int16,
         int32=int32, int64=int64,
     ).items():
@@ -466,6 +512,49 @@ def generate(reference_root):
     out["pobs_min"], out["pobs_max"] = pobs.min_val.a, pobs.max_val.a
     s_p, z_p = pobs.calculate_qparams()
     out["pobs_scale"], out["pobs_zp"] = s_p.a, z_p.a
+
+    # -- moving-average observers (three batches each)
+    batches = [(np.random.default_rng(30 + i).standard_normal((6, 40)) * (1.0 + 0.7 * i)).astype(F32)
+               for i in range(3)]
+    ma = O.MovingAverageMinMaxObserver(averaging_constant=0.05)
+    mac = O.MovingAveragePerChannelMinMaxObserver(ch_axis=0, averaging_constant=0.05)
+    for i, xb_ in enumerate(batches):
+        out[f"ma_x{i}"] = xb_
+        ma(T(xb_))
+        mac(T(xb_))
+        out[f"ma_min{i}"], out[f"ma_max{i}"] = ma.min_val.a, ma.max_val.a
+        out[f"mac_min{i}"], out[f"mac_max{i}"] = mac.min_val.a, mac.max_val.a
+    s_m, z_m = ma.calculate_qparams()
+    out["ma_scale"], out["ma_zp"] = s_m.a, z_m.a
+    s_m, z_m = mac.calculate_qparams()
+    out["mac_scale"], out["mac_zp"] = s_m.a, z_m.a
+
+    # -- histogram observer: range growth (re-binning), a batch inside the range, a constant
+    #    first batch (the empty-range rule of histc), rectified data, a symmetric signed grid
+    def run_hist(tag, xs, bins, **kw):
+        h = O.HistogramObserver(bins=bins, **kw)
+        for i, xb_ in enumerate(xs):
+            out[f"{tag}_x{i}"] = xb_
+            h(T(xb_))
+            out[f"{tag}_hist{i}"] = h.histogram.a
+            out[f"{tag}_range{i}"] = np.asarray([h.min_val.a, h.max_val.a], dtype=np.float64)
+        out[f"{tag}_clip"] = np.asarray(h._search_clip_range(), dtype=np.float64)
+        s_h, z_h = h.calculate_qparams()
+        out[f"{tag}_scale"], out[f"{tag}_zp"] = s_h.a, z_h.a
+
+    g = np.random.default_rng(40)
+    grow = [g.standard_normal(3000).astype(F32), (g.standard_normal(2500) * 2.5).astype(F32),
+            (g.standard_normal(2000) * 0.5).astype(F32), (g.standard_normal((7, 300)) * 4 + 1).astype(F32)]
+    run_hist("hg", grow, 2048)
+    run_hist("hs", grow[:3], 128, qscheme=S.per_tensor_symmetric, qdtype=S.qint8)
+    const = [np.full(37, 0.75, dtype=F32), g.standard_normal(1500).astype(F32)]
+    run_hist("hc", const, 256)
+    relu = [np.maximum(g.standard_normal(4000), 0).astype(F32),
+            np.maximum(g.standard_normal(4000) * 1.5, 0).astype(F32)]
+    run_hist("hr", relu, 2048)
+    # heavy tails: the clip search has something to cut
+    tails = [np.concatenate([g.standard_normal(20000), [40.0, -35.0]]).astype(F32)]
+    run_hist("ht", tails, 2048)
 
     # -- dynamic Linear: from_float + forward (float GEMM = NumPy f32 matmul)
     rng = np.random.default_rng(11)

@@ -52,6 +52,13 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.lq_minmax(one, 0, 0, 4, 0, one, one, one, 1 << 20, None) == 1  # empty has no range
     assert lib.lq_minmax(one, 0, 4, 4, 0, one, one, one, 8, None) == 6  # workspace too small
     assert lib.lq_conv2d_nhwc_s8(one, 1, one, 1, 8, 8, 16, 16, 3, 3, 2, 1, ctypes.byref(e), one, None, None) == 5
+    hist = (one, 0, 64, 0.0, 1.0, 16, None, 0.0, 0.0, one, None, None, one, 1 << 20, None)
+    assert lib.lq_histc(*hist[:5], lib.lq_histc_max_bins() + 1, *hist[6:]) == 5
+    assert lib.lq_histc(*hist[:3], 1.0, 1.0, *hist[5:]) == 1  # empty range: the caller derives it
+    assert lib.lq_histc(*hist[:3], 0.0, float("inf"), *hist[5:]) == 1
+    assert lib.lq_histc(*hist[:2], 0, *hist[3:]) == 1
+    assert lib.lq_histc(*hist[:13], 64, None) == 6  # workspace too small
+    assert lib.lq_histc_workspace_bytes() >= 8 * lib.lq_histc_max_bins()
 
 
 def test_cpu_tensors_are_rejected_not_emulated():
@@ -64,6 +71,22 @@ def test_cpu_tensors_are_rejected_not_emulated():
         Q.MinMaxObserver()(x)
     with pytest.raises(lucid_b200.DeviceMismatch):
         nnq.dynamic.Linear(16, 8)(x)
+
+
+def test_histogram_clip_search_is_host_logic(golden):
+    """The clip search runs on the host from the histogram alone
+    (lucid/quantization/observer.py:840-870): feed it the reference-made histograms."""
+    for tag, last, bins, qd in (("hg", 3, 2048, Q.quint8), ("hs", 2, 128, Q.qint8),
+                                ("hc", 1, 256, Q.quint8), ("hr", 1, 2048, Q.quint8),
+                                ("ht", 0, 2048, Q.quint8)):
+        obs = Q.HistogramObserver(bins=bins, qdtype=qd)
+        lo, hi = golden[f"{tag}_range{last}"].tolist()
+        obs.load_state_dict({"min_val": torch.tensor(lo), "max_val": torch.tensor(hi),
+                             "histogram": torch.from_numpy(golden[f"{tag}_hist{last}"])})
+        assert list(obs._search_clip_range()) == golden[f"{tag}_clip"].tolist()
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        Q.HistogramObserver()(torch.randn(8))
+    assert isinstance(Q.get_default_qconfig().activation(), Q.HistogramObserver)
 
 
 def test_surface_matches_reference_names():

@@ -193,3 +193,57 @@ def test_int_conv_matches_float_conv_on_codes():
     yf = O.conv2d_f32_nchw(x.transpose(0, 3, 1, 2).astype(np.float32),
                            w.transpose(0, 3, 1, 2).astype(np.float32), None, 1, 1)
     assert np.array_equal(acc, yf.transpose(0, 2, 3, 1).astype(np.int32))
+
+
+def test_moving_average_observers(golden):
+    mn, mx = np.inf, -np.inf
+    cmn = cmx = None
+    for i in range(3):
+        x = golden[f"ma_x{i}"]
+        mn, mx = O.moving_average_minmax_observe(x, mn, mx, c=0.05)
+        assert mn == golden[f"ma_min{i}"] and mx == golden[f"ma_max{i}"]
+        cmn, cmx = O.moving_average_per_channel_observe(x, 0, cmn, cmx, c=0.05)
+        assert np.array_equal(cmn, golden[f"mac_min{i}"])
+        assert np.array_equal(cmx, golden[f"mac_max{i}"])
+    s, z = O.calculate_qparams(mn, mx, False, O.QUINT8)
+    assert s == golden["ma_scale"] and z == golden["ma_zp"]
+    s, z = O.calculate_qparams(cmn, cmx, True, O.QINT8)
+    assert np.array_equal(s, golden["mac_scale"]) and np.array_equal(z, golden["mac_zp"])
+    # lucid/test/unit/quantization/test_observer.py:34-39
+    a = O.moving_average_minmax_observe(np.array([-2.0, 2.0]), np.inf, -np.inf, c=0.5)
+    b = O.moving_average_minmax_observe(np.array([-4.0, 4.0]), *a, c=0.5)
+    assert b == (-3.0, 3.0)
+
+
+HIST_CASES = [("hg", 4, 2048, False, O.QUINT8), ("hs", 3, 128, True, O.QINT8),
+              ("hc", 2, 256, False, O.QUINT8), ("hr", 2, 2048, False, O.QUINT8),
+              ("ht", 1, 2048, False, O.QUINT8)]
+
+
+@pytest.mark.parametrize("tag,batches,bins,sym,qd", HIST_CASES)
+def test_histogram_observer(golden, tag, batches, bins, sym, qd):
+    state = None
+    for i in range(batches):
+        state = O.histogram_observe(golden[f"{tag}_x{i}"], state, bins)
+        assert np.array_equal(state[2], golden[f"{tag}_hist{i}"]), (tag, i)
+        assert [state[0], state[1]] == golden[f"{tag}_range{i}"].tolist()
+    clip = O.histogram_search_clip_range(state[0], state[1], state[2], qd[4] - qd[3])
+    assert list(clip) == golden[f"{tag}_clip"].tolist()
+    s, z = O.histogram_qparams(state[0], state[1], state[2], sym, qd)
+    assert s == golden[f"{tag}_scale"] and z == golden[f"{tag}_zp"]
+
+
+def test_histogram_observer_reference_properties(golden):
+    """The two facts the reference's own tests assert
+    (lucid/test/unit/quantization/test_observer.py:54-77)."""
+    g = np.random.default_rng(0)
+    x = g.standard_normal(2000).astype(np.float32)
+    st = O.histogram_observe(x, None, 256)
+    assert st[2].sum() == 2000
+    data = np.concatenate([g.standard_normal(3000), g.uniform(5.0, 12.0, 150)]).astype(np.float32)
+    st = O.histogram_observe(data, None, 512)
+    s_h, _ = O.histogram_qparams(st[0], st[1], st[2], False, O.QUINT8)
+    s_m, _ = O.calculate_qparams(*O.minmax_observe(data), False, O.QUINT8)
+    assert s_h <= s_m
+    # the heavy-tailed fixture really is clipped
+    assert golden["ht_clip"][1] < golden["ht_range0"][1]
