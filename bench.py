@@ -527,7 +527,7 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
 def run_single_kernel_case(args):
     """Small single-kernel runs for profiler captures: `--case gemm` launches one
     integer GEMM shape (operands larger than L2), `--case streams` the config-1
-    quantize / dequantize / min-max kernels."""
+    quantize / dequantize / min-max / histogram kernels, `--case histc` the histogram kernel."""
     import torch
 
     import lucid_b200.quantization as Q
@@ -539,6 +539,31 @@ def run_single_kernel_case(args):
     peaks = load_peaks()
     if args.case == "streams":
         print(json.dumps({"case": "streams", "streams": bench_streams(torch, Q, _lib, dev, peaks, iters=args.steps)}))
+        return 0
+    if args.case == "histc":
+        # one histogram-observer batch per launch on `--shape N` normal samples (default 2^28)
+        n = int(args.shape) if "," not in args.shape else 1 << 28
+        x = torch.randn(n, device=dev)
+        hist, mm = torch.zeros(2048, device=dev), torch.empty(2, device=dev)
+        hws = _lib.histc_workspace(dev)
+        lib = _lib.load()
+        run = lambda: _lib.check(lib.lq_histc(_lib.ptr(x), _lib.F32, n, -6.0, 6.0, 2048, _lib.ptr(hist), -6.0, 6.0,
+                                              _lib.ptr(hist), mm.data_ptr(), mm.data_ptr() + 4, _lib.ptr(hws),
+                                              hws.numel(), _lib.stream_ptr(dev)))
+        for _ in range(args.warmup):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        inside = int(((x >= -6.0) & (x <= 6.0)).sum())
+        assert float(hist.double().sum()) == (args.warmup + args.steps) * inside
+        print(json.dumps({"case": "histc", "elements": n, "ms": ms, "GB/s": 4 * n / ms / 1e6,
+                          "frac_of_measured_hbm": 4 * n / ms / 1e6 / peaks["hbm_gbs"]}))
         return 0
     m, n, k = (int(v) for v in args.shape.split(","))
     a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev)
@@ -653,8 +678,8 @@ def run_config_cases(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs"])
-    ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm")
+    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs", "histc"])
+    ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm; element count for --case histc")
     ap.add_argument("--epi", default="bf16", choices=["bf16", "u8"], help="epilogue of --case gemm")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -55,6 +55,23 @@ def test_histc_values_on_bin_edges():
         assert np.array_equal(host(Q.histc(dev(x), bins, lo, hi)), O.histc(x, bins, lo, hi)), (lo, hi, bins)
 
 
+def test_histc_low_precision_data_sits_on_edges():
+    """bfloat16 activations and quantized grids put a large share of the elements exactly on
+    bin edges (the quotient is an integer): every one of them needs the exact tie-break."""
+    g = np.random.default_rng(17)
+    xb = dev((g.standard_normal(300_000) * 1.5).astype(F32), torch.bfloat16)
+    xh = host(xb)
+    for lo, hi, bins in [(-5.5, 5.5, 2048), (-4.0, 4.0, 2048), (-8.0, 8.0, 4096), (-3.0, 5.0, 1000)]:
+        want = O.histc(xh, bins, lo, hi)
+        assert np.array_equal(host(Q.histc(xb, bins, lo, hi)), want)
+        assert np.array_equal(host(Q.histc(xb.float(), bins, lo, hi)), want)
+    grid = (g.integers(-128, 128, 200_000) * 0.0625).astype(F32)  # all on edges of [-8, 8] / 2048
+    assert np.array_equal(host(Q.histc(dev(grid), 2048, -8.0, 8.0)), O.histc(grid, 2048, -8.0, 8.0))
+    assert np.array_equal(host(Q.histc(dev(grid), 2048)), O.histc(grid, 2048, 0, 0))
+    third = (g.integers(0, 3000, 100_000) / 3.0).astype(F32)
+    assert np.array_equal(host(Q.histc(dev(third), 1000, 0.0, 1000.0)), O.histc(third, 1000, 0.0, 1000.0))
+
+
 def test_histc_constant_and_rectified():
     x = np.full(1000, 0.75, dtype=F32)
     want = O.histc(x, 64, 0, 0)
