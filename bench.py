@@ -541,13 +541,21 @@ def run_single_kernel_case(args):
         print(json.dumps({"case": "streams", "streams": bench_streams(torch, Q, _lib, dev, peaks, iters=args.steps)}))
         return 0
     if args.case == "histc":
-        # one histogram-observer batch per launch on `--shape N` normal samples (default 2^28)
-        n = int(args.shape) if "," not in args.shape else 1 << 28
+        # one histogram-observer batch per launch on `--shape N` normal samples (default 2^28);
+        # `--shape N,edges`: bfloat16 samples on [-4, 4], where most elements sit exactly on a
+        # bin edge (the step is a power of two) and need the exact tie-break
+        parts = args.shape.split(",")
+        edges = len(parts) == 2 and parts[1] == "edges"
+        n = int(parts[0]) if len(parts) <= 2 else 1 << 28
         x = torch.randn(n, device=dev)
+        lo, hi, code, esz = -6.0, 6.0, _lib.F32, 4
+        if edges:
+            x = x.clamp_(-4.0, 4.0).to(torch.bfloat16)
+            lo, hi, code, esz = -4.0, 4.0, _lib.BF16, 2
         hist, mm = torch.zeros(2048, device=dev), torch.empty(2, device=dev)
         hws = _lib.histc_workspace(dev)
         lib = _lib.load()
-        run = lambda: _lib.check(lib.lq_histc(_lib.ptr(x), _lib.F32, n, -6.0, 6.0, 2048, _lib.ptr(hist), -6.0, 6.0,
+        run = lambda: _lib.check(lib.lq_histc(_lib.ptr(x), code, n, lo, hi, 2048, _lib.ptr(hist), lo, hi,
                                               _lib.ptr(hist), mm.data_ptr(), mm.data_ptr() + 4, _lib.ptr(hws),
                                               hws.numel(), _lib.stream_ptr(dev)))
         for _ in range(args.warmup):
@@ -560,10 +568,11 @@ def run_single_kernel_case(args):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / args.steps
-        inside = int(((x >= -6.0) & (x <= 6.0)).sum())
+        inside = int(((x >= lo) & (x <= hi)).sum())
         assert float(hist.double().sum()) == (args.warmup + args.steps) * inside
-        print(json.dumps({"case": "histc", "elements": n, "ms": ms, "GB/s": 4 * n / ms / 1e6,
-                          "frac_of_measured_hbm": 4 * n / ms / 1e6 / peaks["hbm_gbs"]}))
+        print(json.dumps({"case": "histc", "elements": n, "dtype": "bf16" if edges else "f32", "ms": ms,
+                          "GB/s": esz * n / ms / 1e6, "Gelem/s": n / ms / 1e6,
+                          "frac_of_measured_hbm": esz * n / ms / 1e6 / peaks["hbm_gbs"]}))
         return 0
     m, n, k = (int(v) for v in args.shape.split(","))
     a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev)

@@ -126,6 +126,23 @@ int lq_histc(const void* x, int in_dtype, size_t n, double lo, double hi, int bi
              const float* prev_hist, double prev_lo, double prev_hi, float* hist_out,
              float* out_min, float* out_max, void* workspace, size_t workspace_bytes, void* stream);
 
+/* One step of the histogram observer with its state on the device: two kernel launches, no
+ * host synchronisation.  Replaces HistogramObserver.forward
+ * (lucid/quantization/observer.py:819-838), which reads the batch's min / max and its own
+ * range back to the host every batch.
+ *   min_val, max_val: 1 float each, the running range; (+inf, -inf) before the first batch.
+ *   hist:             bins floats, the running histogram.
+ * The first kernel bins x on the current range while measuring x's own range; if the range
+ * held, it folds the running histogram and the step is complete after one pass over x.
+ * Otherwise (first batch, wider range, constant history) it stores the new range, and the
+ * second kernel -- which returns at once when it is not needed -- bins x on the new range and
+ * folds the running histogram, re-binned from the old range.  Results are those of lq_histc
+ * driven by the reference's host logic, bit for bit.  A batch without a finite value leaves
+ * the state unchanged.  Workspace: as lq_histc (the two may share one, in stream order). */
+int lq_histogram_observe(const void* x, int in_dtype, size_t n, int bins, float* min_val,
+                         float* max_val, float* hist, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
 /* (scale, zero_point) from observed ranges, on device.
  * Replaces calculate_qparams (lucid/quantization/_qparams.py:190-215). */
 int lq_calculate_qparams(const float* min_val, const float* max_val, size_t n, int symmetric,

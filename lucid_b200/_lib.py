@@ -76,6 +76,8 @@ _SIGNATURES = {
     "lq_histc": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_double, C.c_double, C.c_int,
                            C.c_void_p, C.c_double, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p,
                            C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lq_histogram_observe": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "lq_calculate_qparams": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int,
                                        C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                                        C.c_void_p]),

@@ -40,12 +40,20 @@ constexpr int kHistMaxBins = 4096;
 constexpr int kFracBits = 19;
 constexpr unsigned int kFracMask = (1u << kFracBits) - 1u;
 
+// What the first kernel of an observer step leaves for the second (see observe_pass1).
+struct ObserveState {
+  int pass2;  // 1: the batch must be binned again, on [new_lo, new_hi]
+  int mode;   // PrevMode of that second pass
+  double new_lo, new_hi, old_lo, old_hi;
+};
+
 struct HistWorkspace {
   unsigned int ticket;
   unsigned int pad[3];
   float pmin[kHistMaxCtas];
   float pmax[kHistMaxCtas];
   unsigned long long counts[kHistMaxBins];
+  ObserveState observe;
 };
 
 enum PrevMode : int { kPrevNone = 0, kPrevAdd = 1, kPrevRebin = 2 };
@@ -57,6 +65,8 @@ struct HistArgs {
   // bins << f, f, and the fraction mask without its lowest bit
   float rstep32, magic32;
   unsigned int magic_bits, limit32, frac_bits32, frac_hi32;
+  int tier1;
+  float step32;  // the step, when binary32 holds it exactly (else 0): enables the binary32 tie-break
   int bins;
   int prev_mode;
   const float* prev;
@@ -65,6 +75,62 @@ struct HistArgs {
   float* out_min;
   float* out_max;
 };
+
+// Largest float <= d and smallest float >= d.
+__host__ __device__ inline float float_at_most(double d) {
+  const float f = (float)d;
+  return (double)f > d ? nextafterf(f, -INFINITY) : f;
+}
+__host__ __device__ inline float float_at_least(double d) {
+  const float f = (float)d;
+  return (double)f < d ? nextafterf(f, INFINITY) : f;
+}
+
+// Everything the counting loop needs for the finite range lo < hi.  False when the step is
+// not a positive finite number.  Runs on the host (lq_histc) and on the device (the observer
+// kernels read their range from device memory).
+__host__ __device__ inline bool derive_binning(double lo, double hi, int bins, bool allow_tier1, HistArgs& a) {
+  a.bins = bins;
+  a.lo = lo;
+  a.step = (hi - lo) / (double)bins;
+  if (!(a.step > 0.0) || !(a.step < INFINITY)) return false;
+  a.rstep = (a.step > 0x1p-900 && a.step < 0x1p900) ? 1.0 / a.step : 0.0;
+  a.flo = float_at_least(lo);
+  a.fhi = float_at_most(hi);
+  // 2^k >= 2 * bins: the fraction's resolution 2^(k-23) then exceeds the error bound
+  int k = 1;
+  while ((1 << k) < 2 * bins) ++k;
+  // tier 1 needs lo in binary32 and 1 / step, hi - lo well inside its exponent range
+  a.tier1 = allow_tier1 && (double)a.flo == lo && a.step > 0x1p-100 && a.step < 0x1p100 && (hi - lo) < 0x1p100;
+  if (a.tier1) {
+    const float r = (float)(1.0 / a.step);
+    int ex;
+    frexpf(r, &ex);         // r = m * 2^ex, m in [0.5, 1)
+    const int sc = 1 - ex;  // r * 2^sc in [1, 2)
+    a.rstep32 = ldexpf(r, sc);
+    const float pow2k = ldexpf(1.0f, k + sc);
+    a.magic32 = nextafterf(pow2k, INFINITY);
+#ifdef __CUDA_ARCH__
+    a.magic_bits = __float_as_uint(pow2k);
+#else
+    memcpy(&a.magic_bits, &pow2k, sizeof(float));
+#endif
+    a.frac_bits32 = (unsigned int)(23 - k);
+    a.limit32 = (unsigned int)bins << a.frac_bits32;
+    a.frac_hi32 = ((1u << a.frac_bits32) - 1u) & ~1u;
+    a.step32 = (double)(float)a.step == a.step ? (float)a.step : 0.0f;
+  }
+  return true;
+}
+
+// Constants of the re-binning of a histogram on [old_lo, old_hi] onto [lo, lo + bins * step]:
+// binary64 widths rounded to binary32, as the reference's Python scalars enter its tensors.
+__host__ __device__ inline void derive_rebinning(double old_lo, double old_hi, HistArgs& a) {
+  a.old_min = (float)old_lo;
+  a.old_width = (float)((old_hi - old_lo) / (double)a.bins);
+  a.new_min = (float)a.lo;
+  a.new_width = (float)a.step;
+}
 
 __device__ __noinline__ unsigned int bin_by_division(double d, double step, unsigned int last) {
   const double q = __ddiv_rn(d, step);
@@ -103,12 +169,43 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// The CTA's copy of the binning constants and its bins (then 32 spare words).  The counting
+// loop keeps the handful of tier-1 constants in registers; the out-of-line path for open
+// elements reads everything from here, so it costs the loop no registers.
+__shared__ HistArgs s_args;
+extern __shared__ __align__(16) unsigned int s_bins[];
+
+// Tiers 2 and 3 (and the binary32 tie-break) for an element tier 1 left open, or for every
+// element when tier 1 is off.
+__device__ __forceinline__ void place_open_inline(float v) {
+  const HistArgs& a = s_args;
+  if (!(v >= a.flo && v <= a.fhi)) return;  // outside the range, or NaN
+  const unsigned int last = (unsigned int)a.bins - 1u;
+  if (a.tier1 && a.step32 != 0.0f) {
+    // Low-precision data on a binary32 step: when v - lo is exact in binary32 (checked with
+    // the error term of the subtraction), the sign of fma(-n, step, v - lo) decides the edge
+    // exactly, and a nonzero distance to it is far above what binary64 rounding could bridge.
+    const float d = __fsub_rn(v, a.flo);
+    const float bb = __fsub_rn(d, v);
+    const float err = __fadd_rn(__fsub_rn(v, __fsub_rn(d, bb)), __fsub_rn(-a.flo, bb));
+    const unsigned int u = __float_as_uint(__fadd_rz(__fmul_rn(d, a.rstep32), a.magic32)) - a.magic_bits;
+    const unsigned int n = u >> a.frac_bits32;
+    if (err == 0.0f && (u & a.frac_hi32) == 0u && n <= last + 1u) {
+      const unsigned int b = __fmaf_rn(-(float)n, a.step32, d) >= 0.0f ? n : n - 1u;
+      atomicAdd(s_bins + (b < last ? b : last), 1u);
+      return;
+    }
+  }
+  atomicAdd(s_bins + bin_in_binary64(__dsub_rn((double)v, a.lo), a.step, a.rstep, last), 1u);
+}
+
+__device__ __noinline__ void place_open(float v) { place_open_inline(v); }
+
 struct Binner {
-  unsigned int* sh;
-  double lo, step, rstep;
-  float flo, fhi, rstep32, magic32;
+  float flo, rstep32, magic32;
   unsigned int magic_bits, limit, frac_bits, frac_hi;
-  unsigned int last;
+  unsigned int spare;  // this lane's spare word after the bins (one per lane: no two lanes of a
+                       // warp ever collide on it, however many elements are left open)
 
   // Tier 1: true when the element is certainly inside the range; `bin` is then its bin.
   __device__ __forceinline__ bool certain(float v, unsigned int& bin) const {
@@ -135,14 +232,9 @@ struct Binner {
         "@!p or.b32 %1, %1, %8;\n\t"
         "}"
         : "=r"(idx), "+r"(open)
-        : "r"(__float_as_uint(s)), "r"(magic_bits), "r"(frac_hi), "r"(limit), "r"(frac_bits), "r"(last + 1u),
+        : "r"(__float_as_uint(s)), "r"(magic_bits), "r"(frac_hi), "r"(limit), "r"(frac_bits), "r"(spare),
           "r"(bit));
     return idx;
-  }
-  // Tiers 2 and 3 for an element tier 1 left open (or every element when tier 1 is off).
-  __device__ __forceinline__ void place(float v) const {
-    if (v >= flo && v <= fhi)  // false for NaN
-      atomicAdd(sh + bin_in_binary64(__dsub_rn((double)v, lo), step, rstep, last), 1u);
   }
 };
 
@@ -157,21 +249,25 @@ __device__ __forceinline__ void count16(const float (&e)[16], const Binner& b, f
     // unconditional shared atomic per element, no branch around it.
     unsigned int open = 0u;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) atomicAdd(b.sh + b.classify(e[j], open, 1u << j), 1u);
-    if (open) {
-      // each lane walks its own open elements; the copy lets it index them
+    for (int j = 0; j < 16; ++j) atomicAdd(s_bins + b.classify(e[j], open, 1u << j), 1u);
+    // Open elements, one element index at a time for the whole warp: the index runs over the
+    // union of the lanes' masks, so sparse data costs an iteration or two and data that sits on
+    // bin edges keeps the warp together (each lane walking its own mask diverged sixteen ways).
+    const unsigned int lanes = __activemask();
+    unsigned int todo = __reduce_or_sync(lanes, open);
+    if (todo) {
       float again[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) again[j] = e[j];
       do {
-        const int j = __ffs(open) - 1;
-        open &= open - 1u;
-        b.place(again[j]);
-      } while (open);
+        const int j = __ffs(todo) - 1;
+        todo &= todo - 1u;
+        if ((open >> j) & 1u) place_open_inline(again[j]);
+      } while (todo);
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) b.place(e[j]);
+    for (int j = 0; j < 16; ++j) place_open(e[j]);
   }
 }
 template <bool TIER1>
@@ -179,9 +275,9 @@ __device__ __forceinline__ void count1(float v, const Binner& b, float& mn, floa
   mn = fminf(mn, v), mx = fmaxf(mx, v);
   unsigned int bin;
   if (TIER1 && b.certain(v, bin))
-    atomicAdd(b.sh + bin, 1u);
+    atomicAdd(s_bins + bin, 1u);
   else
-    b.place(v);
+    place_open(v);
 }
 
 template <typename In>
@@ -236,8 +332,8 @@ __device__ __forceinline__ void block_minmax_h(float& mn, float& mx) {
   __syncthreads();
 }
 
-// Fold of the previous histogram by the last CTA.  `smem` holds 3 * bins words (during the
-// counting phase: the bins, then the spare word of the branch-free counting).
+// Fold of the previous histogram by the last CTA.  `smem` holds hist_smem_bytes(bins): three
+// arrays of `bins` words here; during the counting phase the bins, then 32 spare words.
 __device__ void finish_histogram(const HistArgs& a, HistWorkspace* ws, unsigned int* smem) {
   const int bins = a.bins;
   float* s_prev = reinterpret_cast<float*>(smem);
@@ -305,16 +401,12 @@ __device__ void finish_histogram(const HistArgs& a, HistWorkspace* ws, unsigned 
   for (int j = threadIdx.x; j < bins; j += kHistThreads) a.out[j] = __fadd_rn(a.out[j], s_acc[j]);
 }
 
+// Counting phase of one CTA: x[0..n) into the shared-memory bins, min / max on the side.
 template <typename In, bool TIER1>
-__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
-histc_kernel(const In* __restrict__ x, size_t n, bool vec_ok, HistArgs a, HistWorkspace* ws) {
-  extern __shared__ __align__(16) unsigned int smem[];
-  for (int j = threadIdx.x; j < a.bins; j += kHistThreads) smem[j] = 0u;
-  __syncthreads();
-
-  const Binner b{smem, a.lo, a.step, a.rstep, a.flo, a.fhi, a.rstep32, a.magic32, a.magic_bits, a.limit32,
-                 a.frac_bits32, a.frac_hi32, (unsigned int)(a.bins - 1)};
-  float mn = INFINITY, mx = -INFINITY;
+__device__ __forceinline__ void count_stream(const In* __restrict__ x, size_t n, bool vec_ok, const HistArgs& a,
+                                             unsigned int* smem, float& mn, float& mx) {
+  const Binner b{a.flo, a.rstep32, a.magic32, a.magic_bits, a.limit32, a.frac_bits32, a.frac_hi32,
+                 (unsigned int)a.bins + (threadIdx.x & 31u)};
   constexpr int E = 16 / sizeof(In);
   constexpr int V = Unpack<In>::kVecs;
   const size_t nvec = vec_ok ? n / E : 0;
@@ -349,9 +441,59 @@ histc_kernel(const In* __restrict__ x, size_t n, bool vec_ok, HistArgs a, HistWo
     for (int j = 0; j < E; ++j) count1<TIER1>(load1<In>(p + j), b, mn, mx);
   }
   for (size_t e1 = nvec * E + first; e1 < n; e1 += stride) count1<TIER1>(load1<In>(x + e1), b, mn, mx);
+}
 
+template <typename In>
+__device__ __forceinline__ void count_cta(const In* __restrict__ x, size_t n, bool vec_ok, const HistArgs& a,
+                                          unsigned int* smem, float& mn, float& mx) {
+  for (int j = threadIdx.x; j < a.bins; j += kHistThreads) smem[j] = 0u;
+  if (threadIdx.x == 0) s_args = a;
+  __syncthreads();
+  if (a.tier1)
+    count_stream<In, true>(x, n, vec_ok, a, smem, mn, mx);
+  else
+    count_stream<In, false>(x, n, vec_ok, a, smem, mn, mx);
+}
+
+// min / max only (the first batch of an observer has no range to bin on yet)
+template <typename In>
+__device__ __forceinline__ void range_stream(const In* __restrict__ x, size_t n, bool vec_ok, float& mn, float& mx) {
+  constexpr int E = 16 / sizeof(In);
+  constexpr int V = Unpack<In>::kVecs;
+  const size_t nvec = vec_ok ? n / E : 0;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const size_t first = (size_t)blockIdx.x * kHistThreads + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * kHistThreads;
+  size_t i = first;
+  for (; i + (V - 1) * stride < nvec; i += V * stride) {
+    uint4 cur[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) cur[j] = ld_stream_u4(xv + i + j * stride);
+    float e[16];
+    Unpack<In>::run(cur, e);
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) mn = min3(mn, e[j], e[j + 1]), mx = max3(mx, e[j], e[j + 1]);
+  }
+  for (; i < nvec; i += stride) {
+    const In* p = x + i * E;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const float v = load1<In>(p + j);
+      mn = fminf(mn, v), mx = fmaxf(mx, v);
+    }
+  }
+  for (size_t e1 = nvec * E + first; e1 < n; e1 += stride) {
+    const float v = load1<In>(x + e1);
+    mn = fminf(mn, v), mx = fmaxf(mx, v);
+  }
+}
+
+// Adds the CTA's bins (if any) to the global counters and takes a ticket.  True in the CTA
+// that took the last one; there mn / mx come back reduced over the whole grid.
+__device__ __forceinline__ bool flush_and_ticket(int bins, const unsigned int* smem, HistWorkspace* ws, float& mn,
+                                                 float& mx) {
   block_minmax_h(mn, mx);  // also orders the shared atomics before the flush
-  for (int j = threadIdx.x; j < a.bins; j += kHistThreads) {
+  for (int j = threadIdx.x; j < bins; j += kHistThreads) {
     const unsigned int v = smem[j];
     if (v) atomicAdd(&ws->counts[j], (unsigned long long)v);
   }
@@ -365,7 +507,7 @@ histc_kernel(const In* __restrict__ x, size_t n, bool vec_ok, HistArgs a, HistWo
     is_last = atomicAdd(&ws->ticket, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  if (!is_last) return;
+  if (!is_last) return false;
   __threadfence();
   mn = INFINITY, mx = -INFINITY;
   for (unsigned int k = threadIdx.x; k < gridDim.x; k += kHistThreads) {
@@ -373,28 +515,159 @@ histc_kernel(const In* __restrict__ x, size_t n, bool vec_ok, HistArgs a, HistWo
     mx = fmaxf(mx, __ldcg(&ws->pmax[k]));
   }
   block_minmax_h(mn, mx);
+  __shared__ float s_range[2];
+  if (threadIdx.x == 0) {
+    s_range[0] = mn, s_range[1] = mx;
+    ws->ticket = 0;
+  }
+  __syncthreads();
+  mn = s_range[0], mx = s_range[1];
+  return true;
+}
+
+template <typename In>
+__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
+histc_kernel(const In* __restrict__ x, size_t n, bool vec_ok, HistArgs a, HistWorkspace* ws) {
+  unsigned int* smem = s_bins;
+  float mn = INFINITY, mx = -INFINITY;
+  count_cta<In>(x, n, vec_ok, a, smem, mn, mx);
+  if (!flush_and_ticket(a.bins, smem, ws, mn, mx)) return;
   if (threadIdx.x == 0) {
     if (a.out_min) *a.out_min = mn;
     if (a.out_max) *a.out_max = mx;
-    ws->ticket = 0;
   }
   finish_histogram(a, ws, smem);
 }
 
-// Largest float <= d and smallest float >= d.
-float float_at_most(double d) {
-  float f = (float)d;
-  return (double)f > d ? nextafterf(f, -INFINITY) : f;
+// ---- the histogram observer's step, with its state on the device ----------------------------
+// HistogramObserver.forward (lucid/quantization/observer.py:819-838) reads the batch's min / max
+// and its own range back to the host to decide how to bin.  Here the decision is taken by the
+// kernels, so a step is two launches and no host synchronisation:
+//   pass 1  bins the batch on the CURRENT range while measuring the batch's own range.  If the
+//           range held (the common case once calibration has seen a few batches) its last CTA
+//           folds the running histogram and the step is done after one pass over the batch.
+//           Otherwise (first batch, range grew, constant history) it records the new range.
+//   pass 2  returns at once unless pass 1 asked for it; else bins on the new range and folds
+//           the running histogram, re-binned from the old range.
+template <typename In>
+__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
+observe_pass1(const In* __restrict__ x, size_t n, bool vec_ok, int bins, bool allow_tier1, float* min_val,
+              float* max_val, float* hist, HistWorkspace* ws) {
+  unsigned int* smem = s_bins;
+  const double lo = (double)__ldcg(min_val), hi = (double)__ldcg(max_val);
+  const bool seeded = lo < INFINITY && hi > -INFINITY;  // the seed is (+inf, -inf)
+  HistArgs a{};
+  const bool speculate = seeded && hi > lo && derive_binning(lo, hi, bins, allow_tier1, a);
+  float mn = INFINITY, mx = -INFINITY;
+  if (speculate)
+    count_cta<In>(x, n, vec_ok, a, smem, mn, mx);
+  else
+    range_stream<In>(x, n, vec_ok, mn, mx);
+  if (!flush_and_ticket(speculate ? bins : 0, smem, ws, mn, mx)) return;
+
+  const double new_lo = seeded ? fmin(lo, (double)mn) : (double)mn;
+  const double new_hi = seeded ? fmax(hi, (double)mx) : (double)mx;
+  const bool grew = !(new_lo == lo && new_hi == hi);
+  if (speculate && !grew) {
+    a.prev_mode = kPrevAdd, a.prev = hist, a.out = hist;
+    finish_histogram(a, ws, smem);
+    if (threadIdx.x == 0) ws->observe.pass2 = 0;
+    return;
+  }
+  if (speculate)  // the speculative counts are void
+    for (int j = threadIdx.x; j < bins; j += kHistThreads) ws->counts[j] = 0ull;
+  if (threadIdx.x == 0) {
+    // a batch without a finite value leaves the state as it was
+    const bool usable = new_lo < INFINITY && new_lo > -INFINITY && new_hi < INFINITY && new_hi > -INFINITY;
+    ws->observe.pass2 = usable ? 1 : 0;
+    ws->observe.mode = !seeded ? kPrevNone : (grew ? kPrevRebin : kPrevAdd);
+    ws->observe.new_lo = new_lo, ws->observe.new_hi = new_hi;
+    ws->observe.old_lo = lo, ws->observe.old_hi = hi;
+    if (usable) *min_val = (float)new_lo, *max_val = (float)new_hi;
+  }
 }
-float float_at_least(double d) {
-  float f = (float)d;
-  return (double)f < d ? nextafterf(f, INFINITY) : f;
+
+template <typename In>
+__global__ void __launch_bounds__(kHistThreads, kHistCtasPerSm)
+observe_pass2(const In* __restrict__ x, size_t n, bool vec_ok, int bins, bool allow_tier1, float* hist,
+              HistWorkspace* ws) {
+  unsigned int* smem = s_bins;
+  if (__ldcg(&ws->observe.pass2) == 0) return;
+  const double lo = __ldcg(&ws->observe.new_lo);
+  double hi = __ldcg(&ws->observe.new_hi);
+  if (!(hi > lo)) hi = lo + 1.0;  // a constant tensor is binned on [v, v + 1] (Stats.cpp:63-72)
+  const int mode = __ldcg(&ws->observe.mode);
+  const double old_lo = __ldcg(&ws->observe.old_lo), old_hi = __ldcg(&ws->observe.old_hi);
+  HistArgs a{};
+  if (!derive_binning(lo, hi, bins, allow_tier1, a)) return;  // uniform over the grid
+  float mn = INFINITY, mx = -INFINITY;
+  count_cta<In>(x, n, vec_ok, a, smem, mn, mx);
+  if (!flush_and_ticket(bins, smem, ws, mn, mx)) return;
+  a.prev_mode = mode, a.prev = hist, a.out = hist;
+  if (mode == kPrevRebin) derive_rebinning(old_lo, old_hi, a);
+  finish_histogram(a, ws, smem);
+  if (threadIdx.x == 0) ws->observe.pass2 = 0;
 }
 
 }  // namespace
 }  // namespace lq
 
 using namespace lq;
+
+namespace {
+size_t hist_smem_bytes(int bins) {
+  const size_t words = (size_t)bins * 3 > (size_t)bins + 32 ? (size_t)bins * 3 : (size_t)bins + 32;
+  return words * sizeof(unsigned int);
+}
+// four 16-byte vectors per thread and iteration; grid capped at the resident CTA count
+int hist_grid(size_t n, size_t esz) {
+  const size_t per_cta = (size_t)kHistThreads * 4 * (16 / esz);
+  const size_t want = (n + per_cta - 1) / per_cta;
+  return (int)(want < 1 ? 1 : (want > (size_t)kHistMaxCtas ? (size_t)kHistMaxCtas : want));
+}
+int check_hist_common(const char* who, const void* x, size_t n, int in_dtype, int bins, const void* workspace,
+                      size_t workspace_bytes) {
+  const std::string w(who);
+  if (!x) return fail(LQ_ERR_DEVICE, w + ": null pointer");
+  if (n == 0) return fail(LQ_ERR_SHAPE, w + ": empty input");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, w + ": in_dtype");
+  if (bins < 1 || bins > kHistMaxBins)
+    return fail(LQ_ERR_UNSUPPORTED, w + ": bins must be in [1, " + std::to_string(kHistMaxBins) + "]");
+  if (!workspace) return fail(LQ_ERR_DEVICE, w + ": workspace");
+  if (workspace_bytes < sizeof(HistWorkspace))
+    return fail(LQ_ERR_WORKSPACE, w + ": workspace smaller than lq_histc_workspace_bytes()");
+  if (!aligned16(workspace)) return fail(LQ_ERR_ALIGNMENT, w + ": workspace alignment");
+  return LQ_OK;
+}
+}  // namespace
+
+extern "C" int lq_histogram_observe(const void* x, int in_dtype, size_t n, int bins, float* min_val,
+                                    float* max_val, float* hist, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  if (int rc = check_hist_common("lq_histogram_observe", x, n, in_dtype, bins, workspace, workspace_bytes)) return rc;
+  if (!min_val || !max_val || !hist) return fail(LQ_ERR_DEVICE, "lq_histogram_observe: null state pointer");
+  const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
+  const bool vec_ok = aligned16(x);
+  const bool allow_tier1 = !getenv("LQ_HIST_BINARY64");
+  const int grid = hist_grid(n, esz);
+  const size_t smem = hist_smem_bytes(bins);
+  auto* ws = (HistWorkspace*)workspace;
+  cudaStream_t st = (cudaStream_t)stream;
+  auto launch = [&](auto k1, auto k2, auto ptr) -> int {
+    if (smem > 40 * 1024) {  // static shared memory included, this passes the 48 KB default
+      LQ_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      LQ_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    k1<<<grid, kHistThreads, smem, st>>>(ptr, n, vec_ok, bins, allow_tier1, min_val, max_val, hist, ws);
+    k2<<<grid, kHistThreads, smem, st>>>(ptr, n, vec_ok, bins, allow_tier1, hist, ws);
+    return LQ_OK;
+  };
+  const int rc = in_dtype == LQ_F32
+                     ? launch(observe_pass1<float>, observe_pass2<float>, (const float*)x)
+                     : launch(observe_pass1<__nv_bfloat16>, observe_pass2<__nv_bfloat16>, (const __nv_bfloat16*)x);
+  if (rc != LQ_OK) return rc;
+  return check_cuda(cudaGetLastError(), "lq_histogram_observe launch");
+}
 
 extern "C" size_t lq_histc_workspace_bytes(void) { return sizeof(HistWorkspace); }
 extern "C" int lq_histc_max_bins(void) { return kHistMaxBins; }
@@ -403,47 +676,15 @@ extern "C" int lq_histc(const void* x, int in_dtype, size_t n, double lo, double
                         const float* prev_hist, double prev_lo, double prev_hi, float* hist_out,
                         float* out_min, float* out_max, void* workspace, size_t workspace_bytes,
                         void* stream) {
-  if (!x || !hist_out) return fail(LQ_ERR_DEVICE, "lq_histc: null pointer");
-  if (n == 0) return fail(LQ_ERR_SHAPE, "lq_histc: empty input");
-  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_histc: in_dtype");
-  if (bins < 1 || bins > kHistMaxBins)
-    return fail(LQ_ERR_UNSUPPORTED, "lq_histc: bins must be in [1, " + std::to_string(kHistMaxBins) + "]");
+  if (int rc = check_hist_common("lq_histc", x, n, in_dtype, bins, workspace, workspace_bytes)) return rc;
+  if (!hist_out) return fail(LQ_ERR_DEVICE, "lq_histc: null pointer");
   if (!(hi > lo) || !isfinite(lo) || !isfinite(hi))
     return fail(LQ_ERR_SHAPE, "lq_histc: the range must be finite with lo < hi (the caller derives an empty "
                               "range from the data, as the reference's histc does)");
-  if (!workspace) return fail(LQ_ERR_DEVICE, "lq_histc: workspace");
-  if (workspace_bytes < sizeof(HistWorkspace))
-    return fail(LQ_ERR_WORKSPACE, "lq_histc: workspace smaller than lq_histc_workspace_bytes()");
-  if (!aligned16(workspace)) return fail(LQ_ERR_ALIGNMENT, "lq_histc: workspace alignment");
 
   HistArgs a{};
-  a.lo = lo;
-  a.step = (hi - lo) / (double)bins;
-  if (!(a.step > 0.0) || !isfinite(a.step))
+  if (!derive_binning(lo, hi, bins, !getenv("LQ_HIST_BINARY64"), a))
     return fail(LQ_ERR_SHAPE, "lq_histc: (hi - lo) / bins is not a positive finite number");
-  a.rstep = (a.step > 0x1p-900 && a.step < 0x1p900) ? 1.0 / a.step : 0.0;
-  a.flo = float_at_least(lo);
-  a.fhi = float_at_most(hi);
-  // tier 1 needs lo in binary32 and 1 / step, hi - lo well inside its exponent range
-  // 2^k >= 2 * bins: the fraction's resolution 2^(k-23) then exceeds the error bound
-  int k = 1;
-  while ((1 << k) < 2 * bins) ++k;
-  const bool tier1 = (double)a.flo == lo && a.step > 0x1p-100 && a.step < 0x1p100 && (hi - lo) < 0x1p100 &&
-                     !getenv("LQ_HIST_BINARY64");
-  if (tier1) {
-    const float r = (float)(1.0 / a.step);
-    int ex;
-    frexpf(r, &ex);               // r = m * 2^ex, m in [0.5, 1)
-    const int sc = 1 - ex;        // r * 2^sc in [1, 2)
-    a.rstep32 = ldexpf(r, sc);
-    const float pow2k = ldexpf(1.0f, k + sc);
-    a.magic32 = nextafterf(pow2k, INFINITY);
-    memcpy(&a.magic_bits, &pow2k, sizeof(float));
-    a.frac_bits32 = (unsigned int)(23 - k);
-    a.limit32 = (unsigned int)bins << a.frac_bits32;
-    a.frac_hi32 = ((1u << a.frac_bits32) - 1u) & ~1u;
-  }
-  a.bins = bins;
   a.prev = prev_hist;
   a.out = hist_out;
   a.out_min = out_min;
@@ -454,31 +695,21 @@ extern "C" int lq_histc(const void* x, int in_dtype, size_t n, double lo, double
     a.prev_mode = kPrevAdd;
   } else {
     a.prev_mode = kPrevRebin;
-    a.old_min = (float)prev_lo;
-    a.old_width = (float)((prev_hi - prev_lo) / (double)bins);
-    a.new_min = (float)lo;
-    a.new_width = (float)a.step;
+    derive_rebinning(prev_lo, prev_hi, a);
   }
 
   const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
   const bool vec_ok = aligned16(x);
-  // four 16-byte vectors per thread and iteration; grid capped at the resident CTA count
-  const size_t per_cta = (size_t)kHistThreads * 4 * (16 / esz);
-  size_t want = (n + per_cta - 1) / per_cta;
-  const int grid = (int)(want < 1 ? 1 : (want > (size_t)kHistMaxCtas ? (size_t)kHistMaxCtas : want));
-  const size_t smem = (size_t)bins * 3 * sizeof(unsigned int);
+  const int grid = hist_grid(n, esz);
+  const size_t smem = hist_smem_bytes(bins);
   auto launch = [&](auto kernel, auto ptr) -> int {
     if (smem > 40 * 1024)  // static shared memory included, this passes the 48 KB default
       LQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<grid, kHistThreads, smem, (cudaStream_t)stream>>>(ptr, n, vec_ok, a, (HistWorkspace*)workspace);
     return LQ_OK;
   };
-  int rc;
-  if (in_dtype == LQ_F32)
-    rc = tier1 ? launch(histc_kernel<float, true>, (const float*)x) : launch(histc_kernel<float, false>, (const float*)x);
-  else
-    rc = tier1 ? launch(histc_kernel<__nv_bfloat16, true>, (const __nv_bfloat16*)x)
-               : launch(histc_kernel<__nv_bfloat16, false>, (const __nv_bfloat16*)x);
+  const int rc = in_dtype == LQ_F32 ? launch(histc_kernel<float>, (const float*)x)
+                                    : launch(histc_kernel<__nv_bfloat16>, (const __nv_bfloat16*)x);
   if (rc != LQ_OK) return rc;
   return check_cuda(cudaGetLastError(), "lq_histc launch");
 }

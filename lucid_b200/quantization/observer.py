@@ -250,8 +250,10 @@ class HistogramObserver(ObserverBase):
     """Running histogram of the observed values; the quantization range is the tail clip
     with the smallest clip + rounding L2 error (lucid/quantization/observer.py:773-880).
 
-    The range is host state, as in the reference (which reads it back every batch); the
-    ``min_val`` / ``max_val`` buffers mirror it for ``state_dict`` compatibility."""
+    The state (``min_val``, ``max_val``, ``histogram``) lives on the device and a step is two
+    kernel launches with no host synchronisation: the batch is binned on the current range
+    while its own range is measured, and binned again only if the range grew (the reference
+    reads both ranges back to the host every batch and makes three passes)."""
 
     _CLIP_FRACTIONS = (0.0, 1e-5, 1e-4, 1e-3, 5e-3, 1e-2)
 
@@ -262,48 +264,25 @@ class HistogramObserver(ObserverBase):
         self.register_buffer("min_val", torch.tensor(float("inf")))
         self.register_buffer("max_val", torch.tensor(float("-inf")))
         self.register_buffer("histogram", torch.zeros(bins))
-        self._range = None
-
-    def _load_from_state_dict(self, *args, **kwargs):
-        super()._load_from_state_dict(*args, **kwargs)
-        self._range = None
 
     def _host_range(self):
-        if self._range is None:
-            self._range = (float(self.min_val), float(self.max_val))
-        return self._range
-
-    def _set_range(self, lo, hi):
-        self.min_val = torch.tensor(float(lo))
-        self.max_val = torch.tensor(float(hi))
-        self._range = (float(self.min_val), float(self.max_val))  # rounded to binary32
+        return float(self.min_val), float(self.max_val)
 
     def forward(self, x):
         xc = _check_observed(x)
-        old_min, old_max = self._host_range()
-        bins = self.bins
-        if old_min == float("inf"):
-            new_min, new_max = _range_of(xc)
-            hist = _histc_launch(xc, bins, new_min, new_max if new_max > new_min else new_min + 1.0)[0]
-        else:
-            prev = self.histogram.to(xc.device)
-            if old_max > old_min:
-                # Bin against the current range while measuring this batch's own range.
-                hist, mm = _histc_launch(xc, bins, old_min, old_max, prev=prev, want_range=True)
-                cur_min, cur_max = mm.tolist()
-            else:
-                hist = None
-                cur_min, cur_max = _range_of(xc)
-            new_min, new_max = min(old_min, cur_min), max(old_max, cur_max)
-            grew = not (new_min == old_min and new_max == old_max)
-            if grew:
-                hist = _histc_launch(xc, bins, new_min, new_max, prev=prev,
-                                     prev_range=(old_min, old_max))[0]
-            elif hist is None:
-                # a constant history observed again: the reference bins on [v, v + 1]
-                hist = _histc_launch(xc, bins, new_min, new_min + 1.0, prev=prev)[0]
-        self._set_range(new_min, new_max)
-        self.histogram = hist
+        dev = xc.device
+        if self.histogram.device != dev or self.min_val.device != dev or self.max_val.device != dev:
+            self.to(dev)
+        for name in ("min_val", "max_val", "histogram"):
+            t = getattr(self, name)
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                setattr(self, name, t.to(torch.float32).contiguous())
+        with torch.cuda.device(dev):
+            ws = _lib.histc_workspace(dev)
+            _lib.check(_lib.load().lq_histogram_observe(
+                _lib.ptr(xc), _lib.code_of(xc.dtype), xc.numel(), int(self.bins),
+                _lib.ptr(self.min_val), _lib.ptr(self.max_val), _lib.ptr(self.histogram),
+                _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
         return x
 
     def _search_clip_range(self):

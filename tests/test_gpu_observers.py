@@ -141,6 +141,46 @@ def test_histogram_observer_long_run_against_oracle():
     assert s.item() == so and z.item() == zo
 
 
+def test_histogram_observer_step_is_asynchronous_and_capturable():
+    """A step never reads anything back: three steps captured in a CUDA graph (range held,
+    range grew, range held again) replay to the oracle's state."""
+    g = np.random.default_rng(23)
+    xs = [(g.standard_normal(30_000) * s).astype(F32) for s in (1.0, 0.5, 2.0, 0.7)]
+    obs = Q.HistogramObserver()
+    obs(dev(xs[0]))  # seeds the state and allocates the workspace
+    state = O.histogram_observe(xs[0], None, 2048)
+    bufs = [dev(x) for x in xs[1:]]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for b in bufs:
+                obs(b)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    for x in xs[1:]:
+        state = O.histogram_observe(x, state, 2048)
+    assert np.array_equal(host(obs.histogram), state[2])
+    assert (float(obs.min_val), float(obs.max_val)) == (state[0], state[1])
+
+
+def test_histogram_observer_ignores_batches_without_finite_values():
+    obs = Q.HistogramObserver(bins=64)
+    x = torch.randn(1000, device="cuda")
+    obs(x)
+    before = (obs.histogram.clone(), float(obs.min_val), float(obs.max_val))
+    obs(torch.full((50,), float("nan"), device="cuda"))
+    assert torch.equal(obs.histogram, before[0])
+    assert (float(obs.min_val), float(obs.max_val)) == before[1:]
+    fresh = Q.HistogramObserver(bins=64)
+    fresh(torch.full((50,), float("nan"), device="cuda"))
+    assert float(fresh.min_val) == float("inf") and fresh.histogram.sum().item() == 0
+    fresh(x)
+    assert torch.equal(fresh.histogram, before[0])
+
+
 def test_histogram_observer_state_dict_round_trip():
     g = np.random.default_rng(22)
     a, b = Q.HistogramObserver(bins=512), Q.HistogramObserver(bins=512)

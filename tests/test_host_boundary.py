@@ -59,6 +59,9 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.lq_histc(*hist[:2], 0, *hist[3:]) == 1
     assert lib.lq_histc(*hist[:13], 64, None) == 6  # workspace too small
     assert lib.lq_histc_workspace_bytes() >= 8 * lib.lq_histc_max_bins()
+    assert lib.lq_histogram_observe(one, 0, 64, 16, None, one, one, one, 1 << 20, None) == 3
+    assert lib.lq_histogram_observe(one, 0, 64, 0, one, one, one, one, 1 << 20, None) == 5
+    assert lib.lq_histogram_observe(one, 9, 64, 16, one, one, one, one, 1 << 20, None) == 2
 
 
 def test_cpu_tensors_are_rejected_not_emulated():
