@@ -490,6 +490,15 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
     for label, n, sets, reps in (("config1_4096x4096", 4096, 6, iters), ("large_16384x16384", 16384, 2, max(iters // 4, 5))):
         xs = [torch.randn(n, n, device=dev) for _ in range(sets)]
         qs = [torch.empty(n, n, dtype=torch.int8, device=dev) for _ in range(sets)]
+        q2 = [torch.empty(n, n, dtype=torch.int8, device=dev) for _ in range(2)]
+        sc = [torch.tensor(v, device=dev) for v in (0.03, 0.0, 0.05)]
+        table = torch.arange(255, -1, -1, device=dev, dtype=torch.int32).to(torch.uint8)
+        allb = torch.arange(256, device=dev, dtype=torch.int32).to(torch.uint8).view(torch.int8)
+        bx, by = allb.repeat_interleave(256).contiguous(), allb.repeat(256).contiguous()
+        table2 = torch.empty(65536, dtype=torch.int8, device=dev)
+        _lib.check(lib.lq_qmerge(_lib.MERGE_ADD_RELU, _lib.ptr(bx), _lib.S8, _lib.ptr(sc[0]), _lib.ptr(sc[1]),
+                                 _lib.ptr(by), _lib.S8, _lib.ptr(sc[0]), _lib.ptr(sc[1]), 0.0, 65536, _lib.ptr(sc[2]),
+                                 _lib.ptr(sc[1]), -128, 127, _lib.ptr(table2), _lib.S8, None, _lib.stream_ptr(dev)))
 
         def f_quant(j):
             _lib.check(lib.lq_quantize(_lib.ptr(xs[j]), _lib.F32, n, n, None, None, 0.03, 0.0, 0, -127,
@@ -510,17 +519,36 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
                                     6.0, _lib.ptr(hist), _lib.ptr(mn), _lib.ptr(mx), _lib.ptr(hws),
                                     hws.numel(), _lib.stream_ptr(dev)))
 
+        def f_merge(j):
+            # residual add + ReLU + requantize on 8-bit codes (QFunctional.add_relu), codes out
+            k = (j + 1) % sets
+            _lib.check(lib.lq_qmerge(_lib.MERGE_ADD_RELU, _lib.ptr(qs[j]), _lib.S8, _lib.ptr(sc[0]), _lib.ptr(sc[1]),
+                                     _lib.ptr(qs[k]), _lib.S8, _lib.ptr(sc[0]), _lib.ptr(sc[1]), 0.0, n * n,
+                                     _lib.ptr(sc[2]), _lib.ptr(sc[1]), -128, 127, _lib.ptr(q2[j % 2]), _lib.S8, None,
+                                     _lib.stream_ptr(dev)))
+
+        def f_merge_table(j):
+            # the same merge streamed through its 64 KB table (what QFunctional does on code tensors)
+            k = (j + 1) % sets
+            _lib.check(lib.lq_lut2_u8(_lib.ptr(qs[j]), _lib.ptr(qs[k]), n * n, _lib.ptr(table2), _lib.ptr(q2[j % 2]),
+                                      None, None, None, 1, _lib.stream_ptr(dev)))
+
+        def f_lut(j):
+            # a quantized activation on 8-bit codes: one table lookup per byte
+            _lib.check(lib.lq_lut_u8(_lib.ptr(qs[j]), n * n, _lib.ptr(table), _lib.ptr(q2[j % 2]), _lib.stream_ptr(dev)))
+
         block = {}
         # dequantize last: it overwrites the normal samples with 255 grid values
         for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("minmax_f32", f_minmax, 4),
-                              ("histogram_observe_f32", f_hist, 4), ("dequantize_s8_f32", f_dequant, 5)):
+                              ("histogram_observe_f32", f_hist, 4), ("qmerge_add_relu_s8", f_merge, 3),
+                              ("qmerge_add_relu_s8_table", f_merge_table, 3), ("lut_activation_u8", f_lut, 2), ("dequantize_s8_f32", f_dequant, 5)):
             sec = graph_time(fn, sets, reps)
             gbs = n * n * bpe / sec / 1e9
             block[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                            "frac_of_nominal_8000": gbs / 8000.0}
         out[label] = block
-        del xs, qs
-    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range and histogram)"
+        del xs, qs, q2
+    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range and histogram, 3 B/elem code merge, 2 B/elem table lookup)"
     return out
 
 

@@ -265,6 +265,44 @@ int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, si
                       size_t C, size_t K, size_t R, size_t S, size_t stride, size_t pad,
                       const lq_epilogue_t* ep, void* out, int32_t* status, void* stream);
 
+/* ---- element-wise ops of the quantized region ----------------------------------------- */
+
+enum lq_merge_op {
+  LQ_MERGE_ADD = 0,      /* x + y        QFunctional.add / add_scalar                       */
+  LQ_MERGE_MUL = 1,      /* x * y        QFunctional.mul / mul_scalar                       */
+  LQ_MERGE_ADD_RELU = 2, /* relu(x + y)  QFunctional.add_relu                               */
+  LQ_MERGE_COPY = 3      /* x            each piece of QFunctional.cat; a requantization    */
+};
+
+/* out = fake_quantize(op(x, y)) on the grid (out_scale, out_zp, qmin, qmax): the merges of
+ * QFunctional (lucid/nn/quantized/functional_module.py:230-258), in one pass.
+ * An operand is either values (LQ_F32 | LQ_BF16; scale / zero_point NULL) or codes
+ * (LQ_S8 | LQ_U8 | LQ_S16 with its per-tensor device scale / zero_point), which are dequantized
+ * in registers exactly as lq_dequantize would ((q - z) * s).  y == NULL selects the scalar
+ * operand y_scalar.  The arithmetic is the reference's float32 sequence: op, relu, then
+ * clip(rint(t / S) + Z).  Outputs, either or both: out_codes (codes_dtype LQ_S8 | LQ_U8 |
+ * LQ_S16) and out_f32 = (code - Z) * S, the tensor the reference returns.  n elements. */
+int lq_qmerge(int op, const void* x, int x_dtype, const float* x_scale, const float* x_zp,
+              const void* y, int y_dtype, const float* y_scale, const float* y_zp, float y_scalar,
+              size_t n, const float* out_scale, const float* out_zp, int qmin, int qmax,
+              void* out_codes, int codes_dtype, float* out_f32, void* stream);
+
+/* out[i] = table[in[i]] over n bytes; `table` is 256 bytes on the device.  The quantized
+ * activations (lucid/nn/quantized/activation.py:22-60: float activation, then fake_quantize)
+ * applied to 8-bit codes are a function of one byte, so the caller evaluates
+ * encode(act(decode(c))) for the 256 codes once and streams the tensor through the table. */
+int lq_lut_u8(const void* in_codes, size_t n, const uint8_t* table, void* out_codes, void* stream);
+
+/* out[i] = table[x[i] * 256 + y[i]] over n byte pairs; `table` is 65536 bytes on the device
+ * (16-byte aligned), held in shared memory by every CTA.  A QFunctional merge of two tensors of
+ * 8-bit codes is a function of two bytes: the caller runs lq_qmerge once over the 65536 code
+ * pairs of its grids and streams the tensors through the result, which is bit-identical to
+ * lq_qmerge by construction and costs one shared load per element instead of an IEEE division.
+ * out_f32 (optional): (code - out_zp) * out_scale, the code read as int8 when out_signed. */
+int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, const uint8_t* table,
+               void* out_codes, float* out_f32, const float* out_scale, const float* out_zp,
+               int out_signed, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,6 +20,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "liblucid_b200.so")
 F32, BF16, S8, U8, S16, S32 = 0, 1, 2, 3, 4, 5
 PER_TENSOR, PER_ROW, PER_COL = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_SILU_GATE = 0, 1, 2
+MERGE_ADD, MERGE_MUL, MERGE_ADD_RELU, MERGE_COPY = 0, 1, 2, 3
 ERR_TIMEOUT = 8
 
 _TORCH_CODE = {
@@ -95,6 +96,12 @@ _SIGNATURES = {
                                    C.c_void_p, C.c_void_p]),
     "lq_quantize_per_token": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int,
                                         C.c_int, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_qmerge": (C.c_int, [C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                            C.c_void_p, C.c_void_p, C.c_float, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
+                            C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "lq_lut2_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                             C.c_void_p, C.c_int, C.c_void_p]),
+    "lq_lut_u8": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lq_gemm_s8": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                              C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "lq_gemm_s8_bcast": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,

@@ -1243,3 +1243,261 @@ extern "C" int lq_quantize_dynamic(const void* x, int in_dtype, size_t rows, siz
   return lq_quantize(x, in_dtype, rows, cols, out_scale, out_zp, 0.0f, 0.0f, LQ_PER_TENSOR, qmin, qmax, out,
                      out_dtype, stream);
 }
+
+// ---- element-wise merges and table-driven activations of the quantized region -------------------
+// QFunctional (lucid/nn/quantized/functional_module.py:230-258) snaps x + y, x * y, relu(x + y),
+// x + c, x * c or x itself (the pieces of a cat) to one calibrated grid.  The reference does it on
+// float32 tensors that carry int8 numerics (three passes: the op, the activation, fake_quantize);
+// here the operands may arrive as their 8-bit codes (1 byte per element instead of 4), the
+// dequantize / op / activation / encode chain runs in registers with the reference's float32
+// operation order, and the result leaves as codes, as the fake-quantized float32, or both.
+namespace lq {
+
+struct MergeOperand {
+  const void* p;   // nullptr: the scalar
+  int dtype;
+  const float* s;  // nullptr: p holds values, not codes
+  const float* z;
+  float scalar;
+};
+
+__device__ __forceinline__ void merge_load4(const MergeOperand& o, size_t e, float (&v)[4]) {
+  switch (o.dtype) {
+    case LQ_F32: Quad<float>::load((const float*)o.p + e, v); break;
+    case LQ_BF16: Quad<__nv_bfloat16>::load((const __nv_bfloat16*)o.p + e, v); break;
+    case LQ_S8: Quad<int8_t>::load((const int8_t*)o.p + e, v); break;
+    case LQ_U8: Quad<uint8_t>::load((const uint8_t*)o.p + e, v); break;
+    default: Quad<int16_t>::load((const int16_t*)o.p + e, v); break;
+  }
+}
+__device__ __forceinline__ float merge_load1(const MergeOperand& o, size_t e) {
+  switch (o.dtype) {
+    case LQ_F32: return ((const float*)o.p)[e];
+    case LQ_BF16: return __bfloat162float(((const __nv_bfloat16*)o.p)[e]);
+    case LQ_S8: return (float)((const int8_t*)o.p)[e];
+    case LQ_U8: return (float)((const uint8_t*)o.p)[e];
+    default: return (float)((const int16_t*)o.p)[e];
+  }
+}
+__device__ __forceinline__ float merge_op(int op, float a, float b) {
+  switch (op) {
+    case LQ_MERGE_ADD: return __fadd_rn(a, b);
+    case LQ_MERGE_MUL: return __fmul_rn(a, b);
+    case LQ_MERGE_ADD_RELU: {
+      const float t = __fadd_rn(a, b);
+      return t > 0.0f ? t : 0.0f;
+    }
+    default: return a;  // LQ_MERGE_COPY
+  }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads, 4)
+merge_kernel(int op, MergeOperand x, MergeOperand y, size_t n, const float* __restrict__ out_scale,
+             const float* __restrict__ out_zp, float qmin, float qmax, void* __restrict__ codes, int codes_dtype,
+             float* __restrict__ out_f32) {
+  const float S = __ldg(out_scale), Z = __ldg(out_zp);
+  const Divisor d = make_divisor(S);
+  const float sx = x.s ? __ldg(x.s) : 1.0f, zx = x.s ? __ldg(x.z) : 0.0f;
+  const float sy = y.s ? __ldg(y.s) : 1.0f, zy = y.s ? __ldg(y.z) : 0.0f;
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  const size_t first = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (VEC) {
+    for (size_t g = first; g < n / 4; g += stride) {
+      float a[4], b[4], t[4], c[4];
+      merge_load4(x, g * 4, a);
+      if (y.p) merge_load4(y, g * 4, b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (x.s) a[i] = __fmul_rn(__fsub_rn(a[i], zx), sx);
+        if (!y.p) b[i] = y.scalar;
+        else if (y.s) b[i] = __fmul_rn(__fsub_rn(b[i], zy), sy);
+        t[i] = merge_op(op, a[i], b[i]);
+      }
+      code4_f32(t, d, Z, qmin, qmax, c);
+      if (codes) {
+        if (codes_dtype == LQ_S8) Quad<int8_t>::store((int8_t*)codes + g * 4, c);
+        else if (codes_dtype == LQ_U8) Quad<uint8_t>::store((uint8_t*)codes + g * 4, c);
+        else Quad<int16_t>::store((int16_t*)codes + g * 4, c);
+      }
+      if (out_f32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[i] = __fmul_rn(__fsub_rn(c[i], Z), S);
+        Quad<float>::store(out_f32 + g * 4, c);
+      }
+    }
+  }
+  for (size_t e = (VEC ? (n / 4) * 4 : 0) + first; e < n; e += stride) {
+    float a = merge_load1(x, e);
+    if (x.s) a = __fmul_rn(__fsub_rn(a, zx), sx);
+    float b = y.scalar;
+    if (y.p) {
+      b = merge_load1(y, e);
+      if (y.s) b = __fmul_rn(__fsub_rn(b, zy), sy);
+    }
+    const float c = code_f32(merge_op(op, a, b), d, Z, qmin, qmax);
+    if (codes) {
+      if (codes_dtype == LQ_S8) ((int8_t*)codes)[e] = (int8_t)(int)c;
+      else if (codes_dtype == LQ_U8) ((uint8_t*)codes)[e] = (uint8_t)(int)c;
+      else ((int16_t*)codes)[e] = (int16_t)(int)c;
+    }
+    if (out_f32) out_f32[e] = __fmul_rn(__fsub_rn(c, Z), S);
+  }
+}
+
+// out[i] = table[in[i]]: a unary function of 8-bit codes is 256 bytes of table.  16 codes per
+// 16-byte load, looked up in a shared-memory copy of the table.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+lut_kernel(const uint8_t* __restrict__ in, size_t n, const uint8_t* __restrict__ table, uint8_t* __restrict__ out) {
+  __shared__ __align__(16) uint8_t t[256];
+  t[threadIdx.x] = table[threadIdx.x];  // kThreads == 256
+  __syncthreads();
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  const size_t first = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (VEC) {
+    for (size_t g = first; g < n / 16; g += stride) {
+      const uint4 u = ld_stream_u4(in + g * 16);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      uint32_t r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        r[j] = (uint32_t)t[w[j] & 0xffu] | ((uint32_t)t[(w[j] >> 8) & 0xffu] << 8) |
+               ((uint32_t)t[(w[j] >> 16) & 0xffu] << 16) | ((uint32_t)t[w[j] >> 24] << 24);
+      st_stream_u4(out + g * 16, make_uint4(r[0], r[1], r[2], r[3]));
+    }
+  }
+  for (size_t e = (VEC ? (n / 16) * 16 : 0) + first; e < n; e += stride) out[e] = t[in[e]];
+}
+
+static bool merge_dtype_ok(int dt, bool codes) {
+  return codes ? (dt == LQ_S8 || dt == LQ_U8 || dt == LQ_S16) : (dt == LQ_F32 || dt == LQ_BF16);
+}
+static size_t merge_elem_size(int dt) { return dt == LQ_F32 ? 4 : (dt == LQ_BF16 || dt == LQ_S16) ? 2 : 1; }
+
+}  // namespace lq
+
+extern "C" int lq_qmerge(int op, const void* x, int x_dtype, const float* x_scale, const float* x_zp,
+                         const void* y, int y_dtype, const float* y_scale, const float* y_zp, float y_scalar,
+                         size_t n, const float* out_scale, const float* out_zp, int qmin, int qmax,
+                         void* out_codes, int codes_dtype, float* out_f32, void* stream) {
+  if (n == 0) return LQ_OK;
+  if (op < LQ_MERGE_ADD || op > LQ_MERGE_COPY) return fail(LQ_ERR_UNSUPPORTED, "lq_qmerge: unknown op");
+  if (!x || !out_scale || !out_zp) return fail(LQ_ERR_DEVICE, "lq_qmerge: null pointer");
+  if (!out_codes && !out_f32) return fail(LQ_ERR_DEVICE, "lq_qmerge: no output requested");
+  if ((x_scale == nullptr) != (x_zp == nullptr) || (y_scale == nullptr) != (y_zp == nullptr))
+    return fail(LQ_ERR_DEVICE, "lq_qmerge: scale and zero_point of an operand go together");
+  if (!merge_dtype_ok(x_dtype, x_scale != nullptr)) return fail(LQ_ERR_DTYPE, "lq_qmerge: x dtype");
+  if (y && !merge_dtype_ok(y_dtype, y_scale != nullptr)) return fail(LQ_ERR_DTYPE, "lq_qmerge: y dtype");
+  if (out_codes && !merge_dtype_ok(codes_dtype, true)) return fail(LQ_ERR_DTYPE, "lq_qmerge: codes dtype");
+  if (qmin > qmax) return fail(LQ_ERR_SHAPE, "lq_qmerge: qmin > qmax");
+  const MergeOperand mx{x, x_dtype, x_scale, x_zp, 0.0f};
+  const MergeOperand my{y, y ? y_dtype : LQ_F32, y ? y_scale : nullptr, y ? y_zp : nullptr, y_scalar};
+  auto al = [](const void* p, size_t esz) { return p == nullptr || ((uintptr_t)p % (4 * esz)) == 0; };
+  const bool vec = n >= 4 && al(x, merge_elem_size(x_dtype)) && al(y, merge_elem_size(my.dtype)) &&
+                   al(out_codes, merge_elem_size(codes_dtype)) && al(out_f32, 4);
+  const int grid = grid_for(vec ? n / 4 : n, (size_t)kNumSMs * 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (vec)
+    merge_kernel<true><<<grid, kThreads, 0, st>>>(op, mx, my, n, out_scale, out_zp, (float)qmin, (float)qmax,
+                                                  out_codes, codes_dtype, out_f32);
+  else
+    merge_kernel<false><<<grid, kThreads, 0, st>>>(op, mx, my, n, out_scale, out_zp, (float)qmin, (float)qmax,
+                                                   out_codes, codes_dtype, out_f32);
+  return check_cuda(cudaGetLastError(), "lq_qmerge launch");
+}
+
+extern "C" int lq_lut_u8(const void* in_codes, size_t n, const uint8_t* table, void* out_codes, void* stream) {
+  if (n == 0) return LQ_OK;
+  if (!in_codes || !table || !out_codes) return fail(LQ_ERR_DEVICE, "lq_lut_u8: null pointer");
+  const bool vec = n >= 16 && aligned16(in_codes) && aligned16(out_codes);
+  const int grid = grid_for(vec ? n / 16 : n, (size_t)kNumSMs * 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (vec)
+    lut_kernel<true><<<grid, kThreads, 0, st>>>((const uint8_t*)in_codes, n, table, (uint8_t*)out_codes);
+  else
+    lut_kernel<false><<<grid, kThreads, 0, st>>>((const uint8_t*)in_codes, n, table, (uint8_t*)out_codes);
+  return check_cuda(cudaGetLastError(), "lq_lut_u8 launch");
+}
+
+// out[i] = table[x[i] * 256 + y[i]]: a binary function of two 8-bit codes is 64 KB of table,
+// which fits in shared memory.  The exact merge (two decodes, the op, an IEEE division, round,
+// clip: about twenty dependent float instructions per element) becomes one byte permute, one
+// shared load and one insert; the caller fills the table by running lq_qmerge once over the
+// 65536 code pairs of its grids.
+namespace lq {
+constexpr int kLut2Bytes = 65536;
+
+__global__ void __launch_bounds__(kThreads)
+lut2_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ y, size_t n, const uint8_t* __restrict__ table,
+            uint8_t* __restrict__ out, float* __restrict__ out_f32, const float* __restrict__ out_scale,
+            const float* __restrict__ out_zp, int out_signed, bool vec) {
+  extern __shared__ __align__(16) uint8_t t2[];
+  for (int i = threadIdx.x; i < kLut2Bytes / 16; i += kThreads)
+    reinterpret_cast<uint4*>(t2)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+  __syncthreads();
+  const float S = out_f32 ? __ldg(out_scale) : 1.0f, Z = out_f32 ? __ldg(out_zp) : 0.0f;
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  const size_t first = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  const size_t nvec = vec ? n / 16 : 0;
+  for (size_t g = first; g < nvec; g += stride) {
+    const uint4 a = ld_stream_u4(x + g * 16), b = ld_stream_u4(y + g * 16);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // index = x byte in bits 8-15, y byte in bits 0-7; one byte permute interleaves two pairs
+      const uint32_t lo = __byte_perm(bw[j], aw[j], 0x5140), hi = __byte_perm(bw[j], aw[j], 0x7362);
+      r[j] = (uint32_t)t2[lo & 0xffffu] | ((uint32_t)t2[lo >> 16] << 8) | ((uint32_t)t2[hi & 0xffffu] << 16) |
+             ((uint32_t)t2[hi >> 16] << 24);
+    }
+    st_stream_u4(out + g * 16, make_uint4(r[0], r[1], r[2], r[3]));
+    if (out_f32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t byte = (r[j] >> (8 * k)) & 0xffu;
+          const float c = out_signed ? (float)(int8_t)byte : (float)byte;
+          v[k] = __fmul_rn(__fsub_rn(c, Z), S);
+        }
+        Quad<float>::store(out_f32 + g * 16 + j * 4, v);
+      }
+    }
+  }
+  for (size_t e = nvec * 16 + first; e < n; e += stride) {
+    const uint8_t c = t2[((uint32_t)x[e] << 8) | y[e]];
+    out[e] = c;
+    if (out_f32) out_f32[e] = __fmul_rn(__fsub_rn(out_signed ? (float)(int8_t)c : (float)c, Z), S);
+  }
+}
+}  // namespace lq
+
+extern "C" int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, const uint8_t* table,
+                          void* out_codes, float* out_f32, const float* out_scale, const float* out_zp,
+                          int out_signed, void* stream) {
+  if (n == 0) return LQ_OK;
+  if (!x_codes || !y_codes || !table || !out_codes) return fail(LQ_ERR_DEVICE, "lq_lut2_u8: null pointer");
+  if (out_f32 && (!out_scale || !out_zp)) return fail(LQ_ERR_DEVICE, "lq_lut2_u8: out_f32 needs the output grid");
+  if (!aligned16(table)) return fail(LQ_ERR_ALIGNMENT, "lq_lut2_u8: the table must be 16-byte aligned");
+  static cudaError_t attr = cudaFuncSetAttribute(lut2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLut2Bytes);
+  // the attribute is per device: set it again when the call runs on another one
+  static int attr_dev = -1;
+  int devid = 0;
+  LQ_CUDA(cudaGetDevice(&devid));
+  if (devid != attr_dev) {
+    attr = cudaFuncSetAttribute(lut2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLut2Bytes);
+    attr_dev = devid;
+  }
+  if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(lut2)");
+  const bool vec = n >= 16 && aligned16(x_codes) && aligned16(y_codes) && aligned16(out_codes) &&
+                   (!out_f32 || aligned16(out_f32));
+  // persistent CTAs, three per SM (3 x 64 KB of tables); small inputs take fewer
+  const size_t want = ((vec ? n / 16 : n) + kThreads - 1) / kThreads;
+  const int grid = (int)(want < (size_t)(kNumSMs * 3) ? (want ? want : 1) : (size_t)(kNumSMs * 3));
+  lut2_kernel<<<grid, kThreads, kLut2Bytes, (cudaStream_t)stream>>>(
+      (const uint8_t*)x_codes, (const uint8_t*)y_codes, n, table, (uint8_t*)out_codes, out_f32, out_scale, out_zp,
+      out_signed, vec);
+  return check_cuda(cudaGetLastError(), "lq_lut2_u8 launch");
+}

@@ -1,9 +1,11 @@
 """Quantized inference modules of the hot path
 (lucid/nn/quantized/__init__.py:45-73): Linear, LinearReLU, Conv2d, ConvReLU2d,
-the dynamic Linear family and the boundary stubs."""
+the dynamic Linear family, the boundary stubs, the element-wise merges and the activations."""
 
 from . import dynamic, functional  # noqa: F401
+from .activation import ELU, Hardsigmoid, Hardswish, LeakyReLU, Sigmoid, Tanh  # noqa: F401
 from .conv import Conv2d, ConvReLU2d  # noqa: F401
+from .functional_module import FloatFunctional, QFunctional  # noqa: F401
 from .linear import Linear, LinearReLU  # noqa: F401
 from .modules import DeQuantize, Quantize  # noqa: F401
 from .sharded import ColumnShardedLinear  # noqa: F401

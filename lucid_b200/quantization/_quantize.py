@@ -41,10 +41,16 @@ def _intrinsic():
         return None
 
 
+_ACTIVATIONS = (torch.nn.Sigmoid, torch.nn.Hardswish, torch.nn.Hardsigmoid, torch.nn.Tanh, torch.nn.ELU,
+                torch.nn.LeakyReLU)
+
+
 def _observed_types() -> tuple:
+    from ..nn.quantized.functional_module import FloatFunctional
+
     nni = _intrinsic()
     fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
-    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub) + fused
+    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub, FloatFunctional) + _ACTIVATIONS + fused
 
 
 def _quant_mapping() -> dict:
@@ -55,6 +61,13 @@ def _quant_mapping() -> dict:
         torch.nn.Conv2d: nnq.Conv2d.from_float,
         QuantStub: nnq.Quantize.from_float,
         DeQuantStub: nnq.DeQuantize.from_float,
+        nnq.FloatFunctional: nnq.QFunctional.from_float,
+        torch.nn.Sigmoid: nnq.Sigmoid.from_float,
+        torch.nn.Hardswish: nnq.Hardswish.from_float,
+        torch.nn.Hardsigmoid: nnq.Hardsigmoid.from_float,
+        torch.nn.Tanh: nnq.Tanh.from_float,
+        torch.nn.ELU: nnq.ELU.from_float,
+        torch.nn.LeakyReLU: nnq.LeakyReLU.from_float,
     }
     nni = _intrinsic()
     if nni is not None:
@@ -74,6 +87,8 @@ def _make_observer_hook(obs):
 def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
     """Attach an activation observer (forward hook) to every quantizable module; nothing
     numeric changes.  Fused containers are observed as a unit, not their children."""
+    from ..nn.quantized.functional_module import FloatFunctional
+
     qcfg = qconfig if qconfig is not None else get_default_qconfig()
     model = model if inplace else copy.deepcopy(model)
     model.eval()
@@ -92,7 +107,8 @@ def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: boo
         mod.qconfig = qcfg
         obs = qcfg.activation()
         mod.activation_post_process = obs
-        mod._lq_hook = mod.register_forward_hook(_make_observer_hook(obs))
+        if not isinstance(mod, FloatFunctional):  # a functional feeds its observer itself
+            mod._lq_hook = mod.register_forward_hook(_make_observer_hook(obs))
         n_matched += 1
     if n_matched == 0:
         warnings.warn("prepare(): the qconfig matched no quantizable modules -- convert() will "

@@ -251,6 +251,10 @@ def isinf(t):
     return Tensor(np.isinf(t.a))
 
 
+def cat(tensors, dim=0):
+    return Tensor(np.concatenate([t.a for t in tensors], axis=dim))
+
+
 def where(c, a, b):
     return Tensor(np.where(_t(c), _t(a), _t(b)))
 
@@ -381,7 +385,7 @@ def install(reference_root):
         Tensor=Tensor, tensor=tensor, zeros=zeros, ones=ones, zeros_like=zeros_like,
         full_like=full_like, minimum=minimum, maximum=maximum, abs=_abs, round=_round,
         clip=clip, moveaxis=moveaxis, amin=amin, amax=amax, isinf=isinf, dtype=dtype,
-        where=where, arange=arange, scatter_add=scatter_add, histc=histc,
+        where=where, arange=arange, scatter_add=scatter_add, histc=histc, cat=cat,
         device=device, float32=float32, float64=float64, int8=int8, int16=int16,
         int32=int32, int64=int64,
     ).items():
@@ -410,6 +414,8 @@ def install(reference_root):
     mods["linear"] = _load("lucid.nn.quantized.linear", os.path.join(nq, "linear.py"))
     mods["dyn_linear"] = _load("lucid.nn.quantized.dynamic.linear",
                                os.path.join(nq, "dynamic", "linear.py"))
+    mods["functional_module"] = _load("lucid.nn.quantized.functional_module",
+                                      os.path.join(nq, "functional_module.py"))
     return mods
 
 
@@ -555,6 +561,27 @@ def generate(reference_root):
     # heavy tails: the clip search has something to cut
     tails = [np.concatenate([g.standard_normal(20000), [40.0, -35.0]]).astype(F32)]
     run_hist("ht", tails, 2048)
+
+    # -- QFunctional: every merge on one grid; operands are fake-quantized tensors on their own
+    #    grids (what the producing layers hand over) and one raw float pair
+    g = np.random.default_rng(50)
+    xa_ = (g.standard_normal((6, 50)) * 1.3).astype(F32)
+    ya_ = (g.standard_normal((6, 50)) * 0.8).astype(F32)
+    out["qf_xraw"], out["qf_yraw"] = xa_, ya_
+    xq = Fn.quantize(T(xa_), 0.04, 120.0, S.quint8)
+    yq = Fn.quantize(T(ya_), 0.025, 0.0, S.qint8)
+    out["qf_xq"], out["qf_yq"] = xq.a, yq.a
+    xf, yf_ = Fn.dequantize(xq, 0.04, 120.0), Fn.dequantize(yq, 0.025, 0.0)
+    for tag_, (sc_, zp_, qd_) in {"u8": (0.05, 110.0, S.quint8), "s8": (0.03, -5.0, S.qint8)}.items():
+        qf = m["functional_module"].QFunctional(tensor(sc_), tensor(zp_), qd_)
+        out[f"qf_{tag_}_grid"] = np.asarray([sc_, zp_, qd_.quant_min, qd_.quant_max], dtype=np.float64)
+        out[f"qf_{tag_}_add"] = qf.add(xf, yf_).a
+        out[f"qf_{tag_}_mul"] = qf.mul(xf, yf_).a
+        out[f"qf_{tag_}_add_relu"] = qf.add_relu(xf, yf_).a
+        out[f"qf_{tag_}_add_scalar"] = qf.add_scalar(xf, 0.75).a
+        out[f"qf_{tag_}_mul_scalar"] = qf.mul_scalar(xf, -1.5).a
+        out[f"qf_{tag_}_cat"] = qf.cat([xf, yf_], dim=1).a
+        out[f"qf_{tag_}_add_raw"] = qf.add(T(xa_), T(ya_)).a
 
     # -- dynamic Linear: from_float + forward (float GEMM = NumPy f32 matmul)
     rng = np.random.default_rng(11)

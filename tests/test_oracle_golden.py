@@ -247,3 +247,19 @@ def test_histogram_observer_reference_properties(golden):
     assert s_h <= s_m
     # the heavy-tailed fixture really is clipped
     assert golden["ht_clip"][1] < golden["ht_range0"][1]
+
+
+@pytest.mark.parametrize("tag", ["u8", "s8"])
+def test_qfunctional_merges(golden, tag):
+    sc, zp, qmin, qmax = golden[f"qf_{tag}_grid"].tolist()
+    xf = O.dequantize(golden["qf_xq"], 0.04, 120.0)
+    yf = O.dequantize(golden["qf_yq"], 0.025, 0.0)
+    args = (sc, zp, int(qmin), int(qmax))
+    assert np.array_equal(O.qfunctional("add", xf, yf, *args), golden[f"qf_{tag}_add"])
+    assert np.array_equal(O.qfunctional("mul", xf, yf, *args), golden[f"qf_{tag}_mul"])
+    assert np.array_equal(O.qfunctional("add_relu", xf, yf, *args), golden[f"qf_{tag}_add_relu"])
+    assert np.array_equal(O.qfunctional("add", xf, 0.75, *args), golden[f"qf_{tag}_add_scalar"])
+    assert np.array_equal(O.qfunctional("mul", xf, -1.5, *args), golden[f"qf_{tag}_mul_scalar"])
+    assert np.array_equal(O.qfunctional("cat", xf, [yf], *args, dim=1), golden[f"qf_{tag}_cat"])
+    assert np.array_equal(O.qfunctional("add", golden["qf_xraw"], golden["qf_yraw"], *args),
+                          golden[f"qf_{tag}_add_raw"])
