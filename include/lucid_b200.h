@@ -303,6 +303,27 @@ int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, const uint8_t
                void* out_codes, float* out_f32, const float* out_scale, const float* out_zp,
                int out_signed, void* stream);
 
+/* ---- quantized embedding tables -------------------------------------------------------- */
+
+/* Gather + dequantize of the rows of a per-row int8 table.  Replaces the forward of
+ * nn.quantized.Embedding / EmbeddingBag (lucid/nn/quantized/sparse.py:141-146, 292-301), which
+ * dequantize the whole table on every call before gathering; here only the rows asked for are
+ * read.  weight: (num_embeddings, dim) codes; scale / zero_point: num_embeddings floats
+ * (dequantize with ch_axis = 0).  indices: n_idx int32 (index_bits 32) or int64 (64).
+ *   offsets == NULL: out[i, :] = dequantized row indices[i] (LQ_F32 | LQ_BF16); a row equal to
+ *     padding_idx (pass -1 for none) is zeros, as in the engine's embedding_forward
+ *     (lucid/_C/backend/cpu/CpuBackend.h:8970-9010).  An index outside the table leaves its row
+ *     zero and writes LQ_ERR_SHAPE to *status (optional device word; the reference checks on
+ *     the host).
+ *   offsets != NULL: n_bags bag starts (same integer width as indices); out[b, :] (LQ_F32) pools
+ *     bag b with mode 0 = sum, 1 = mean, 2 = max exactly as embedding_bag_forward
+ *     (CpuBackend.h:5989-6080): rows added in index order, padding and out-of-range indices
+ *     skipped, the mean divided by the number of rows added, an empty max bag = zeros. */
+int lq_embedding_s8(const int8_t* weight, const float* scale, const float* zero_point,
+                    size_t num_embeddings, size_t dim, const void* indices, int index_bits, size_t n_idx,
+                    const void* offsets, size_t n_bags, int include_last_offset, int mode,
+                    long long padding_idx, void* out, int out_dtype, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -102,6 +102,9 @@ _SIGNATURES = {
     "lq_lut2_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                              C.c_void_p, C.c_int, C.c_void_p]),
     "lq_lut_u8": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_embedding_s8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int,
+                                  C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_longlong, C.c_void_p,
+                                  C.c_int, C.c_void_p, C.c_void_p]),
     "lq_gemm_s8": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                              C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "lq_gemm_s8_bcast": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,

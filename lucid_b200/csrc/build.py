@@ -15,7 +15,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ["capi.cu", "stream_kernels.cu", "histogram.cu", "gemm_s8.cu"]
+SOURCES = ["capi.cu", "stream_kernels.cu", "histogram.cu", "embedding.cu", "gemm_s8.cu"]
 HEADERS = ["common.cuh", os.path.join(ROOT, "include", "lucid_b200.h")]
 LIB = os.path.join(HERE, "liblucid_b200.so")
 

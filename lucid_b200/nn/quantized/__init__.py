@@ -9,3 +9,4 @@ from .functional_module import FloatFunctional, QFunctional  # noqa: F401
 from .linear import Linear, LinearReLU  # noqa: F401
 from .modules import DeQuantize, Quantize  # noqa: F401
 from .sharded import ColumnShardedLinear  # noqa: F401
+from .sparse import Embedding, EmbeddingBag  # noqa: F401

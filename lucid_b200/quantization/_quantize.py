@@ -147,7 +147,9 @@ def convert(model: torch.nn.Module, inplace: bool = False):
 def _dynamic_mapping() -> dict:
     import lucid_b200.nn.quantized as nnq
 
-    return {torch.nn.Linear: nnq.dynamic.Linear.from_float}
+    return {torch.nn.Linear: nnq.dynamic.Linear.from_float,
+            torch.nn.Embedding: lambda mod, dtype: nnq.Embedding.from_float(mod),
+            torch.nn.EmbeddingBag: lambda mod, dtype: nnq.EmbeddingBag.from_float(mod)}
 
 
 def _swap_dynamic(module, mapping, types, dtype) -> None:
