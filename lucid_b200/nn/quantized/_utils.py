@@ -38,12 +38,19 @@ def quantize_weight(mod) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]
     A module with a ``qconfig`` uses its weight observer factory; otherwise the
     default per-output-channel symmetric qint8 observer."""
     weight = mod.weight.detach()
-    qconfig = getattr(mod, "qconfig", None)
-    wobs = qconfig.weight() if qconfig is not None and hasattr(qconfig, "weight") else \
-        PerChannelMinMaxObserver(ch_axis=0, qscheme=per_channel_symmetric, qdtype=qint8)
-    wobs(weight)
-    scale, zero_point = wobs.calculate_qparams()
+    wfq = getattr(mod, "weight_fake_quant", None)
+    if wfq is not None:  # a QAT layer: refresh its weight observer on the trained weight
+        wfq(weight)
+        scale, zero_point = wfq.calculate_qparams()
+        wobs = wfq
+    else:
+        qconfig = getattr(mod, "qconfig", None)
+        wobs = qconfig.weight() if qconfig is not None and hasattr(qconfig, "weight") else \
+            PerChannelMinMaxObserver(ch_axis=0, qscheme=per_channel_symmetric, qdtype=qint8)
+        wobs(weight)
+        scale, zero_point = wobs.calculate_qparams()
     ch_axis = wobs.ch_axis
+    scale, zero_point = scale.to(weight.device), zero_point.to(weight.device)
     codes = quantize(weight, scale, zero_point, wobs.qdtype, ch_axis=ch_axis)
     return codes, scale, zero_point, (ch_axis if ch_axis is not None else 0)
 

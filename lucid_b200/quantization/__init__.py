@@ -12,4 +12,6 @@ from .observer import (FixedQParamsObserver, HistogramObserver, MinMaxObserver, 
                        NoopObserver, ObserverBase, PerChannelMinMaxObserver, PlaceholderObserver,
                        histc, minmax)
 from ._quantize import DeQuantStub, QuantStub, convert, prepare, quantize_dynamic  # noqa: F401,E402
-from .qconfig import QConfig, get_default_qconfig  # noqa: F401,E402
+from ._fake_quantize import FakeQuantize  # noqa: F401,E402
+from ._quantize import prepare_qat  # noqa: F401,E402
+from .qconfig import QConfig, get_default_qat_qconfig, get_default_qconfig  # noqa: F401,E402

@@ -15,7 +15,7 @@ import warnings
 import torch
 
 from ._qscheme import QDtype, qint8
-from .qconfig import QConfig, get_default_qconfig
+from .qconfig import QConfig, get_default_qat_qconfig, get_default_qconfig
 
 
 class QuantStub(torch.nn.Module):
@@ -73,6 +73,10 @@ def _quant_mapping() -> dict:
     if nni is not None:
         m[nni.LinearReLU] = nnq.LinearReLU.from_float
         m[nni.ConvReLU2d] = nnq.ConvReLU2d.from_float
+    from ..nn import qat as nnqat
+
+    m[nnqat.Linear] = nnq.Linear.from_float
+    m[nnqat.Conv2d] = nnq.Conv2d.from_float
     return m
 
 
@@ -141,6 +145,42 @@ def convert(model: torch.nn.Module, inplace: bool = False):
     if build is not None and hasattr(model, "activation_post_process"):
         return build(model)
     _convert_recursive(model, mapping, always)
+    return model
+
+
+def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
+    """Swap every float ``Linear`` / ``Conv2d`` for its QAT form (weight and output each behind a
+    ``FakeQuantize``) and leave the model in training mode
+    (lucid/quantization/_quantize.py:575-640)."""
+    from ..nn import qat as nnqat
+
+    qcfg = qconfig if qconfig is not None else get_default_qat_qconfig()
+    model = model if inplace else copy.deepcopy(model)
+    mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv2d: nnqat.Conv2d.from_float}
+    n_matched = 0
+
+    def swap(module):
+        nonlocal n_matched
+        for name, child in list(module.named_children()):
+            build = mapping.get(type(child))
+            if build is not None:
+                child.qconfig = qcfg
+                module._modules[name] = build(child)
+                n_matched += 1
+            else:
+                swap(child)
+
+    build = mapping.get(type(model))
+    if build is not None:
+        model.qconfig = qcfg
+        model = build(model)
+        n_matched += 1
+    else:
+        swap(model)
+    if n_matched == 0:
+        warnings.warn("prepare_qat(): the qconfig matched no quantizable modules -- convert() will "
+                      "leave this model unchanged.", stacklevel=2)
+    model.train()
     return model
 
 

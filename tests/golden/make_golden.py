@@ -410,6 +410,7 @@ def install(reference_root):
     mods["qparams"] = _load("lucid.quantization._qparams", os.path.join(q, "_qparams.py"))
     mods["functional"] = _load("lucid.quantization._functional", os.path.join(q, "_functional.py"))
     mods["observer"] = _load("lucid.quantization.observer", os.path.join(q, "observer.py"))
+    mods["fake_quantize"] = _load("lucid.quantization._fake_quantize", os.path.join(q, "_fake_quantize.py"))
     mods["utils"] = _load("lucid.nn.quantized._utils", os.path.join(nq, "_utils.py"))
     mods["linear"] = _load("lucid.nn.quantized.linear", os.path.join(nq, "linear.py"))
     mods["dyn_linear"] = _load("lucid.nn.quantized.dynamic.linear",
@@ -561,6 +562,25 @@ def generate(reference_root):
     # heavy tails: the clip search has something to cut
     tails = [np.concatenate([g.standard_normal(20000), [40.0, -35.0]]).astype(F32)]
     run_hist("ht", tails, 2048)
+
+    # -- FakeQuantize module: moving-average activations over three batches, a frozen observer,
+    #    fake-quant switched off; per-channel symmetric weights
+    FQ = m["fake_quantize"].FakeQuantize
+    fq = FQ(observer=O.MovingAverageMinMaxObserver, averaging_constant=0.1)
+    g = np.random.default_rng(60)
+    for i in range(3):
+        xb_ = (g.standard_normal((5, 24)) * (1 + i)).astype(F32)
+        out[f"fqm_x{i}"] = xb_
+        out[f"fqm_y{i}"] = fq(T(xb_)).a
+        out[f"fqm_qp{i}"] = np.asarray([fq.scale.a, fq.zero_point.a], dtype=F32)
+    fq.disable_observer()
+    wide = (g.standard_normal((5, 24)) * 9).astype(F32)
+    out["fqm_xwide"], out["fqm_ywide"] = wide, fq(T(wide)).a
+    out["fqm_qpwide"] = np.asarray([fq.scale.a, fq.zero_point.a], dtype=F32)
+    wfq = FQ(observer=O.PerChannelMinMaxObserver, ch_axis=0, qscheme=S.per_channel_symmetric, qdtype=S.qint8)
+    wt = (g.standard_normal((6, 20)) * 0.05).astype(F32)
+    out["fqm_w"], out["fqm_wy"] = wt, wfq(T(wt)).a
+    out["fqm_wscale"], out["fqm_wzp"] = wfq.scale.a, wfq.zero_point.a
 
     # -- QFunctional: every merge on one grid; operands are fake-quantized tensors on their own
     #    grids (what the producing layers hand over) and one raw float pair

@@ -263,3 +263,20 @@ def test_qfunctional_merges(golden, tag):
     assert np.array_equal(O.qfunctional("cat", xf, [yf], *args, dim=1), golden[f"qf_{tag}_cat"])
     assert np.array_equal(O.qfunctional("add", golden["qf_xraw"], golden["qf_yraw"], *args),
                           golden[f"qf_{tag}_add_raw"])
+
+
+def test_fake_quantize_module(golden):
+    """FakeQuantize.forward (lucid/quantization/_fake_quantize.py:182-199): observe, refresh the
+    qparams, fake-quantize; a frozen observer keeps them."""
+    mn, mx = np.inf, -np.inf
+    for i in range(3):
+        x = golden[f"fqm_x{i}"]
+        mn, mx = O.moving_average_minmax_observe(x, mn, mx, c=0.1)
+        s, z = O.calculate_qparams(mn, mx, False, O.QUINT8)
+        assert [s, z] == golden[f"fqm_qp{i}"].tolist()
+        assert np.array_equal(O.fake_quantize(x, s, z, 0, 255), golden[f"fqm_y{i}"])
+    assert [s, z] == golden["fqm_qpwide"].tolist()
+    assert np.array_equal(O.fake_quantize(golden["fqm_xwide"], s, z, 0, 255), golden["fqm_ywide"])
+    ws, wz = O.calculate_qparams(*O.per_channel_minmax_observe(golden["fqm_w"]), True, O.QINT8)
+    assert np.array_equal(ws, golden["fqm_wscale"]) and np.array_equal(wz, golden["fqm_wzp"])
+    assert np.array_equal(O.fake_quantize(golden["fqm_w"], ws, wz, -128, 127, ch_axis=0), golden["fqm_wy"])
