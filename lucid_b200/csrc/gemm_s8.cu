@@ -503,6 +503,95 @@ __device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, 
   }
 }
 
+// Four outputs -> four codes without the division: q~ = y * RN(1 / s_o) is within |q| * 2^-23 of
+// the true quotient, so rint(q~) equals rint(RN(y / s_o)) unless q~ lies within that distance of a
+// half-integer.  q~ + 1.5 * 2^23 rounds to the nearest integer (ties to even) in the mantissa;
+// d = q~ - that integer is exact, and |d| <= 0.499 certifies the rounding for every |q~| <= 4096
+// (beyond that the code is clipped either way: the grid and its zero point lie within +-512).
+// Returns false when some element is not certain (NaN included); the caller then takes the
+// exact division for the group.
+__device__ __forceinline__ bool requant4_certain(const float (&y)[4], const RowCtx& rc, float (&c)[4]) {
+  bool ok = true;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float q = __fmul_rn(y[i], rc.so.y);
+    const float n = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+    ok = ok && (fabsf(__fsub_rn(q, n)) <= 0.499f);
+    c[i] = fminf(fmaxf(__fadd_rn(n, rc.zo), rc.fqmin), rc.fqmax);
+  }
+  return ok;
+}
+
+// Lean requantising epilogue: 8-bit codes to one destination, tile inside N.  Compared with
+// epilogue_tile: the per-column parameters of the warp's columns are combined once per tile into
+// a table in the warp's staging area (scale product folded when the activation scale is per
+// tensor) and read back with broadcast 16-byte shared loads, the division is replaced by
+// requant4_certain, and every thread stores its 16 finished bytes straight to global memory
+// (its row's next 16 bytes follow one block later, so L2 merges the sectors) -- no staging pass.
+template <int BN, int PARTS>
+__device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc, uint32_t taddr, uint8_t* stg,
+                                                 int lane, int part, int n0) {
+  constexpr int WCOLS = BN / PARTS;
+  constexpr int NB = WCOLS / 16;
+  const int c0 = part * WCOLS;
+  float* t_scale = reinterpret_cast<float*>(stg);
+  float* t_bias = t_scale + WCOLS;
+  int* t_rowsum = reinterpret_cast<int*>(t_bias + WCOLS);
+  const bool fold_sa = ep.a_scale_mode != LQ_PER_ROW;
+  const bool has_bias = ep.bias != nullptr;
+  const bool has_zp = ep.b_rowsum != nullptr && rc.zpa != 0;
+  __syncwarp();
+  for (int j = lane; j < WCOLS; j += 32) {
+    const int col = n0 + c0 + j;
+    const float sb = ep.b_scale ? __ldg(ep.b_scale + col) : 1.0f;
+    t_scale[j] = fold_sa ? __fmul_rn(rc.sa, sb) : sb;
+    if (has_bias) t_bias[j] = __ldg(ep.bias + col);
+    if (has_zp) t_rowsum[j] = __ldg(ep.b_rowsum + col);
+  }
+  __syncwarp();
+  const bool row_ok = (rc.row_mask >> lane) & 1u;
+  uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
+  const bool relu = ep.act == LQ_ACT_RELU;
+  const bool is_signed = rc.fqmin < 0.0f;
+#pragma unroll 1
+  for (int blk = 0; blk < NB; ++blk) {
+    uint32_t acc[16];
+    tc_ld16_sync(taddr + c0 + blk * 16, acc);
+    uint32_t w[4];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 s4 = *reinterpret_cast<const float4*>(t_scale + blk * 16 + 4 * q4);
+      const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+      float y[4];
+      if (has_zp) {
+        const int4 r4 = *reinterpret_cast<const int4*>(t_rowsum + blk * 16 + 4 * q4);
+        const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = (float)((int)acc[4 * q4 + i] - rc.zpa * rs[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = (float)(int)acc[4 * q4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] = __fmul_rn(y[i], fold_sa ? sc[i] : __fmul_rn(rc.sa, sc[i]));
+      if (has_bias) {
+        const float4 b4 = *reinterpret_cast<const float4*>(t_bias + blk * 16 + 4 * q4);
+        y[0] = __fadd_rn(y[0], b4.x), y[1] = __fadd_rn(y[1], b4.y);
+        y[2] = __fadd_rn(y[2], b4.z), y[3] = __fadd_rn(y[3], b4.w);
+      }
+      if (relu) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = fmaxf(y[i], 0.0f);
+      }
+      float c[4];
+      if (!requant4_certain(y, rc, c)) code4_f32(y, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
+      w[q4] = is_signed ? pack4_s8(c) : pack4_u8(c);
+    }
+    if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __syncwarp();
+}
+
 // ---- the kernel ---------------------------------------------------------------------
 template <int BN, bool PAIR, int EW>
 __global__ void __launch_bounds__(threads_for(EW), 1)
@@ -674,6 +763,9 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     uint8_t* stg = tail + 512 + (warp - 2) * 4096;  // this warp's output staging
     const int part = (warp - 2) >> 2;
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
+    // the lean requantising epilogue: one destination, vector stores, aligned parameter arrays
+    const bool q8_lean = ep.n_dst == 1 && ep.vec_ok && ep.par_vec && !(g.debug & 64) &&
+                         (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
@@ -722,6 +814,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       } else if (ep.out_dtype == LQ_S32) {
         epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
+      } else if (q8_lean && n0 + BN <= g.N && rc.so.fast && fabsf(rc.zo) <= 512.0f) {
+        epilogue_tile_q8<BN, PARTS>(ep, rc, taddr, stg, lane, part, n0);
       } else {
         epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       }
