@@ -553,10 +553,8 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
   uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
   const bool relu = ep.act == LQ_ACT_RELU;
   const bool is_signed = rc.fqmin < 0.0f;
-#pragma unroll 1
-  for (int blk = 0; blk < NB; ++blk) {
-    uint32_t acc[16];
-    tc_ld16_sync(taddr + c0 + blk * 16, acc);
+  // one block of 16 columns: accumulators in registers -> 16 bytes in global memory
+  auto finish_block = [&](int blk, const uint32_t (&acc)[16]) {
     uint32_t w[4];
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
@@ -588,6 +586,14 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
       w[q4] = is_signed ? pack4_s8(c) : pack4_u8(c);
     }
     if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  };
+  // Two accumulator buffers: the TMEM load of the next block is in flight while this one is
+  // finished (wait::ld covers every outstanding load, so it comes after the arithmetic).
+#pragma unroll 1
+  for (int blk = 0; blk < NB; ++blk) {
+    uint32_t acc_a[16];
+    tc_ld16_sync(taddr + c0 + blk * 16, acc_a);
+    finish_block(blk, acc_a);
   }
   __syncwarp();
 }
@@ -766,6 +772,15 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // the lean requantising epilogue: one destination, vector stores, aligned parameter arrays
     const bool q8_lean = ep.n_dst == 1 && ep.vec_ok && ep.par_vec && !(g.debug & 64) &&
                          (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
+    // what does not change from tile to tile is read once
+    RowCtx rc_launch;
+    rc_launch.sa = (ep.a_scale && ep.a_scale_mode != LQ_PER_ROW) ? __ldg(ep.a_scale) : 1.0f;
+    rc_launch.zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0;
+    rc_launch.so = make_divisor(ep.out_scale ? __ldg(ep.out_scale) : 1.0f);
+    rc_launch.zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
+    rc_launch.fqmin = (float)ep.qmin, rc_launch.fqmax = (float)ep.qmax;
+    rc_launch.row_mask = 0u, rc_launch.row0 = 0;
+    const bool q8_lean_grid = rc_launch.so.fast && fabsf(rc_launch.zo) <= 512.0f;
     int acc = 0;
     uint32_t acc_phase = 0;
     const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
@@ -789,13 +804,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         m_global = tm_idx * BM + row;
         row_ok = m_global < g.M;
       }
-      RowCtx rc;
-      rc.sa = 1.0f;
-      if (ep.a_scale) rc.sa = ep.a_scale_mode == LQ_PER_ROW ? (row_ok ? __ldg(ep.a_scale + m_global) : 1.0f) : __ldg(ep.a_scale);
-      rc.zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0;
-      rc.so = make_divisor(ep.out_scale ? __ldg(ep.out_scale) : 1.0f);
-      rc.zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
-      rc.fqmin = (float)ep.qmin, rc.fqmax = (float)ep.qmax;
+      RowCtx rc = rc_launch;
+      if (ep.a_scale && ep.a_scale_mode == LQ_PER_ROW) rc.sa = row_ok ? __ldg(ep.a_scale + m_global) : 1.0f;
       rc.row_mask = __ballot_sync(0xffffffffu, row_ok && !(g.debug & 8));
       rc.row0 = (long long)__shfl_sync(0xffffffffu, m_global, 0);
 
@@ -814,7 +824,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
       } else if (ep.out_dtype == LQ_S32) {
         epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
-      } else if (q8_lean && n0 + BN <= g.N && rc.so.fast && fabsf(rc.zo) <= 512.0f) {
+      } else if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
         epilogue_tile_q8<BN, PARTS>(ep, rc, taddr, stg, lane, part, n0);
       } else {
         epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
@@ -1014,7 +1024,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
 // fill the clusters; single CTAs (128 x 256, or 128 x 128 for narrow outputs) otherwise.
 enum class Shape { kPair256, kSingle256, kSingle128 };
 
-Shape pick_shape(size_t m_subtiles, size_t N, bool gated) {
+Shape pick_shape(size_t m_subtiles, size_t N, bool gated, size_t k_blocks) {
   const char* force = getenv("LQ_GEMM_SHAPE");
   if (force) {
     if (!strcmp(force, "pair")) return Shape::kPair256;
@@ -1022,6 +1032,9 @@ Shape pick_shape(size_t m_subtiles, size_t N, bool gated) {
     if (!strcmp(force, "single128") && !gated) return Shape::kSingle128;
   }
   if (N <= 128 && !gated) return Shape::kSingle128;
+  // With a handful of k-blocks a tile is all epilogue: the pair's saving on operand traffic buys
+  // nothing and its cluster handshakes cost (measured 63 vs 68 us at 50176 x 1024 x 256).
+  if (k_blocks <= 4) return Shape::kSingle256;
   const size_t tiles_n = (N + 255) / 256;
   const size_t pair_tiles = ((m_subtiles + 1) / 2) * tiles_n;
   // a pair tile on a half-empty M pair wastes a CTA; need at least ~one wave of clusters
@@ -1074,7 +1087,7 @@ int gemm_impl(const char* who, const void* a, int a_signed, const int8_t* b, siz
   Geometry g = {};
   g.conv = 0, g.M = (int)M, g.N = (int)N, g.K = (int)K;
   g.tiles_m = (int)((M + BM - 1) / BM);
-  const Shape sh = pick_shape((size_t)g.tiles_m, N, e->act == LQ_ACT_SILU_GATE);
+  const Shape sh = pick_shape((size_t)g.tiles_m, N, e->act == LQ_ACT_SILU_GATE, (K + BK - 1) / BK);
   const int bn = sh == Shape::kSingle128 ? 128 : 256;
   g.tiles_n = (int)((N + bn - 1) / bn);
   g.num_kb = (int)((K + BK - 1) / BK);
@@ -1142,7 +1155,7 @@ extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, s
   g.tiles_p = (int)((P + g.tile_h - 1) / g.tile_h);
   g.M = (int)(N * P * Q), g.N = (int)K, g.K = (int)(R * S * C);
   g.tiles_m = (int)N * g.tiles_p * g.tiles_q;
-  const Shape sh = pick_shape((size_t)g.tiles_m, K, false);
+  const Shape sh = pick_shape((size_t)g.tiles_m, K, false, R * S * ((C + BK - 1) / BK));
   const int bn = sh == Shape::kSingle128 ? 128 : 256;
   g.tiles_n = (int)((K + bn - 1) / bn);
   g.cblocks = (int)((C + BK - 1) / BK);
