@@ -60,6 +60,23 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.lq_histc(*hist[:13], 64, None) == 6  # workspace too small
     assert lib.lq_histc_workspace_bytes() >= 8 * lib.lq_histc_max_bins()
     assert lib.lq_histogram_observe(one, 0, 64, 16, None, one, one, one, 1 << 20, None) == 3
+    # element-wise merges, tables, embeddings
+    merge = [0, one, 0, None, None, None, 0, None, None, 0.0, 8, one, one, 0, 255, one, 3, None, None]
+    assert lib.lq_qmerge(*merge[:10], 0, *merge[11:]) == 0  # nothing to do
+    assert lib.lq_qmerge(7, *merge[1:]) == 5
+    assert lib.lq_qmerge(*merge[:2], 3, *merge[3:]) == 2  # codes need their scale / zero point
+    assert lib.lq_qmerge(*merge[:3], one, None, *merge[5:]) == 3  # ... both of them
+    assert lib.lq_qmerge(*merge[:15], None, 3, None, None) == 3  # no output requested
+    assert lib.lq_qmerge(*merge[:13], 5, 4, *merge[15:]) == 1  # qmin > qmax
+    assert lib.lq_lut_u8(one, 8, None, one, None) == 3
+    assert lib.lq_lut2_u8(one, one, 8, ctypes.c_void_p(24), one, None, None, None, 0, None) == 4  # table alignment
+    assert lib.lq_lut2_u8(one, one, 8, one, one, one, None, None, 0, None) == 3  # f32 output needs the grid
+    emb = [one, one, one, 10, 16, one, 64, 4, None, 0, 0, 0, -1, one, 0, None, None]
+    assert lib.lq_embedding_s8(*emb[:6], 16, *emb[7:]) == 2  # index width
+    assert lib.lq_embedding_s8(*emb[:4], 0, *emb[5:]) == 1  # empty table
+    assert lib.lq_embedding_s8(*emb[:14], 2, *emb[15:]) == 2  # lookups leave as f32 / bf16
+    assert lib.lq_embedding_s8(*emb[:8], one, 2, 0, 3, *emb[12:]) == 5  # pooling mode
+    assert lib.lq_embedding_s8(*emb[:8], one, 2, 0, 0, -1, one, 1, None, None) == 2  # bags pool in f32
     assert lib.lq_histogram_observe(one, 0, 64, 0, one, one, one, one, 1 << 20, None) == 5
     assert lib.lq_histogram_observe(one, 9, 64, 16, one, one, one, one, 1 << 20, None) == 2
 
