@@ -266,7 +266,7 @@ def run_b200_arm(args):
         for name, cols in (("qkv", N_QKV), ("o", D_MODEL), ("h", D_FF), ("d", D_MODEL)):
             peers[name] = PeerOutputs(M_TOKENS, cols, torch.bfloat16, dev)
 
-    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None):
+    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, fence=True):
         if record:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
             e0.record()
@@ -280,16 +280,21 @@ def run_b200_arm(args):
             e1.record()
             gemm_events.append((e0, e1))
         if peer is not None:
-            peer.fence()
+            # The fence (a 4-byte all-reduce) orders what follows on this stream after the peer
+            # stores of every rank.  It is needed before something consumes the gathered tensor:
+            # after the gate/up GEMM (its output is encoded next) and at the end of the step,
+            # where one fence covers the three result tensors.
+            if fence:
+                peer.fence()
             return buf
         return gather_columns(out) if world > 1 else out
 
     def step(xs, record=False):
         """One pass of the hot path; returns the down-projection output."""
         a, s = Q.quantize_per_token(xs[0], Q.qint8)
-        qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"))
+        qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"), fence=False)
         a, s = Q.quantize_per_token(xs[1], Q.qint8)
-        o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"))
+        o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"), fence=False)
         a, s = Q.quantize_per_token(xs[2], Q.qint8)
         h = gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, peer=peers.get("h"))
         a, s = Q.quantize_per_token(h, Q.qint8)

@@ -45,12 +45,15 @@ _ACTIVATIONS = (torch.nn.Sigmoid, torch.nn.Hardswish, torch.nn.Hardsigmoid, torc
                 torch.nn.LeakyReLU)
 
 
+_CONV_TRANSPOSE = (torch.nn.ConvTranspose1d, torch.nn.ConvTranspose2d, torch.nn.ConvTranspose3d)
+
+
 def _observed_types() -> tuple:
     from ..nn.quantized.functional_module import FloatFunctional
 
     nni = _intrinsic()
     fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
-    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub, FloatFunctional) + _ACTIVATIONS + fused
+    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub, FloatFunctional) + _ACTIVATIONS + _CONV_TRANSPOSE + fused
 
 
 def _quant_mapping() -> dict:
@@ -62,6 +65,9 @@ def _quant_mapping() -> dict:
         QuantStub: nnq.Quantize.from_float,
         DeQuantStub: nnq.DeQuantize.from_float,
         nnq.FloatFunctional: nnq.QFunctional.from_float,
+        torch.nn.ConvTranspose1d: nnq.ConvTranspose1d.from_float,
+        torch.nn.ConvTranspose2d: nnq.ConvTranspose2d.from_float,
+        torch.nn.ConvTranspose3d: nnq.ConvTranspose3d.from_float,
         torch.nn.Sigmoid: nnq.Sigmoid.from_float,
         torch.nn.Hardswish: nnq.Hardswish.from_float,
         torch.nn.Hardsigmoid: nnq.Hardsigmoid.from_float,

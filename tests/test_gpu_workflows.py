@@ -89,3 +89,35 @@ def test_quantize_dynamic_mlp():
 def test_prepare_without_match_warns():
     with pytest.warns(UserWarning):
         Q.prepare(torch.nn.Sequential(torch.nn.ReLU()))
+
+
+def test_conv_transpose_runs_the_reference_sequence():
+    """dequantize(weight, ch_axis=1) -> float transposed conv -> fake_quantize
+    (lucid/nn/quantized/conv_transpose.py:112-130), through prepare / convert."""
+    import numpy as np
+
+    from gpu_util import host
+    from oracle import lucid_oracle as O
+
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(Q.QuantStub(), torch.nn.ConvTranspose2d(8, 12, 3, stride=2, padding=1,
+                                                                        output_padding=1)).cuda()
+    x = torch.randn(2, 8, 9, 9, device="cuda")
+    prepared = Q.prepare(model)
+    prepared(x)
+    qmodel = Q.convert(prepared)
+    ct = qmodel[1]
+    assert type(ct) is nnq.ConvTranspose2d and tuple(ct.weight_int8.shape) == (8, 12, 3, 3)
+    assert list(ct.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point", "bias", "scale",
+                                     "zero_point"]
+    w = host(model[1].weight.detach())
+    s_o, z_o = O.calculate_qparams(*O.per_channel_minmax_observe(w, ch_axis=1), True, O.QINT8)
+    assert np.array_equal(host(ct.weight_scale), s_o)
+    assert np.array_equal(host(ct.weight_int8), O.quantize(w, s_o, z_o, O.QINT8, ch_axis=1))
+    xq = qmodel[0](x)
+    y = ct(xq)
+    w_dq = torch.from_numpy(O.dequantize(host(ct.weight_int8), s_o, z_o, ch_axis=1)).cuda()
+    y_f = torch.nn.functional.conv_transpose2d(xq.detach(), w_dq, ct.bias, 2, 1, 1)
+    want = O.fake_quantize(host(y_f), float(ct.scale), float(ct.zero_point), 0, 255)
+    assert np.array_equal(host(y), want)
+    assert _mean_rel_err(y, model(x).detach()) < 0.08
