@@ -263,10 +263,20 @@ def run_b200_arm(args):
     if p2p:
         from lucid_b200.nn.quantized.sharded import PeerOutputs
 
-        for name, cols in (("qkv", N_QKV), ("o", D_MODEL), ("h", D_FF), ("d", D_MODEL)):
-            peers[name] = PeerOutputs(M_TOKENS, cols, torch.bfloat16, dev)
+        from lucid_b200.nn.quantized.sharded import quantize_shard_bcast, shard_absmax
 
-    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, fence=True):
+        for name, cols in (("qkv", N_QKV), ("o", D_MODEL), ("d", D_MODEL)):
+            peers[name] = PeerOutputs(M_TOKENS, cols, torch.bfloat16, dev)
+        # The hidden tensor is exchanged as int8 codes from 4 ranks up (measured: 6904 vs 6362
+        # TOPS at 8 ranks, 6400 vs 6176 at 4); at 2 ranks the extra abs-max all-reduce costs more
+        # than the halved bytes save (4266 vs 4516), so the bf16 tensor is exchanged there.
+        if world >= 4:
+            peers["hq"] = PeerOutputs(M_TOKENS, D_FF, torch.int8, dev)
+            h_scale = torch.empty(M_TOKENS, dtype=torch.float32, device=dev)
+        else:
+            peers["h"] = PeerOutputs(M_TOKENS, D_FF, torch.bfloat16, dev)
+
+    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, fence=True, gather=True):
         if record:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
             e0.record()
@@ -287,7 +297,7 @@ def run_b200_arm(args):
             if fence:
                 peer.fence()
             return buf
-        return gather_columns(out) if world > 1 else out
+        return gather_columns(out) if (world > 1 and gather) else out
 
     def step(xs, record=False):
         """One pass of the hot path; returns the down-projection output."""
@@ -296,13 +306,26 @@ def run_b200_arm(args):
         a, s = Q.quantize_per_token(xs[1], Q.qint8)
         o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"), fence=False)
         a, s = Q.quantize_per_token(xs[2], Q.qint8)
-        h = gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, peer=peers.get("h"))
-        a, s = Q.quantize_per_token(h, Q.qint8)
+        if "hq" in peers:
+            # The gate/up output only feeds the per-token encode of the down projection: keep the
+            # bf16 shard local, all-reduce the per-token abs-max (rows floats), encode the shard
+            # with the global scales and store the CODES into every rank's operand buffer -- half
+            # the exchanged bytes of the bf16 tensor, and the encode is sharded, not replicated.
+            gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, gather=False)
+            am = shard_absmax(out_h)
+            a, ptrs = peers["hq"].next()
+            s = quantize_shard_bcast(out_h, am, ptrs, D_FF, rank * out_h.shape[1], out_scale=h_scale)
+            peers["hq"].fence()
+        else:
+            h = gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, peer=peers.get("h"))
+            a, s = Q.quantize_per_token(h, Q.qint8)
         # the down projection contracts over the full ffn width: K is not sharded
         d = gemm(a, s, w_d, s_d, out_d, record=record, peer=peers.get("d"))
         return qkv, o, d
 
-    launches_per_step = 8  # 4 per-token encodes + 4 GEMMs (library collectives not counted)
+    # 4 per-token encodes + 4 GEMMs; with the fused shard encode: 3 encodes + 4 GEMMs + the
+    # shard's row range reduction + the broadcast encode (library collectives not counted)
+    launches_per_step = 9 if "hq" in peers else 8
 
     def barrier():
         if world > 1:

@@ -252,6 +252,21 @@ int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, size_t M, siz
                      const lq_epilogue_t* ep, void* const* outs, int n_dst, size_t ldo,
                      size_t col0, int32_t* status, void* stream);
 
+/* Per-token symmetric int8 encode of a COLUMN SHARD with the exchange fused in: row r of
+ * x (rows x cols, row stride ldx; LQ_F32 | LQ_BF16) is encoded with
+ * scale[r] = max(row_absmax[r] / ((qmax - qmin) / 2), eps) -- the expressions of
+ * lq_quantize_per_token -- and the codes are stored at columns [col0, col0 + cols) of every
+ * one of the n_dst (1..8) row-major (rows, ldo) int8 destinations: this GPU's buffer and the
+ * peers' copies mapped into this process (plain peer stores over NVLink).  row_absmax is the
+ * per-token max |x| over ALL shards (the caller all-reduces the per-shard maxima from lq_minmax,
+ * mode LQ_PER_ROW; max is order-free, so the scales and codes equal the single-GPU encode of
+ * the unsharded tensor bit for bit).  out_scale (optional): rows floats.  `outs` is a HOST
+ * array of device pointers.  No counterpart in the reference, which has no distributed code. */
+int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
+                           const float* row_absmax, int qmin, int qmax, float eps,
+                           void* const* outs, int n_dst, size_t ldo, size_t col0,
+                           float* out_scale, void* stream);
+
 /* sum_k b[n,k] for the zero-point correction term (N ints). */
 int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream);
 

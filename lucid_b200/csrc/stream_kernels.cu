@@ -1501,3 +1501,86 @@ extern "C" int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, co
       out_signed, vec);
   return check_cuda(cudaGetLastError(), "lq_lut2_u8 launch");
 }
+
+// ---- per-token encode of a column shard, stored into every rank's operand buffer ----------------
+// Output-channel-sharded layers: when a sharded GEMM's output only feeds the per-token int8
+// encode of the next layer, exchanging it as bf16 and encoding the whole tensor on every rank
+// moves twice the bytes and repeats the encode w times.  Instead each rank reduces the per-token
+// abs-max of its own column shard, the ranks all-reduce those (max is order-free, so the scales
+// equal the single-GPU ones bit for bit), and this kernel encodes the rank's shard with the
+// global scales and stores the CODES into the column slice of every rank's (rows, ldo) buffer:
+// its own and, with plain peer stores over NVLink, the peers'.
+namespace lq {
+struct BcastDst {
+  int8_t* p[8];
+};
+
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, size_t ldx,
+                           const float* __restrict__ row_absmax, float half, float eps, float qmin, float qmax,
+                           BcastDst dst, int n_dst, size_t ldo, size_t col0, float* __restrict__ out_scale) {
+  constexpr int E = VecOf<In>::kElems;  // 4 (binary32) or 8 (bfloat16) elements per 16-byte vector
+  const uint32_t nvec = (uint32_t)(cols / E);
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    // the same expressions as the single-GPU per-token encode
+    const float sc = fmaxf(__fdiv_rn(__ldg(row_absmax + r), half), eps);
+    if (threadIdx.x == 0 && out_scale) out_scale[r] = sc;
+    const Divisor d = make_divisor(sc);
+    const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    const uint4* xv = reinterpret_cast<const uint4*>(x + r * ldx);
+    const size_t obase = r * ldo + col0;
+    for (uint32_t i = threadIdx.x; i < nvec; i += kThreads) {
+      const uint4 v = ld_stream_u4(xv + i);
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+      if (E == 4) {
+        const float f[4] = {__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3])};
+        int c[4];
+        code4_int(f, d, ig, 0.0f, qmin, qmax, c);
+        const uint32_t w = pack4i_s8(c);
+        for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint32_t*>(dst.p[k] + obase + (size_t)i * 4) = w;
+      } else {
+        const float f0[4] = {bf16_bits_to_f32(wv[0] & 0xffffu), bf16_bits_to_f32(wv[0] >> 16),
+                             bf16_bits_to_f32(wv[1] & 0xffffu), bf16_bits_to_f32(wv[1] >> 16)};
+        const float f1[4] = {bf16_bits_to_f32(wv[2] & 0xffffu), bf16_bits_to_f32(wv[2] >> 16),
+                             bf16_bits_to_f32(wv[3] & 0xffffu), bf16_bits_to_f32(wv[3] >> 16)};
+        int c0[4], c1[4];
+        code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
+        code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        const uint2 w = make_uint2(pack4i_s8(c0), pack4i_s8(c1));
+        for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint2*>(dst.p[k] + obase + (size_t)i * 8) = w;
+      }
+    }
+  }
+}
+}  // namespace lq
+
+extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
+                                      const float* row_absmax, int qmin, int qmax, float eps,
+                                      void* const* outs, int n_dst, size_t ldo, size_t col0,
+                                      float* out_scale, void* stream) {
+  if (rows == 0 || cols == 0) return LQ_OK;
+  if (!x || !row_absmax || !outs) return fail(LQ_ERR_DEVICE, "lq_quantize_rows_bcast: null pointer");
+  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: 1..8 destinations");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_quantize_rows_bcast: in_dtype");
+  if (qmin < -128 || qmax > 127 || qmin >= qmax) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: grid outside int8");
+  const size_t e = in_dtype == LQ_F32 ? 4 : 8;
+  if (cols % e || ldx % e || !aligned16(x) || ldo % 8 || col0 % 8 || ldo < col0 + cols)
+    return fail(LQ_ERR_ALIGNMENT, "lq_quantize_rows_bcast: shard and destination must be vector aligned");
+  BcastDst dst{};
+  for (int k = 0; k < n_dst; ++k) {
+    if (!outs[k] || (reinterpret_cast<uintptr_t>(outs[k]) & 7u)) return fail(LQ_ERR_ALIGNMENT, "lq_quantize_rows_bcast: destination pointer");
+    dst.p[k] = (int8_t*)outs[k];
+  }
+  const float half = (float)((qmax - qmin) / 2.0);
+  const int grid = (int)(rows < (size_t)kMaxBlocks ? rows : (size_t)kMaxBlocks);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == LQ_F32)
+    quantize_rows_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, ldx, row_absmax, half, eps,
+                                                                 (float)qmin, (float)qmax, dst, n_dst, ldo, col0, out_scale);
+  else
+    quantize_rows_bcast_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, ldx,
+                                                                         row_absmax, half, eps, (float)qmin, (float)qmax,
+                                                                         dst, n_dst, ldo, col0, out_scale);
+  return check_cuda(cudaGetLastError(), "lq_quantize_rows_bcast launch");
+}

@@ -89,6 +89,40 @@ class PeerOutputs:
         dist.all_reduce(self._flag, group=self.group)
 
 
+def shard_absmax(x_shard: torch.Tensor, group=None) -> torch.Tensor:
+    """Per-token ``max |x|`` over all column shards: one range reduction of this rank's shard
+    and a ``MAX`` all-reduce of ``rows`` floats (order-free, so bit-identical on every rank)."""
+    from ...quantization.observer import minmax
+
+    mn, mx = minmax(x_shard.reshape(-1, x_shard.shape[-1]), per_row=True)
+    am = torch.maximum(mn.abs_(), mx.abs_())
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(am, op=dist.ReduceOp.MAX, group=group)
+    return am
+
+
+def quantize_shard_bcast(x_shard: torch.Tensor, row_absmax: torch.Tensor, dst_ptrs, ldo: int, col0: int,
+                         out_scale: torch.Tensor | None = None, qdtype=qint8, eps: float = 1e-8):
+    """Encode this rank's ``(rows, cols)`` shard with the global per-token scales and store
+    the codes into columns ``[col0, col0 + cols)`` of every destination in ``dst_ptrs`` (raw
+    device pointers of ``(rows, ldo)`` int8 buffers: own first, then the peers').  Returns the
+    per-token scales."""
+    import ctypes as C
+
+    _lib.require_cuda(x_shard, "shard")
+    x2 = x_shard.reshape(-1, x_shard.shape[-1]).contiguous()
+    rows, cols = x2.shape
+    if out_scale is None:
+        out_scale = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    arr = (C.c_void_p * len(dst_ptrs))(*[C.c_void_p(int(p)) for p in dst_ptrs])
+    with torch.cuda.device(x2.device):
+        _lib.check(_lib.load().lq_quantize_rows_bcast(
+            _lib.ptr(x2), _lib.code_of(x2.dtype), rows, cols, cols, _lib.ptr(row_absmax), qdtype.quant_min,
+            qdtype.quant_max, C.c_float(eps), arr, len(dst_ptrs), int(ldo), int(col0), _lib.ptr(out_scale),
+            _lib.stream_ptr(x2.device)))
+    return out_scale
+
+
 class ColumnShardedLinear(torch.nn.Module):
     """This rank's shard of a per-token W8A8 linear plus the output all-gather."""
 

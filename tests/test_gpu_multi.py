@@ -66,6 +66,20 @@ def _worker(rank, world, port, ret):
         gl.use_peer_outputs(max_rows=m, gated=True)
         for _ in range(2):
             ok = ok and torch.equal(gl.forward_codes(a, s, act=_lib.ACT_SILU_GATE), h_full)
+        # the gated output feeding a per-token encode: shard kept local, abs-max all-reduced,
+        # codes stored into every rank's operand buffer == the unsharded per-token encode
+        from lucid_b200.nn.quantized.sharded import PeerOutputs, quantize_shard_bcast, shard_absmax
+
+        want_codes, want_scales = Q.quantize_per_token(h_full, Q.qint8)
+        h_local = QF.gemm_s8(a, gl.weight_int8, out_dtype=torch.bfloat16, a_scale=s, b_scale=gl.weight_scale,
+                             act=_lib.ACT_SILU_GATE)
+        ok = ok and torch.equal(h_local, h_full[:, sl])
+        codes = PeerOutputs(m, ff, torch.int8, dev)
+        for _ in range(3):
+            buf, ptrs = codes.next()
+            scales = quantize_shard_bcast(h_local, shard_absmax(h_local), ptrs, ff, rank * per)
+            codes.fence()
+            ok = ok and torch.equal(buf, want_codes) and torch.equal(scales, want_scales)
         torch.cuda.synchronize()
         _lib.check_device_status(dev)
         ret[rank] = bool(ok)

@@ -8,6 +8,7 @@ from oracle import lucid_oracle as O
 
 pytestmark = pytest.mark.gpu
 
+import lucid_b200 as L  # noqa: E402
 import lucid_b200.quantization as Q  # noqa: E402
 from gpu_util import dev, host, qd_of  # noqa: E402
 
@@ -273,3 +274,27 @@ def test_extreme_scales_and_values_take_the_full_division():
         with np.errstate(over="ignore", divide="ignore"):
             ref = O.quantize(x, float(scale), 0.0, O.QINT8)
         assert np.array_equal(got, ref), scale
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_shard_encode_with_broadcast_equals_unsharded_per_token_encode(dtype):
+    """Column shards encoded separately with the all-reduced abs-max and stored into the
+    slices of two destination buffers reproduce quantize_per_token of the whole tensor."""
+    from lucid_b200.nn.quantized.sharded import quantize_shard_bcast, shard_absmax
+
+    torch.manual_seed(4)
+    rows, cols, shards = 257, 1024, 4
+    x = (torch.randn(rows, cols, device="cuda") * torch.rand(rows, 1, device="cuda") * 3).to(dtype)
+    x[5] = 0  # an all-zero token takes the eps scale
+    want_codes, want_scales = Q.quantize_per_token(x, Q.qint8)
+    per = cols // shards
+    parts = [x[:, i * per:(i + 1) * per].contiguous() for i in range(shards)]
+    # what the MAX all-reduce leaves on every rank
+    am = torch.stack([shard_absmax(p) for p in parts]).max(dim=0).values
+    bufs = [torch.full((rows, cols), 99, dtype=torch.int8, device="cuda") for _ in range(2)]
+    for i, p in enumerate(parts):
+        scales = quantize_shard_bcast(p, am, [b.data_ptr() for b in bufs], cols, i * per)
+        assert torch.equal(scales, want_scales)
+    assert torch.equal(bufs[0], want_codes) and torch.equal(bufs[1], want_codes)
+    with pytest.raises(L.ShapeMismatch):
+        quantize_shard_bcast(parts[0], am, [bufs[0].data_ptr()], cols, 3)  # column offset off the vector grid
