@@ -267,6 +267,18 @@ int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols
                            void* const* outs, int n_dst, size_t ldo, size_t col0,
                            float* out_scale, void* stream);
 
+/* lq_gemm_s8_bcast through NVSwitch multicast: `multicast_out` is the multicast address of a
+ * row-major (M, ldo) buffer that every rank of the group has bound (CUDA multicast object /
+ * torch symmetric memory `multicast_ptr`).  Each finished 16-byte piece is issued ONCE as a
+ * multimem store and the switch writes it into every rank's buffer (this GPU's included), so a
+ * GPU's egress is its own output volume instead of (ranks - 1) times it.  Rows, column offset
+ * and output width must be multiples of 16 bytes.  Consumers are ordered after the kernels of
+ * all ranks by the caller, as for lq_gemm_s8_bcast.  (lq_quantize_rows_bcast takes the same
+ * kind of address with n_dst = -1.)  No counterpart in the reference. */
+int lq_gemm_s8_multicast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                         const lq_epilogue_t* ep, void* multicast_out, size_t ldo, size_t col0,
+                         int32_t* status, void* stream);
+
 /* sum_k b[n,k] for the zero-point correction term (N ints). */
 int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream);
 

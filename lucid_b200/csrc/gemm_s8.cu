@@ -74,6 +74,7 @@ struct Epi {
   void* out;           // first destination
   void* more_outs[7];  // further destinations of the same tiles (peer GPUs' buffers)
   int n_dst;           // number of destinations (>= 1)
+  int multicast;       // `out` is an NVSwitch multicast address: one multimem store reaches every rank
   long long col0;      // column offset of this GEMM's columns inside every destination
   long long ldo;  // elements
   int n_out;      // columns of out (N, or N/2 for the gated epilogue)
@@ -330,6 +331,15 @@ struct RowCtx {
   long long row0;    // global output row of the warp's first row
 };
 
+// One 16-byte store to a multicast address: NVSwitch writes it into the buffer of every GPU
+// bound to the multicast object (the issuing GPU's included), so the link carries each tile once
+// instead of once per peer.
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // Flush the warp's staging buffer (32 rows x 128 B, 16-byte pieces XOR-swizzled by row):
 // eight lanes write one full 128-byte line of a row.
 template <int ESZ>
@@ -349,7 +359,9 @@ __device__ __forceinline__ void flush_group(const uint8_t* stg, int lane, const 
       // (plain stores over NVLink; the exchange overlaps the mainloop of the next tile)
       for (int dsti = 0; dsti < ep.n_dst; ++dsti) {
         uint8_t* dst = reinterpret_cast<uint8_t*>(dsti == 0 ? ep.out : ep.more_outs[dsti - 1]) + off;
-        if (ep.vec_ok && nvalid >= EPP) {
+        if (ep.multicast) {
+          multimem_st16(dst, v);  // the host admits only shapes whose pieces are all whole
+        } else if (ep.vec_ok && nvalid >= EPP) {
           *reinterpret_cast<uint4*>(dst) = v;
         } else {
           const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
@@ -770,7 +782,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int part = (warp - 2) >> 2;
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
     // the lean requantising epilogue: one destination, vector stores, aligned parameter arrays
-    const bool q8_lean = ep.n_dst == 1 && ep.vec_ok && ep.par_vec && !(g.debug & 64) &&
+    const bool q8_lean = ep.n_dst == 1 && !ep.multicast && ep.vec_ok && ep.par_vec && !(g.debug & 64) &&
                          (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
     // what does not change from tile to tile is read once
     RowCtx rc_launch;
@@ -964,7 +976,7 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
   d->a_scale = e->a_scale, d->a_zp = e->a_zp, d->b_rowsum = e->b_rowsum, d->b_scale = e->b_scale;
   d->bias = e->bias, d->out_scale = e->out_scale, d->out_zp = e->out_zp;
   d->out = out, d->ldo = (long long)ldo, d->n_out = (int)n_out, d->status = status;
-  d->n_dst = 1, d->col0 = 0;
+  d->n_dst = 1, d->col0 = 0, d->multicast = 0;
   for (auto& m : d->more_outs) m = nullptr;
   const size_t esz = dtype_size(e->out_dtype);
   d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
@@ -1068,7 +1080,7 @@ namespace lq {
 namespace {
 int gemm_impl(const char* who, const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
               const lq_epilogue_t* e, void* const* outs, int n_dst, size_t ldo, size_t col0,
-              int32_t* status, void* stream) {
+              int32_t* status, void* stream, bool multicast = false) {
   const std::string w(who);
   if (M == 0 || N == 0) return LQ_OK;
   if (!a || !b || !outs) return fail(LQ_ERR_DEVICE, w + ": null pointer");
@@ -1100,6 +1112,12 @@ int gemm_impl(const char* who, const void* a, int a_signed, const int8_t* b, siz
   ep.n_dst = n_dst, ep.col0 = (long long)col0;
   const size_t esz = dtype_size(e->out_dtype);
   ep.vec_ok = ep.vec_ok && ((col0 * esz) % 16 == 0);
+  if (multicast) {
+    // multimem stores are whole 16-byte pieces: the output width must tile them exactly
+    if (!ep.vec_ok || (n_out * esz) % 16 != 0)
+      return fail(LQ_ERR_ALIGNMENT, w + ": multicast output needs 16-byte aligned rows, offset and width");
+    ep.multicast = 1;
+  }
   for (int i = 1; i < n_dst; ++i) {
     ep.more_outs[i - 1] = outs[i];
     ep.vec_ok = ep.vec_ok && aligned16(outs[i]);
@@ -1121,6 +1139,14 @@ extern "C" int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, si
                                 size_t K, const lq_epilogue_t* e, void* const* outs, int n_dst,
                                 size_t ldo, size_t col0, int32_t* status, void* stream) {
   return gemm_impl("lq_gemm_s8_bcast", a, a_signed, b, M, N, K, e, outs, n_dst, ldo, col0, status, stream);
+}
+
+extern "C" int lq_gemm_s8_multicast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N,
+                                    size_t K, const lq_epilogue_t* e, void* multicast_out, size_t ldo,
+                                    size_t col0, int32_t* status, void* stream) {
+  if (M != 0 && N != 0 && !multicast_out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8_multicast: null pointer");
+  void* outs[1] = {multicast_out};
+  return gemm_impl("lq_gemm_s8_multicast", a, a_signed, b, M, N, K, e, outs, 1, ldo, col0, status, stream, true);
 }
 
 extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H,

@@ -1519,7 +1519,8 @@ template <typename In>
 __global__ void __launch_bounds__(kThreads)
 quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, size_t ldx,
                            const float* __restrict__ row_absmax, float half, float eps, float qmin, float qmax,
-                           BcastDst dst, int n_dst, size_t ldo, size_t col0, float* __restrict__ out_scale) {
+                           BcastDst dst, int n_dst, bool multicast, size_t ldo, size_t col0,
+                           float* __restrict__ out_scale) {
   constexpr int E = VecOf<In>::kElems;  // 4 (binary32) or 8 (bfloat16) elements per 16-byte vector
   const uint32_t nvec = (uint32_t)(cols / E);
   for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -1538,7 +1539,10 @@ quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, s
         int c[4];
         code4_int(f, d, ig, 0.0f, qmin, qmax, c);
         const uint32_t w = pack4i_s8(c);
-        for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint32_t*>(dst.p[k] + obase + (size_t)i * 4) = w;
+        if (multicast)
+          asm volatile("multimem.st.weak.global.b32 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 4), "r"(w) : "memory");
+        else
+          for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint32_t*>(dst.p[k] + obase + (size_t)i * 4) = w;
       } else {
         const float f0[4] = {bf16_bits_to_f32(wv[0] & 0xffffu), bf16_bits_to_f32(wv[0] >> 16),
                              bf16_bits_to_f32(wv[1] & 0xffffu), bf16_bits_to_f32(wv[1] >> 16)};
@@ -1548,7 +1552,11 @@ quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, s
         code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
         code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
         const uint2 w = make_uint2(pack4i_s8(c0), pack4i_s8(c1));
-        for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint2*>(dst.p[k] + obase + (size_t)i * 8) = w;
+        if (multicast)
+          asm volatile("multimem.st.weak.global.b64 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 8),
+                       "l"((unsigned long long)w.x | ((unsigned long long)w.y << 32)) : "memory");
+        else
+          for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint2*>(dst.p[k] + obase + (size_t)i * 8) = w;
       }
     }
   }
@@ -1561,7 +1569,10 @@ extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, 
                                       float* out_scale, void* stream) {
   if (rows == 0 || cols == 0) return LQ_OK;
   if (!x || !row_absmax || !outs) return fail(LQ_ERR_DEVICE, "lq_quantize_rows_bcast: null pointer");
-  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: 1..8 destinations");
+  // n_dst == -1: outs[0] is an NVSwitch multicast address (one multimem store reaches every rank)
+  const bool multicast = n_dst == -1;
+  if (multicast) n_dst = 1;
+  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: 1..8 destinations (or -1: multicast)");
   if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_quantize_rows_bcast: in_dtype");
   if (qmin < -128 || qmax > 127 || qmin >= qmax) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: grid outside int8");
   const size_t e = in_dtype == LQ_F32 ? 4 : 8;
@@ -1577,10 +1588,10 @@ extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, 
   cudaStream_t st = (cudaStream_t)stream;
   if (in_dtype == LQ_F32)
     quantize_rows_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, ldx, row_absmax, half, eps,
-                                                                 (float)qmin, (float)qmax, dst, n_dst, ldo, col0, out_scale);
+                                                                 (float)qmin, (float)qmax, dst, n_dst, multicast, ldo, col0, out_scale);
   else
     quantize_rows_bcast_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, ldx,
                                                                          row_absmax, half, eps, (float)qmin, (float)qmax,
-                                                                         dst, n_dst, ldo, col0, out_scale);
+                                                                         dst, n_dst, multicast, ldo, col0, out_scale);
   return check_cuda(cudaGetLastError(), "lq_quantize_rows_bcast launch");
 }

@@ -106,8 +106,9 @@ def gemm_s8_bcast(a, b, dst_ptrs, dst_shape, col0, *, out_dtype=torch.bfloat16, 
                   out_zp=None, qmin=0, qmax=0):
     """`gemm_s8` whose epilogue stores every tile into several `(M, ld)` buffers at column
     offset `col0`: `dst_ptrs` are raw device addresses (this GPU's buffer first, then the same
-    buffer on its peers, e.g. `_SymmetricMemory.buffer_ptrs`), `dst_shape = (M, ld)`.  The
-    caller synchronises the ranks before the buffers are read."""
+    buffer on its peers, e.g. `_SymmetricMemory.buffer_ptrs`) or ONE int, the buffer's NVSwitch
+    multicast address (`_SymmetricMemory.multicast_ptr`); `dst_shape = (M, ld)`.  The caller
+    synchronises the ranks before the buffers are read."""
     _lib.require_cuda(a, "activation codes")
     _lib.require_cuda(b, "weight codes")
     if a.dtype not in (torch.int8, torch.uint8) or b.dtype != torch.int8:
@@ -126,8 +127,13 @@ def gemm_s8_bcast(a, b, dst_ptrs, dst_shape, col0, *, out_dtype=torch.bfloat16, 
     keep: list = []
     e = _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
                   qmin, qmax, keep)
-    ptrs = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
     with torch.cuda.device(dev):
+        if isinstance(dst_ptrs, int):  # an NVSwitch multicast address: one store reaches every rank
+            _lib.check(_lib.load().lq_gemm_s8_multicast(
+                _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e), C.c_void_p(dst_ptrs),
+                int(dst_shape[1]), int(col0), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+            return
+        ptrs = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
         _lib.check(_lib.load().lq_gemm_s8_bcast(
             _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e), ptrs,
             len(dst_ptrs), int(dst_shape[1]), int(col0), _lib.ptr(_lib.status_word(dev)),

@@ -65,7 +65,7 @@ class PeerOutputs:
         self.rows, self.cols, self.dtype = rows, cols, dtype
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
-        self.bufs, self.ptrs = [], []
+        self.bufs, self.ptrs, self.mc_ptrs = [], [], []
         for _ in range(2):
             t = symm_mem.empty((rows, cols), dtype=dtype, device=device)
             h = symm_mem.rendezvous(t, self.group)
@@ -73,15 +73,22 @@ class PeerOutputs:
             # this GPU's buffer first, then the peers'
             self.ptrs.append([own] + [int(p) for r, p in enumerate(h.buffer_ptrs) if r != self.rank])
             self.bufs.append(t)
+            self.mc_ptrs.append(int(getattr(h, "multicast_ptr", 0) or 0))
             self._keep = getattr(self, "_keep", []) + [h]
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.turn = 0
 
-    def next(self):
-        """(local tensor, destination pointers) of the buffer to fill now."""
+    @property
+    def has_multicast(self) -> bool:
+        """The buffers are bound to an NVSwitch multicast object (one store reaches all ranks)."""
+        return all(p != 0 for p in self.mc_ptrs)
+
+    def next(self, multicast: bool = False):
+        """(local tensor, destinations) of the buffer to fill now: the list of every rank's
+        address (own first), or -- ``multicast=True`` -- the one multicast address."""
         i = self.turn
         self.turn ^= 1
-        return self.bufs[i], self.ptrs[i]
+        return self.bufs[i], (self.mc_ptrs[i] if multicast else self.ptrs[i])
 
     def fence(self) -> None:
         """All ranks' stores into the current buffer are complete and visible after this
@@ -114,12 +121,14 @@ def quantize_shard_bcast(x_shard: torch.Tensor, row_absmax: torch.Tensor, dst_pt
     rows, cols = x2.shape
     if out_scale is None:
         out_scale = torch.empty(rows, dtype=torch.float32, device=x2.device)
-    arr = (C.c_void_p * len(dst_ptrs))(*[C.c_void_p(int(p)) for p in dst_ptrs])
+    multicast = isinstance(dst_ptrs, int)  # an NVSwitch multicast address instead of a list
+    plist = [dst_ptrs] if multicast else list(dst_ptrs)
+    arr = (C.c_void_p * len(plist))(*[C.c_void_p(int(p)) for p in plist])
     with torch.cuda.device(x2.device):
         _lib.check(_lib.load().lq_quantize_rows_bcast(
             _lib.ptr(x2), _lib.code_of(x2.dtype), rows, cols, cols, _lib.ptr(row_absmax), qdtype.quant_min,
-            qdtype.quant_max, C.c_float(eps), arr, len(dst_ptrs), int(ldo), int(col0), _lib.ptr(out_scale),
-            _lib.stream_ptr(x2.device)))
+            qdtype.quant_max, C.c_float(eps), arr, -1 if multicast else len(plist), int(ldo), int(col0),
+            _lib.ptr(out_scale), _lib.stream_ptr(x2.device)))
     return out_scale
 
 

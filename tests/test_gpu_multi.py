@@ -75,11 +75,29 @@ def _worker(rank, world, port, ret):
                              act=_lib.ACT_SILU_GATE)
         ok = ok and torch.equal(h_local, h_full[:, sl])
         codes = PeerOutputs(m, ff, torch.int8, dev)
-        for _ in range(3):
-            buf, ptrs = codes.next()
+        for it in range(4):
+            # unicast peer stores, then (where the buffers have one) the NVSwitch multicast address
+            mc = it >= 2 and codes.has_multicast
+            buf, ptrs = codes.next(multicast=mc)
+            buf.fill_(77)
+            codes.fence()
             scales = quantize_shard_bcast(h_local, shard_absmax(h_local), ptrs, ff, rank * per)
             codes.fence()
             ok = ok and torch.equal(buf, want_codes) and torch.equal(scales, want_scales)
+        # the GEMM epilogue through the multicast address
+        outs = PeerOutputs(m, n, torch.bfloat16, dev)
+        if outs.has_multicast:
+            npr = n // world
+            for _ in range(2):
+                buf, mc_ptr = outs.next(multicast=True)
+                buf.fill_(0)
+                outs.fence()
+                QF.gemm_s8_bcast(a, wq[rank * npr:(rank + 1) * npr].contiguous(), mc_ptr, (m, n), rank * npr,
+                                 a_scale=s, b_scale=ws[rank * npr:(rank + 1) * npr].contiguous(),
+                                 bias=bias[rank * npr:(rank + 1) * npr].contiguous())
+                outs.fence()
+                ok = ok and torch.equal(buf, full)
+        ret["multicast"] = bool(codes.has_multicast)
         torch.cuda.synchronize()
         _lib.check_device_status(dev)
         ret[rank] = bool(ok)
