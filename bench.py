@@ -518,8 +518,12 @@ def run_b200_arm(args):
             "clocks": clocks,
             "streams": streams,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        if graph is not None:
+            # release the captured collectives before the communicator goes away
+            torch.cuda.synchronize()
+            graph.reset()
         dist.destroy_process_group()
     return 0
 
