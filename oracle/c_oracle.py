@@ -102,3 +102,27 @@ def gemm_i8(a, w):
     lib().lo_gemm_i8_i32(_p(a), C.c_int(int(a.dtype == np.int8)), _p(w), C.c_size_t(m),
                          C.c_size_t(n), C.c_size_t(k), _p(acc))
     return acc
+
+
+def histc(x, bins, lo, hi):
+    x = np.ascontiguousarray(np.asarray(x, dtype=np.float32).ravel())
+    out = np.empty(bins, dtype=np.float32)
+    lib().lo_histc_f32(_p(x), C.c_size_t(x.size), C.c_int(bins), C.c_double(lo), C.c_double(hi), _p(out))
+    return out
+
+
+def histogram_rebin(hist, old_min, old_max, new_min, new_max):
+    hist = np.ascontiguousarray(hist, dtype=np.float32)
+    out = np.empty_like(hist)
+    lib().lo_hist_rebin_f32(_p(hist), C.c_int(hist.size), C.c_double(old_min), C.c_double(old_max),
+                            C.c_double(new_min), C.c_double(new_max), _p(out))
+    return out
+
+
+def qfunctional(op, x, y, scale, zp, qmin, qmax):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.ascontiguousarray(np.broadcast_to(np.asarray(y, dtype=np.float32), x.shape))
+    out = np.empty_like(x)
+    lib().lo_qfunctional_f32(C.c_int({"add": 0, "mul": 1, "add_relu": 2}[op]), _p(x), _p(y), C.c_size_t(x.size),
+                             C.c_float(scale), C.c_float(zp), C.c_int(qmin), C.c_int(qmax), _p(out))
+    return out

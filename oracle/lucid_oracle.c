@@ -18,6 +18,7 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 /* clip: v < lo ? lo : (v > hi ? hi : v)   lucid/_C/backend/cpu/CpuBackend.h:6863-6892 */
 static inline float clipf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
@@ -141,4 +142,67 @@ void lo_gemm_i8_i32(const void* a, int a_signed, const int8_t* w, size_t M, size
       }
       acc[m * N + n] = s;
     }
+}
+
+/* ---- histogram observer ----------------------------------------------------------------
+ * histc: lucid/_C/ops/composite/Stats.cpp:47-91 over the counting loop of
+ * lucid/_C/backend/cpu/CpuBackend.h:13276-13318 (binary64 arithmetic, values outside
+ * [lo, hi] skipped, truncation, the top edge folded into the last bin; an empty range is taken
+ * from the data, a constant tensor gets [v, v + 1]).  Counts leave as binary32, as the reference
+ * casts them to the input dtype.  NaN elements are skipped. */
+void lo_histc_f32(const float* x, size_t n, int bins, double lo, double hi, float* out) {
+  if (lo == hi && n > 0) {
+    double mn = x[0], mx = x[0];
+    for (size_t i = 1; i < n; ++i) {
+      if (x[i] < mn) mn = x[i];
+      if (x[i] > mx) mx = x[i];
+    }
+    lo = mn, hi = mx;
+    if (lo == hi) hi = lo + 1.0;
+  }
+  const double step = (hi - lo) / (double)bins;
+  double* counts = (double*)calloc((size_t)bins, sizeof(double));
+  for (size_t i = 0; i < n; ++i) {
+    const double v = (double)x[i];
+    if (v != v || v < lo || v > hi) continue;
+    long long b = (long long)((v - lo) / step);
+    if (b >= bins) b = bins - 1;
+    counts[b] += 1.0;
+  }
+  for (int b = 0; b < bins; ++b) out[b] = (float)counts[b];
+  free(counts);
+}
+
+/* HistogramObserver._rebin, lucid/quantization/observer.py:786-817: binary32 centres of the old
+ * bins, their destination on the new grid (clipped, truncated), scatter-add in index order. */
+void lo_hist_rebin_f32(const float* hist, int bins, double old_min, double old_max, double new_min,
+                       double new_max, float* out) {
+  const float old_width = (float)((old_max - old_min) / bins);
+  const float new_width = (float)((new_max - new_min) / bins);
+  const float omin = (float)old_min, nmin = (float)new_min, top = (float)(bins - 1);
+  for (int b = 0; b < bins; ++b) out[b] = 0.0f;
+  for (int i = 0; i < bins; ++i) {
+    volatile float t = (float)i + 0.5f;
+    volatile float u = t * old_width;
+    volatile float centre = omin + u;
+    volatile float num = centre - nmin;
+    float raw = num / new_width;
+    raw = raw < 0.0f ? 0.0f : (raw > top ? top : raw);
+    const int dst = raw == raw ? (int)raw : 0;
+    volatile float acc = out[dst] + hist[i];
+    out[dst] = acc;
+  }
+}
+
+/* QFunctional.add / mul / add_relu, lucid/nn/quantized/functional_module.py:230-246: the
+ * binary32 merge, then fake_quantize (op 0 add, 1 mul, 2 relu(add)). */
+void lo_qfunctional_f32(int op, const float* x, const float* y, size_t n, float scale, float zp, int qmin,
+                        int qmax, float* out) {
+  for (size_t i = 0; i < n; ++i) {
+    volatile float t = op == 1 ? x[i] * y[i] : x[i] + y[i];
+    if (op == 2 && !(t > 0.0f)) t = 0.0f;
+    const float c = code_of(t, scale, zp, (float)qmin, (float)qmax);
+    volatile float d = c - zp;
+    out[i] = d * scale;
+  }
 }

@@ -280,3 +280,31 @@ def test_fake_quantize_module(golden):
     ws, wz = O.calculate_qparams(*O.per_channel_minmax_observe(golden["fqm_w"]), True, O.QINT8)
     assert np.array_equal(ws, golden["fqm_wscale"]) and np.array_equal(wz, golden["fqm_wzp"])
     assert np.array_equal(O.fake_quantize(golden["fqm_w"], ws, wz, -128, 127, ch_axis=0), golden["fqm_wy"])
+
+
+def test_c_restatement_of_histogram_and_merges(golden):
+    """The plain-C restatements agree with the NumPy ones and with the reference-made fixtures."""
+    g = np.random.default_rng(70)
+    for n, bins, lo, hi in [(10_000, 2048, 0.0, 0.0), (5_000, 100, -1.5, 2.25), (333, 7, -0.1, 0.1),
+                            (64, 16, 0.75, 0.75)]:
+        x = (g.standard_normal(n) * 2).astype(np.float32)
+        assert np.array_equal(CO.histc(x, bins, lo, hi), O.histc(x, bins, lo, hi))
+    assert np.array_equal(CO.histc(np.full(9, 0.75, np.float32), 8, 0, 0), O.histc(np.full(9, 0.75), 8, 0, 0))
+    # the fixtures' second batch widened the range: first histogram re-binned + second counts
+    lo0, hi0 = golden["hg_range0"].tolist()
+    lo1, hi1 = golden["hg_range1"].tolist()
+    reb = CO.histogram_rebin(golden["hg_hist0"], lo0, hi0, lo1, hi1)
+    assert np.array_equal(reb, O.histogram_rebin(golden["hg_hist0"], lo0, hi0, lo1, hi1))
+    assert np.array_equal(CO.histc(golden["hg_x1"], 2048, lo1, hi1) + reb, golden["hg_hist1"])
+    lo0, hi0 = golden["hc_range0"].tolist()  # a constant first batch: zero-width old range
+    lo1, hi1 = golden["hc_range1"].tolist()
+    assert np.array_equal(CO.histc(golden["hc_x1"], 256, lo1, hi1) +
+                          CO.histogram_rebin(golden["hc_hist0"], lo0, hi0, lo1, hi1), golden["hc_hist1"])
+    xf = O.dequantize(golden["qf_xq"], 0.04, 120.0)
+    yf = O.dequantize(golden["qf_yq"], 0.025, 0.0)
+    for tag in ("u8", "s8"):
+        sc, zp, qmin, qmax = golden[f"qf_{tag}_grid"].tolist()
+        for op in ("add", "mul", "add_relu"):
+            assert np.array_equal(CO.qfunctional(op, xf, yf, sc, zp, int(qmin), int(qmax)), golden[f"qf_{tag}_{op}"])
+        assert np.array_equal(CO.qfunctional("add", xf, 0.75, sc, zp, int(qmin), int(qmax)),
+                              golden[f"qf_{tag}_add_scalar"])
