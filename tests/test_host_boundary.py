@@ -206,3 +206,50 @@ def test_package_never_imports_the_oracle():
     code = ("import sys, lucid_b200, lucid_b200.nn.quantized, lucid_b200.quantization;"
             "assert not any(m == 'oracle' or m.startswith('oracle.') for m in sys.modules)")
     subprocess.check_call([sys.executable, "-c", code], cwd=ROOT)
+
+
+def test_workflow_routing_needs_no_gpu():
+    """prepare / prepare_qat / quantize_dynamic decide what to swap on the host."""
+    import lucid_b200.nn.qat as nnqat
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(8, 8)
+            self.act = torch.nn.Hardswish()
+            self.up = torch.nn.ConvTranspose2d(4, 4, 2)
+            self.skip = nnq.FloatFunctional()
+
+        def forward(self, x):
+            return self.skip.add(self.act(self.fc(x)), x)
+
+    ff = nnq.FloatFunctional()
+    a, b = torch.randn(4), torch.randn(4)
+    assert torch.equal(ff.add(a, b), a + b) and torch.equal(ff.add_relu(a, b), torch.relu(a + b))
+    assert torch.equal(ff.cat([a, b]), torch.cat([a, b])) and torch.equal(ff.mul_scalar(a, 2.0), a * 2.0)
+    prepared = Q.prepare(Block())
+    for name in ("fc", "act", "up", "skip"):
+        assert isinstance(getattr(prepared, name).activation_post_process, Q.HistogramObserver), name
+    assert not hasattr(prepared.skip, "_lq_hook") and hasattr(prepared.fc, "_lq_hook")
+    qat = Q.prepare_qat(Block())
+    assert type(qat.fc) is nnqat.Linear and qat.training
+    assert isinstance(qat.fc.weight_fake_quant, Q.FakeQuantize)
+    assert isinstance(qat.fc.activation_post_process.activation_post_process, Q.MovingAverageMinMaxObserver)
+    assert qat.fc.weight_fake_quant.ch_axis == 0 and qat.fc.activation_post_process.ch_axis is None
+    fq = Q.FakeQuantize()
+    assert fq.disable_observer() is fq and fq.disable_fake_quant()(a) is a
+    with pytest.raises(ValueError):
+        nnqat.Linear(4, 4)
+    with pytest.raises(ValueError):
+        nnq.EmbeddingBag(10, 4, mode="sun")
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        nnq.QFunctional(0.1, 0.0).add(a, b)
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        nnq.Embedding(10, 4)(torch.tensor([1, 2]))
+    with pytest.raises(lucid_b200.DeviceMismatch):
+        nnq.Sigmoid(0.1, 0.0)(a)
+    emb = nnq.Embedding(10, 4, padding_idx=0)
+    assert list(emb.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point"]
+    ct = nnq.ConvTranspose2d(4, 6, 3, stride=2)
+    assert tuple(ct.weight_int8.shape) == (4, 6, 3, 3) and ct.weight_ch_axis == 1
+    assert list(ct.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point", "bias", "scale", "zero_point"]
