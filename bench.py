@@ -149,20 +149,32 @@ def make_cpu_sample(tokens=128, row_fraction=8, seed=0):
     return sample, desc
 
 
-def cpu_threads():
+def host_cores():
     try:
-        from threadpoolctl import threadpool_info
-
-        n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
-        return max(n) if n else (os.cpu_count() or 1)
-    except Exception:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
         return os.cpu_count() or 1
+
+
+def use_all_host_cores():
+    """Give the BLAS under NumPy every core this process may run on, whatever OMP_NUM_THREADS
+    says (torch.distributed.run sets it to 1 for its children), and return the count in use."""
+    want = host_cores()
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+
+        threadpool_limits(limits=want, user_api="blas")
+        n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
+        return max(n) if n else 1
+    except Exception:
+        return 1
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    cores = use_all_host_cores()
     sample, desc = make_cpu_sample()
     for _ in range(max(args.warmup, 1)):
         cpu_reference_step(sample, None)
@@ -178,8 +190,9 @@ def run_reference_arm(args):
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": M_TOKENS, "d_model": D_MODEL, "d_ff": D_FF,
-                   "sharding": "none (host cores)"},
-        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+                   "n_qkv": N_QKV, "sharding": "none (host cores)",
+                   "l2": "bounded sample of the workload on the host cores"},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
                          "sample": desc + "; NumPy transcription of the reference float path "
                          "(the Accelerate engine cannot build on Linux)"},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -209,7 +222,6 @@ def run_b200_arm(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=180))
     peaks = load_peaks()
 
@@ -256,32 +268,32 @@ def run_b200_arm(args):
 
     gemm_events: list = []
     # N > 1: every GEMM's epilogue stores its column shard into all ranks' (M, N) buffers
-    # (symmetric memory, peer stores over NVLink) -- or, with --exchange nccl, the shards are
-    # all-gathered afterwards.
+    # (symmetric memory, peer stores over NVLink) and publishes a step count to the peers' flag
+    # words; consumers wait on the flags with a bounded device-side wait, so a step contains no
+    # collective call -- or, with --exchange nccl, the shards are all-gathered afterwards.
     p2p = world > 1 and args.exchange in ("p2p", "p2p-unicast")
-    peers = {}
+    peers, hidden, encoders, shard_inputs = {}, None, None, False
     if p2p:
-        from lucid_b200.nn.quantized.sharded import PeerOutputs
-
-        from lucid_b200.nn.quantized.sharded import quantize_shard_bcast, shard_absmax
+        from lucid_b200.nn.quantized.sharded import HiddenExchange, PeerOutputs, TokenShardedEncoder
 
         for name, cols in (("qkv", N_QKV), ("o", D_MODEL), ("d", D_MODEL)):
             peers[name] = PeerOutputs(M_TOKENS, cols, torch.bfloat16, dev)
-        # The hidden tensor is exchanged as int8 codes from 4 ranks up (measured: 6904 vs 6362
-        # TOPS at 8 ranks, 6400 vs 6176 at 4); at 2 ranks the extra abs-max all-reduce costs more
-        # than the halved bytes save (4266 vs 4516), so the bf16 tensor is exchanged there.
+        # The hidden tensor is exchanged as int8 codes from 4 ranks up (half the bytes, and the
+        # encode is sharded); at 2 ranks the extra abs-max exchange costs more than the halved
+        # bytes save, so the bf16 tensor is exchanged there.
         if world >= 4:
-            peers["hq"] = PeerOutputs(M_TOKENS, D_FF, torch.int8, dev)
-            h_scale = torch.empty(M_TOKENS, dtype=torch.float32, device=dev)
+            hidden = HiddenExchange(M_TOKENS, D_FF, dev)
         else:
             peers["h"] = PeerOutputs(M_TOKENS, D_FF, torch.bfloat16, dev)
+        # the three replicated input activations: each rank encodes 1/w of the token rows
+        shard_inputs = args.shard_encode == "on" or (args.shard_encode == "auto" and world >= 4)
+        encoders = [TokenShardedEncoder(M_TOKENS, D_MODEL, dev) for _ in range(3)]
 
     # NVSwitch multicast stores when the buffers are bound to a multicast object
-    # (measured: 6984 vs 6844 TOPS at 8 ranks; no gain at 2 and 4, where a unicast copy per peer is cheap)
     use_mc = bool(peers) and world >= 8 and args.exchange != "p2p-unicast" and \
         all(p.has_multicast for p in peers.values())
 
-    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, fence=True, gather=True):
+    def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, wait=False, gather=True):
         if record:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
             e0.record()
@@ -290,47 +302,56 @@ def run_b200_arm(args):
         else:
             buf, ptrs = peer.next(multicast=use_mc)
             QF.gemm_s8_bcast(a, w, ptrs, (peer.rows, peer.cols), rank * out.shape[1], a_scale=a_s,
-                             b_scale=w_s, act=act)
+                             b_scale=w_s, act=act, signal=peer.sync.signal_arg)
         if record:
             e1.record()
             gemm_events.append((e0, e1))
         if peer is not None:
-            # The fence (a 4-byte all-reduce) orders what follows on this stream after the peer
-            # stores of every rank.  It is needed before something consumes the gathered tensor:
-            # after the gate/up GEMM (its output is encoded next) and at the end of the step,
-            # where one fence covers the three result tensors.
-            if fence:
-                peer.fence()
+            # The wait orders what follows on this stream after the peer stores of every rank.  It
+            # is needed before something consumes the gathered tensor: after the gate/up GEMM (its
+            # output is encoded next); the three result tensors are waited for at the end of the step.
+            if wait:
+                peer.sync.wait()
             return buf
         return gather_columns(out) if (world > 1 and gather) else out
 
-    def step(xs, record=False):
-        """One pass of the hot path; returns the down-projection output."""
-        a, s = Q.quantize_per_token(xs[0], Q.qint8)
-        qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"), fence=False)
-        a, s = Q.quantize_per_token(xs[1], Q.qint8)
-        o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"), fence=False)
-        a, s = Q.quantize_per_token(xs[2], Q.qint8)
-        if "hq" in peers:
+    def encode(i, xs, local):
+        if encoders is not None and (shard_inputs or local):
+            return encoders[i](xs[i], multicast=use_mc, local=local)
+        return Q.quantize_per_token(xs[i], Q.qint8)
+
+    def step(xs, record=False, local=False):
+        """One pass of the hot path; returns the QKV, O and down-projection outputs.  `local`:
+        `xs` holds only this rank's 1/w of the token rows (the end-to-end path, where each rank
+        copies its rows in from the host)."""
+        a, s = encode(0, xs, local)
+        qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"))
+        a, s = encode(1, xs, local)
+        o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"))
+        a, s = encode(2, xs, local)
+        if hidden is not None:
             # The gate/up output only feeds the per-token encode of the down projection: keep the
-            # bf16 shard local, all-reduce the per-token abs-max (rows floats), encode the shard
-            # with the global scales and store the CODES into every rank's operand buffer -- half
-            # the exchanged bytes of the bf16 tensor, and the encode is sharded, not replicated.
+            # bf16 shard local, exchange the per-token abs-max of the shards (rows floats per rank),
+            # encode the shard with the global scales and store the CODES into every rank's operand
+            # buffer -- half the exchanged bytes of the bf16 tensor, and the encode is sharded.
             gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, gather=False)
-            am = shard_absmax(out_h)
-            a, ptrs = peers["hq"].next(multicast=use_mc)
-            s = quantize_shard_bcast(out_h, am, ptrs, D_FF, rank * out_h.shape[1], out_scale=h_scale)
-            peers["hq"].fence()
+            a, s = hidden(out_h, multicast=use_mc)
         else:
-            h = gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, peer=peers.get("h"))
+            h = gemm(a, s, w_gu, s_gu, out_h, act=_lib.ACT_SILU_GATE, record=record, peer=peers.get("h"), wait=True)
             a, s = Q.quantize_per_token(h, Q.qint8)
         # the down projection contracts over the full ffn width: K is not sharded
         d = gemm(a, s, w_d, s_d, out_d, record=record, peer=peers.get("d"))
+        for name in ("qkv", "o", "d"):
+            if name in peers:
+                peers[name].sync.wait()
         return qkv, o, d
 
-    # 4 per-token encodes + 4 GEMMs; with the fused shard encode: 3 encodes + 4 GEMMs + the
-    # shard's row range reduction + the broadcast encode (library collectives not counted)
-    launches_per_step = 9 if "hq" in peers else 8
+    # kernels of this library per step and rank: 4 per-token encodes + 4 GEMMs on one GPU; sharded:
+    # the exchange adds signal / wait kernels (one warp each) and the shard's abs-max pass
+    if not p2p:
+        launches_per_step = 8
+    else:
+        launches_per_step = 4 + 3 + (3 * 3 if shard_inputs else 3) + (6 if hidden is not None else 2)
 
     def barrier():
         if world > 1:
@@ -346,7 +367,8 @@ def run_b200_arm(args):
     # captured once in a CUDA graph and replayed (every rank must agree, or all stay eager).  Each
     # step ends with a fence across the ranks, so replaying the same buffers every step is safe.
     graph = None
-    if world > 1 and args.graph:
+    use_graph = args.graph == "on" or (args.graph == "auto" and p2p)
+    if world > 1 and use_graph:
         ok = 1
         try:
             side = torch.cuda.Stream(dev)
@@ -415,29 +437,67 @@ def run_b200_arm(args):
     tops = OPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
     _lib.check_device_status(dev)
 
+    # ---- parity of what the timed path produced (outside the timed region) ---------------
+    parity = parity_check(torch, dist, world, rank, dev, step, x_dev, peers, hidden,
+                          {"qkv": (w_qkv, s_qkv), "o": (w_o, s_o), "d": (w_d, s_d)}, out_h)
+    if parity["mismatches"] != 0:
+        print(f"rank {rank}: parity check failed: {parity}", file=sys.stderr)
+
     # ---- end to end: pinned host activations in, result out, public API --------------
     # Every step copies its three activations from pinned host memory and its result back;
     # lucid_b200.HostPipeline overlaps the copy legs of neighbouring steps with the compute.
     import lucid_b200
 
     # N > 1: the host link is shared by all GPUs of the box, so each rank copies only its 1/w of
-    # the token rows and the ranks all-gather the rest over NVLink; each rank returns its 1/w of
-    # the result rows (the full result reaches the host exactly once).
+    # the token rows in and its 1/w of the result rows out (the full result reaches the host
+    # exactly once).  With the p2p exchange the rank encodes just those rows and the codes travel
+    # over NVLink (token-sharded encode); with the NCCL exchange the bf16 rows are all-gathered.
     rows_per = M_TOKENS // world
     r0, r1 = rank * rows_per, (rank + 1) * rows_per
     host_in = [h[r0:r1] for h in host_x] if world > 1 else host_x
     host_res = host_out[r0:r1] if world > 1 else host_out
-    full_x = [torch.empty_like(t) for t in x_dev] if world > 1 else None
+    full_x = [torch.empty_like(t) for t in x_dev] if (world > 1 and not p2p) else None
+    e2e_graphs = {}
 
     def layer(x0, x1, x2):
-        if world > 1:
-            for full, shard in zip(full_x, (x0, x1, x2)):
-                dist.all_gather_into_tensor(full, shard)
-            return step(full_x)[2][r0:r1]
-        return step((x0, x1, x2))[2]
+        if world == 1:
+            return step((x0, x1, x2))[2]
+        if p2p:
+            g_out = e2e_graphs.get(x0.data_ptr())
+            if g_out is not None:
+                g_out[0].replay()
+                return g_out[1]
+            return step((x0, x1, x2), local=True)[2][r0:r1]
+        for full, shard in zip(full_x, (x0, x1, x2)):
+            dist.all_gather_into_tensor(full, shard)
+        return step(full_x)[2][r0:r1]
 
     pipe_e2e = lucid_b200.HostPipeline(layer, [x[r0:r1] for x in x_dev] if world > 1 else x_dev,
                                        torch.empty((rows_per, D_MODEL), dtype=torch.bfloat16, device=dev) if world > 1 else out_d, dev)
+    if graph is not None and p2p:
+        # one captured step per staging slot of the pipeline (the step reads the slot's buffers)
+        ok = 1
+        captured = {}
+        try:
+            for bufs in pipe_e2e.bufs_in:
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    step(bufs, local=True)
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize()
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph):
+                    y = step(bufs, local=True)[2][r0:r1]
+                captured[bufs[0].data_ptr()] = (gph, y)
+        except Exception as exc:  # noqa: BLE001 - stay eager on any capture failure
+            ok = 0
+            print(f"rank {rank}: end-to-end graph capture failed ({type(exc).__name__}: {exc})", file=sys.stderr)
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag) == 1:
+            e2e_graphs = captured
+        barrier()
     for _ in range(3):
         pipe_e2e.submit(host_in, host_res)
     pipe_e2e.drain()
@@ -468,6 +528,7 @@ def run_b200_arm(args):
     # ---- CPU baseline on a bounded sample (rank 0, N = 1 only) ------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = use_all_host_cores()
         sample, desc = make_cpu_sample()
         cpu_reference_step(sample, None)
         t0 = time.perf_counter()
@@ -476,9 +537,16 @@ def run_b200_arm(args):
             ops += cpu_reference_step(sample, None)
             reps += 1
         dt = time.perf_counter() - t0
-        cpu = {"value": ops / dt / 1e12, "unit": "TOPS", "cores": cpu_threads(), "kind": "port",
+        cpu = {"value": ops / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
                "sample": desc + f"; {reps} passes in {dt:.1f} s; NumPy transcription of the "
                "reference float path (its Accelerate engine cannot build on Linux)"}
+
+    # ---- the other BASELINE configurations and the library comparator (one GPU only) ----
+    configs, library_ref = None, None
+    if rank == 0 and world == 1:
+        configs = config_cases(torch, dev, peaks, iters=20)
+        library_ref = library_int8_gemm(torch, dev, {"qkv": (w_qkv, None), "o": (w_o, None), "gate_up": (w_gu, None),
+                                                      "down": (w_d, None)})
 
     if rank == 0:
         gemm_ops_per_launch = OPS_PER_STEP / 4 / world
@@ -516,16 +584,225 @@ def run_b200_arm(args):
                               "1/w of the result rows out" if world > 1 else "")},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
+            "parity_check": parity,
             "streams": streams,
+            "configs": configs,
         }
+        line["roofline"]["library_ref"] = library_ref
         print(json.dumps(line), flush=True)
     if world > 1:
-        if graph is not None:
-            # release the captured collectives before the communicator goes away
-            torch.cuda.synchronize()
-            graph.reset()
+        torch.cuda.synchronize()
+        for gph in [graph] + [v[0] for v in e2e_graphs.values()]:
+            if gph is not None:
+                gph.reset()
         dist.destroy_process_group()
-    return 0
+    return 0 if parity["mismatches"] == 0 else 1
+
+
+def exact_rows_gemm(xq, w_dev, torch, slab=2048):
+    """Exact int32 `xq (r, K) @ w (N, K)^T` on the host, the weight fetched in slabs of rows."""
+    from oracle import lucid_oracle as O
+
+    out = np.empty((xq.shape[0], w_dev.shape[0]), dtype=np.int32)
+    for n0 in range(0, w_dev.shape[0], slab):
+        out[:, n0:n0 + slab] = O.int_gemm_exact(xq, w_dev[n0:n0 + slab].cpu().numpy())
+    return out
+
+
+def parity_check(torch, dist, world, rank, dev, step, x_dev, peers, hidden, weights, out_h, n_rows=32):
+    """Run one more step and compare `n_rows` sampled token rows of what every rank holds after
+    the exchange with the CPU oracle: QKV, O and down outputs bit for bit (bf16 = the f32
+    epilogue rounded once), and -- where the hidden tensor travels as codes -- its codes and
+    scales against the oracle's per-token encode of the device's own hidden values.  Each rank
+    computes the oracle for its own weight shard; the shards are all-gathered (a few hundred KB)
+    so that every rank checks ALL columns of its buffers, the peers' contributions included."""
+    from oracle import lucid_oracle as O
+
+    import lucid_b200.quantization as Q
+
+    rows = np.sort(np.random.default_rng(7).choice(M_TOKENS, n_rows, replace=False))
+    rows_t = torch.from_numpy(rows).to(dev)
+    qkv, o, d = step(x_dev)
+    torch.cuda.synchronize()
+
+    def f32(t):
+        return t.float().cpu().numpy()
+
+    def gathered(local_block):
+        """(n_rows, n_local) float32 oracle block of this rank -> (n_rows, N) of all ranks."""
+        if world == 1:
+            return local_block
+        t = torch.from_numpy(np.ascontiguousarray(local_block)).to(dev)
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        return torch.cat(parts, dim=1).cpu().numpy()
+
+    mismatches, detail = 0, {}
+    for name, got, xin in (("qkv", qkv, x_dev[0]), ("o", o, x_dev[1])):
+        xq, xs = O.per_token_quantize(f32(xin[rows_t]))
+        w, ws = weights[name]
+        ref = O.bf16_round(O.epilogue_f32(exact_rows_gemm(xq, w, torch), xs, 0, None, ws.cpu().numpy(), None))
+        bad = int((f32(got[rows_t]) != gathered(ref)).sum())
+        detail[name] = bad
+        mismatches += bad
+    # hidden tensor: the device's own bf16 values (SiLU goes through a library exp, so the values
+    # are compared with a tolerance elsewhere); their per-token encode must be exact
+    if hidden is not None:
+        h_rows = gathered(f32(out_h[rows_t]))
+        hq_ref, hs_ref = O.per_token_quantize(h_rows)
+        hq_got = hidden.out.bufs[0][rows_t].cpu().numpy()
+        hs_got = hidden.scale[rows_t].cpu().numpy()
+        bad = int((hq_got != hq_ref).sum()) + int((hs_got != hs_ref.astype(np.float32)).sum())
+        detail["hidden_codes"] = bad
+        mismatches += bad
+        hq, hs = hq_got, hs_got
+    else:
+        h_full = peers["h"].bufs[(peers["h"].turn - 1) % len(peers["h"].bufs)] if "h" in peers else out_h
+        hq_t, hs_t = Q.quantize_per_token(h_full[rows_t].contiguous(), Q.qint8)
+        hq_ref, hs_ref = O.per_token_quantize(f32(h_full[rows_t]))
+        hq, hs = hq_t.cpu().numpy(), hs_t.cpu().numpy()
+        bad = int((hq != hq_ref).sum()) + int((hs != hs_ref.astype(np.float32)).sum())
+        detail["hidden_codes"] = bad
+        mismatches += bad
+    w, ws = weights["d"]
+    ref = O.bf16_round(O.epilogue_f32(exact_rows_gemm(hq, w, torch), hs, 0, None, ws.cpu().numpy(), None))
+    bad = int((f32(d[rows_t]) != gathered(ref)).sum())
+    detail["d"] = bad
+    mismatches += bad
+    if world > 1:
+        t = torch.tensor([mismatches], dtype=torch.int64, device=dev)
+        dist.all_reduce(t)
+        mismatches = int(t)
+    return {"rows": n_rows, "mismatches": mismatches, "per_tensor_rank0": detail,
+            "checked": "qkv, o, hidden codes + scales, down: bit-exact vs the CPU oracle on every rank's full buffers"}
+
+
+def library_int8_gemm(torch, dev, weights, iters=10):
+    """cuBLASLt's s8 GEMM (`torch._int_mm`, int32 out, no epilogue) on the four projection shapes,
+    timed in this process right after the timed region: the library comparator of the roofline
+    block.  Never on the product path."""
+    out = {}
+    total_ops, total_s = 0.0, 0.0
+    for name, (w, _) in weights.items():
+        n, k = w.shape
+        a = torch.randint(-128, 128, (M_TOKENS, k), dtype=torch.int8, device=dev)
+        wt = w.t()  # (K, N) column-major view: the layout _int_mm takes without a copy
+        try:
+            for _ in range(3):
+                torch._int_mm(a, wt)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            for _ in range(iters):
+                torch._int_mm(a, wt)
+            e1.record()
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001 - a comparator that cannot run is reported, not fatal
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            continue
+        sec = e0.elapsed_time(e1) / iters * 1e-3
+        ops = 2.0 * M_TOKENS * n * k
+        out[name] = {"ms": sec * 1e3, "TOPS": ops / sec / 1e12}
+        total_ops += ops
+        total_s += sec
+    if total_s > 0:
+        out["all_four"] = {"TOPS": total_ops / total_s / 1e12}
+    out["what"] = "torch._int_mm (cuBLASLt s8 x s8 -> s32, no epilogue) on the same shapes, same process, after the timed region"
+    return out
+
+
+def config_cases(torch, dev, peaks, iters=20):
+    """Device-resident timings of BASELINE configurations 2-4 with their own rooflines:
+    config 2 dynamic Linear and config 3 gated MLP against the tensor peak, config 4's conv stack
+    per layer (the 1x1 layers against HBM with their algorithmic bytes, the 3x3 against the tensor
+    peak).  Timed as a loop of eager calls with CUDA events; inputs rotate where they would
+    otherwise sit in L2 (config 4's activations are a few MB: they are L2-resident between
+    layers by design, as in a real stack)."""
+    import lucid_b200.nn.quantized as nnq
+    from lucid_b200 import _lib
+    from lucid_b200.nn.quantized import functional as QF
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    tensor_peak = 2.0 * peaks["bf16_burst"]  # kernels timed alone: the burst figure
+
+    def timed(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def tensor_block(ms, ops):
+        t = ops / ms / 1e9
+        return {"ms": ms, "TOPS": t, "bound": "tensor", "peak_TOPS": tensor_peak, "frac": t / tensor_peak,
+                "frac_of_nominal_4500": t / 4500.0}
+
+    out = {}
+    # config 2: dynamic Linear, f32 in/out (range reduction + qparams + u8 encode + GEMM)
+    lin = torch.nn.Linear(4096, 4096).to(dev)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(4096, 4096, device=dev, generator=g) * 0.02)
+        lin.bias.copy_(torch.randn(4096, device=dev, generator=g) * 0.01)
+    qlin = nnq.dynamic.Linear.from_float(lin)
+    x2 = torch.randn(2048, 4096, device=dev, generator=g)
+    out["c2_dynamic_linear"] = tensor_block(timed(lambda: qlin(x2), iters), 2 * 2048 * 4096 * 4096)
+    out["c2_dynamic_linear"]["what"] = "module forward: fused min-max + qparams + u8 encode, GEMM with zero-point correction + bias, f32 out"
+    del lin, qlin, x2
+    # config 3: gated MLP block, bf16
+    d, ff = 4096, 11008
+    mlp = nnq.dynamic.GatedMLP.from_float(torch.randn(ff, d, device=dev, generator=g) * 0.02,
+                                          torch.randn(ff, d, device=dev, generator=g) * 0.02,
+                                          torch.randn(d, ff, device=dev, generator=g) * 0.02)
+    x3 = torch.randn(8, 512, d, device=dev, generator=g).to(torch.bfloat16)
+    out["c3_gated_mlp"] = tensor_block(timed(lambda: mlp(x3), iters), 3 * 2 * 4096 * d * ff)
+    out["c3_gated_mlp"]["what"] = "2 per-token encodes + gate/up GEMM with SiLU-gate epilogue + down GEMM, bf16"
+    del mlp, x3
+    # config 4: conv stack on codes, fused bias + ReLU + requantise
+    n, h, w = 64, 28, 28
+    a = torch.randint(-127, 128, (n, h, w, 512), dtype=torch.int8, device=dev, generator=g)
+    layers = []
+    for cin, cout, r, pad in ((512, 256, 1, 0), (256, 256, 3, 1), (256, 1024, 1, 0)):
+        wq = torch.randint(-127, 128, (cout, r, r, cin), dtype=torch.int8, device=dev, generator=g)
+        layers.append((wq, torch.rand(cout, device=dev) * 1e-3 + 1e-4, torch.randn(cout, device=dev) * 0.01, pad))
+    one = torch.tensor(0.02, device=dev)
+    zero = torch.tensor(0.0, device=dev)
+
+    def conv(t, wq, ws, b, pad):
+        return QF.conv2d_nhwc_s8(t, wq, pad=pad, out_dtype=torch.uint8, a_scale=one, b_scale=ws, bias=b,
+                                 act=_lib.ACT_RELU, out_scale=one, out_zp=zero, qmin=0, qmax=255)
+
+    def conv_stack():
+        t = a
+        for wq, ws, b, pad in layers:
+            t = conv(t, wq, ws, b, pad)
+        return t
+
+    ms = timed(conv_stack, iters)
+    px = n * h * w
+    ops = [2 * px * 512 * 256, 2 * px * 9 * 256 * 256, 2 * px * 256 * 1024]
+    nbytes = [px * 512 + 512 * 256 + px * 256, px * 256 + 9 * 256 * 256 + px * 256, px * 256 + 256 * 1024 + px * 1024]
+    stack = {"ms": ms, "TOPS": sum(ops) / ms / 1e9, "layers": []}
+    t = a
+    for i, (wq, ws, b, pad) in enumerate(layers):
+        lms = timed(lambda t=t, wq=wq, ws=ws, b=b, pad=pad: conv(t, wq, ws, b, pad), iters)
+        if i == 1:
+            blk = tensor_block(lms, ops[i])
+        else:
+            gbs = nbytes[i] / lms / 1e6
+            blk = {"ms": lms, "TOPS": ops[i] / lms / 1e9, "bound": "hbm", "GB/s": gbs, "peak_GB/s": peaks["hbm_gbs"],
+                   "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes": nbytes[i]}
+        blk["layer"] = ("1x1 512->256", "3x3 256->256", "1x1 256->1024")[i]
+        stack["layers"].append(blk)
+        t = conv(t, wq, ws, b, pad)
+    stack["what"] = "N=64, 28x28 NHWC codes; per-layer launches timed alone (inputs of a few MB stay in L2 between layers)"
+    out["c4_conv_stack"] = stack
+    _lib.check_device_status(dev)
+    return out
 
 
 def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
@@ -709,83 +986,12 @@ def run_single_kernel_case(args):
 
 
 def run_config_cases(args):
-    """Device-resident timings of the other BASELINE configurations (parity-test cases, not
-    bench lines): config 2 dynamic Linear, config 3 gated MLP block, config 4 conv stack."""
+    """`--case configs`: configurations 2-4 alone (the default run carries the same block)."""
     import torch
-
-    import lucid_b200.nn.quantized as nnq
-    import lucid_b200.quantization as Q
-    from lucid_b200 import _lib
-    from lucid_b200.nn.quantized import functional as QF
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    g = torch.Generator(device=dev).manual_seed(0)
-
-    def timed(fn, iters):
-        for _ in range(5):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters
-
-    out = {}
-    # config 2: dynamic Linear, f32 in/out (range reduction + qparams + encode + GEMM)
-    lin = torch.nn.Linear(4096, 4096).to(dev)
-    with torch.no_grad():
-        lin.weight.copy_(torch.randn(4096, 4096, device=dev, generator=g) * 0.02)
-        lin.bias.copy_(torch.randn(4096, device=dev, generator=g) * 0.01)
-    qlin = nnq.dynamic.Linear.from_float(lin)
-    x2 = torch.randn(2048, 4096, device=dev, generator=g)
-    ms = timed(lambda: qlin(x2), args.steps)
-    out["config2_dynamic_linear"] = {"ms": ms, "TOPS": 2 * 2048 * 4096 * 4096 / ms / 1e9,
-                                     "note": "module forward: min-max, qparams, u8 encode, GEMM with zero-point correction + bias, f32 out"}
-    # config 3: gated MLP block, bf16
-    d, ff = 4096, 11008
-    mlp = nnq.dynamic.GatedMLP.from_float(torch.randn(ff, d, device=dev, generator=g) * 0.02,
-                                          torch.randn(ff, d, device=dev, generator=g) * 0.02,
-                                          torch.randn(d, ff, device=dev, generator=g) * 0.02)
-    x3 = torch.randn(8, 512, d, device=dev, generator=g).to(torch.bfloat16)
-    ms = timed(lambda: mlp(x3), args.steps)
-    out["config3_gated_mlp"] = {"ms": ms, "TOPS": 3 * 2 * 4096 * d * ff / ms / 1e9,
-                                "note": "2 per-token encodes + gate/up GEMM with SiLU-gate epilogue + down GEMM, bf16"}
-    # config 4: conv stack on codes, fused bias + ReLU + requantise
-    n, h, w = 64, 28, 28
-    a = torch.randint(-127, 128, (n, h, w, 512), dtype=torch.int8, device=dev, generator=g)
-    layers = []
-    for cin, cout, r, pad in ((512, 256, 1, 0), (256, 256, 3, 1), (256, 1024, 1, 0)):
-        wq = torch.randint(-127, 128, (cout, r, r, cin), dtype=torch.int8, device=dev, generator=g)
-        layers.append((wq, torch.rand(cout, device=dev) * 1e-3 + 1e-4, torch.randn(cout, device=dev) * 0.01, pad))
-    one = torch.tensor(0.02, device=dev)
-    zero = torch.tensor(0.0, device=dev)
-
-    def conv_stack():
-        t = a
-        for wq, ws, b, pad in layers:
-            t = QF.conv2d_nhwc_s8(t, wq, pad=pad, out_dtype=torch.uint8, a_scale=one, b_scale=ws, bias=b,
-                                  act=_lib.ACT_RELU, out_scale=one, out_zp=zero, qmin=0, qmax=255)
-        return t
-
-    ms = timed(conv_stack, args.steps)
-    ops = 2 * n * h * w * (512 * 256 + 9 * 256 * 256 + 256 * 1024)
-    out["config4_conv_stack"] = {"ms": ms, "TOPS": ops / ms / 1e9,
-                                 "note": "1x1 512->256, 3x3 256->256, 1x1 256->1024 on NHWC codes, N=64, 28x28"}
-    per = []
-    t = a
-    for wq, ws, b, pad in layers:
-        f = lambda t=t, wq=wq, ws=ws, b=b, pad=pad: QF.conv2d_nhwc_s8(
-            t, wq, pad=pad, out_dtype=torch.uint8, a_scale=one, b_scale=ws, bias=b, act=_lib.ACT_RELU,
-            out_scale=one, out_zp=zero, qmin=0, qmax=255)
-        per.append(timed(f, args.steps) * 1e3)
-        t = f()
-    out["config4_conv_stack"]["layer_us"] = per
-    _lib.check_device_status(dev)
-    print(json.dumps({"case": "configs", "configs": out}))
+    print(json.dumps({"case": "configs", "configs": config_cases(torch, dev, load_peaks(), iters=args.steps)}))
     return 0
 
 
@@ -799,9 +1005,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--graph", action="store_true",
-                    help="N > 1: capture the step in a CUDA graph and replay it (off by default: measured "
-                         "4601 vs 4505 TOPS at 2 ranks, but the process did not exit after printing its line)")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1: capture the step in a CUDA graph and replay it (auto: with the p2p exchange, "
+                         "whose step holds no collective call)")
+    ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
+                         "(auto: from 4 ranks)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-unicast", "nccl"],
                     help="N > 1: fused epilogue stores into every rank's buffer (default; through NVSwitch "
                          "multicast when the buffers are bound to a multicast object, 'p2p-unicast' forces one "

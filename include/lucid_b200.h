@@ -61,12 +61,23 @@ int lq_version(void);
 /* Copies the calling thread's last error text (NUL terminated) into buf. */
 int lq_last_error(char* buf, size_t n);
 
+/* The library reads its LQ_* environment knobs (LQ_GEMM_SHAPE, LQ_GEMM_EPI_WARPS,
+ * LQ_GEMM_STREAMK, LQ_GEMM_VERBOSE: force a tile shape / epilogue width / schedule of the
+ * contraction, all numerically identical) once, at first use; this re-reads them (tests switch
+ * variants inside one process). */
+void lq_reload_env(void);
+
 /* ---- calibration ------------------------------------------------------- */
 
 /* Bytes of workspace lq_minmax needs for the per-tensor mode.  The workspace
  * must be zero-filled once before its first use; the kernel leaves it zeroed
  * again, so it can be reused by later calls on the same stream. */
 size_t lq_minmax_workspace_bytes(void);
+
+/* Number of launches of the bulk-copy pipelined stream kernels (dequantize, per-token encode of
+ * long rows) on the current device that gave up on a bounded wait since the last call; the
+ * count is cleared.  Such a launch left its output incomplete.  Synchronises the device. */
+int lq_stream_timeouts(unsigned int* count);
 
 /* Running-range reduction.
  * Replaces MinMaxObserver.forward (lucid/quantization/observer.py:364-370; the
@@ -239,6 +250,20 @@ typedef struct lq_epilogue {
 int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
                const lq_epilogue_t* ep, void* out, size_t ldo, int32_t* status, void* stream);
 
+/* Bytes of scratch lq_gemm_s8_ws / lq_gemm_s8_sharded / lq_conv2d_nhwc_s8_ex can use (about
+ * 24 MB: one 128 x 256 int32 partial tile per SM plus a 4 KB header).  Zero-fill it once before
+ * its first use; every launch leaves it zeroed again.  One workspace serves one stream at a time.
+ * After a call reported LQ_ERR_TIMEOUT through its status word, zero the workspace again. */
+size_t lq_gemm_workspace_bytes(void);
+
+/* lq_gemm_s8 with a scratch workspace: when the tile count does not fill whole waves of SMs,
+ * the k-blocks of all tiles are dealt out in equal contiguous runs ("stream-K") and tiles cut
+ * by a run boundary are completed from int32 partial sums in the workspace (integer addition,
+ * so the result is bit-identical to lq_gemm_s8).  workspace == NULL behaves as lq_gemm_s8. */
+int lq_gemm_s8_ws(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                  const lq_epilogue_t* ep, void* out, size_t ldo, void* workspace,
+                  size_t workspace_bytes, int32_t* status, void* stream);
+
 /* The same contraction with the exchange step of an output-channel-sharded Linear fused
  * into its epilogue: every finished tile is stored into ALL `n_dst` destinations (1..8), each
  * the base of a row-major (M, ldo) buffer, at column offset `col0`.  outs[0] is normally this
@@ -254,18 +279,38 @@ int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, size_t M, siz
 
 /* Per-token symmetric int8 encode of a COLUMN SHARD with the exchange fused in: row r of
  * x (rows x cols, row stride ldx; LQ_F32 | LQ_BF16) is encoded with
- * scale[r] = max(row_absmax[r] / ((qmax - qmin) / 2), eps) -- the expressions of
+ * scale[r] = max(absmax[r] / ((qmax - qmin) / 2), eps) -- the expressions of
  * lq_quantize_per_token -- and the codes are stored at columns [col0, col0 + cols) of every
  * one of the n_dst (1..8) row-major (rows, ldo) int8 destinations: this GPU's buffer and the
- * peers' copies mapped into this process (plain peer stores over NVLink).  row_absmax is the
- * per-token max |x| over ALL shards (the caller all-reduces the per-shard maxima from lq_minmax,
- * mode LQ_PER_ROW; max is order-free, so the scales and codes equal the single-GPU encode of
- * the unsharded tensor bit for bit).  out_scale (optional): rows floats.  `outs` is a HOST
- * array of device pointers.  No counterpart in the reference, which has no distributed code. */
+ * peers' copies mapped into this process (plain peer stores over NVLink; n_dst = -1: outs[0] is
+ * the buffer's NVSwitch multicast address).  absmax[r] is the per-token max |x| over ALL shards:
+ * the maximum of row_absmax[p * absmax_stride + r] over p < absmax_parts, one part per rank
+ * (filled by lq_absmax_rows_bcast, or one part holding an all-reduced value; max is order-free,
+ * so the scales and codes equal the single-GPU encode of the unsharded tensor bit for bit).
+ * out_scale (optional): rows floats.  `outs` is a HOST array of device pointers.  No
+ * counterpart in the reference, which has no distributed code. */
 int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
-                           const float* row_absmax, int qmin, int qmax, float eps,
-                           void* const* outs, int n_dst, size_t ldo, size_t col0,
-                           float* out_scale, void* stream);
+                           const float* row_absmax, int absmax_parts, size_t absmax_stride,
+                           int qmin, int qmax, float eps, void* const* outs, int n_dst, size_t ldo,
+                           size_t col0, float* out_scale, void* stream);
+
+/* Per-row max |x| of a column shard (rows x cols, row stride ldx), stored at
+ * outs[k][slot0 + r] for each of the n_dst (1..8) float tables: the max all-reduce that the
+ * sharded per-token encode needs, as plain peer stores (rank p passes slot0 = p * rows, and
+ * lq_quantize_rows_bcast reads the table with absmax_parts = ranks).  No counterpart in the
+ * reference. */
+int lq_absmax_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
+                         float* const* outs, int n_dst, size_t slot0, void* stream);
+
+/* lq_quantize_per_token of a ROW shard of a replicated activation with the exchange fused in:
+ * this rank encodes its `rows` rows (cols % 16 == 0, contiguous) and stores the codes at rows
+ * [row0, row0 + rows) of each of the n_dst (1..8) (total_rows, cols) int8 buffers in `outs` --
+ * or once through multicast_out, the buffer's NVSwitch multicast address, when that is not
+ * NULL -- and the scales at scale_outs[k][row0 + r].  Each rank thus encodes 1 / ranks of the
+ * tokens instead of all of them.  No counterpart in the reference. */
+int lq_quantize_per_token_bcast(const void* x, int in_dtype, size_t rows, size_t cols, int qmin, int qmax,
+                                float eps, void* const* outs, float* const* scale_outs, int n_dst,
+                                void* multicast_out, size_t row0, void* stream);
 
 /* lq_gemm_s8_bcast through NVSwitch multicast: `multicast_out` is the multicast address of a
  * row-major (M, ldo) buffer that every rank of the group has bound (CUDA multicast object /
@@ -279,6 +324,36 @@ int lq_gemm_s8_multicast(const void* a, int a_signed, const int8_t* b, size_t M,
                          const lq_epilogue_t* ep, void* multicast_out, size_t ldo, size_t col0,
                          int32_t* status, void* stream);
 
+/* lq_gemm_s8_bcast / lq_gemm_s8_multicast plus the signal of the exchange step, so that no
+ * collective has to follow the kernel: once every CTA has stored its tiles, the kernel adds 1 to
+ * *signal_counter (a device word of this rank, zero before the first step) and stores the new
+ * value, with release semantics at system scope, into each of the n_flags (<= 8) addresses in
+ * `peer_flags` -- this rank's flag word on every rank that consumes the buffer (its own
+ * included), e.g. element `rank` of a flags array in symmetric memory.  Consumers wait with
+ * lq_peer_wait.  n_dst = 1..8: `outs` holds that many destinations (plain peer stores);
+ * n_dst = -1: outs[0] is the buffer's NVSwitch multicast address.  `outs` and `peer_flags` are
+ * HOST arrays of device pointers.  The workspace (lq_gemm_workspace_bytes) is required.  No
+ * counterpart in the reference, which has no distributed code. */
+int lq_gemm_s8_sharded(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                       const lq_epilogue_t* ep, void* const* outs, int n_dst, size_t ldo, size_t col0,
+                       int32_t* const* peer_flags, int n_flags, int32_t* signal_counter,
+                       void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* Signal without a GEMM: a one-thread kernel that adds 1 to *signal_counter and stores the new
+ * value (release, system scope) into the n_flags addresses; everything enqueued on `stream`
+ * before it -- e.g. an encode kernel that stored into the peers' buffers -- has completed by then. */
+int lq_peer_signal(int32_t* const* peer_flags, int n_flags, int32_t* signal_counter, void* stream);
+
+/* Consumer side of the exchange: a one-warp kernel that adds 1 to *epoch (a device word of this
+ * rank, zero before the first step) and waits until each of the n (<= 32) words flags[0..n) has
+ * reached the new value (acquire loads at system scope; the producers count steps the same
+ * way, so the comparison is "at least").  Work enqueued on `stream` after it sees every store
+ * the producers made before their signals.  The wait is bounded: after timeout_cycles SM clock
+ * cycles (0 = about one second) the kernel gives up, writes LQ_ERR_TIMEOUT to *status (optional)
+ * and returns; nothing traps or spins forever. */
+int lq_peer_wait(const int32_t* flags, int n, int32_t* epoch, long long timeout_cycles,
+                 int32_t* status, void* stream);
+
 /* sum_k b[n,k] for the zero-point correction term (N ints). */
 int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream);
 
@@ -291,6 +366,28 @@ int lq_rowsum_s8(const int8_t* b, size_t N, size_t K, int32_t* out, void* stream
 int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H, size_t W,
                       size_t C, size_t K, size_t R, size_t S, size_t stride, size_t pad,
                       const lq_epilogue_t* ep, void* out, int32_t* status, void* stream);
+
+/* General geometry of the NHWC convolution: what nn.quantized.Conv2d accepts
+ * (lucid/nn/quantized/conv.py:119-184: stride, dilation, groups, explicit or "same" padding).
+ * x: (N, H, W, C) codes; w: (K, R, S, C / groups) signed codes, the filters of group g at rows
+ * [g*K/groups, (g+1)*K/groups); out: (N, P, Q, K).
+ *   out[n,p,q,k] = epilogue(sum_{r,s,c} x[n, p*stride_h + r*dil_h - pad_h,
+ *                                         q*stride_w + s*dil_w - pad_w, g(k)*C/groups + c] * w[k,r,s,c])
+ * pad_h / pad_w are the padding BEFORE the first row / column; rows and columns past the far edge
+ * read code 0 as well, so an asymmetric "same" padding is expressed by P and Q alone.
+ * C / groups must be a multiple of 16. */
+typedef struct lq_conv_geometry {
+  size_t N, H, W, C;       /* input                                          */
+  size_t K, R, S;          /* filters                                        */
+  size_t P, Q;             /* output extent                                  */
+  size_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, groups;
+} lq_conv_geometry_t;
+
+/* lq_conv2d_nhwc_s8 for any stride (<= 8), dilation, group count and padding, with an optional
+ * workspace as for lq_gemm_s8_ws (NULL: none).  One launch per group. */
+int lq_conv2d_nhwc_s8_ex(const void* x, int x_signed, const int8_t* w, const lq_conv_geometry_t* geometry,
+                         const lq_epilogue_t* ep, void* out, void* workspace, size_t workspace_bytes,
+                         int32_t* status, void* stream);
 
 /* ---- element-wise ops of the quantized region ----------------------------------------- */
 

@@ -15,6 +15,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "liblucid_b200.so")
+TEST_LIB_PATH = os.path.join(_HERE, "csrc", "liblucid_b200_testing.so")
 
 # dtype / mode codes of include/lucid_b200.h
 F32, BF16, S8, U8, S16, S32 = 0, 1, 2, 3, 4, 5
@@ -54,6 +55,14 @@ _STATUS_EXC = {1: ShapeMismatch, 2: DtypeMismatch, 3: DeviceMismatch, 4: ShapeMi
                5: NotImplementedError, 6: LucidError, 7: LucidError, 8: TimeoutError}
 
 
+class ConvGeometry(C.Structure):
+    """``lq_conv_geometry_t``."""
+
+    _fields_ = [(n, C.c_size_t) for n in
+                ("N", "H", "W", "C", "K", "R", "S", "P", "Q", "stride_h", "stride_w", "pad_h", "pad_w",
+                 "dil_h", "dil_w", "groups")]
+
+
 class Epilogue(C.Structure):
     _fields_ = [
         ("out_dtype", C.c_int32), ("act", C.c_int32), ("a_scale_mode", C.c_int32),
@@ -67,7 +76,27 @@ class Epilogue(C.Structure):
 _SIGNATURES = {
     "lq_version": (C.c_int, []),
     "lq_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
+    "lq_reload_env": (None, []),
     "lq_minmax_workspace_bytes": (C.c_size_t, []),
+    "lq_stream_timeouts": (C.c_int, [C.POINTER(C.c_uint)]),
+    "lq_gemm_workspace_bytes": (C.c_size_t, []),
+    "lq_gemm_s8_ws": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
+                                C.c_void_p]),
+    "lq_gemm_s8_sharded": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                     C.POINTER(Epilogue), C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_size_t,
+                                     C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p, C.c_size_t,
+                                     C.c_void_p, C.c_void_p]),
+    "lq_peer_signal": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p]),
+    "lq_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p]),
+    "lq_absmax_rows_bcast": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t,
+                                       C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_void_p]),
+    "lq_quantize_per_token_bcast": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_int,
+                                              C.c_float, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
+                                              C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lq_conv2d_nhwc_s8_ex": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(ConvGeometry),
+                                       C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                       C.c_void_p]),
     "lq_minmax": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.c_void_p,
                             C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "lq_minmax_noalloc_max_elems": (C.c_size_t, []),
@@ -111,7 +140,7 @@ _SIGNATURES = {
                                    C.POINTER(Epilogue), C.POINTER(C.c_void_p), C.c_int, C.c_size_t,
                                    C.c_size_t, C.c_void_p, C.c_void_p]),
     "lq_quantize_rows_bcast": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,
-                                         C.c_int, C.c_int, C.c_float, C.POINTER(C.c_void_p), C.c_int, C.c_size_t,
+                                         C.c_int, C.c_size_t, C.c_int, C.c_int, C.c_float, C.POINTER(C.c_void_p), C.c_int, C.c_size_t,
                                          C.c_size_t, C.c_void_p, C.c_void_p]),
     "lq_gemm_s8_multicast": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                        C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
@@ -198,6 +227,32 @@ def minmax_workspace(device: torch.device) -> torch.Tensor:
     return ws
 
 
+_gemm_ws: dict = {}
+
+
+def gemm_workspace(device: torch.device) -> torch.Tensor:
+    """Zero-initialised scratch of the integer contraction (stream-K partial tiles, exchange
+    ticket) for the current (device, stream); the kernels leave it zeroed."""
+    if torch.cuda.is_current_stream_capturing():
+        # A capture runs on a stream of its own; allocating (and zero-filling) a workspace there
+        # would put a 24 MB fill into every replay.  Captured steps share one workspace per device,
+        # created eagerly below, so run the step once before capturing it.
+        ws = _gemm_ws.get((device.index, "capture"))
+        if ws is None:
+            raise LucidError("run the step once eagerly before capturing it in a CUDA graph "
+                             "(the contraction's workspace is created on first use)")
+        return ws
+    if (device.index, "capture") not in _gemm_ws:
+        _gemm_ws[(device.index, "capture")] = torch.zeros(int(load().lq_gemm_workspace_bytes()),
+                                                          dtype=torch.uint8, device=device)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _gemm_ws.get(key)
+    if ws is None:
+        ws = torch.zeros(int(load().lq_gemm_workspace_bytes()), dtype=torch.uint8, device=device)
+        _gemm_ws[key] = ws
+    return ws
+
+
 _hist_ws: dict = {}
 
 
@@ -224,9 +279,33 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_device_status(device: torch.device) -> None:
-    """Synchronising check of the timeout word (tests and debugging)."""
+    """Synchronising check of what the kernels report from the device: the status word of the
+    contraction / exchange kernels and the give-up count of the pipelined stream kernels.  Raises
+    ``TimeoutError`` when a bounded device-side wait ran out since the last check (the outputs of
+    that launch are incomplete; the scratch workspaces are re-zeroed here)."""
     w = _status_words.get(device.index)
-    if w is not None and int(w.item()) != 0:
-        code = int(w.item())
-        w.zero_()
-        raise _STATUS_EXC.get(code, LucidError)(f"lucid_b200: device-side status {code}")
+    code = int(w.item()) if w is not None else 0
+    n = C.c_uint(0)
+    with torch.cuda.device(device):
+        check(load().lq_stream_timeouts(C.byref(n)))
+    if code != 0 or n.value != 0:
+        if w is not None:
+            w.zero_()
+        for (dev_index, _), ws in _gemm_ws.items():
+            if dev_index == device.index:
+                ws.zero_()
+        what = f"status {code}" if code else f"{n.value} pipelined stream launch(es) gave up"
+        raise _STATUS_EXC.get(code or ERR_TIMEOUT, LucidError)(f"lucid_b200: device-side {what}")
+
+
+_lazy_checks: dict = {}
+
+
+def check_device_status_lazily(device: torch.device, every: int = 256) -> None:
+    """Called by the module layer on every forward: every ``every``-th call per device reads
+    the device status (one small synchronising copy), so that a timeout inside a long-running
+    service surfaces within a bounded number of calls instead of never."""
+    k = _lazy_checks.get(device.index, 0) + 1
+    _lazy_checks[device.index] = k
+    if k % every == 0 and not torch.cuda.is_current_stream_capturing():
+        check_device_status(device)

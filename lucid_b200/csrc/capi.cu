@@ -20,6 +20,26 @@ int check_cuda(cudaError_t e, const char* what) {
   return LQ_ERR_CUDA;
 }
 
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  return dev;
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static int count[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) return kNumSMs;
+  std::lock_guard<std::mutex> lock(mu);
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMs;
+    count[dev] = n;
+  }
+  return count[dev];
+}
+
 }  // namespace lq
 
 extern "C" int lq_version(void) { return LQ_VERSION; }

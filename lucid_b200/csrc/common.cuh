@@ -5,13 +5,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 
 #include "lucid_b200.h"
 
 namespace lq {
 
-constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs (sizes static tables; grids ask sm_count())
+constexpr int kMaxDevices = 64;
 
 // ---- host-side error plumbing -------------------------------------------
 void set_error(const std::string& msg);
@@ -25,6 +27,31 @@ int check_cuda(cudaError_t e, const char* what);
   } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Index of the current device, or -1.
+int current_device();
+// Multiprocessor count of the current device (asked once per device).
+int sm_count();
+
+// Per-device one-time set-up at a call site.  Function attributes (the opt-in to more than
+// 48 KB of dynamic shared memory) and occupancy answers belong to a device, not to the process:
+// a process that drives a second GPU has to repeat them there.
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+  cudaError_t err[kMaxDevices] = {};
+  template <typename F>
+  cudaError_t run(F&& fn) {
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
+      err[dev] = fn();
+      done[dev] = true;
+    }
+    return err[dev];
+  }
+};
 
 // ---- device-side exact arithmetic ---------------------------------------
 // Every step is a separate IEEE binary32 operation; the intrinsics keep the

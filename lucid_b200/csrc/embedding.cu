@@ -137,7 +137,7 @@ extern "C" int lq_embedding_s8(const int8_t* weight, const float* scale, const f
     if (out_dtype != LQ_F32 && out_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_embedding_s8: out_dtype");
     const bool vec = dim % 16 == 0 && aligned16(weight) && aligned16(out);
     const size_t want = (n_idx + kEmbThreads / 32 - 1) / (kEmbThreads / 32);
-    const int grid = (int)(want < (size_t)kNumSMs * 32 ? want : (size_t)kNumSMs * 32);
+    const int grid = (int)(want < (size_t)sm_count() * 32 ? want : (size_t)sm_count() * 32);
 #define LQ_EMB(IDX, OUT) \
   embedding_kernel<IDX, OUT><<<grid, kEmbThreads, 0, st>>>(weight, scale, zero_point, (long long)num_embeddings, dim, \
                                                             indices, n_idx, padding_idx, (OUT*)out, vec, status)
@@ -155,7 +155,7 @@ extern "C" int lq_embedding_s8(const int8_t* weight, const float* scale, const f
   const bool vec = dim % 4 == 0 && (reinterpret_cast<uintptr_t>(weight) & 3u) == 0;
   const size_t total = n_bags * ((dim + 3) / 4);
   const size_t want = (total + kEmbThreads - 1) / kEmbThreads;
-  const int grid = (int)(want < (size_t)kNumSMs * 32 ? want : (size_t)kNumSMs * 32);
+  const int grid = (int)(want < (size_t)sm_count() * 32 ? want : (size_t)sm_count() * 32);
   if (index_bits == 64)
     embedding_bag_kernel<long long><<<grid, kEmbThreads, 0, st>>>(weight, scale, zero_point, (long long)num_embeddings,
                                                                   dim, indices, n_idx, offsets, n_bags,

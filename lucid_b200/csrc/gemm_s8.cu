@@ -4,15 +4,22 @@
 //   epilogue warps read TMEM (tcgen05.ld), apply scales / bias / activation /
 //   requantisation in registers and store.
 //
-// One persistent CTA per SM; 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer
-// and TMEM owner, warps 2..5 = epilogue (one TMEM lane quadrant each).  Two
-// accumulator stages in TMEM let the epilogue of tile i overlap the mainloop of
-// tile i+1.  The same mainloop serves the Linear GEMM and the NHWC implicit-GEMM
-// convolution (the producer walks filter taps with shifted 4-D TMA boxes whose
-// out-of-image elements are zero-filled, which is the padding).
+// One persistent CTA per SM (or one CTA pair per two SMs): warp 0 = TMA producer,
+// warp 1 = MMA issuer and TMEM owner, then 8 or 16 epilogue warps (four per TMEM
+// lane quadrant, each taking a share of the tile's columns).  Two accumulator
+// stages in TMEM let the epilogue of one work item overlap the mainloop of the
+// next.  The same mainloop serves the Linear GEMM and the NHWC implicit-GEMM
+// convolution (the producer walks filter taps with shifted, optionally strided
+// 4-D TMA boxes whose out-of-image elements are zero-filled, which is the padding).
 //
-// Every wait on an mbarrier is bounded: when the budget runs out the CTA raises
-// an abort flag, reports LQ_ERR_TIMEOUT through the status word, drains and
+// Work is scheduled either tile by tile (round robin over the CTAs) or, when the
+// tile count does not fill whole waves, as equal contiguous runs of k-blocks per
+// CTA ("stream-K"): a tile cut by a run boundary is finished by the CTA that holds
+// its first k-blocks, which adds the other CTAs' int32 partial sums from an
+// L2-resident scratch before the epilogue (integer addition: order-free, exact).
+//
+// Every wait (mbarrier, scratch flag) is bounded: when the budget runs out the CTA
+// raises an abort flag, reports LQ_ERR_TIMEOUT through the status word, drains and
 // frees its TMEM before returning, so the context stays usable.
 #include <cuda.h>
 
@@ -34,7 +41,13 @@ constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
 // more ring stages, fewer polling warps), 16 when the epilogue is the long pole (small K).
 constexpr int threads_for(int ew) { return 64 + 32 * ew; }  // producer warp, MMA warp, epilogue warps
 constexpr int kTmemCols = 512;
-constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s
+constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s: default budget of every device-side wait
+// stream-K / exchange scratch (caller's workspace): a 4 KB header, then one slot per CTA
+constexpr int kWsHeaderBytes = 4096;
+constexpr int kWsMaxCtas = 192;                      // slots sized for up to 192 SMs
+constexpr int kWsSlotBytes = BM * 256 * 4;           // one CTA's 128 x 256 int32 partial tile
+constexpr int kWsFlagsOffset = 256;                  // header: ticket at 0, 2 words per CTA from here
+static_assert(kWsFlagsOffset + kWsMaxCtas * 8 <= kWsHeaderBytes, "flags must fit the header");
 
 template <int BN, bool PAIR, int EW>
 struct Cfg {
@@ -56,10 +69,15 @@ struct Geometry {
   int M, N, K;         // GEMM extents (conv: M = imgs*P*Q, K = R*S*C)
   int tiles_m, tiles_n, num_kb;
   // conv only
-  int P, Q, C, R, S, pad;
+  int P, Q, C, R, S;
+  int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
   int tile_h, tile_w, tiles_p, tiles_q;
   int cblocks;         // ceil(C / BK)
-  int debug;           // timing probes: 1 no loads, 2 no MMAs, 4 epilogue skips TMEM reads and stores, 8 epilogue skips stores
+  int streamk;         // 1: contiguous runs of k-blocks per CTA instead of whole tiles
+  long long wait_budget;  // clock64 cycles a device-side wait may take
+#ifdef LQ_TESTING
+  int test_no_loads;   // test-only build: the producer issues nothing, so the first wait runs out
+#endif
 };
 
 struct Epi {
@@ -81,6 +99,12 @@ struct Epi {
   int vec_ok;     // 16-byte vector stores allowed
   int par_vec;    // per-column parameter arrays are 16-byte aligned (vector loads)
   int32_t* status;
+  uint8_t* ws;    // scratch (stream-K partial tiles and flags, completion ticket) or null
+  // exchange step of a sharded layer: once every CTA has stored its tiles, the last one bumps
+  // this rank's counter and stores the new value into its flag word on every peer
+  int32_t* signal_counter;
+  int32_t* peer_flags[8];
+  int n_flags;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------
@@ -111,15 +135,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the CTA is aborting or the budget ran out.  SLEEP_NS > 0
 // backs off between polls (long waits by warps that are not on the critical path).
 template <int SLEEP_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0) {
+    if ((it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         return false;
       }
@@ -128,8 +153,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 // Warp-uniform wait: every lane polls, the warp agrees on the outcome.
 template <int SLEEP_NS = 0>
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag));
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               long long budget) {
+  return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag, budget));
+}
+// Bounded wait on a global-memory word written by another CTA (ld.acquire.gpu): true once
+// *p == want.
+__device__ __forceinline__ bool flag_wait_eq(const unsigned int* p, unsigned int want, volatile int* abort_flag,
+                                             long long budget) {
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v == want) return true;
+    __nanosleep(100);
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > budget) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
 }
 // One lane of a converged warp.  The surrounding control flow stays warp-uniform so that
 // loop state and descriptors can live in uniform registers.
@@ -331,6 +376,48 @@ struct RowCtx {
   long long row0;    // global output row of the warp's first row
 };
 
+// Partial sums of a tile that other CTAs computed (stream-K): contributor i's 128 x BN int32
+// tile lies in scratch slot `cta0 + i * cta_step`, as [lane quadrant][16-column block][16-byte
+// piece][lane] so that a warp's store or load of one piece is one contiguous 512-byte run.
+struct Partials {
+  const uint8_t* slots;  // first slot of the scratch; null = nothing to add
+  int n, cta0, cta_step;
+};
+template <int BN>
+__device__ __forceinline__ size_t partial_index(int quad, int colblk, int piece, int lane) {
+  return (size_t)(((quad * (BN / 16) + colblk) * 4 + piece) * 32 + lane) * 16;
+}
+// acc[0..16) += the contributors' sums of the same 16 columns (L2 loads: the data was written
+// by other SMs during this launch)
+template <int BN>
+__device__ __forceinline__ void add_partials16(uint32_t (&acc)[16], const Partials& ps, int quad, int colblk,
+                                               int lane) {
+  for (int i = 0; i < ps.n; ++i) {
+    const uint8_t* slot = ps.slots + (size_t)(ps.cta0 + i * ps.cta_step) * kWsSlotBytes;
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slot + partial_index<BN>(quad, colblk, pc, lane)));
+      acc[4 * pc] += v.x, acc[4 * pc + 1] += v.y, acc[4 * pc + 2] += v.z, acc[4 * pc + 3] += v.w;
+    }
+  }
+}
+// This warp's share (32 lanes x BN / PARTS columns) of an accumulator tile, raw, into the
+// CTA's scratch slot.
+template <int BN, int PARTS>
+__device__ __forceinline__ void dump_partial(uint32_t taddr, uint8_t* slot, int quad, int part, int lane) {
+  constexpr int NB = BN / PARTS / 16;
+#pragma unroll 1
+  for (int blk = 0; blk < NB; ++blk) {
+    const int colblk = part * NB + blk;
+    uint32_t acc[16];
+    tc_ld16_sync(taddr + colblk * 16, acc);
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc)
+      __stcg(reinterpret_cast<uint4*>(slot + partial_index<BN>(quad, colblk, pc, lane)),
+             make_uint4(acc[4 * pc], acc[4 * pc + 1], acc[4 * pc + 2], acc[4 * pc + 3]));
+  }
+}
+
 // One 16-byte store to a multicast address: NVSwitch writes it into the buffer of every GPU
 // bound to the multicast object (the issuing GPU's included), so the link carries each tile once
 // instead of once per peer.
@@ -452,7 +539,7 @@ __device__ __forceinline__ void finish16(const float (&y)[16], uint32_t (&w)[16]
 template <int BN, int KIND, bool GATED, int PARTS>
 __device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, const RowCtx& rc,
                                               uint32_t taddr, uint8_t* stg, int lane, int part,
-                                              int n0, int on0) {
+                                              int n0, int on0, const Partials& ps, int quad) {
   constexpr int ESZ = KindInfo<KIND>::kEsz;
   constexpr int OUTC = GATED ? BN / 2 : BN;   // output columns of the tile
   constexpr int WCOLS = OUTC / PARTS;         // ... of this warp
@@ -469,8 +556,13 @@ __device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, 
       tc_ld16(taddr + BN / 2 + oc, acc_u);
       tc_wait_ld_dep16(acc);
       tc_wait_ld_dep16(acc_u);
+      if (ps.n) {
+        add_partials16<BN>(acc, ps, quad, oc >> 4, lane);
+        add_partials16<BN>(acc_u, ps, quad, (BN / 2 + oc) >> 4, lane);
+      }
     } else {
       tc_ld16_sync(taddr + oc, acc);
+      if (ps.n) add_partials16<BN>(acc, ps, quad, oc >> 4, lane);
     }
     uint32_t w[16];
     if (KIND == KIND_S32) {
@@ -515,6 +607,14 @@ __device__ __forceinline__ void epilogue_tile(const Epi& ep, const Geometry& g, 
   }
 }
 
+// Four integral floats already inside an 8-bit grid (signed or unsigned) -> four packed codes:
+// the low byte of each integer.
+__device__ __forceinline__ uint32_t pack4_low_bytes(const float (&c)[4]) {
+  const uint32_t a = (uint32_t)__float2int_rz(c[0]), b = (uint32_t)__float2int_rz(c[1]);
+  const uint32_t d = (uint32_t)__float2int_rz(c[2]), e = (uint32_t)__float2int_rz(c[3]);
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(d, e, 0x0040), 0x5410);
+}
+
 // Four outputs -> four codes without the division: q~ = y * RN(1 / s_o) is within |q| * 2^-23 of
 // the true quotient, so rint(q~) equals rint(RN(y / s_o)) unless q~ lies within that distance of a
 // half-integer.  q~ + 1.5 * 2^23 rounds to the nearest integer (ties to even) in the mantissa;
@@ -535,45 +635,51 @@ __device__ __forceinline__ bool requant4_certain(const float (&y)[4], const RowC
 }
 
 // Lean requantising epilogue: 8-bit codes to one destination, tile inside N.  Compared with
-// epilogue_tile: the per-column parameters of the warp's columns are combined once per tile into
-// a table in the warp's staging area (scale product folded when the activation scale is per
-// tensor) and read back with broadcast 16-byte shared loads, the division is replaced by
-// requant4_certain, and every thread stores its 16 finished bytes straight to global memory
-// (its row's next 16 bytes follow one block later, so L2 merges the sectors) -- no staging pass.
-template <int BN, int PARTS>
+// epilogue_tile: the per-column parameters of the warp's columns are combined once per column
+// of tiles into a table in the warp's staging area (scale product folded when the activation
+// scale is per tensor; `fill` says the warp moved to another column of tiles) and read back with
+// broadcast 16-byte shared loads, the division is replaced by requant4_certain, and every thread
+// stores its 16 finished bytes straight to global memory (its row's next 16 bytes follow one
+// block later, so L2 merges the sectors) -- no staging pass.  What the epilogue descriptor asks
+// for (bias, ReLU, zero-point correction) is a template argument, so the 16-column loop has no
+// branch on it; signed and unsigned grids share one byte pack (the codes are already clipped
+// into their grid, so the low byte of the integer is the code either way).  Taken for a
+// per-tensor activation scale, whose product with the weight scale folds into the table.
+template <int BN, int PARTS, bool HAS_BIAS, bool RELU, bool HAS_ZP>
 __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc, uint32_t taddr, uint8_t* stg,
-                                                 int lane, int part, int n0) {
+                                                 int lane, int part, int n0, bool fill, const Partials& ps,
+                                                 int quad) {
   constexpr int WCOLS = BN / PARTS;
   constexpr int NB = WCOLS / 16;
   const int c0 = part * WCOLS;
   float* t_scale = reinterpret_cast<float*>(stg);
   float* t_bias = t_scale + WCOLS;
   int* t_rowsum = reinterpret_cast<int*>(t_bias + WCOLS);
-  const bool fold_sa = ep.a_scale_mode != LQ_PER_ROW;
-  const bool has_bias = ep.bias != nullptr;
-  const bool has_zp = ep.b_rowsum != nullptr && rc.zpa != 0;
-  __syncwarp();
-  for (int j = lane; j < WCOLS; j += 32) {
-    const int col = n0 + c0 + j;
-    const float sb = ep.b_scale ? __ldg(ep.b_scale + col) : 1.0f;
-    t_scale[j] = fold_sa ? __fmul_rn(rc.sa, sb) : sb;
-    if (has_bias) t_bias[j] = __ldg(ep.bias + col);
-    if (has_zp) t_rowsum[j] = __ldg(ep.b_rowsum + col);
+  if (fill) {
+    __syncwarp();
+    for (int j = lane; j < WCOLS; j += 32) {
+      const int col = n0 + c0 + j;
+      const float sb = ep.b_scale ? __ldg(ep.b_scale + col) : 1.0f;
+      t_scale[j] = __fmul_rn(rc.sa, sb);
+      if (HAS_BIAS) t_bias[j] = __ldg(ep.bias + col);
+      if (HAS_ZP) t_rowsum[j] = __ldg(ep.b_rowsum + col);
+    }
+    __syncwarp();
   }
-  __syncwarp();
   const bool row_ok = (rc.row_mask >> lane) & 1u;
   uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
-  const bool relu = ep.act == LQ_ACT_RELU;
-  const bool is_signed = rc.fqmin < 0.0f;
-  // one block of 16 columns: accumulators in registers -> 16 bytes in global memory
-  auto finish_block = [&](int blk, const uint32_t (&acc)[16]) {
+#pragma unroll 1
+  for (int blk = 0; blk < NB; ++blk) {
+    uint32_t acc[16];
+    tc_ld16_sync(taddr + c0 + blk * 16, acc);
+    if (ps.n) add_partials16<BN>(acc, ps, quad, (c0 >> 4) + blk, lane);
     uint32_t w[4];
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       const float4 s4 = *reinterpret_cast<const float4*>(t_scale + blk * 16 + 4 * q4);
       const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
       float y[4];
-      if (has_zp) {
+      if (HAS_ZP) {
         const int4 r4 = *reinterpret_cast<const int4*>(t_rowsum + blk * 16 + 4 * q4);
         const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
@@ -583,36 +689,78 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
         for (int i = 0; i < 4; ++i) y[i] = (float)(int)acc[4 * q4 + i];
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) y[i] = __fmul_rn(y[i], fold_sa ? sc[i] : __fmul_rn(rc.sa, sc[i]));
-      if (has_bias) {
+      for (int i = 0; i < 4; ++i) y[i] = __fmul_rn(y[i], sc[i]);
+      if (HAS_BIAS) {
         const float4 b4 = *reinterpret_cast<const float4*>(t_bias + blk * 16 + 4 * q4);
         y[0] = __fadd_rn(y[0], b4.x), y[1] = __fadd_rn(y[1], b4.y);
         y[2] = __fadd_rn(y[2], b4.z), y[3] = __fadd_rn(y[3], b4.w);
       }
-      if (relu) {
+      if (RELU) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) y[i] = fmaxf(y[i], 0.0f);
       }
       float c[4];
       if (!requant4_certain(y, rc, c)) code4_f32(y, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
-      w[q4] = is_signed ? pack4_s8(c) : pack4_u8(c);
+      w[q4] = pack4_low_bytes(c);
     }
     if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-  };
-  // Two accumulator buffers: the TMEM load of the next block is in flight while this one is
-  // finished (wait::ld covers every outstanding load, so it comes after the arithmetic).
-#pragma unroll 1
-  for (int blk = 0; blk < NB; ++blk) {
-    uint32_t acc_a[16];
-    tc_ld16_sync(taddr + c0 + blk * 16, acc_a);
-    finish_block(blk, acc_a);
   }
-  __syncwarp();
+}
+
+// Runtime flags -> template arguments (three uniform branches per tile, none per element).
+template <int BN, int PARTS, bool... Fs>
+__device__ __forceinline__ void q8_dispatch(int mask, const Epi& ep, const RowCtx& rc, uint32_t taddr, uint8_t* stg,
+                                            int lane, int part, int n0, bool fill, const Partials& ps, int quad) {
+  if constexpr (sizeof...(Fs) == 3) {
+    epilogue_tile_q8<BN, PARTS, Fs...>(ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
+  } else if (mask & 1) {
+    q8_dispatch<BN, PARTS, Fs..., true>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
+  } else {
+    q8_dispatch<BN, PARTS, Fs..., false>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
+  }
+}
+
+// ---- work schedule ------------------------------------------------------------------
+// Tile mode: worker w takes tiles w, w + W, ... whole (M fastest, so neighbouring workers share
+// a B tile in L2).  Stream-K mode: the k-blocks of all tiles form one sequence of
+// total_tiles * num_kb units and worker w takes units [U*w/W, U*(w+1)/W): the tail of one tile,
+// some whole tiles and the head of another.
+struct Sched {
+  int streamk, num_workers, num_kb;
+  int tile, total_tiles;  // tile mode
+  long long u, u_end;     // stream-K
+};
+__device__ __forceinline__ long long run_begin(long long units, int worker, int num_workers) {
+  return units * worker / num_workers;
+}
+__device__ __forceinline__ Sched make_sched(const Geometry& g, int worker, int num_workers, int total_tiles) {
+  Sched s;
+  s.streamk = g.streamk, s.num_workers = num_workers, s.num_kb = g.num_kb;
+  s.tile = worker, s.total_tiles = total_tiles;
+  const long long units = (long long)total_tiles * g.num_kb;
+  s.u = run_begin(units, worker, num_workers), s.u_end = run_begin(units, worker + 1, num_workers);
+  return s;
+}
+// Next work item: k-blocks [kb0, kb1) of `tile`.  False when the worker is done.
+__device__ __forceinline__ bool sched_next(Sched& s, int& tile, int& kb0, int& kb1) {
+  if (!s.streamk) {
+    if (s.tile >= s.total_tiles) return false;
+    tile = s.tile, kb0 = 0, kb1 = s.num_kb;
+    s.tile += s.num_workers;
+    return true;
+  }
+  if (s.u >= s.u_end) return false;
+  tile = (int)(s.u / s.num_kb);
+  kb0 = (int)(s.u - (long long)tile * s.num_kb);
+  const long long left = s.u_end - s.u;
+  kb1 = left < (long long)(s.num_kb - kb0) ? kb0 + (int)left : s.num_kb;
+  s.u += kb1 - kb0;
+  return true;
 }
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int BN, bool PAIR, int EW>
-__global__ void __launch_bounds__(threads_for(EW), 1)
+__global__ void __maxnreg__(EW == 16 ? 112 : 200)
 gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const Geometry g, const Epi ep, const uint32_t idesc) {
   using C = Cfg<BN, PAIR, EW>;
@@ -632,13 +780,18 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   const uint32_t bar_empty = bar_full + 8 * C::kStages;
   const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
   const uint32_t bar_tempty = bar_tfull + 16;
+  const long long budget = g.wait_budget;
 
   // PAIR: CTA `rank` of the 2-CTA cluster owns M sub-tile 2*pair_m + rank and B rows
   // [rank*BN/2, (rank+1)*BN/2) of the tile; the leader (rank 0) issues the MMAs.
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = rank == 0;
-  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int raw_worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  // Stream-K numbers the workers against the launch order: the CTA that finishes a cut tile
+  // waits for partial sums of workers with higher numbers, i.e. of CTAs that were launched
+  // before it, and those wait for nobody.
+  const int worker = g.streamk ? num_workers - 1 - raw_worker : raw_worker;
   const int tiles_mw = PAIR ? (g.tiles_m + 1) / 2 : g.tiles_m;  // M tiles per worker
   const int total_tiles = tiles_mw * g.tiles_n;
 
@@ -679,84 +832,90 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   if (warp == 0) {
     // ===== TMA producer (one per CTA) =====
-    {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = worker; tile < total_tiles && ok && !(g.debug & 1); tile += num_workers) {
-        const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
-        const int n0 = (tile / tiles_mw) * BN + (int)rank * C::kBRows;
-        int m0 = tm_idx * BM, img = 0, p0 = 0, q0 = 0;
+    Sched sc = make_sched(g, worker, num_workers, total_tiles);
+    int stage = 0, tile, kb0, kb1;
+    uint32_t phase = 0;
+    bool ok = true;
+#ifdef LQ_TESTING
+    if (g.test_no_loads) ok = false;
+#endif
+    while (ok && sched_next(sc, tile, kb0, kb1)) {
+      const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
+      const int n0 = (tile / tiles_mw) * BN + (int)rank * C::kBRows;
+      int m0 = tm_idx * BM, img = 0, y0 = 0, x0 = 0;
+      if (g.conv) {
+        const int per_img = g.tiles_p * g.tiles_q;
+        img = tm_idx / per_img;  // >= number of images for the padding sub-tile: zero-filled
+        const int rem = tm_idx - img * per_img;
+        // input coordinates of the tile's first output pixel at tap (0, 0)
+        y0 = (rem / g.tiles_q) * g.tile_h * g.stride_h - g.pad_h;
+        x0 = (rem % g.tiles_q) * g.tile_w * g.stride_w - g.pad_w;
+      }
+      const uint32_t a_bytes = g.conv ? (uint32_t)(BK * g.tile_w * g.tile_h) : (uint32_t)C::kABytes;
+      const uint32_t stage_tx = (a_bytes + (uint32_t)C::kBBytes) * (PAIR ? 2u : 1u);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, budget)) {
+          ok = false;
+          break;
+        }
+        const uint32_t a_dst = smem_u32(smem_a + stage * C::kABytes);
+        const uint32_t b_dst = smem_u32(smem_b + stage * C::kBBytes);
+        int ax = kb * BK, bx = kb * BK, ay = 0, ax2 = 0;
         if (g.conv) {
-          const int per_img = g.tiles_p * g.tiles_q;
-          img = tm_idx / per_img;  // >= number of images for the padding sub-tile: zero-filled
-          const int rem = tm_idx - img * per_img;
-          p0 = (rem / g.tiles_q) * g.tile_h;
-          q0 = (rem % g.tiles_q) * g.tile_w;
+          const int tap = kb / g.cblocks;
+          const int cb = kb - tap * g.cblocks;
+          const int r = tap / g.S, sft = tap - r * g.S;
+          ax = cb * BK, bx = tap * g.C + cb * BK;
+          ay = y0 + r * g.dil_h, ax2 = x0 + sft * g.dil_w;
         }
-        const uint32_t a_bytes = g.conv ? (uint32_t)(BK * g.tile_w * g.tile_h) : (uint32_t)C::kABytes;
-        const uint32_t stage_tx = (a_bytes + (uint32_t)C::kBBytes) * (PAIR ? 2u : 1u);
-        for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
-          const uint32_t a_dst = smem_u32(smem_a + stage * C::kABytes);
-          const uint32_t b_dst = smem_u32(smem_b + stage * C::kBBytes);
-          int ax = kb * BK, bx = kb * BK, r = 0, sft = 0;
-          if (g.conv) {
-            const int tap = kb / g.cblocks;
-            const int cb = kb - tap * g.cblocks;
-            r = tap / g.S, sft = tap - r * g.S;
-            ax = cb * BK, bx = tap * g.C + cb * BK;
-          }
-          if (!elect_one()) {
-          } else if (PAIR) {
-            // both CTAs' bytes are counted on the leader's barrier
-            const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
-            if (leader) mbar_expect_tx(bar_full + 8 * stage, stage_tx);
-            if (g.conv) tma_load_4d_pair(a_dst, &tm_a, ax, q0 + sft - g.pad, p0 + r - g.pad, img, full);
-            else tma_load_2d_pair(a_dst, &tm_a, ax, m0, full);
-            tma_load_2d_pair(b_dst, &tm_b, bx, n0, full);
-          } else {
-            const uint32_t full = bar_full + 8 * stage;
-            mbar_expect_tx(full, stage_tx);
-            if (g.conv) tma_load_4d(a_dst, &tm_a, ax, q0 + sft - g.pad, p0 + r - g.pad, img, full);
-            else tma_load_2d(a_dst, &tm_a, ax, m0, full);
-            tma_load_2d(b_dst, &tm_b, bx, n0, full);
-          }
-          if (++stage == C::kStages) stage = 0, phase ^= 1u;
+        if (!elect_one()) {
+        } else if (PAIR) {
+          // both CTAs' bytes are counted on the leader's barrier
+          const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
+          if (leader) mbar_expect_tx(bar_full + 8 * stage, stage_tx);
+          if (g.conv) tma_load_4d_pair(a_dst, &tm_a, ax, ax2, ay, img, full);
+          else tma_load_2d_pair(a_dst, &tm_a, ax, m0, full);
+          tma_load_2d_pair(b_dst, &tm_b, bx, n0, full);
+        } else {
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, stage_tx);
+          if (g.conv) tma_load_4d(a_dst, &tm_a, ax, ax2, ay, img, full);
+          else tma_load_2d(a_dst, &tm_a, ax, m0, full);
+          tma_load_2d(b_dst, &tm_b, bx, n0, full);
         }
+        if (++stage == C::kStages) stage = 0, phase ^= 1u;
       }
     }
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only when paired) =====
     if (leader) {
-      int stage = 0, acc = 0;
+      Sched sc = make_sched(g, worker, num_workers, total_tiles);
+      int stage = 0, acc = 0, tile, kb0, kb1;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = worker; tile < total_tiles && ok; tile += num_workers) {
-        if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) break;
+      while (ok && sched_next(sc, tile, kb0, kb1)) {
+        if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, budget)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < g.num_kb; ++kb) {
-          if (!(g.debug & 1) && !mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag)) {
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, budget)) {
             ok = false;
             break;
           }
-          if (!(g.debug & 32)) tc_fence_after();
+          tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(smem_a + stage * C::kABytes));
           const uint64_t bdesc = make_smem_desc(smem_u32(smem_b + stage * C::kBBytes));
           const bool issuer = elect_one();
+          const uint32_t first = kb == kb0 ? 0u : 1u;  // the first MMA of a work item overwrites
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K && !(g.debug & 2) && issuer; ++k) {
+          for (int k = 0; k < BK / UMMA_K && issuer; ++k) {
             // advancing K inside the swizzle atom = advancing the start address
             const uint64_t koff = (uint64_t)(k * (UMMA_K >> 4));
-            if (PAIR) tc_mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
-            else tc_mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) tc_mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, idesc, k != 0 ? 1u : first);
+            else tc_mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, k != 0 ? 1u : first);
           }
           // frees the stage (in both CTAs when paired) once the MMAs have read it
-          if ((g.debug & 16) || !issuer) {
+          if (!issuer) {
           } else if (PAIR) tc_commit_pair(bar_empty + 8 * stage);
           else tc_commit(bar_empty + 8 * stage);
           __syncwarp();
@@ -782,8 +941,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int part = (warp - 2) >> 2;
     const bool gated = ep.act == LQ_ACT_SILU_GATE;
     // the lean requantising epilogue: one destination, vector stores, aligned parameter arrays
-    const bool q8_lean = ep.n_dst == 1 && !ep.multicast && ep.vec_ok && ep.par_vec && !(g.debug & 64) &&
-                         (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
+    const bool q8_lean = ep.n_dst == 1 && !ep.multicast && ep.vec_ok && ep.par_vec &&
+                         ep.a_scale_mode != LQ_PER_ROW && (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
     // what does not change from tile to tile is read once
     RowCtx rc_launch;
     rc_launch.sa = (ep.a_scale && ep.a_scale_mode != LQ_PER_ROW) ? __ldg(ep.a_scale) : 1.0f;
@@ -793,10 +952,19 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     rc_launch.fqmin = (float)ep.qmin, rc_launch.fqmax = (float)ep.qmax;
     rc_launch.row_mask = 0u, rc_launch.row0 = 0;
     const bool q8_lean_grid = rc_launch.so.fast && fabsf(rc_launch.zo) <= 512.0f;
-    int acc = 0;
+    const int q8_mask = (ep.bias != nullptr ? 1 : 0) | (ep.act == LQ_ACT_RELU ? 2 : 0) |
+                        ((ep.b_rowsum != nullptr && rc_launch.zpa != 0) ? 4 : 0);
+    int q8_filled_tn = -1;  // column of tiles whose parameters this warp's table holds
+    // stream-K scratch of this CTA: its slot for a partial tile and its two flag words
+    // (arrivals of the writing warps, departures of the reading warps)
+    uint8_t* const sk_slots = ep.ws ? ep.ws + kWsHeaderBytes : nullptr;
+    unsigned int* const sk_flags = ep.ws ? reinterpret_cast<unsigned int*>(ep.ws + kWsFlagsOffset) : nullptr;
+    const long long units = (long long)total_tiles * g.num_kb;
+    Sched sc = make_sched(g, worker, num_workers, total_tiles);
+    int acc = 0, tile, kb0, kb1;
     uint32_t acc_phase = 0;
     const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
-    for (int tile = worker; tile < total_tiles; tile += num_workers) {
+    while (sched_next(sc, tile, kb0, kb1)) {
       const int tm_idx = (tile % tiles_mw) * (PAIR ? 2 : 1) + (int)rank;
       const int tn_idx = tile / tiles_mw;
       // output row of this thread; valid rows of a tile are a prefix and map to
@@ -818,28 +986,67 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       }
       RowCtx rc = rc_launch;
       if (ep.a_scale && ep.a_scale_mode == LQ_PER_ROW) rc.sa = row_ok ? __ldg(ep.a_scale + m_global) : 1.0f;
-      rc.row_mask = __ballot_sync(0xffffffffu, row_ok && !(g.debug & 8));
+      rc.row_mask = __ballot_sync(0xffffffffu, row_ok);
       rc.row0 = (long long)__shfl_sync(0xffffffffu, m_global, 0);
 
-      if (!mbar_wait_warp<200>(bar_tfull + 8 * acc, acc_phase, abort_flag)) break;
+      if (!mbar_wait_warp<200>(bar_tfull + 8 * acc, acc_phase, abort_flag, budget)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
       const int n0 = tn_idx * BN;
-      if (g.debug & 4) {
-      } else if (gated) {
-        const int on0 = tn_idx * (BN / 2);
-        if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0);
-        else epilogue_tile<BN, KIND_BF16, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0);
-      } else if (ep.out_dtype == LQ_BF16) {
-        epilogue_tile<BN, KIND_BF16, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
-      } else if (ep.out_dtype == LQ_F32) {
-        epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
-      } else if (ep.out_dtype == LQ_S32) {
-        epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
-      } else if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
-        epilogue_tile_q8<BN, PARTS>(ep, rc, taddr, stg, lane, part, n0);
+      Partials ps;
+      ps.slots = nullptr, ps.n = 0, ps.cta0 = 0, ps.cta_step = 0;
+      if (kb0 > 0) {
+        // a tile whose first k-blocks belong to another CTA: leave the raw sums in this CTA's slot
+        dump_partial<BN, PARTS>(taddr, sk_slots + (size_t)blockIdx.x * kWsSlotBytes, quad, part, lane);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(sk_flags + 2 * blockIdx.x, 1u);
       } else {
-        epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0);
+        if (kb1 < g.num_kb) {
+          // this CTA finishes a cut tile: the workers after it hold the rest of its k-blocks
+          const long long tile_end = (long long)(tile + 1) * g.num_kb;
+          int n = 0;
+          while (worker + 1 + n < num_workers && run_begin(units, worker + 1 + n, num_workers) < tile_end) ++n;
+          ps.slots = sk_slots, ps.n = n;
+          ps.cta_step = PAIR ? -2 : -1;
+          ps.cta0 = (num_workers - 1 - (worker + 1)) * (PAIR ? 2 : 1) + (int)rank;
+          int ready = 1;
+          if (lane == 0)
+            for (int i = 0; i < n && ready; ++i)
+              ready = flag_wait_eq(sk_flags + 2 * (ps.cta0 + i * ps.cta_step), (unsigned)EW, abort_flag, budget) ? 1 : 0;
+          if (!__shfl_sync(0xffffffffu, ready, 0)) break;
+        }
+        if (gated) {
+          const int on0 = tn_idx * (BN / 2);
+          if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
+          else epilogue_tile<BN, KIND_BF16, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
+        } else if (ep.out_dtype == LQ_BF16) {
+          epilogue_tile<BN, KIND_BF16, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+        } else if (ep.out_dtype == LQ_F32) {
+          epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+        } else if (ep.out_dtype == LQ_S32) {
+          epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+        } else if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
+          q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
+          q8_filled_tn = tn_idx;
+        } else {
+          epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+          q8_filled_tn = -1;  // the generic path stages through the table's memory
+        }
+        if (ps.n) {
+          // the last reading warp re-arms the contributors' flags for the next launch
+          __syncwarp();
+          if (lane == 0) {
+            for (int i = 0; i < ps.n; ++i) {
+              unsigned int* f = sk_flags + 2 * (ps.cta0 + i * ps.cta_step);
+              if (atomicAdd(f + 1, 1u) == (unsigned)(EW - 1)) {
+                f[1] = 0u;
+                __threadfence();
+                f[0] = 0u;
+              }
+            }
+          }
+        }
       }
       // hand the accumulator stage back to the MMA issuer
       tc_fence_before();
@@ -863,6 +1070,21 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   if (PAIR) cluster_sync_all();  // the peer may still signal this CTA's barriers / read its tiles
+  if (ep.n_flags > 0 && threadIdx.x == 0 && !*abort_flag) {
+    // Exchange step: every CTA's stores into the peers' buffers are complete (barrier above) and
+    // made visible system-wide before its ticket; the CTA that draws the last ticket publishes
+    // this rank's new step count to its flag word on every peer.
+    __threadfence_system();
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(ep.ws);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *ticket = 0u;
+      __threadfence_system();
+      const int v = *ep.signal_counter + 1;
+      *ep.signal_counter = v;
+      for (int i = 0; i < ep.n_flags; ++i)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ep.peer_flags[i]), "r"(v) : "memory");
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     if (PAIR)
@@ -896,44 +1118,81 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
+// A tensor map is a pure function of (address, extents, strides, box, traversal strides), so
+// encoded maps are kept in a small table: a layer that runs the same buffers every step pays the
+// driver call once.
+struct MapKey {
+  const void* base;
+  uint64_t dims[4], strides[3];
+  uint32_t box[4], estr[4], rank;
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapCache {
+  static constexpr int kEntries = 256;
+  std::mutex mu;
+  MapKey keys[kEntries];
+  CUtensorMap maps[kEntries];
+  bool used[kEntries] = {};
+  static size_t hash(const MapKey& k) {
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(&k);
+    size_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey); ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h;
+  }
+};
+
+int encode_map(CUtensorMap* tm, const MapKey& key) {
+  static MapCache cache;
+  const size_t slot = MapCache::hash(key) % MapCache::kEntries;
+  {
+    std::lock_guard<std::mutex> lock(cache.mu);
+    if (cache.used[slot] && cache.keys[slot] == key) {
+      *tm = cache.maps[slot];
+      return LQ_OK;
+    }
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4];
+  for (int i = 0; i < 4; ++i) dims[i] = key.dims[i], box[i] = key.box[i], estr[i] = key.estr[i];
+  for (int i = 0; i < 3; ++i) strides[i] = key.strides[i];
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, key.rank, const_cast<void*>(key.base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (" + std::to_string(key.rank) + "-D) failed: " + std::to_string((int)r));
+  std::lock_guard<std::mutex> lock(cache.mu);
+  cache.keys[slot] = key, cache.maps[slot] = *tm, cache.used[slot] = true;
+  return LQ_OK;
+}
+
 int encode_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t k, uint64_t row_stride,
               uint32_t box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t dims[2] = {k, rows};
-  cuuint64_t strides[1] = {row_stride};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (2-D) failed: " + std::to_string((int)r));
-  return LQ_OK;
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base, key.rank = 2;
+  key.dims[0] = k, key.dims[1] = rows;
+  key.strides[0] = row_stride;
+  key.box[0] = (uint32_t)BK, key.box[1] = box_rows;
+  key.estr[0] = key.estr[1] = 1;
+  return encode_map(tm, key);
 }
 
+// NHWC activations of one channel group: extents (c, w, h, n) with pixel stride `c_stride`
+// bytes; the box covers tile_w x tile_h output pixels, i.e. (tile - 1) * stride + 1 input
+// positions walked with the convolution stride as the traversal stride.
 int encode_nhwc(CUtensorMap* tm, const void* base, uint64_t n, uint64_t h, uint64_t w, uint64_t c,
-                uint32_t box_w, uint32_t box_h) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t dims[4] = {c, w, h, n};
-  cuuint64_t strides[3] = {c, c * w, c * w * h};
-  cuuint32_t box[4] = {(cuuint32_t)BK, box_w, box_h, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed: " + std::to_string((int)r));
-  return LQ_OK;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMs;
-  }
-  return n;
+                uint64_t c_stride, uint32_t tile_w, uint32_t tile_h, uint32_t stride_w, uint32_t stride_h) {
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base, key.rank = 4;
+  key.dims[0] = c, key.dims[1] = w, key.dims[2] = h, key.dims[3] = n;
+  key.strides[0] = c_stride, key.strides[1] = c_stride * w, key.strides[2] = c_stride * w * h;
+  key.box[0] = (uint32_t)BK, key.box[1] = (tile_w - 1) * stride_w + 1, key.box[2] = (tile_h - 1) * stride_h + 1;
+  key.box[3] = 1;
+  key.estr[0] = 1, key.estr[1] = stride_w, key.estr[2] = stride_h, key.estr[3] = 1;
+  return encode_map(tm, key);
 }
 
 int check_epilogue(const lq_epilogue_t* e, size_t N, const char* who, bool allow_gate) {
@@ -971,30 +1230,65 @@ size_t dtype_size(int dt) {
 }
 
 void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_out, int32_t* status) {
+  memset(d, 0, sizeof(Epi));
   d->out_dtype = e->out_dtype, d->act = e->act, d->a_scale_mode = e->a_scale_mode;
   d->qmin = e->qmin, d->qmax = e->qmax;
   d->a_scale = e->a_scale, d->a_zp = e->a_zp, d->b_rowsum = e->b_rowsum, d->b_scale = e->b_scale;
   d->bias = e->bias, d->out_scale = e->out_scale, d->out_zp = e->out_zp;
   d->out = out, d->ldo = (long long)ldo, d->n_out = (int)n_out, d->status = status;
   d->n_dst = 1, d->col0 = 0, d->multicast = 0;
-  for (auto& m : d->more_outs) m = nullptr;
   const size_t esz = dtype_size(e->out_dtype);
   d->vec_ok = aligned16(out) && ((ldo * esz) % 16 == 0);
   d->par_vec = aligned16(e->b_scale) && aligned16(e->bias) && aligned16(e->b_rowsum);
 }
 
+// Environment knobs (read once): LQ_GEMM_SHAPE=pair|single256|single128 and
+// LQ_GEMM_EPI_WARPS=8|16 force a tile shape / epilogue width, LQ_GEMM_STREAMK=0|1 the
+// schedule (the tests cover every variant this way; all of them compute the same numbers),
+// LQ_GEMM_VERBOSE prints each launch's geometry.
+struct Knobs {
+  int shape = -1, epi_warps = 0, streamk = -1;
+  bool verbose = false;
+  void read() {
+    shape = -1, epi_warps = 0, streamk = -1;
+    if (const char* f = getenv("LQ_GEMM_SHAPE")) {
+      if (!strcmp(f, "pair")) shape = 0;
+      else if (!strcmp(f, "single256")) shape = 1;
+      else if (!strcmp(f, "single128")) shape = 2;
+    }
+    if (const char* f = getenv("LQ_GEMM_EPI_WARPS")) epi_warps = atoi(f);
+    if (const char* f = getenv("LQ_GEMM_STREAMK")) streamk = atoi(f) != 0;
+    verbose = getenv("LQ_GEMM_VERBOSE") != nullptr;
+  }
+};
+Knobs& knobs_storage() {
+  static Knobs k = [] {
+    Knobs v;
+    v.read();
+    return v;
+  }();
+  return k;
+}
+const Knobs& knobs() { return knobs_storage(); }
+
+// CTA pairs that can be resident at once, per device.
+template <int BN, bool PAIR, int EW>
+struct LaunchState {
+  PerDeviceOnce once;
+  int max_clusters[kMaxDevices] = {};
+};
+
 template <int BN, bool PAIR, int EW>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep,
            uint32_t idesc, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  static int max_clusters = 0;
+  static LaunchState<BN, PAIR, EW> state;
   auto kernel = gemm_s8_kernel<BN, PAIR, EW>;
   constexpr int smem = Cfg<BN, PAIR, EW>::kSmemBytes;
   constexpr int kGemmThreads = threads_for(EW);
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (PAIR && attr_err == cudaSuccess) {
+  const int dev = current_device();
+  const cudaError_t attr_err = state.once.run([&]() -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (PAIR && e == cudaSuccess) {
       cudaLaunchConfig_t probe = {};
       probe.gridDim = dim3(2 * sm_count(), 1, 1);
       probe.blockDim = dim3(kGemmThreads, 1, 1);
@@ -1003,23 +1297,37 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
       at[0].id = cudaLaunchAttributeClusterDimension;
       at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
       probe.attrs = at, probe.numAttrs = 1;
-      if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &probe) != cudaSuccess || max_clusters <= 0) {
+      int mc = 0;
+      if (cudaOccupancyMaxActiveClusters(&mc, kernel, &probe) != cudaSuccess || mc <= 0) {
         cudaGetLastError();
-        max_clusters = sm_count() / 2;
+        mc = sm_count() / 2;
       }
+      state.max_clusters[dev] = mc;
     }
+    return e;
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
   const int tiles_mw = PAIR ? (g.tiles_m + 1) / 2 : g.tiles_m;
-  const int total = tiles_mw * g.tiles_n;
+  const int total_tiles = tiles_mw * g.tiles_n;
+  // workers that get something to do: one per tile, or (stream-K) one per run of k-blocks
+  int total = total_tiles;
+  if (g.streamk) {
+    const long long runs = (long long)total_tiles * g.num_kb / (knobs().streamk == 1 ? 2 : 8);
+    total = runs < 1 ? 1 : (runs > (1 << 20) ? (1 << 20) : (int)runs);
+  }
   if (!PAIR) {
     const int grid = total < sm_count() ? total : sm_count();
+    if (knobs().verbose)
+      fprintf(stderr, "[lq] launch BN=%d EW=%d: %d tiles x %d k-blocks on %d CTAs%s\n", BN, EW, total_tiles, g.num_kb, grid,
+              g.streamk ? " (stream-K)" : "");
     kernel<<<grid, kGemmThreads, smem, st>>>(ta, tb, g, ep, idesc);
     return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
   }
+  const int max_clusters = state.max_clusters[dev];
   const int clusters = total < max_clusters ? total : max_clusters;
-  if (getenv("LQ_GEMM_VERBOSE"))
-    fprintf(stderr, "[lq] paired launch: %d tiles on %d clusters (max active %d)\n", total, clusters, max_clusters);
+  if (knobs().verbose)
+    fprintf(stderr, "[lq] paired launch EW=%d: %d tiles x %d k-blocks on %d clusters (max active %d)%s\n", EW, total_tiles,
+            g.num_kb, clusters, max_clusters, g.streamk ? " (stream-K)" : "");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
@@ -1032,34 +1340,62 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
   return check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, ep, idesc), "gemm_s8_kernel (paired) launch");
 }
 
-// Tile shape policy: CTA pairs (256 x 256 tiles, cta_group::2) when there is enough work to
-// fill the clusters; single CTAs (128 x 256, or 128 x 128 for narrow outputs) otherwise.
-enum class Shape { kPair256, kSingle256, kSingle128 };
+// Tile shape and schedule.  Candidates: CTA pairs on 256 x 256 tiles (cta_group::2), single CTAs
+// on 128 x 256 or 128 x 128 tiles; each either tile by tile or stream-K.  The cost of a candidate
+// is the number of k-block steps the busiest CTA runs (a step = one 128-deep k-block of a
+// 256-column CTA tile; a 128-column tile costs a little more than half of it because the MMA
+// re-reads A per column block), plus the exposed epilogue of its last tile; stream-K evens the
+// steps out over all CTAs at the price of one partial-tile round trip through L2.
+enum class Shape { kPair256 = 0, kSingle256 = 1, kSingle128 = 2 };
+struct Plan {
+  Shape shape;
+  bool streamk;
+};
 
-Shape pick_shape(size_t m_subtiles, size_t N, bool gated, size_t k_blocks) {
-  const char* force = getenv("LQ_GEMM_SHAPE");
-  if (force) {
-    if (!strcmp(force, "pair")) return Shape::kPair256;
-    if (!strcmp(force, "single256")) return Shape::kSingle256;
-    if (!strcmp(force, "single128") && !gated) return Shape::kSingle128;
+Plan pick_plan(size_t m_subtiles, size_t N, bool gated, size_t k_blocks, bool have_ws) {
+  const Knobs& kn = knobs();
+  const int sms = sm_count();
+  const bool sk_allowed = have_ws && kn.streamk != 0;
+  Plan best = {Shape::kSingle256, false};
+  double best_cost = 1e300;
+  for (int c = 0; c < 3; ++c) {
+    const Shape sh = (Shape)c;
+    if (kn.shape >= 0 && kn.shape != c && !(c == 1 && kn.shape == 2 && gated)) continue;
+    if (sh == Shape::kSingle128 && gated) continue;
+    if (sh == Shape::kPair256 && m_subtiles < 2 && kn.shape != 0) continue;
+    // With a handful of k-blocks a tile is all epilogue: the pair's saving on operand traffic
+    // buys nothing and its cluster handshakes cost (measured 63 vs 68 us at 50176 x 1024 x 256).
+    if (sh == Shape::kPair256 && k_blocks <= 4 && kn.shape != 0) continue;
+    if (sh == Shape::kSingle128 && N > 128 && kn.shape != 2 && k_blocks <= 4) continue;
+    const size_t bn = sh == Shape::kSingle128 ? 128 : 256;
+    const size_t tiles_n = (N + bn - 1) / bn;
+    const size_t tiles = (sh == Shape::kPair256 ? (m_subtiles + 1) / 2 : m_subtiles) * tiles_n;
+    const size_t workers = sh == Shape::kPair256 ? (size_t)(sms / 2) : (size_t)sms;
+    // steps of one tile on one CTA, and the part of its epilogue that nothing hides
+    const double tile_steps = (double)k_blocks * (sh == Shape::kSingle128 ? 0.58 : (sh == Shape::kSingle256 ? 1.03 : 1.0));
+    const double epi_steps = sh == Shape::kSingle128 ? 12.0 : 24.0;
+    const size_t waves = (tiles + workers - 1) / workers;
+    const double dp = (double)waves * (tile_steps > epi_steps ? tile_steps : epi_steps) + epi_steps;
+    if (dp < best_cost) best_cost = dp, best = {sh, false};
+    const size_t units = tiles * k_blocks;
+    if (sk_allowed && kn.streamk == 1 && k_blocks >= 2) {
+      // forced (tests): any shape with something to cut
+      if (best_cost >= 0.0 || dp < -best_cost) best_cost = -dp, best = {sh, true};
+    } else if (sk_allowed && k_blocks >= 16 && tiles * 2 >= workers && units >= 8 * workers && tiles <= 8 * workers) {
+      const double sk = (double)tiles / (double)workers * tile_steps + epi_steps + 16.0;
+      if (sk < best_cost) best_cost = sk, best = {sh, true};
+    }
   }
-  if (N <= 128 && !gated) return Shape::kSingle128;
-  // With a handful of k-blocks a tile is all epilogue: the pair's saving on operand traffic buys
-  // nothing and its cluster handshakes cost (measured 63 vs 68 us at 50176 x 1024 x 256).
-  if (k_blocks <= 4) return Shape::kSingle256;
-  const size_t tiles_n = (N + 255) / 256;
-  const size_t pair_tiles = ((m_subtiles + 1) / 2) * tiles_n;
-  // a pair tile on a half-empty M pair wastes a CTA; need at least ~one wave of clusters
-  if (m_subtiles >= 2 && pair_tiles >= (size_t)(sm_count() / 2)) return Shape::kPair256;
-  return Shape::kSingle256;
+  return best;
 }
 
-int dispatch(Shape sh, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,
+int dispatch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,
              int a_signed, cudaStream_t st) {
   // tiles whose mainloop (k-blocks x ~0.28 us) is shorter than their epilogue get 16 epilogue warps
   bool wide_epi = g.num_kb <= 32;
-  if (const char* f = getenv("LQ_GEMM_EPI_WARPS")) wide_epi = atoi(f) == 16;
-  switch (sh) {
+  if (knobs().epi_warps) wide_epi = knobs().epi_warps == 16;
+  g.streamk = plan.streamk ? 1 : 0;
+  switch (plan.shape) {
     case Shape::kPair256:
       return wide_epi ? launch<256, true, 16>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st)
                       : launch<256, true, 8>(ta, tb, g, ep, make_idesc(a_signed, 256, 256), st);
@@ -1071,125 +1407,282 @@ int dispatch(Shape sh, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g
   }
 }
 
-}  // namespace
-}  // namespace lq
+// Everything a sharded / workspace-carrying call adds to the plain contraction.
+struct Extras {
+  void* const* outs = nullptr;  // destinations (null: the single `out`)
+  int n_dst = 1;
+  bool multicast = false;
+  size_t col0 = 0;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  int32_t* const* peer_flags = nullptr;
+  int n_flags = 0;
+  int32_t* signal_counter = nullptr;
+  long long wait_budget = 0;  // 0: default
+};
 
-using namespace lq;
+int check_workspace(const std::string& w, const Extras& x) {
+  if (!x.ws) return LQ_OK;
+  if (!aligned16(x.ws)) return fail(LQ_ERR_ALIGNMENT, w + ": workspace must be 16-byte aligned");
+  if (x.ws_bytes < lq_gemm_workspace_bytes())
+    return fail(LQ_ERR_WORKSPACE, w + ": workspace smaller than lq_gemm_workspace_bytes()");
+  if (2 * sm_count() > 2 * kWsMaxCtas) return fail(LQ_ERR_UNSUPPORTED, w + ": more SMs than the workspace layout covers");
+  return LQ_OK;
+}
 
-namespace lq {
-namespace {
 int gemm_impl(const char* who, const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
-              const lq_epilogue_t* e, void* const* outs, int n_dst, size_t ldo, size_t col0,
-              int32_t* status, void* stream, bool multicast = false) {
+              const lq_epilogue_t* e, void* out, size_t ldo, int32_t* status, void* stream, const Extras& x) {
   const std::string w(who);
   if (M == 0 || N == 0) return LQ_OK;
-  if (!a || !b || !outs) return fail(LQ_ERR_DEVICE, w + ": null pointer");
-  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, w + ": between 1 and 8 destinations");
-  for (int i = 0; i < n_dst; ++i)
-    if (!outs[i]) return fail(LQ_ERR_DEVICE, w + ": null destination pointer");
+  if (!a || !b) return fail(LQ_ERR_DEVICE, w + ": null pointer");
+  if (x.n_dst < 1 || x.n_dst > 8) return fail(LQ_ERR_SHAPE, w + ": between 1 and 8 destinations");
+  if (x.outs) {
+    for (int i = 0; i < x.n_dst; ++i)
+      if (!x.outs[i]) return fail(LQ_ERR_DEVICE, w + ": null destination pointer");
+    out = x.outs[0];
+  }
+  if (!out) return fail(LQ_ERR_DEVICE, w + ": null pointer");
   if (K == 0) return fail(LQ_ERR_SHAPE, w + ": K must be positive");
   if (K % 16 != 0) return fail(LQ_ERR_ALIGNMENT, w + ": K must be a multiple of 16 (pad with zero codes)");
   if (!aligned16(a) || !aligned16(b)) return fail(LQ_ERR_ALIGNMENT, w + ": a and b must be 16-byte aligned");
   if (M > 0x7fffffffu || N > 0x7fffffffu || K > 0x7fffffffu) return fail(LQ_ERR_SHAPE, w + ": extent too large");
   int rc = check_epilogue(e, N, who, true);
   if (rc) return rc;
+  if ((rc = check_workspace(w, x))) return rc;
+  if (x.n_flags < 0 || x.n_flags > 8) return fail(LQ_ERR_SHAPE, w + ": at most 8 flag words");
+  if (x.n_flags > 0 && (!x.ws || !x.peer_flags || !x.signal_counter))
+    return fail(LQ_ERR_DEVICE, w + ": signalling needs a workspace, the flag addresses and the step counter");
   const size_t n_out = e->act == LQ_ACT_SILU_GATE ? N / 2 : N;
-  if (ldo < col0 + n_out) return fail(LQ_ERR_SHAPE, w + ": ldo smaller than column offset + output width");
+  if (ldo < x.col0 + n_out) return fail(LQ_ERR_SHAPE, w + ": ldo smaller than column offset + output width");
 
   Geometry g = {};
   g.conv = 0, g.M = (int)M, g.N = (int)N, g.K = (int)K;
   g.tiles_m = (int)((M + BM - 1) / BM);
-  const Shape sh = pick_shape((size_t)g.tiles_m, N, e->act == LQ_ACT_SILU_GATE, (K + BK - 1) / BK);
-  const int bn = sh == Shape::kSingle128 ? 128 : 256;
-  g.tiles_n = (int)((N + bn - 1) / bn);
   g.num_kb = (int)((K + BK - 1) / BK);
-  if (const char* dbg = getenv("LQ_GEMM_DEBUG")) g.debug = atoi(dbg);
+  g.wait_budget = x.wait_budget > 0 ? x.wait_budget : kWaitBudgetCycles;
+  const Plan plan = pick_plan((size_t)g.tiles_m, N, e->act == LQ_ACT_SILU_GATE, (size_t)g.num_kb, x.ws != nullptr);
+  const int bn = plan.shape == Shape::kSingle128 ? 128 : 256;
+  g.tiles_n = (int)((N + bn - 1) / bn);
   CUtensorMap ta, tb;
   if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
-  if ((rc = encode_2d(&tb, b, N, K, K, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
+  if ((rc = encode_2d(&tb, b, N, K, K, plan.shape == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
   Epi ep;
-  fill_epi(&ep, e, outs[0], ldo, n_out, status);
-  ep.n_dst = n_dst, ep.col0 = (long long)col0;
+  fill_epi(&ep, e, out, ldo, n_out, status);
+  ep.n_dst = x.n_dst, ep.col0 = (long long)x.col0;
+  ep.ws = (uint8_t*)x.ws;
   const size_t esz = dtype_size(e->out_dtype);
-  ep.vec_ok = ep.vec_ok && ((col0 * esz) % 16 == 0);
-  if (multicast) {
+  ep.vec_ok = ep.vec_ok && ((x.col0 * esz) % 16 == 0);
+  if (x.multicast) {
     // multimem stores are whole 16-byte pieces: the output width must tile them exactly
     if (!ep.vec_ok || (n_out * esz) % 16 != 0)
       return fail(LQ_ERR_ALIGNMENT, w + ": multicast output needs 16-byte aligned rows, offset and width");
     ep.multicast = 1;
   }
-  for (int i = 1; i < n_dst; ++i) {
-    ep.more_outs[i - 1] = outs[i];
-    ep.vec_ok = ep.vec_ok && aligned16(outs[i]);
+  for (int i = 1; i < x.n_dst; ++i) {
+    ep.more_outs[i - 1] = x.outs[i];
+    ep.vec_ok = ep.vec_ok && aligned16(x.outs[i]);
   }
-  return dispatch(sh, ta, tb, g, ep, a_signed, (cudaStream_t)stream);
+  ep.n_flags = x.n_flags, ep.signal_counter = x.signal_counter;
+  for (int i = 0; i < x.n_flags; ++i) {
+    if (!x.peer_flags[i]) return fail(LQ_ERR_DEVICE, w + ": null flag address");
+    ep.peer_flags[i] = x.peer_flags[i];
+  }
+  return dispatch(plan, ta, tb, g, ep, a_signed, (cudaStream_t)stream);
 }
+
+// One channel group of the convolution.
+int conv_group(const void* x, int x_signed, const int8_t* w, const lq_conv_geometry_t& cg, size_t Cg, size_t Kg,
+               size_t P, size_t Q, const lq_epilogue_t* e, void* out, int32_t* status, void* ws, size_t ws_bytes,
+               void* stream) {
+  Geometry g = {};
+  g.conv = 1;
+  g.P = (int)P, g.Q = (int)Q, g.C = (int)Cg, g.R = (int)cg.R, g.S = (int)cg.S;
+  g.pad_h = (int)cg.pad_h, g.pad_w = (int)cg.pad_w, g.stride_h = (int)cg.stride_h, g.stride_w = (int)cg.stride_w;
+  g.dil_h = (int)cg.dil_h, g.dil_w = (int)cg.dil_w;
+  g.wait_budget = kWaitBudgetCycles;
+  // output pixels per tile: tile_w x tile_h <= 128; a TMA box spans at most 256 input positions
+  size_t tw = Q < (size_t)BM ? Q : (size_t)BM;
+  const size_t tw_cap = 255 / cg.stride_w + 1;
+  if (tw > tw_cap) tw = tw_cap;
+  size_t th = (size_t)BM / tw;
+  if (th > P) th = P;
+  const size_t th_cap = 255 / cg.stride_h + 1;
+  if (th > th_cap) th = th_cap;
+  g.tile_w = (int)tw, g.tile_h = (int)th;
+  g.tiles_q = (int)((Q + tw - 1) / tw);
+  g.tiles_p = (int)((P + th - 1) / th);
+  g.M = (int)(cg.N * P * Q), g.N = (int)Kg, g.K = (int)(cg.R * cg.S * Cg);
+  g.tiles_m = (int)cg.N * g.tiles_p * g.tiles_q;
+  g.cblocks = (int)((Cg + BK - 1) / BK);
+  g.num_kb = (int)(cg.R * cg.S) * g.cblocks;
+  Extras xs;
+  xs.ws = ws, xs.ws_bytes = ws_bytes;
+  int rc = check_workspace("lq_conv2d_nhwc_s8", xs);
+  if (rc) return rc;
+  const Plan plan = pick_plan((size_t)g.tiles_m, Kg, false, (size_t)g.num_kb, ws != nullptr);
+  const int bn = plan.shape == Shape::kSingle128 ? 128 : 256;
+  g.tiles_n = (int)((Kg + bn - 1) / bn);
+  CUtensorMap ta, tb;
+  if ((rc = encode_nhwc(&ta, x, cg.N, cg.H, cg.W, Cg, cg.C, (uint32_t)tw, (uint32_t)th, (uint32_t)cg.stride_w,
+                        (uint32_t)cg.stride_h)))
+    return rc;
+  const size_t kk = cg.R * cg.S * Cg;
+  if ((rc = encode_2d(&tb, w, Kg, kk, kk, plan.shape == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
+  Epi ep;
+  fill_epi(&ep, e, out, cg.K, Kg, status);
+  ep.ws = (uint8_t*)ws;
+  return dispatch(plan, ta, tb, g, ep, x_signed, (cudaStream_t)stream);
+}
+
 }  // namespace
 }  // namespace lq
+
+using namespace lq;
+
+extern "C" void lq_reload_env(void) { knobs_storage().read(); }
+
+extern "C" size_t lq_gemm_workspace_bytes(void) {
+  return (size_t)kWsHeaderBytes + (size_t)kWsMaxCtas * kWsSlotBytes;
+}
 
 extern "C" int lq_gemm_s8(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
                           const lq_epilogue_t* e, void* out, size_t ldo, int32_t* status,
                           void* stream) {
-  if (M != 0 && N != 0 && !out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8: null pointer");
-  void* outs[1] = {out};
-  return gemm_impl("lq_gemm_s8", a, a_signed, b, M, N, K, e, outs, 1, ldo, 0, status, stream);
+  return gemm_impl("lq_gemm_s8", a, a_signed, b, M, N, K, e, out, ldo, status, stream, Extras());
+}
+
+extern "C" int lq_gemm_s8_ws(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                             const lq_epilogue_t* e, void* out, size_t ldo, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
+  Extras x;
+  x.ws = workspace, x.ws_bytes = workspace_bytes;
+  return gemm_impl("lq_gemm_s8_ws", a, a_signed, b, M, N, K, e, out, ldo, status, stream, x);
 }
 
 extern "C" int lq_gemm_s8_bcast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N,
                                 size_t K, const lq_epilogue_t* e, void* const* outs, int n_dst,
                                 size_t ldo, size_t col0, int32_t* status, void* stream) {
-  return gemm_impl("lq_gemm_s8_bcast", a, a_signed, b, M, N, K, e, outs, n_dst, ldo, col0, status, stream);
+  if (!outs) return fail(LQ_ERR_DEVICE, "lq_gemm_s8_bcast: null pointer");
+  Extras x;
+  x.outs = outs, x.n_dst = n_dst, x.col0 = col0;
+  return gemm_impl("lq_gemm_s8_bcast", a, a_signed, b, M, N, K, e, nullptr, ldo, status, stream, x);
 }
 
 extern "C" int lq_gemm_s8_multicast(const void* a, int a_signed, const int8_t* b, size_t M, size_t N,
                                     size_t K, const lq_epilogue_t* e, void* multicast_out, size_t ldo,
                                     size_t col0, int32_t* status, void* stream) {
-  if (M != 0 && N != 0 && !multicast_out) return fail(LQ_ERR_DEVICE, "lq_gemm_s8_multicast: null pointer");
-  void* outs[1] = {multicast_out};
-  return gemm_impl("lq_gemm_s8_multicast", a, a_signed, b, M, N, K, e, outs, 1, ldo, col0, status, stream, true);
+  Extras x;
+  x.multicast = true, x.col0 = col0;
+  return gemm_impl("lq_gemm_s8_multicast", a, a_signed, b, M, N, K, e, multicast_out, ldo, status, stream, x);
+}
+
+extern "C" int lq_gemm_s8_sharded(const void* a, int a_signed, const int8_t* b, size_t M, size_t N, size_t K,
+                                  const lq_epilogue_t* e, void* const* outs, int n_dst, size_t ldo,
+                                  size_t col0, int32_t* const* peer_flags, int n_flags,
+                                  int32_t* signal_counter, void* workspace, size_t workspace_bytes,
+                                  int32_t* status, void* stream) {
+  if (!outs) return fail(LQ_ERR_DEVICE, "lq_gemm_s8_sharded: null pointer");
+  Extras x;
+  x.col0 = col0, x.ws = workspace, x.ws_bytes = workspace_bytes;
+  x.peer_flags = peer_flags, x.n_flags = n_flags, x.signal_counter = signal_counter;
+  if (n_dst == -1) {  // outs[0] is an NVSwitch multicast address
+    x.multicast = true;
+    return gemm_impl("lq_gemm_s8_sharded", a, a_signed, b, M, N, K, e, outs[0], ldo, status, stream, x);
+  }
+  x.outs = outs, x.n_dst = n_dst;
+  return gemm_impl("lq_gemm_s8_sharded", a, a_signed, b, M, N, K, e, nullptr, ldo, status, stream, x);
+}
+
+extern "C" int lq_conv2d_nhwc_s8_ex(const void* x, int x_signed, const int8_t* w, const lq_conv_geometry_t* cgp,
+                                    const lq_epilogue_t* e, void* out, void* workspace, size_t workspace_bytes,
+                                    int32_t* status, void* stream) {
+  const char* who = "lq_conv2d_nhwc_s8";
+  const std::string sw(who);
+  if (!cgp) return fail(LQ_ERR_DEVICE, sw + ": null geometry");
+  const lq_conv_geometry_t cg = *cgp;
+  if (cg.N == 0 || cg.K == 0) return LQ_OK;
+  if (!x || !w || !out) return fail(LQ_ERR_DEVICE, sw + ": null pointer");
+  if (cg.H == 0 || cg.W == 0 || cg.C == 0 || cg.R == 0 || cg.S == 0) return fail(LQ_ERR_SHAPE, sw + ": zero extent");
+  if (cg.stride_h == 0 || cg.stride_w == 0 || cg.dil_h == 0 || cg.dil_w == 0 || cg.groups == 0)
+    return fail(LQ_ERR_SHAPE, sw + ": stride, dilation and groups must be positive");
+  if (cg.stride_h > 8 || cg.stride_w > 8) return fail(LQ_ERR_UNSUPPORTED, sw + ": stride above 8 (TMA traversal stride)");
+  if (cg.C % cg.groups != 0 || cg.K % cg.groups != 0) return fail(LQ_ERR_SHAPE, sw + ": groups must divide C and K");
+  const size_t Cg = cg.C / cg.groups, Kg = cg.K / cg.groups;
+  if (Cg % 16 != 0) return fail(LQ_ERR_ALIGNMENT, sw + ": channels per group must be a multiple of 16");
+  if (!aligned16(x) || !aligned16(w)) return fail(LQ_ERR_ALIGNMENT, sw + ": x and w must be 16-byte aligned");
+  const size_t eff_r = (cg.R - 1) * cg.dil_h + 1, eff_s = (cg.S - 1) * cg.dil_w + 1;
+  if (cg.P == 0 || cg.Q == 0) return fail(LQ_ERR_SHAPE, sw + ": empty output");
+  // every output pixel's window must start inside the padded input: the last rows / columns
+  // may hang over the far edge (implicit zero padding there)
+  if ((cg.P - 1) * cg.stride_h >= cg.H + cg.pad_h || (cg.Q - 1) * cg.stride_w >= cg.W + cg.pad_w)
+    return fail(LQ_ERR_SHAPE, sw + ": output extent larger than the padded input allows");
+  if (cg.pad_h >= eff_r + cg.H || cg.pad_w >= eff_s + cg.W) return fail(LQ_ERR_SHAPE, sw + ": padding larger than the input");
+  int rc = check_epilogue(e, cg.K, who, false);
+  if (rc) return rc;
+  // out-of-image taps read code 0, which stands for the value 0.0 only when the zero point is 0;
+  // a geometry without any such tap (no padding, no overhang) takes the usual correction term
+  const bool reads_outside = cg.pad_h != 0 || cg.pad_w != 0 || (cg.P - 1) * cg.stride_h + eff_r > cg.H ||
+                             (cg.Q - 1) * cg.stride_w + eff_s > cg.W;
+  if (e->a_zp && reads_outside)
+    return fail(LQ_ERR_UNSUPPORTED, sw + ": with implicit padding the activation zero point must be 0 (padding reads code 0)");
+  if (e->a_scale_mode != LQ_PER_TENSOR && e->out_dtype != LQ_S32) return fail(LQ_ERR_UNSUPPORTED, sw + ": per-tensor activation scale only");
+  if (cg.N * cg.P * cg.Q > 0x7fffffffu) return fail(LQ_ERR_SHAPE, sw + ": too many output pixels");
+
+  if (cg.R == 1 && cg.S == 1 && cg.pad_h == 0 && cg.pad_w == 0 && cg.stride_h == 1 && cg.stride_w == 1 &&
+      cg.groups == 1 && cg.P == cg.H && cg.Q == cg.W) {
+    // a 1x1 convolution over NHWC pixels is a plain GEMM with M = N*H*W
+    Extras xs;
+    xs.ws = workspace, xs.ws_bytes = workspace_bytes;
+    return gemm_impl(who, x, x_signed, w, cg.N * cg.H * cg.W, cg.K, cg.C, e, out, cg.K, status, stream, xs);
+  }
+  const size_t esz = dtype_size(e->out_dtype);
+  for (size_t gi = 0; gi < cg.groups; ++gi) {
+    // group gi: input channels [gi*Cg, ...), filters / output channels [gi*Kg, ...)
+    lq_epilogue_t eg = *e;
+    if (eg.b_scale) eg.b_scale += gi * Kg;
+    if (eg.bias) eg.bias += gi * Kg;
+    if (eg.b_rowsum) eg.b_rowsum += gi * Kg;
+    rc = conv_group(static_cast<const uint8_t*>(x) + gi * Cg, x_signed, w + gi * Kg * cg.R * cg.S * Cg, cg, Cg, Kg,
+                    cg.P, cg.Q, &eg, static_cast<uint8_t*>(out) + gi * Kg * esz, status, workspace, workspace_bytes,
+                    stream);
+    if (rc) return rc;
+  }
+  return LQ_OK;
 }
 
 extern "C" int lq_conv2d_nhwc_s8(const void* x, int x_signed, const int8_t* w, size_t N, size_t H,
                                  size_t W, size_t C, size_t K, size_t R, size_t S, size_t stride,
                                  size_t pad, const lq_epilogue_t* e, void* out, int32_t* status,
                                  void* stream) {
-  if (N == 0 || K == 0) return LQ_OK;
-  if (!x || !w || !out) return fail(LQ_ERR_DEVICE, "lq_conv2d_nhwc_s8: null pointer");
-  if (H == 0 || W == 0 || C == 0 || R == 0 || S == 0) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: zero extent");
-  if (stride != 1) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: only stride 1 is implemented");
-  if (C % 16 != 0) return fail(LQ_ERR_ALIGNMENT, "lq_conv2d_nhwc_s8: C must be a multiple of 16");
-  if (!aligned16(x) || !aligned16(w)) return fail(LQ_ERR_ALIGNMENT, "lq_conv2d_nhwc_s8: x and w must be 16-byte aligned");
+  if (stride == 0) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: stride must be positive");
   if (H + 2 * pad < R || W + 2 * pad < S) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: filter larger than padded input");
-  int rc = check_epilogue(e, K, "lq_conv2d_nhwc_s8", false);
-  if (rc) return rc;
-  if (e->a_zp) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: activation zero point must be 0 (padding reads code 0)");
-  if (e->a_scale_mode != LQ_PER_TENSOR && e->out_dtype != LQ_S32) return fail(LQ_ERR_UNSUPPORTED, "lq_conv2d_nhwc_s8: per-tensor activation scale only");
-  const size_t P = H + 2 * pad - R + 1, Q = W + 2 * pad - S + 1;
-  if (N * P * Q > 0x7fffffffu) return fail(LQ_ERR_SHAPE, "lq_conv2d_nhwc_s8: too many output pixels");
-
-  if (R == 1 && S == 1 && pad == 0) {
-    // a 1x1 convolution over NHWC pixels is a plain GEMM with M = N*H*W
-    return lq_gemm_s8(x, x_signed, w, N * H * W, K, C, e, out, K, status, stream);
-  }
-  Geometry g = {};
-  g.conv = 1;
-  g.P = (int)P, g.Q = (int)Q, g.C = (int)C, g.R = (int)R, g.S = (int)S, g.pad = (int)pad;
-  g.tile_w = (int)(Q < (size_t)BM ? Q : BM);
-  g.tile_h = BM / g.tile_w;
-  if ((size_t)g.tile_h > P) g.tile_h = (int)P;
-  g.tiles_q = (int)((Q + g.tile_w - 1) / g.tile_w);
-  g.tiles_p = (int)((P + g.tile_h - 1) / g.tile_h);
-  g.M = (int)(N * P * Q), g.N = (int)K, g.K = (int)(R * S * C);
-  g.tiles_m = (int)N * g.tiles_p * g.tiles_q;
-  const Shape sh = pick_shape((size_t)g.tiles_m, K, false, R * S * ((C + BK - 1) / BK));
-  const int bn = sh == Shape::kSingle128 ? 128 : 256;
-  g.tiles_n = (int)((K + bn - 1) / bn);
-  g.cblocks = (int)((C + BK - 1) / BK);
-  g.num_kb = (int)(R * S) * g.cblocks;
-  CUtensorMap ta, tb;
-  if ((rc = encode_nhwc(&ta, x, N, H, W, C, (uint32_t)g.tile_w, (uint32_t)g.tile_h))) return rc;
-  if ((rc = encode_2d(&tb, w, K, R * S * C, R * S * C, sh == Shape::kPair256 ? 128u : (uint32_t)bn))) return rc;
-  Epi ep;
-  fill_epi(&ep, e, out, K, K, status);
-  return dispatch(sh, ta, tb, g, ep, x_signed, (cudaStream_t)stream);
+  lq_conv_geometry_t cg;
+  cg.N = N, cg.H = H, cg.W = W, cg.C = C, cg.K = K, cg.R = R, cg.S = S;
+  cg.stride_h = cg.stride_w = stride, cg.pad_h = cg.pad_w = pad, cg.dil_h = cg.dil_w = 1, cg.groups = 1;
+  cg.P = (H + 2 * pad - R) / stride + 1, cg.Q = (W + 2 * pad - S) / stride + 1;
+  return lq_conv2d_nhwc_s8_ex(x, x_signed, w, &cg, e, out, nullptr, 0, status, stream);
 }
+
+#ifdef LQ_TESTING
+// Test-only build: a GEMM whose producer issues no loads and whose waits give up after
+// `budget_cycles`, on single-CTA tiles.  Every role leaves its loop when the first wait runs out,
+// the status word receives LQ_ERR_TIMEOUT and the kernel returns normally.
+extern "C" int lq_test_gemm_wait_expiry(const void* a, const int8_t* b, size_t M, size_t N, size_t K, void* out,
+                                        long long budget_cycles, int32_t* status, void* stream) {
+  if (!a || !b || !out || !status) return fail(LQ_ERR_DEVICE, "lq_test_gemm_wait_expiry: null pointer");
+  if (K % 16 != 0 || M == 0 || N == 0 || K == 0) return fail(LQ_ERR_SHAPE, "lq_test_gemm_wait_expiry: shape");
+  Geometry g = {};
+  g.M = (int)M, g.N = (int)N, g.K = (int)K;
+  g.tiles_m = (int)((M + BM - 1) / BM), g.tiles_n = (int)((N + 255) / 256), g.num_kb = (int)((K + BK - 1) / BK);
+  g.wait_budget = budget_cycles, g.test_no_loads = 1;
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = encode_2d(&ta, a, M, K, K, BM))) return rc;
+  if ((rc = encode_2d(&tb, b, N, K, K, 256u))) return rc;
+  lq_epilogue_t e = {};
+  e.out_dtype = LQ_S32;
+  Epi ep;
+  fill_epi(&ep, &e, out, N, N, status);
+  return launch<256, false, 8>(ta, tb, g, ep, make_idesc(1, 256), (cudaStream_t)stream);
+}
+#endif

@@ -623,7 +623,9 @@ size_t hist_smem_bytes(int bins) {
 int hist_grid(size_t n, size_t esz) {
   const size_t per_cta = (size_t)kHistThreads * 4 * (16 / esz);
   const size_t want = (n + per_cta - 1) / per_cta;
-  return (int)(want < 1 ? 1 : (want > (size_t)kHistMaxCtas ? (size_t)kHistMaxCtas : want));
+  size_t cap = (size_t)sm_count() * kHistCtasPerSm;
+  if (cap > (size_t)kHistMaxCtas) cap = (size_t)kHistMaxCtas;  // slots of the workspace
+  return (int)(want < 1 ? 1 : (want > cap ? cap : want));
 }
 int check_hist_common(const char* who, const void* x, size_t n, int in_dtype, int bins, const void* workspace,
                       size_t workspace_bytes) {

@@ -16,7 +16,11 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kCtasPerSm = 8;
-constexpr int kMaxBlocks = kNumSMs * kCtasPerSm;  // 1184
+constexpr int kMaxBlocks = kNumSMs * kCtasPerSm;  // 1184: per-CTA partial slots of the range-reduction workspace
+inline size_t row_grid_cap() {
+  const size_t c = (size_t)sm_count() * kCtasPerSm;
+  return c < (size_t)kMaxBlocks ? c : (size_t)kMaxBlocks;
+}
 
 struct QParamRef {
   const float* s;
@@ -387,8 +391,9 @@ affine_scalar_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __r
   }
 }
 
-inline int grid_for(size_t work_items, size_t cap = (size_t)kNumSMs * 64) {
+inline int grid_for(size_t work_items, size_t ctas_per_sm = 64) {
   size_t blocks = (work_items + kThreads - 1) / kThreads;
+  const size_t cap = (size_t)sm_count() * ctas_per_sm;
   if (blocks > cap) blocks = cap;
   if (blocks == 0) blocks = 1;
   return (int)blocks;
@@ -566,7 +571,11 @@ __device__ __forceinline__ bool run_chunks(const uint8_t* src, size_t total_byte
   int s = 0;
   uint32_t phase = 0;
   for (size_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-    if (!__syncthreads_and(pipe::bar_wait(bar0 + 8 * s, phase) ? 1 : 0)) return false;
+    if (!__syncthreads_and(pipe::bar_wait(bar0 + 8 * s, phase) ? 1 : 0)) {
+      // give copies still in flight time to land before the CTA's shared memory is released
+      for (int i = 0; i < 50; ++i) __nanosleep(20000);
+      return false;
+    }
     consume(buf0 + s * chunk_bytes, c, bytes_of(c));
     pipe::fence_async_smem();  // this thread's reads of the slot precede its refill
     __syncthreads();
@@ -579,7 +588,8 @@ __device__ __forceinline__ bool run_chunks(const uint8_t* src, size_t total_byte
 }
 
 // Number of times a pipelined kernel gave up on a bounded wait (never expected; a copy that
-// does not complete means the source range was not readable).
+// does not complete means the source range was not readable).  The output of such a launch is
+// incomplete; lq_stream_timeouts() reports and clears the count.
 __device__ unsigned int g_pipe_timeouts = 0;
 
 template <Op OP, typename In, typename Out, bool MASK>
@@ -670,10 +680,12 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
     auto kernel = affine_pipe_kernel<OP, In, Out, MASK>;
     constexpr int stages = kRingBytes / kChunkBytes;
     constexpr size_t smem = kRingHeader + kRingBytes;
-    static cudaError_t attr = enable_ring(kernel, smem);
+    static PerDeviceOnce once;
+    const cudaError_t attr = once.run([&] { return enable_ring(kernel, smem); });
     if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
     const size_t nchunks = (n * sizeof(In) + kChunkBytes - 1) / kChunkBytes;
-    const int grid = (int)(nchunks < (size_t)(kNumSMs * 3) ? nchunks : (size_t)(kNumSMs * 3));
+    const size_t cap = (size_t)sm_count() * 3;
+    const int grid = (int)(nchunks < cap ? nchunks : cap);
     kernel<<<grid, kThreads, smem, st>>>((const In*)x, (Out*)out, mask, n, cols, q, (float)qmin, (float)qmax, stages);
   } else if (vec) {
     // 4 groups per thread at full occupancy (32 registers): measured fastest on B200 -- the
@@ -972,6 +984,18 @@ using namespace lq;
 
 extern "C" size_t lq_minmax_workspace_bytes(void) { return sizeof(MinMaxWorkspace); }
 
+extern "C" int lq_stream_timeouts(unsigned int* count) {
+  if (!count) return fail(LQ_ERR_DEVICE, "lq_stream_timeouts: null pointer");
+  unsigned int v = 0;
+  LQ_CUDA(cudaMemcpyFromSymbol(&v, g_pipe_timeouts, sizeof(v)));
+  if (v != 0) {
+    const unsigned int zero = 0;
+    LQ_CUDA(cudaMemcpyToSymbol(g_pipe_timeouts, &zero, sizeof(zero)));
+  }
+  *count = v;
+  return LQ_OK;
+}
+
 extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, int mode,
                          float* out_min, float* out_max, void* workspace, size_t workspace_bytes,
                          void* stream) {
@@ -989,18 +1013,22 @@ extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, 
     const bool vec_ok = aligned16(x);
     // two packets per thread-iteration; grid in multiples of the SM count
     size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
-    int grid = (int)(want < 1 ? 1 : (want > (size_t)(kNumSMs * 4) ? kNumSMs * 4 : want));
+    const size_t gcap = (size_t)sm_count() * 4;
+    int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
     auto* ws = (MinMaxWorkspace*)workspace;
     if (vec_ok && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
       // bulk-copy ring variant (kept for comparison; the register-staged kernel is faster)
       constexpr int stages = kRingBytes / kChunkBytes;
       constexpr size_t smem = kRingHeader + kRingBytes;
-      static cudaError_t a32 = enable_ring(minmax_pipe_kernel<float>, smem);
-      static cudaError_t a16 = enable_ring(minmax_pipe_kernel<__nv_bfloat16>, smem);
-      if (a32 != cudaSuccess || a16 != cudaSuccess)
-        return check_cuda(a32 != cudaSuccess ? a32 : a16, "cudaFuncSetAttribute(ring)");
+      static PerDeviceOnce once;
+      const cudaError_t attr = once.run([&] {
+        const cudaError_t a32 = enable_ring(minmax_pipe_kernel<float>, smem);
+        return a32 != cudaSuccess ? a32 : enable_ring(minmax_pipe_kernel<__nv_bfloat16>, smem);
+      });
+      if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
       const size_t nchunks = (n * esz + kChunkBytes - 1) / kChunkBytes;
-      const int pgrid = (int)(nchunks < (size_t)(kNumSMs * 3) ? nchunks : (size_t)(kNumSMs * 3));
+      const size_t pcap = (size_t)sm_count() * 3;
+      const int pgrid = (int)(nchunks < pcap ? nchunks : pcap);
       if (in_dtype == LQ_F32)
         minmax_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, n, ws, out_min, out_max, stages);
       else
@@ -1018,7 +1046,7 @@ extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, 
       else
         minmax_rows_warp_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, vec_ok, out_min, out_max);
     } else {
-      int grid = (int)(rows < (size_t)kMaxBlocks ? rows : kMaxBlocks);
+      int grid = (int)(rows < row_grid_cap() ? rows : row_grid_cap());
       if (in_dtype == LQ_F32)
         minmax_rows_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, vec_ok, out_min, out_max);
       else
@@ -1114,7 +1142,7 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
   const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
   const bool vec_ok = aligned16(x) && aligned16(out) && ((cols * esz) % 16 == 0) && (cols % 16 == 0);
   const float half = (float)((double)(qmax - qmin) / 2.0);
-  const int grid = (int)(rows < (size_t)kMaxBlocks ? rows : kMaxBlocks);
+  const int grid = (int)(rows < row_grid_cap() ? rows : row_grid_cap());
   cudaStream_t st = (cudaStream_t)stream;
   if (in_dtype != LQ_F32 && in_dtype != LQ_BF16)
     return fail(LQ_ERR_DTYPE, "lq_quantize_per_token: in_dtype must be f32|bf16");
@@ -1125,14 +1153,16 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     int stages = (int)(kRowRing / row_bytes);
     if (stages > 8) stages = 8;
     const size_t smem = kRingHeader + (size_t)stages * row_bytes;
-    static cudaError_t a32 = enable_ring(per_token_pipe_kernel<float>, kRingHeader + kRowRing);
-    static cudaError_t a16 = enable_ring(per_token_pipe_kernel<__nv_bfloat16>, kRingHeader + kRowRing);
-    if (a32 != cudaSuccess || a16 != cudaSuccess)
-      return check_cuda(a32 != cudaSuccess ? a32 : a16, "cudaFuncSetAttribute(ring)");
+    static PerDeviceOnce once;
+    const cudaError_t attr = once.run([&] {
+      const cudaError_t a32 = enable_ring(per_token_pipe_kernel<float>, kRingHeader + kRowRing);
+      return a32 != cudaSuccess ? a32 : enable_ring(per_token_pipe_kernel<__nv_bfloat16>, kRingHeader + kRowRing);
+    });
+    if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
     int ctas_per_sm = (int)((200 * 1024) / smem);
     if (ctas_per_sm > 8) ctas_per_sm = 8;
     if (ctas_per_sm < 1) ctas_per_sm = 1;
-    const size_t cap = (size_t)kNumSMs * ctas_per_sm;
+    const size_t cap = (size_t)sm_count() * ctas_per_sm;
     const int pgrid = (int)(rows < cap ? rows : cap);
     if (in_dtype == LQ_F32)
       per_token_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
@@ -1176,7 +1206,6 @@ namespace lq {
 namespace {
 constexpr size_t kNoAllocMaxElems = size_t(1) << 30;  // 2^30 elements per call
 static __device__ __align__(256) unsigned char g_minmax_scratch[sizeof(MinMaxWorkspace)];
-constexpr int kMaxDevices = 64;
 std::mutex g_scratch_mu;
 void* g_scratch_ptr[kMaxDevices] = {};
 
@@ -1217,7 +1246,8 @@ extern "C" int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* o
   LQ_CUDA(cudaMemsetAsync(scratch, 0, 16, st));
   const bool vec_ok = aligned16(x);
   size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
-  int grid = (int)(want < 1 ? 1 : (want > (size_t)(kNumSMs * 4) ? kNumSMs * 4 : want));
+  const size_t gcap = (size_t)sm_count() * 4;
+  int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
   auto* ws = (MinMaxWorkspace*)scratch;
   if (in_dtype == LQ_F32)
     minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max);
@@ -1396,7 +1426,7 @@ extern "C" int lq_qmerge(int op, const void* x, int x_dtype, const float* x_scal
   auto al = [](const void* p, size_t esz) { return p == nullptr || ((uintptr_t)p % (4 * esz)) == 0; };
   const bool vec = n >= 4 && al(x, merge_elem_size(x_dtype)) && al(y, merge_elem_size(my.dtype)) &&
                    al(out_codes, merge_elem_size(codes_dtype)) && al(out_f32, 4);
-  const int grid = grid_for(vec ? n / 4 : n, (size_t)kNumSMs * 16);
+  const int grid = grid_for(vec ? n / 4 : n, 16);
   cudaStream_t st = (cudaStream_t)stream;
   if (vec)
     merge_kernel<true><<<grid, kThreads, 0, st>>>(op, mx, my, n, out_scale, out_zp, (float)qmin, (float)qmax,
@@ -1411,7 +1441,7 @@ extern "C" int lq_lut_u8(const void* in_codes, size_t n, const uint8_t* table, v
   if (n == 0) return LQ_OK;
   if (!in_codes || !table || !out_codes) return fail(LQ_ERR_DEVICE, "lq_lut_u8: null pointer");
   const bool vec = n >= 16 && aligned16(in_codes) && aligned16(out_codes);
-  const int grid = grid_for(vec ? n / 16 : n, (size_t)kNumSMs * 8);
+  const int grid = grid_for(vec ? n / 16 : n, 8);
   cudaStream_t st = (cudaStream_t)stream;
   if (vec)
     lut_kernel<true><<<grid, kThreads, 0, st>>>((const uint8_t*)in_codes, n, table, (uint8_t*)out_codes);
@@ -1481,21 +1511,17 @@ extern "C" int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, co
   if (!x_codes || !y_codes || !table || !out_codes) return fail(LQ_ERR_DEVICE, "lq_lut2_u8: null pointer");
   if (out_f32 && (!out_scale || !out_zp)) return fail(LQ_ERR_DEVICE, "lq_lut2_u8: out_f32 needs the output grid");
   if (!aligned16(table)) return fail(LQ_ERR_ALIGNMENT, "lq_lut2_u8: the table must be 16-byte aligned");
-  static cudaError_t attr = cudaFuncSetAttribute(lut2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLut2Bytes);
-  // the attribute is per device: set it again when the call runs on another one
-  static int attr_dev = -1;
-  int devid = 0;
-  LQ_CUDA(cudaGetDevice(&devid));
-  if (devid != attr_dev) {
-    attr = cudaFuncSetAttribute(lut2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLut2Bytes);
-    attr_dev = devid;
-  }
+  static PerDeviceOnce once;
+  const cudaError_t attr = once.run([&] {
+    return cudaFuncSetAttribute(lut2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLut2Bytes);
+  });
   if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(lut2)");
   const bool vec = n >= 16 && aligned16(x_codes) && aligned16(y_codes) && aligned16(out_codes) &&
                    (!out_f32 || aligned16(out_f32));
   // persistent CTAs, three per SM (3 x 64 KB of tables); small inputs take fewer
   const size_t want = ((vec ? n / 16 : n) + kThreads - 1) / kThreads;
-  const int grid = (int)(want < (size_t)(kNumSMs * 3) ? (want ? want : 1) : (size_t)(kNumSMs * 3));
+  const size_t lcap = (size_t)sm_count() * 3;
+  const int grid = (int)(want < lcap ? (want ? want : 1) : lcap);
   lut2_kernel<<<grid, kThreads, kLut2Bytes, (cudaStream_t)stream>>>(
       (const uint8_t*)x_codes, (const uint8_t*)y_codes, n, table, (uint8_t*)out_codes, out_f32, out_scale, out_zp,
       out_signed, vec);
@@ -1518,14 +1544,18 @@ struct BcastDst {
 template <typename In>
 __global__ void __launch_bounds__(kThreads)
 quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, size_t ldx,
-                           const float* __restrict__ row_absmax, float half, float eps, float qmin, float qmax,
+                           const float* __restrict__ row_absmax, int absmax_parts, size_t absmax_stride,
+                           float half, float eps, float qmin, float qmax,
                            BcastDst dst, int n_dst, bool multicast, size_t ldo, size_t col0,
                            float* __restrict__ out_scale) {
   constexpr int E = VecOf<In>::kElems;  // 4 (binary32) or 8 (bfloat16) elements per 16-byte vector
   const uint32_t nvec = (uint32_t)(cols / E);
   for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
     // the same expressions as the single-GPU per-token encode
-    const float sc = fmaxf(__fdiv_rn(__ldg(row_absmax + r), half), eps);
+    // (max over the shards' maxima: order-free, so the value is the unsharded row's abs-max)
+    float am = __ldcg(row_absmax + r);
+    for (int p = 1; p < absmax_parts; ++p) am = fmaxf(am, __ldcg(row_absmax + p * absmax_stride + r));
+    const float sc = fmaxf(__fdiv_rn(am, half), eps);
     if (threadIdx.x == 0 && out_scale) out_scale[r] = sc;
     const Divisor d = make_divisor(sc);
     const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
@@ -1564,7 +1594,8 @@ quantize_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, s
 }  // namespace lq
 
 extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
-                                      const float* row_absmax, int qmin, int qmax, float eps,
+                                      const float* row_absmax, int absmax_parts, size_t absmax_stride,
+                                      int qmin, int qmax, float eps,
                                       void* const* outs, int n_dst, size_t ldo, size_t col0,
                                       float* out_scale, void* stream) {
   if (rows == 0 || cols == 0) return LQ_OK;
@@ -1573,6 +1604,8 @@ extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, 
   const bool multicast = n_dst == -1;
   if (multicast) n_dst = 1;
   if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: 1..8 destinations (or -1: multicast)");
+  if (absmax_parts < 1 || absmax_parts > 64 || (absmax_parts > 1 && absmax_stride < rows))
+    return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: abs-max parts / stride");
   if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_quantize_rows_bcast: in_dtype");
   if (qmin < -128 || qmax > 127 || qmin >= qmax) return fail(LQ_ERR_SHAPE, "lq_quantize_rows_bcast: grid outside int8");
   const size_t e = in_dtype == LQ_F32 ? 4 : 8;
@@ -1584,14 +1617,155 @@ extern "C" int lq_quantize_rows_bcast(const void* x, int in_dtype, size_t rows, 
     dst.p[k] = (int8_t*)outs[k];
   }
   const float half = (float)((qmax - qmin) / 2.0);
-  const int grid = (int)(rows < (size_t)kMaxBlocks ? rows : (size_t)kMaxBlocks);
+  const int grid = (int)(rows < row_grid_cap() ? rows : row_grid_cap());
   cudaStream_t st = (cudaStream_t)stream;
   if (in_dtype == LQ_F32)
-    quantize_rows_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, ldx, row_absmax, half, eps,
-                                                                 (float)qmin, (float)qmax, dst, n_dst, multicast, ldo, col0, out_scale);
+    quantize_rows_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, ldx, row_absmax, absmax_parts,
+                                                                 absmax_stride, half, eps, (float)qmin, (float)qmax, dst, n_dst,
+                                                                 multicast, ldo, col0, out_scale);
   else
     quantize_rows_bcast_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, ldx,
-                                                                         row_absmax, half, eps, (float)qmin, (float)qmax,
-                                                                         dst, n_dst, multicast, ldo, col0, out_scale);
+                                                                         row_absmax, absmax_parts, absmax_stride, half, eps,
+                                                                         (float)qmin, (float)qmax, dst, n_dst, multicast, ldo,
+                                                                         col0, out_scale);
   return check_cuda(cudaGetLastError(), "lq_quantize_rows_bcast launch");
+}
+
+// ---- pieces of the exchange that are not a GEMM ------------------------------------------------
+namespace lq {
+struct FloatDst {
+  float* p[8];
+};
+
+// Per-row abs-max of this rank's column shard, stored into slot `slot0 + r` of every rank's
+// (parts, rows) table: the max all-reduce of the sharded per-token encode as plain peer stores.
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+absmax_rows_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, size_t ldx, bool vec_ok,
+                         FloatDst dst, int n_dst, size_t slot0) {
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float mn = 0.0f, mx = 0.0f;  // the range is extended to include 0 anyway
+    minmax_accumulate(x + r * ldx, cols, threadIdx.x, kThreads, vec_ok, mn, mx);
+    block_minmax(mn, mx);
+    if (threadIdx.x < n_dst) dst.p[threadIdx.x][slot0 + r] = fmaxf(fabsf(mn), fabsf(mx));
+  }
+}
+
+// Per-token encode of a ROW shard with the exchange fused in: this rank encodes its rows of a
+// replicated activation (abs-max, scale, codes: the expressions of lq_quantize_per_token) and
+// stores codes and scales at rows [row0, row0 + rows) of every rank's buffers.
+template <typename In>
+__global__ void __launch_bounds__(kThreads)
+per_token_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps, float qmin,
+                       float qmax, BcastDst dst, FloatDst sdst, int n_dst, bool multicast, size_t row0) {
+  constexpr int E = VecOf<In>::kElems;
+  __shared__ float s_scale;
+  const uint32_t nvec = (uint32_t)(cols / E);
+  for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const In* xr = x + r * cols;
+    float mn = 0.0f, mx = 0.0f;
+    minmax_accumulate(xr, cols, threadIdx.x, kThreads, true, mn, mx);
+    block_minmax(mn, mx);
+    if (threadIdx.x == 0) s_scale = fmaxf(__fdiv_rn(fmaxf(fabsf(mn), fabsf(mx)), half), eps);
+    __syncthreads();
+    const float sc = s_scale;
+    // every destination receives the scale with a plain store (a multicast address is used for
+    // the codes only)
+    if (threadIdx.x < n_dst) sdst.p[threadIdx.x][row0 + r] = sc;
+    const Divisor d = make_divisor(sc);
+    const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    const uint4* xv = reinterpret_cast<const uint4*>(xr);
+    const size_t obase = (row0 + r) * cols;
+    for (uint32_t i = threadIdx.x; i < nvec; i += kThreads) {
+      const uint4 v = __ldcg(xv + i);  // second read of the row: served by L2
+      const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+      if (E == 4) {
+        const float f[4] = {__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3])};
+        int c[4];
+        code4_int(f, d, ig, 0.0f, qmin, qmax, c);
+        const uint32_t w = pack4i_s8(c);
+        if (multicast)
+          asm volatile("multimem.st.weak.global.b32 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 4), "r"(w) : "memory");
+        else
+          for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint32_t*>(dst.p[k] + obase + (size_t)i * 4) = w;
+      } else {
+        const float f0[4] = {bf16_bits_to_f32(wv[0] & 0xffffu), bf16_bits_to_f32(wv[0] >> 16),
+                             bf16_bits_to_f32(wv[1] & 0xffffu), bf16_bits_to_f32(wv[1] >> 16)};
+        const float f1[4] = {bf16_bits_to_f32(wv[2] & 0xffffu), bf16_bits_to_f32(wv[2] >> 16),
+                             bf16_bits_to_f32(wv[3] & 0xffffu), bf16_bits_to_f32(wv[3] >> 16)};
+        int c0[4], c1[4];
+        code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
+        code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        const uint2 w = make_uint2(pack4i_s8(c0), pack4i_s8(c1));
+        if (multicast)
+          asm volatile("multimem.st.weak.global.b64 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 8),
+                       "l"((unsigned long long)w.x | ((unsigned long long)w.y << 32)) : "memory");
+        else
+          for (int k = 0; k < n_dst; ++k) *reinterpret_cast<uint2*>(dst.p[k] + obase + (size_t)i * 8) = w;
+      }
+    }
+    __syncthreads();  // s_scale is rewritten by the next row
+  }
+}
+}  // namespace lq
+
+extern "C" int lq_absmax_rows_bcast(const void* x, int in_dtype, size_t rows, size_t cols, size_t ldx,
+                                    float* const* outs, int n_dst, size_t slot0, void* stream) {
+  if (rows == 0 || cols == 0) return LQ_OK;
+  if (!x || !outs) return fail(LQ_ERR_DEVICE, "lq_absmax_rows_bcast: null pointer");
+  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_absmax_rows_bcast: 1..8 destinations");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_absmax_rows_bcast: in_dtype");
+  const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
+  const bool vec_ok = aligned16(x) && ((cols * esz) % 16 == 0) && ((ldx * esz) % 16 == 0);
+  FloatDst dst{};
+  for (int k = 0; k < n_dst; ++k) {
+    if (!outs[k]) return fail(LQ_ERR_DEVICE, "lq_absmax_rows_bcast: null destination");
+    dst.p[k] = outs[k];
+  }
+  const int grid = (int)(rows < row_grid_cap() ? rows : row_grid_cap());
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == LQ_F32)
+    absmax_rows_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, ldx, vec_ok, dst, n_dst, slot0);
+  else
+    absmax_rows_bcast_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, ldx, vec_ok, dst,
+                                                                        n_dst, slot0);
+  return check_cuda(cudaGetLastError(), "lq_absmax_rows_bcast launch");
+}
+
+extern "C" int lq_quantize_per_token_bcast(const void* x, int in_dtype, size_t rows, size_t cols, int qmin, int qmax,
+                                           float eps, void* const* outs, float* const* scale_outs, int n_dst,
+                                           void* multicast_out, size_t row0, void* stream) {
+  if (rows == 0 || cols == 0) return LQ_OK;
+  if (!x || !scale_outs || (!outs && !multicast_out)) return fail(LQ_ERR_DEVICE, "lq_quantize_per_token_bcast: null pointer");
+  if (n_dst < 1 || n_dst > 8) return fail(LQ_ERR_SHAPE, "lq_quantize_per_token_bcast: 1..8 destinations");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_quantize_per_token_bcast: in_dtype");
+  if (qmin < -128 || qmax > 127 || qmin >= qmax) return fail(LQ_ERR_SHAPE, "lq_quantize_per_token_bcast: grid outside int8");
+  const size_t e = in_dtype == LQ_F32 ? 4 : 8;
+  if (cols % 16 || !aligned16(x)) return fail(LQ_ERR_ALIGNMENT, "lq_quantize_per_token_bcast: cols % 16 and a 16-byte aligned input");
+  (void)e;
+  BcastDst dst{};
+  FloatDst sdst{};
+  for (int k = 0; k < n_dst; ++k) {
+    if (!scale_outs[k]) return fail(LQ_ERR_DEVICE, "lq_quantize_per_token_bcast: null scale destination");
+    sdst.p[k] = scale_outs[k];
+    if (!multicast_out) {
+      if (!outs[k] || (reinterpret_cast<uintptr_t>(outs[k]) & 7u)) return fail(LQ_ERR_ALIGNMENT, "lq_quantize_per_token_bcast: destination pointer");
+      dst.p[k] = (int8_t*)outs[k];
+    }
+  }
+  if (multicast_out) {
+    if (reinterpret_cast<uintptr_t>(multicast_out) & 7u) return fail(LQ_ERR_ALIGNMENT, "lq_quantize_per_token_bcast: multicast address");
+    dst.p[0] = (int8_t*)multicast_out;
+  }
+  const float half = (float)((qmax - qmin) / 2.0);
+  const int grid = (int)(rows < row_grid_cap() ? rows : row_grid_cap());
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == LQ_F32)
+    per_token_bcast_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax,
+                                                             dst, sdst, n_dst, multicast_out != nullptr, row0);
+  else
+    per_token_bcast_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps,
+                                                                     (float)qmin, (float)qmax, dst, sdst, n_dst,
+                                                                     multicast_out != nullptr, row0);
+  return check_cuda(cudaGetLastError(), "lq_quantize_per_token_bcast launch");
 }

@@ -21,15 +21,33 @@ class QCodes:
     zero_point: torch.Tensor  # 0-d f32
     layout: str = "rowmajor"  # "rowmajor" | "nhwc"
     zp_is_zero: bool | None = None  # known on the host without a sync, when not None
+    # identity of the float tensor at tag time (set by `tag`): an in-place op on the tensor
+    # (relu_(), `y += identity`, nn.ReLU(inplace=True)) keeps the Python attribute but bumps
+    # the version counter, and the codes no longer describe the values
+    version: int = -1
+    data_ptr: int = 0
 
 
 def tag(t: torch.Tensor, qc: QCodes) -> torch.Tensor:
+    qc.version, qc.data_ptr = t._version, t.data_ptr()
     t._lq_codes = qc
     return t
 
 
 def codes_of(t: torch.Tensor):
-    return getattr(t, "_lq_codes", None)
+    """The codes riding on ``t``, or None when there are none or ``t`` was modified in place
+    since it was tagged (the consumer then re-encodes the float values, as the reference,
+    which only ever sees the float tensor, does)."""
+    qc = getattr(t, "_lq_codes", None)
+    if qc is None:
+        return None
+    if qc.version != t._version or qc.data_ptr != t.data_ptr():
+        try:
+            del t._lq_codes
+        except AttributeError:
+            pass
+        return None
+    return qc
 
 
 def quantize_weight(mod) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:

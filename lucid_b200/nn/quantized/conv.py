@@ -55,77 +55,83 @@ class Conv2d(torch.nn.Module):
         self.register_buffer("scale", torch.tensor(1.0))
         self.register_buffer("zero_point", torch.tensor(0.0))
         self._cache = _WeightCache()
+        # An untagged input is encoded on the affine quint8 grid of its live range; its zero point
+        # is 0 exactly when the range has no negative part.  Set to False (e.g. by a caller that
+        # knows the layer follows a ReLU) to skip the one-scalar read-back of that zero point.
+        self._input_may_be_negative = True
 
     def _activation(self, y):
         return F.relu(y) if self._RELU else y
 
-    def _resolved_padding(self):
+    def _geometry(self, h: int, w: int):
+        """((pad_top, pad_left), (P, Q)) for an input of h x w, following the reference's
+        ``_resolve_pad`` (lucid/nn/quantized/conv.py:119-144; "same": pad_lo = total // 2, the
+        larger half after the last row / column)."""
+        kh, kw = self.kernel_size
+        (sh, sw), (dh, dw) = self.stride, self.dilation
         if self.padding_str == "valid":
-            return (0, 0)
-        if self.padding_str == "same":
-            kh, kw = self.kernel_size
-            if kh % 2 == 1 and kw % 2 == 1 and self.stride == (1, 1) and self.dilation == (1, 1):
-                return (kh // 2, kw // 2)
-            return None  # asymmetric "same": float route
-        return self.padding
+            lo, hi = (0, 0), (0, 0)
+        elif self.padding_str == "same":
+            def pair(size, k, st, dl):
+                out = (size + st - 1) // st
+                total = max(0, (out - 1) * st + (k - 1) * dl + 1 - size)
+                return total // 2, total - total // 2
+            (lh, hh), (lw, hw) = pair(h, kh, sh, dh), pair(w, kw, sw, dw)
+            lo, hi = (lh, lw), (hh, hw)
+        else:
+            lo, hi = self.padding, self.padding
+        p = (h + lo[0] + hi[0] - dh * (kh - 1) - 1) // sh + 1
+        q = (w + lo[1] + hi[1] - dw * (kw - 1) - 1) // sw + 1
+        return lo, hi, (p, q)
 
     def _int8_ok(self):
         def probe():
             return bool((self.weight_zero_point == 0).all().item())
         sym = self._cache.get(self.weight_int8, "wz0:%d" % self.weight_zero_point._version, probe)
-        pad = self._resolved_padding()
-        ok = (sym and self.groups == 1 and self.dilation == (1, 1) and self.stride == (1, 1) and
-              self.padding_mode == "zeros" and pad is not None and pad[0] == pad[1] and
-              self.in_channels % 16 == 0 and self.out_qdtype.bits == 8 and self.weight_ch_axis == 0)
+        ok = (sym and self.padding_mode == "zeros" and (self.in_channels // self.groups) % 16 == 0 and
+              max(self.stride) <= 8 and self.out_qdtype.bits == 8 and self.weight_ch_axis == 0)
         if not ok and not getattr(self, "_warned", False):
-            warnings.warn(f"{type(self).__name__}: geometry outside the implicit-GEMM path; "
-                          "running the dequantize-to-float route", stacklevel=3)
+            warnings.warn(f"{type(self).__name__}: configuration outside the implicit-GEMM path "
+                          "(affine weights, non-zero padding mode, channels per group not a multiple "
+                          "of 16, stride above 8 or a non-8-bit grid); running the dequantize-to-float route",
+                          stacklevel=3)
             self._warned = True
         return ok
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _lib.require_cuda(x, "input")
+        _lib.check_device_status_lazily(x.device)
         if backends.quantized.use_int8() and self._int8_ok():
             return self._forward_int8(x)
         return self._forward_float(x)
 
     def forward_codes(self, a_nhwc: torch.Tensor, a_scale, zp_is_zero: bool = True, a_zp=None):
-        """NHWC codes in -> NHWC codes out on this module's output grid."""
+        """NHWC codes in -> NHWC codes out on this module's output grid.  One kernel per group;
+        a non-zero input zero point costs one extra copy (the padded frame)."""
         w = self.weight_int8
         w_krsc = self._cache.get(w, "krsc", lambda: w.permute(0, 2, 3, 1).contiguous())
-        pad = self._resolved_padding()[0]
+        n, h, wd, c = a_nhwc.shape
+        lo, hi, out_hw = self._geometry(h, wd)
         unsigned = not self.out_qdtype.signed
         common = dict(out_dtype=torch.uint8 if unsigned else torch.int8, b_scale=self.weight_scale,
                       bias=self.bias, act=_lib.ACT_RELU if self._RELU else _lib.ACT_NONE,
                       out_scale=self.scale, out_zp=self.zero_point,
-                      qmin=self.out_qdtype.quant_min, qmax=self.out_qdtype.quant_max)
+                      qmin=self.out_qdtype.quant_min, qmax=self.out_qdtype.quant_max,
+                      stride=self.stride, dilation=self.dilation, groups=self.groups)
         if zp_is_zero:
-            return QF.conv2d_nhwc_s8(a_nhwc, w_krsc, pad=pad, a_scale=a_scale, **common)
-        # non-zero input zero point: lay the codes into a frame filled with the code of 0.0,
-        # then the plain zero-point correction is exact (every tap holds a real code)
-        n, h, wd, c = a_nhwc.shape
-        if pad:
-            frame = torch.empty((n, h + 2 * pad, wd + 2 * pad, c), dtype=a_nhwc.dtype, device=a_nhwc.device)
+            return QF.conv2d_nhwc_s8(a_nhwc, w_krsc, pad=lo, out_hw=out_hw, a_scale=a_scale, **common)
+        # Non-zero input zero point: the reference pads the float activation with 0.0, whose code
+        # is the zero point, so lay the codes into a frame filled with that code; then every tap
+        # holds a real code and the kernel's zero-point correction term is exact.
+        if any(lo) or any(hi):
+            frame = torch.empty((n, h + lo[0] + hi[0], wd + lo[1] + hi[1], c), dtype=a_nhwc.dtype,
+                                device=a_nhwc.device)
             frame.copy_(a_zp.to(a_nhwc.dtype).reshape(1, 1, 1, 1).expand_as(frame))
-            frame[:, pad:pad + h, pad:pad + wd, :] = a_nhwc
+            frame[:, lo[0]:lo[0] + h, lo[1]:lo[1] + wd, :] = a_nhwc
             a_nhwc = frame
-        kh, kw = self.kernel_size
-        p, q = a_nhwc.shape[1] - kh + 1, a_nhwc.shape[2] - kw + 1
         rowsum = self._cache.get(w, "rowsum", lambda: QF.rowsum_s8(w_krsc))
-        if kh == 1 and kw == 1:
-            out = QF.gemm_s8(a_nhwc.reshape(-1, c), w_krsc.reshape(self.out_channels, -1),
-                             a_scale=a_scale, a_zp=a_zp, b_rowsum=rowsum, **common)
-            return out.reshape(n, p, q, self.out_channels)
-        # im2col-free needs zero point 0; fold the correction on the accumulator instead
-        acc = QF.conv2d_nhwc_s8(a_nhwc, w_krsc, pad=0, out_dtype=torch.int32)
-        acc = acc - (a_zp.to(torch.int32) * rowsum).reshape(1, 1, 1, -1)
-        y = acc.to(torch.float32) * (a_scale * self.weight_scale).reshape(1, 1, 1, -1)
-        if self.bias is not None:
-            y = y + self.bias.reshape(1, 1, 1, -1)
-        y = self._activation(y)
-        from ...quantization import quantize_to
-        return quantize_to(y, self.scale, self.zero_point, self.out_qdtype.quant_min,
-                           self.out_qdtype.quant_max, common["out_dtype"])
+        return QF.conv2d_nhwc_s8(a_nhwc, w_krsc, pad=0, out_hw=out_hw, a_scale=a_scale, a_zp=a_zp,
+                                 b_rowsum=rowsum, **common)
 
     def _forward_int8(self, x):
         qc = codes_of(x)
@@ -133,7 +139,12 @@ class Conv2d(torch.nn.Module):
             a, s, z = qc.codes, qc.scale, qc.zero_point
         else:
             a, s, z = encode_activation(x.permute(0, 2, 3, 1))
-        zp0 = bool((z == 0).item()) if qc is None or qc.zp_is_zero is None else qc.zp_is_zero
+        if qc is not None and qc.zp_is_zero is not None:
+            zp0 = qc.zp_is_zero
+        elif qc is None and not self._input_may_be_negative:
+            zp0 = True
+        else:
+            zp0 = bool((z == 0).item())
         codes = self.forward_codes(a, s, zp0, z)
         y = dequantize(codes, self.scale, self.zero_point).permute(0, 3, 1, 2)
         out_zp0 = self._cache.get(self.weight_int8, "ozp0:%d" % self.zero_point._version,
@@ -143,16 +154,14 @@ class Conv2d(torch.nn.Module):
     def _forward_float(self, x):
         w = dequantize(self.weight_int8, self.weight_scale, self.weight_zero_point,
                        ch_axis=self.weight_ch_axis)
-        pad = self._resolved_padding()
+        lo, hi, _ = self._geometry(x.shape[2], x.shape[3])
         x = x.to(torch.float32)
-        if pad is None:
-            y = F.conv2d(x, w, self.bias, self.stride, "same", self.dilation, self.groups)
-        elif self.padding_mode != "zeros":
-            mode = {"reflect": "reflect", "replicate": "replicate", "circular": "circular"}[self.padding_mode]
-            xp = F.pad(x, (pad[1], pad[1], pad[0], pad[0]), mode=mode)
+        mode = "constant" if self.padding_mode == "zeros" else self.padding_mode
+        if mode != "constant" or lo != hi:
+            xp = F.pad(x, (lo[1], hi[1], lo[0], hi[0]), mode=mode)
             y = F.conv2d(xp, w, self.bias, self.stride, 0, self.dilation, self.groups)
         else:
-            y = F.conv2d(x, w, self.bias, self.stride, pad, self.dilation, self.groups)
+            y = F.conv2d(x, w, self.bias, self.stride, lo, self.dilation, self.groups)
         y = self._activation(y).contiguous()
         return fake_quantize(y, self.scale, self.zero_point, self.out_qdtype.quant_min,
                              self.out_qdtype.quant_max)

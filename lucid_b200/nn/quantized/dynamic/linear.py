@@ -16,10 +16,14 @@ quantize(ch_axis=0) -> linear).
 
 from __future__ import annotations
 
-import torch
+import warnings
 
-from .... import _lib
-from ....quantization import (PerChannelMinMaxObserver, QDtype, per_channel_symmetric, qint8, quantize,
+import torch
+import torch.nn.functional as F
+
+from .... import _lib, backends
+from ....quantization import (PerChannelMinMaxObserver, QDtype, calculate_qparams, dequantize, fake_quantize,
+                              minmax, per_channel_symmetric, per_tensor_affine, qint8, quantize,
                               quantize_dynamic_per_tensor, quantize_per_token, quint8)
 from .. import functional as QF
 from ..linear import _WeightCache
@@ -48,10 +52,34 @@ class Linear(torch.nn.Module):
             self.bias = None
         self._cache = _WeightCache()
 
+    def _int8_ok(self) -> bool:
+        """The integer path needs symmetric weights (zero point 0) on the row axis and
+        ``in_features % 16 == 0``; anything else takes the reference's float sequence."""
+        def probe():
+            return bool((self.weight_zero_point == 0).all().item())
+        sym = self._cache.get(self.weight_int8, "wz0:%d" % self.weight_zero_point._version, probe)
+        ok = sym and self.weight_ch_axis == 0 and self.in_features % 16 == 0
+        if not ok and not getattr(self, "_warned", False):
+            warnings.warn("dynamic.Linear: configuration outside the integer path (affine weights or "
+                          "in_features % 16 != 0); running the dequantize-to-float route", stacklevel=3)
+            self._warned = True
+        return ok
+
+    def _forward_float(self, x: torch.Tensor) -> torch.Tensor:
+        """The reference's own sequence (lucid/nn/quantized/dynamic/linear.py:84-99) on device:
+        fake-quantize the input on its live affine grid, dequantize the weight, float GEMM."""
+        x32 = x.to(torch.float32)
+        mn, mx = minmax(x32.reshape(-1))
+        s, z = calculate_qparams(mn, mx, per_tensor_affine, self.act_qdtype)
+        xq = fake_quantize(x32.contiguous(), s, z, self.act_qdtype.quant_min, self.act_qdtype.quant_max)
+        w = dequantize(self.weight_int8, self.weight_scale, self.weight_zero_point, ch_axis=self.weight_ch_axis)
+        return F.linear(xq, w, self.bias)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _lib.require_cuda(x, "input")
-        if self.in_features % 16 != 0:
-            raise NotImplementedError("dynamic.Linear needs in_features % 16 == 0 on the integer path")
+        _lib.check_device_status_lazily(x.device)
+        if not (backends.quantized.use_int8() and self._int8_ok()):
+            return self._forward_float(x)
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         a, x_scale, x_zp = quantize_dynamic_per_tensor(x2, self.act_qdtype)

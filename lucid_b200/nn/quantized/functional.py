@@ -31,8 +31,28 @@ def _f32(t, dev, what):
     return t.contiguous()
 
 
+def _need(t, count, what):
+    if t is not None and t.numel() != count:
+        raise _lib.ShapeMismatch(f"{what} has {t.numel()} entries, expected {count}")
+
+
+def _check_out(out, rows, cols, dev, what):
+    """`out=` of the contraction wrappers: the kernel writes rows x cols elements at the row
+    stride of `out`, so anything smaller, of another dtype or on another device is refused."""
+    if not isinstance(out, torch.Tensor) or not out.is_cuda or out.device != dev:
+        raise _lib.DeviceMismatch(f"{what}: out= must be a CUDA tensor on {dev}")
+    if out.dtype not in _OUT_CODE:
+        raise _lib.DtypeMismatch(f"{what}: unsupported output dtype {out.dtype}")
+    if out.dim() != 2 or out.shape[0] != rows or out.shape[1] != cols:
+        raise _lib.ShapeMismatch(f"{what}: out= is {tuple(out.shape)}, expected {(rows, cols)}")
+    if out.stride(1) != 1 or out.stride(0) < cols:
+        raise _lib.ShapeMismatch(f"{what}: out= must have unit column stride and a row stride >= {cols}")
+
+
 def _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
-              qmin, qmax, keep):
+              qmin, qmax, keep, m=None, n=None):
+    """Marshal the epilogue descriptor.  `m` / `n` (rows of the activation operand, rows of the
+    weight operand) bound every per-row / per-channel vector the kernel will index."""
     if out_dtype not in _OUT_CODE:
         raise _lib.DtypeMismatch(f"unsupported GEMM output dtype {out_dtype}")
     a_scale = _f32(a_scale, dev, "a_scale")
@@ -44,6 +64,11 @@ def _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_s
     if b_rowsum is not None:
         b_rowsum = b_rowsum.to(device=dev, dtype=torch.int32).contiguous()
     keep.extend([a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp])
+    if m is not None and a_scale is not None and a_scale.numel() not in (1, m):
+        raise _lib.ShapeMismatch(f"a_scale has {a_scale.numel()} entries, expected 1 or {m}")
+    if n is not None:
+        _need(b_scale, n, "b_scale"), _need(bias, n, "bias"), _need(b_rowsum, n, "b_rowsum")
+    _need(a_zp, 1, "a_zp"), _need(out_scale, 1, "out_scale"), _need(out_zp, 1, "out_zp")
     e = _lib.Epilogue()
     e.out_dtype = _OUT_CODE[out_dtype]
     e.act = act
@@ -91,24 +116,31 @@ def gemm_s8(a, b, *, out_dtype=torch.int32, a_scale=None, a_zp=None, b_rowsum=No
     dev = a.device
     if out is None:
         out = torch.empty((m, n_out), dtype=out_dtype, device=dev)
+    else:
+        _check_out(out, m, n_out, dev, "gemm_s8")
     keep: list = []
     e = _epilogue(dev, out.dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
-                  qmin, qmax, keep)
+                  qmin, qmax, keep, m, n)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().lq_gemm_s8(
+        ws = _lib.gemm_workspace(dev)
+        _lib.check(_lib.load().lq_gemm_s8_ws(
             _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e),
-            _lib.ptr(out), out.stride(0), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+            _lib.ptr(out), out.stride(0), _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)),
+            _lib.stream_ptr(dev)))
     return out
 
 
 def gemm_s8_bcast(a, b, dst_ptrs, dst_shape, col0, *, out_dtype=torch.bfloat16, a_scale=None, a_zp=None,
                   b_rowsum=None, b_scale=None, bias=None, act=_lib.ACT_NONE, out_scale=None,
-                  out_zp=None, qmin=0, qmax=0):
+                  out_zp=None, qmin=0, qmax=0, signal=None):
     """`gemm_s8` whose epilogue stores every tile into several `(M, ld)` buffers at column
     offset `col0`: `dst_ptrs` are raw device addresses (this GPU's buffer first, then the same
     buffer on its peers, e.g. `_SymmetricMemory.buffer_ptrs`) or ONE int, the buffer's NVSwitch
-    multicast address (`_SymmetricMemory.multicast_ptr`); `dst_shape = (M, ld)`.  The caller
-    synchronises the ranks before the buffers are read."""
+    multicast address (`_SymmetricMemory.multicast_ptr`); `dst_shape = (M, ld)`.
+    `signal = (flag_addresses, counter_tensor)`: when the last tile is stored the kernel bumps
+    this rank's step counter and publishes it to the given flag words (this rank's word on every
+    rank); consumers wait with `peer_wait`.  Without `signal` the caller synchronises the ranks
+    before the buffers are read."""
     _lib.require_cuda(a, "activation codes")
     _lib.require_cuda(b, "weight codes")
     if a.dtype not in (torch.int8, torch.uint8) or b.dtype != torch.int8:
@@ -126,44 +158,86 @@ def gemm_s8_bcast(a, b, dst_ptrs, dst_shape, col0, *, out_dtype=torch.bfloat16, 
     dev = a.device
     keep: list = []
     e = _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
-                  qmin, qmax, keep)
+                  qmin, qmax, keep, m, n)
+    multicast = isinstance(dst_ptrs, int)  # an NVSwitch multicast address: one store reaches every rank
+    plist = [dst_ptrs] if multicast else [int(p) for p in dst_ptrs]
+    ptrs = (C.c_void_p * len(plist))(*plist)
+    if signal is not None:
+        flag_addrs, counter = signal
+        flags = (C.c_void_p * len(flag_addrs))(*[int(p) for p in flag_addrs])
+        n_flags, counter_ptr = len(flag_addrs), _lib.ptr(counter)
+    else:
+        flags, n_flags, counter_ptr = None, 0, None
     with torch.cuda.device(dev):
-        if isinstance(dst_ptrs, int):  # an NVSwitch multicast address: one store reaches every rank
-            _lib.check(_lib.load().lq_gemm_s8_multicast(
-                _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e), C.c_void_p(dst_ptrs),
-                int(dst_shape[1]), int(col0), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
-            return
-        ptrs = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
-        _lib.check(_lib.load().lq_gemm_s8_bcast(
+        ws = _lib.gemm_workspace(dev)
+        _lib.check(_lib.load().lq_gemm_s8_sharded(
             _lib.ptr(a), int(a.dtype == torch.int8), _lib.ptr(b), m, n, k, C.byref(e), ptrs,
-            len(dst_ptrs), int(dst_shape[1]), int(col0), _lib.ptr(_lib.status_word(dev)),
-            _lib.stream_ptr(dev)))
+            -1 if multicast else len(plist), int(dst_shape[1]), int(col0), flags, n_flags, counter_ptr,
+            _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
 
 
-def conv2d_nhwc_s8(x, w_krsc, *, pad=0, stride=1, out_dtype=torch.int32, a_scale=None,
-                   b_scale=None, bias=None, act=_lib.ACT_NONE, out_scale=None, out_zp=None,
-                   qmin=0, qmax=0):
-    """NHWC implicit-GEMM convolution on codes: ``x (N, H, W, C)`` int8/uint8
-    with zero point 0, ``w_krsc (K, R, S, C)`` int8.  Returns ``(N, P, Q, K)``."""
+def peer_signal(flag_addrs, counter: torch.Tensor) -> None:
+    """Publish this rank's next step count to its flag word on every rank (stream-ordered after
+    the kernels that stored into the peers' buffers)."""
+    dev = counter.device
+    flags = (C.c_void_p * len(flag_addrs))(*[int(p) for p in flag_addrs])
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().lq_peer_signal(flags, len(flag_addrs), _lib.ptr(counter), _lib.stream_ptr(dev)))
+
+
+def peer_wait(flags: torch.Tensor, epoch: torch.Tensor, timeout_cycles: int = 0) -> None:
+    """Stream-ordered, bounded wait until every producer's flag word in `flags` reached this
+    rank's next step count (`epoch` is bumped); a timeout lands in the device status word."""
+    dev = flags.device
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().lq_peer_wait(_lib.ptr(flags), flags.numel(), _lib.ptr(epoch), int(timeout_cycles),
+                                            _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+
+
+def _pair(v):
+    return (int(v), int(v)) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+
+def conv_out_size(size: int, k: int, stride: int, pad: int, dil: int) -> int:
+    return (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+
+
+def conv2d_nhwc_s8(x, w_krsc, *, pad=0, stride=1, dilation=1, groups=1, out_hw=None, out_dtype=torch.int32,
+                   a_scale=None, a_zp=None, b_rowsum=None, b_scale=None, bias=None, act=_lib.ACT_NONE,
+                   out_scale=None, out_zp=None, qmin=0, qmax=0):
+    """NHWC implicit-GEMM convolution on codes: ``x (N, H, W, C)`` int8/uint8, ``w_krsc (K, R, S,
+    C / groups)`` int8.  ``pad`` is the padding before the first row / column (int or pair);
+    ``out_hw`` overrides the output extent (an asymmetric "same" padding is the leading padding
+    plus a larger output).  Out-of-image taps read code 0, so a non-zero activation zero point
+    (``a_zp`` with ``b_rowsum``) is accepted only for geometries that read no such tap.
+    Returns ``(N, P, Q, K)``."""
     _lib.require_cuda(x, "activation codes")
     _lib.require_cuda(w_krsc, "weight codes")
     if x.dtype not in (torch.int8, torch.uint8) or w_krsc.dtype != torch.int8:
         raise _lib.DtypeMismatch("conv2d_nhwc_s8 takes int8/uint8 activations and int8 weights")
-    if x.dim() != 4 or w_krsc.dim() != 4 or x.shape[3] != w_krsc.shape[3]:
-        raise _lib.ShapeMismatch(f"conv2d_nhwc_s8 shapes {tuple(x.shape)} * {tuple(w_krsc.shape)}")
+    if x.dim() != 4 or w_krsc.dim() != 4 or groups < 1 or x.shape[3] != w_krsc.shape[3] * groups:
+        raise _lib.ShapeMismatch(f"conv2d_nhwc_s8 shapes {tuple(x.shape)} * {tuple(w_krsc.shape)}, groups {groups}")
     x = x.contiguous()
     w_krsc = w_krsc.contiguous()
     n, h, w, c = x.shape
     k, r, s, _ = w_krsc.shape
-    p = (h + 2 * pad - r) // stride + 1
-    q = (w + 2 * pad - s) // stride + 1
+    (ph, pw), (sh, sw), (dh, dw) = _pair(pad), _pair(stride), _pair(dilation)
+    if out_hw is None:
+        p, q = conv_out_size(h, r, sh, ph, dh), conv_out_size(w, s, sw, pw, dw)
+    else:
+        p, q = int(out_hw[0]), int(out_hw[1])
+    if p < 1 or q < 1:
+        raise _lib.ShapeMismatch(f"conv2d_nhwc_s8: empty output ({p}, {q})")
     dev = x.device
     out = torch.empty((n, p, q, k), dtype=out_dtype, device=dev)
     keep: list = []
-    e = _epilogue(dev, out_dtype, act, a_scale, None, None, b_scale, bias, out_scale, out_zp,
-                  qmin, qmax, keep)
+    e = _epilogue(dev, out_dtype, act, a_scale, a_zp, b_rowsum, b_scale, bias, out_scale, out_zp,
+                  qmin, qmax, keep, None, k)
+    g = _lib.ConvGeometry(N=n, H=h, W=w, C=c, K=k, R=r, S=s, P=p, Q=q, stride_h=sh, stride_w=sw, pad_h=ph,
+                          pad_w=pw, dil_h=dh, dil_w=dw, groups=groups)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().lq_conv2d_nhwc_s8(
-            _lib.ptr(x), int(x.dtype == torch.int8), _lib.ptr(w_krsc), n, h, w, c, k, r, s, stride,
-            pad, C.byref(e), _lib.ptr(out), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+        ws = _lib.gemm_workspace(dev)
+        _lib.check(_lib.load().lq_conv2d_nhwc_s8_ex(
+            _lib.ptr(x), int(x.dtype == torch.int8), _lib.ptr(w_krsc), C.byref(g), C.byref(e), _lib.ptr(out),
+            _lib.ptr(ws), ws.numel(), _lib.ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
     return out

@@ -94,6 +94,7 @@ class Linear(torch.nn.Module):
     # -- forward -----------------------------------------------------------------
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _lib.require_cuda(x, "input")
+        _lib.check_device_status_lazily(x.device)
         if backends.quantized.use_int8() and self._int8_ok():
             return self._forward_int8(x)
         return self._forward_float(x)

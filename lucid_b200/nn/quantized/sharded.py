@@ -49,33 +49,73 @@ def gather_columns(local: torch.Tensor, group=None, out: torch.Tensor | None = N
     return out
 
 
+def _symmetric(shape, dtype, device, group):
+    """A zero-filled tensor in symmetric memory and its rendezvous handle (collective)."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    t = symm_mem.empty(shape, dtype=dtype, device=device)
+    t.zero_()
+    h = symm_mem.rendezvous(t, group)
+    return t, h
+
+
+class PeerFlags:
+    """Step counters of one exchanged buffer, replacing a collective as the fence: rank ``r``
+    publishes its step count to word ``r`` of every rank's flag array once its stores into the
+    peers' buffers are complete (`signal`, or fused into the GEMM via `signal_arg`), and a
+    consumer waits -- on its own stream, with a bounded device-side wait -- until all words have
+    reached its own step count (`wait`).  All state lives on the device, so a step that uses
+    these can be captured in a CUDA graph and replayed.  Construction is collective."""
+
+    def __init__(self, device: torch.device, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.flags, self._h = _symmetric((self.world,), torch.int32, device, self.group)
+        # this rank's word on every rank (own included)
+        self.flag_addrs = [int(p) + 4 * self.rank for p in self._h.buffer_ptrs]
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anyone signals
+
+    @property
+    def signal_arg(self):
+        return self.flag_addrs, self.counter
+
+    def signal(self) -> None:
+        QF.peer_signal(self.flag_addrs, self.counter)
+
+    def wait(self, timeout_cycles: int = 0) -> None:
+        QF.peer_wait(self.flags, self.epoch, timeout_cycles)
+
+
 class PeerOutputs:
     """Double-buffered `(rows, cols)` output that every rank of the group can write: the
     GEMM epilogue of each rank stores its column shard straight into all ranks' copies
     (symmetric memory, plain peer stores over NVLink), so the exchange step needs no separate
     all-gather kernel and no re-layout.  Two buffers alternate: a rank may start writing the
-    other buffer while peers still read this one; the barrier after each GEMM orders the rest.
+    other buffer while peers still read this one; `sync` (a `PeerFlags`) orders the rest.
 
     Construction is collective (all ranks, same order)."""
 
-    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device: torch.device, group=None):
-        import torch.distributed._symmetric_memory as symm_mem
-
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device: torch.device, group=None,
+                 buffers: int = 2):
         self.group = group if group is not None else dist.group.WORLD
         self.rows, self.cols, self.dtype = rows, cols, dtype
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
-        self.bufs, self.ptrs, self.mc_ptrs = [], [], []
-        for _ in range(2):
-            t = symm_mem.empty((rows, cols), dtype=dtype, device=device)
-            h = symm_mem.rendezvous(t, self.group)
+        self.bufs, self.ptrs, self.mc_ptrs, self._keep = [], [], [], []
+        for _ in range(buffers):
+            t, h = _symmetric((rows, cols), dtype, device, self.group)
             own = int(h.buffer_ptrs[self.rank])
             # this GPU's buffer first, then the peers'
             self.ptrs.append([own] + [int(p) for r, p in enumerate(h.buffer_ptrs) if r != self.rank])
             self.bufs.append(t)
             self.mc_ptrs.append(int(getattr(h, "multicast_ptr", 0) or 0))
-            self._keep = getattr(self, "_keep", []) + [h]
+            self._keep.append(h)
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.sync = PeerFlags(device, self.group)
         self.turn = 0
 
     @property
@@ -87,13 +127,104 @@ class PeerOutputs:
         """(local tensor, destinations) of the buffer to fill now: the list of every rank's
         address (own first), or -- ``multicast=True`` -- the one multicast address."""
         i = self.turn
-        self.turn ^= 1
+        self.turn = (self.turn + 1) % len(self.bufs)
         return self.bufs[i], (self.mc_ptrs[i] if multicast else self.ptrs[i])
 
     def fence(self) -> None:
-        """All ranks' stores into the current buffer are complete and visible after this
-        (stream-ordered): a 4-byte all-reduce follows each rank's GEMM on its stream."""
+        """Collective form of the fence (a 4-byte all-reduce after each rank's GEMM on its
+        stream); `sync.wait()` after a signalling GEMM is the device-flag form."""
         dist.all_reduce(self._flag, group=self.group)
+
+
+class TokenShardedEncoder:
+    """Per-token int8 encode of a REPLICATED `(rows, cols)` activation, sharded over token rows:
+    rank ``r`` encodes rows ``[r*rows/w, (r+1)*rows/w)`` and stores their codes and scales into
+    every rank's operand buffers (peer stores, or one multicast store for the codes), so each
+    rank encodes ``1/w`` of the tokens instead of all of them.  Bit-identical to the unsharded
+    encode (rows are independent).  Construction is collective."""
+
+    def __init__(self, rows: int, cols: int, device: torch.device, group=None):
+        self.out = PeerOutputs(rows, cols, torch.int8, device, group, buffers=1)
+        self.world, self.rank = self.out.world, self.out.rank
+        if rows % self.world != 0:
+            raise _lib.ShapeMismatch(f"{rows} token rows do not split over {self.world} ranks")
+        self.rows, self.cols = rows, cols
+        self.scale, self._sh = _symmetric((rows,), torch.float32, device, self.out.group)
+        self.scale_ptrs = [int(self._sh.buffer_ptrs[self.rank])] + \
+            [int(p) for r, p in enumerate(self._sh.buffer_ptrs) if r != self.rank]
+
+    def __call__(self, x: torch.Tensor, multicast: bool = False, local: bool = False):
+        """Encode this rank's rows of `x` -- the full replicated tensor, or with ``local=True``
+        just this rank's `(rows / w, cols)` rows -- and exchange; returns (codes, scales) of all
+        rows, valid after the wait that this call enqueues."""
+        import ctypes as C
+
+        per = self.rows // self.world
+        r0 = self.rank * per
+        shard = x.reshape(per, self.cols) if local else x.reshape(self.rows, self.cols)[r0:r0 + per]
+        if not shard.is_contiguous():
+            shard = shard.contiguous()
+        codes, dst = self.out.next(multicast=multicast and self.out.has_multicast)
+        mc = isinstance(dst, int)
+        plist = self.out.ptrs[0] if mc else dst
+        outs = (C.c_void_p * len(plist))(*[int(p) for p in plist])
+        souts = (C.c_void_p * len(self.scale_ptrs))(*self.scale_ptrs)
+        dev = x.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().lq_quantize_per_token_bcast(
+                _lib.ptr(shard), _lib.code_of(x.dtype), per, self.cols, qint8.quant_min, qint8.quant_max,
+                C.c_float(1e-8), outs, souts, len(plist), C.c_void_p(dst) if mc else None, r0,
+                _lib.stream_ptr(dev)))
+        self.out.sync.signal()
+        self.out.sync.wait()
+        return codes, self.scale
+
+
+class HiddenExchange:
+    """Exchange of a column-sharded hidden tensor as per-token int8 CODES: the ranks exchange
+    the per-token abs-max of their shards (a `(world, rows)` table in symmetric memory, plain
+    peer stores -- the max all-reduce of the encode), then each rank encodes its shard with the
+    global scales and stores the codes into every rank's `(rows, cols)` operand buffer.  Scales
+    and codes equal the single-GPU encode of the unsharded tensor bit for bit (max is
+    order-free).  Construction is collective."""
+
+    def __init__(self, rows: int, cols: int, device: torch.device, group=None):
+        self.out = PeerOutputs(rows, cols, torch.int8, device, group, buffers=1)
+        self.world, self.rank, self.rows, self.cols = self.out.world, self.out.rank, rows, cols
+        self.table, self._th = _symmetric((self.world, rows), torch.float32, device, self.out.group)
+        self.table_ptrs = [int(self._th.buffer_ptrs[self.rank])] + \
+            [int(p) for r, p in enumerate(self._th.buffer_ptrs) if r != self.rank]
+        self.table_sync = PeerFlags(device, self.out.group)
+        self.scale = torch.empty(rows, dtype=torch.float32, device=device)
+
+    def __call__(self, h_shard: torch.Tensor, multicast: bool = False):
+        """`h_shard`: this rank's `(rows, cols / world)` columns.  Returns (codes, scales) of the
+        full tensor, valid after the wait that this call enqueues."""
+        import ctypes as C
+
+        rows, n_local = h_shard.shape
+        dev = h_shard.device
+        lib = _lib.load()
+        touts = (C.c_void_p * len(self.table_ptrs))(*self.table_ptrs)
+        with torch.cuda.device(dev):
+            _lib.check(lib.lq_absmax_rows_bcast(_lib.ptr(h_shard), _lib.code_of(h_shard.dtype), rows, n_local,
+                                                h_shard.stride(0), touts, len(self.table_ptrs),
+                                                self.rank * self.rows, _lib.stream_ptr(dev)))
+        self.table_sync.signal()
+        self.table_sync.wait()
+        codes, dst = self.out.next(multicast=multicast and self.out.has_multicast)
+        mc = isinstance(dst, int)
+        plist = [dst] if mc else dst
+        outs = (C.c_void_p * len(plist))(*[int(p) for p in plist])
+        with torch.cuda.device(dev):
+            _lib.check(lib.lq_quantize_rows_bcast(
+                _lib.ptr(h_shard), _lib.code_of(h_shard.dtype), rows, n_local, h_shard.stride(0),
+                _lib.ptr(self.table), self.world, self.rows, qint8.quant_min, qint8.quant_max, C.c_float(1e-8),
+                outs, -1 if mc else len(plist), self.cols, self.rank * n_local, _lib.ptr(self.scale),
+                _lib.stream_ptr(dev)))
+        self.out.sync.signal()
+        self.out.sync.wait()
+        return codes, self.scale
 
 
 def shard_absmax(x_shard: torch.Tensor, group=None) -> torch.Tensor:
@@ -126,7 +257,7 @@ def quantize_shard_bcast(x_shard: torch.Tensor, row_absmax: torch.Tensor, dst_pt
     arr = (C.c_void_p * len(plist))(*[C.c_void_p(int(p)) for p in plist])
     with torch.cuda.device(x2.device):
         _lib.check(_lib.load().lq_quantize_rows_bcast(
-            _lib.ptr(x2), _lib.code_of(x2.dtype), rows, cols, cols, _lib.ptr(row_absmax), qdtype.quant_min,
+            _lib.ptr(x2), _lib.code_of(x2.dtype), rows, cols, cols, _lib.ptr(row_absmax), 1, rows, qdtype.quant_min,
             qdtype.quant_max, C.c_float(eps), arr, -1 if multicast else len(plist), int(ldo), int(col0),
             _lib.ptr(out_scale), _lib.stream_ptr(x2.device)))
     return out_scale
@@ -172,8 +303,8 @@ class ColumnShardedLinear(torch.nn.Module):
             buf, ptrs = peer.next()
             QF.gemm_s8_bcast(a, self.weight_int8, ptrs, (peer.rows, peer.cols), self.rank * n_local,
                              out_dtype=out_dtype, a_scale=a_scale, b_scale=self.weight_scale,
-                             bias=self.bias, act=act)
-            peer.fence()
+                             bias=self.bias, act=act, signal=peer.sync.signal_arg)
+            peer.sync.wait()
             return buf[: a.shape[0]]
         local = QF.gemm_s8(a, self.weight_int8, out_dtype=out_dtype, a_scale=a_scale,
                            b_scale=self.weight_scale, bias=self.bias, act=act)

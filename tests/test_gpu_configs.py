@@ -20,6 +20,11 @@ def _status():
     _lib.check_device_status(torch.device("cuda", torch.cuda.current_device()))
 
 
+def _exact_rows(xq, w, slab=4096):
+    """O.int_gemm_exact with the weight taken in slabs of rows (bounds the float64 staging)."""
+    return np.concatenate([O.int_gemm_exact(xq, w[n0:n0 + slab]) for n0 in range(0, w.shape[0], slab)], axis=1)
+
+
 def test_config3_gated_mlp_bf16_full_size():
     """x (8 x 512 tokens, d = 4096) -> int8 gate/up 4096 -> 11008 (SiLU-gated) -> int8 down;
     bf16 in/out, per-channel weights ~ N(0, 0.02^2), per-token activation scales."""
@@ -94,7 +99,7 @@ def test_config4_conv_stack_full_batch():
         a_dev, a_scale, a_ref = out, os_, ref
 
 
-@pytest.mark.parametrize("name,n,k", [("qkv", 10240, 8192), ("down", 8192, 28672)])
+@pytest.mark.parametrize("name,n,k", [("qkv", 10240, 8192), ("o", 8192, 8192), ("down", 8192, 28672)])
 def test_config5_llama70b_linears(name, n, k):
     """M = 4096 tokens, bf16 activations quantized per token, int8 per-channel weights."""
     m = 4096
@@ -126,4 +131,43 @@ def test_config5_llama70b_linears(name, n, k):
     assert torch.equal(QF.gemm_s8(a1, w, out_dtype=torch.int32) + QF.gemm_s8(a2, w, out_dtype=torch.int32), s12)
     perm = torch.randperm(n, device="cuda", generator=g)
     assert torch.equal(QF.gemm_s8(a1, w[perm].contiguous(), out_dtype=torch.int32), QF.gemm_s8(a1, w, out_dtype=torch.int32)[:, perm])
+    _status()
+
+
+def test_config5_gate_up_full_size():
+    """The gate / up projections of config 5 as the bench runs them: one GEMM over the
+    [gate; up] weight interleaved in blocks of 128 rows (N = 2 x 28672), SiLU-gate epilogue, bf16
+    out.  Sampled rows against the oracle (the SiLU goes through a library exp: 1e-2 relative on
+    bf16), and the epilogue-free accumulators of the same operands bit for bit."""
+    m, d, ff = 4096, 8192, 28672
+    g = torch.Generator(device="cuda").manual_seed(55)
+    x = torch.randn(m, d, device="cuda", generator=g).to(torch.bfloat16)
+    w_gu = torch.empty((2 * ff, d), dtype=torch.int8, device="cuda")
+    s_gu = torch.empty(2 * ff, dtype=torch.float32, device="cuda")
+    slab = 2048
+    for r0 in range(0, ff, slab):  # encode gate and up in slabs, interleaved as the kernel pairs them
+        parts = []
+        for _ in range(2):
+            wf = torch.randn(slab, d, device="cuda", generator=g) * 0.02
+            obs = Q.PerChannelMinMaxObserver(ch_axis=0)
+            obs(wf)
+            s, z = obs.calculate_qparams()
+            parts.append((Q.quantize(wf, s, z, Q.qint8, ch_axis=0), s))
+        w_gu[2 * r0:2 * (r0 + slab)] = nnq.dynamic.interleave_gate_up(parts[0][0], parts[1][0])
+        s_gu[2 * r0:2 * (r0 + slab)] = nnq.dynamic.interleave_gate_up(parts[0][1], parts[1][1])
+    a, sa = Q.quantize_per_token(x, Q.qint8)
+    h = QF.gemm_s8(a, w_gu, out_dtype=torch.bfloat16, a_scale=sa, b_scale=s_gu, act=_lib.ACT_SILU_GATE)
+    _status()
+    assert h.shape == (m, ff)
+    rows = np.random.default_rng(2).choice(m, 32, replace=False)
+    xq, xs = O.per_token_quantize(host(x)[rows])
+    assert np.array_equal(host(a)[rows], xq) and np.array_equal(host(sa)[rows], xs.astype(np.float32))
+    gu = host(w_gu).reshape(ff // 128, 2, 128, d)
+    gs = host(s_gu).reshape(ff // 128, 2, 128)
+    yg = O.epilogue_f32(_exact_rows(xq, gu[:, 0].reshape(ff, d)), xs, 0, None, gs[:, 0].reshape(ff), None)
+    yu = O.epilogue_f32(_exact_rows(xq, gu[:, 1].reshape(ff, d)), xs, 0, None, gs[:, 1].reshape(ff), None)
+    assert rel_max(host(h)[rows], O.silu_f32(yg) * yu) < 1e-2
+    rows_t = torch.from_numpy(np.sort(rows)).cuda()
+    acc = QF.gemm_s8(a[rows_t].contiguous(), w_gu, out_dtype=torch.int32)
+    assert np.array_equal(host(acc), _exact_rows(host(a)[np.sort(rows)], host(w_gu)))
     _status()

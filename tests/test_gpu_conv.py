@@ -30,11 +30,19 @@ CASES = [  # n, h, w, c, k, r, pad
 ]
 
 
-@pytest.fixture(params=["auto", "pair", "single256"])
+@pytest.fixture(params=["auto", "pair", "single256", "auto-sk", "pair-sk"])
 def tile_shape(request, monkeypatch):
-    if request.param != "auto":
-        monkeypatch.setenv("LQ_GEMM_SHAPE", request.param)
-    return request.param
+    """Tile policy of the contraction; `-sk` forces the stream-K schedule (tiles cut across CTAs)."""
+    spec = request.param
+    if spec.endswith("-sk"):
+        spec = spec[:-3]
+        monkeypatch.setenv("LQ_GEMM_STREAMK", "1")
+    if spec != "auto":
+        monkeypatch.setenv("LQ_GEMM_SHAPE", spec)
+    _lib.load().lq_reload_env()
+    yield spec
+    monkeypatch.undo()
+    _lib.load().lq_reload_env()
 
 
 @pytest.mark.parametrize("n,h,w,c,k,r,pad", CASES)
@@ -108,3 +116,162 @@ def test_conv_module_matches_reference_float_form():
                                         host(qm2.scale), host(qm2.zero_point), relu=False, pad=1)
     d2 = np.abs(host(y2) - y2_ref)
     assert (d2 > 0).mean() < 2e-3 and d2.max() <= float(qm2.scale) * 1.001
+
+
+GEOMETRIES = [  # n, h, w, c, k, (r, s), stride, pad_lo, pad_hi, dilation, groups
+    (2, 56, 56, 64, 128, (3, 3), (2, 2), (1, 1), (1, 1), (1, 1), 1),    # ResNet down-sampling 3x3
+    (2, 56, 56, 64, 128, (1, 1), (2, 2), (0, 0), (0, 0), (1, 1), 1),    # ... and its 1x1 projection
+    (1, 224, 224, 16, 64, (7, 7), (2, 2), (3, 3), (3, 3), (1, 1), 1),   # stem-shaped 7x7 stride 2
+    (3, 15, 17, 32, 48, (3, 3), (2, 2), (1, 1), (1, 1), (1, 1), 1),     # odd H x W
+    (2, 14, 14, 64, 96, (3, 3), (1, 1), (1, 1), (1, 1), (1, 1), 2),     # groups 2
+    (2, 13, 13, 128, 128, (3, 3), (2, 2), (1, 1), (1, 1), (1, 1), 4),   # groups 4, stride 2, odd
+    (1, 20, 20, 32, 32, (3, 3), (1, 1), (2, 2), (2, 2), (2, 2), 1),     # dilation 2
+    (2, 12, 12, 16, 32, (4, 4), (1, 1), (1, 1), (2, 2), (1, 1), 1),     # "same" with an even kernel: asymmetric
+    (1, 9, 40, 48, 16, (3, 5), (3, 2), (0, 2), (1, 2), (1, 1), 1),      # mixed strides / kernel / padding
+    (1, 130, 300, 16, 16, (3, 3), (2, 2), (1, 1), (1, 1), (1, 1), 1),   # rows wider than one tile
+]
+
+
+@pytest.mark.parametrize("n,h,w,c,k,rs,stride,plo,phi,dil,groups", GEOMETRIES)
+def test_conv_general_geometry_exact(n, h, w, c, k, rs, stride, plo, phi, dil, groups, tile_shape):
+    """Stride, dilation, groups and asymmetric padding (what lucid/nn/quantized/conv.py:119-184
+    accepts): accumulators bit-exact against the exact integer convolution."""
+    rng = np.random.default_rng(h * 31 + w + c + k)
+    x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8)
+    wt = rng.integers(-128, 128, (k, rs[0], rs[1], c // groups)).astype(np.int8)
+    ref = O.int_conv2d_nhwc_general(x, wt, stride, plo, phi, dil, groups)
+    acc = QF.conv2d_nhwc_s8(dev(x), dev(wt), pad=plo, stride=stride, dilation=dil, groups=groups,
+                            out_hw=ref.shape[1:3], out_dtype=torch.int32)
+    _sync_status()
+    assert acc.shape == ref.shape
+    assert np.array_equal(host(acc), ref)
+
+
+def test_conv_zero_point_inside_kernel():
+    """A non-zero activation zero point with a geometry that reads no out-of-image tap takes the
+    kernel's correction term (one launch, requantised codes out)."""
+    rng = np.random.default_rng(21)
+    n, h, w, c, k = 2, 12, 12, 32, 48
+    x = rng.integers(0, 256, (n, h, w, c)).astype(np.uint8)
+    wt = rng.integers(-128, 128, (k, 3, 3, c)).astype(np.int8)
+    ws = (rng.random(k) * 1e-3 + 1e-4).astype(np.float32)
+    b = (rng.standard_normal(k) * 0.1).astype(np.float32)
+    zp, sa = np.float32(117), np.float32(0.02)
+    acc = O.int_conv2d_nhwc_general(x, wt, (2, 2)).reshape(-1, k)
+    rowsum = wt.reshape(k, -1).astype(np.int64).sum(axis=1).astype(np.int32)
+    y = O.epilogue_f32(acc, sa, zp, rowsum, ws, b, relu=True)
+    os_, oz = O.calculate_qparams(y.min(), y.max(), False, O.QUINT8)
+    ref = O.requantize_f32(y, os_, oz, 0, 255).astype(np.uint8).reshape(n, 5, 5, k)
+    out = QF.conv2d_nhwc_s8(dev(x), dev(wt), stride=2, out_dtype=torch.uint8, a_scale=dev(sa), a_zp=dev(zp),
+                            b_rowsum=dev(rowsum), b_scale=dev(ws), bias=dev(b), act=_lib.ACT_RELU,
+                            out_scale=dev(os_), out_zp=dev(oz), qmin=0, qmax=255)
+    _sync_status()
+    assert np.array_equal(host(out), ref)
+    with pytest.raises(NotImplementedError):  # with padding the zero point must be 0
+        QF.conv2d_nhwc_s8(dev(x), dev(wt), pad=1, out_dtype=torch.int32, a_zp=dev(zp), b_rowsum=dev(rowsum))
+
+
+class _CountConv:
+    """Counts calls of the library's float convolution while a block runs."""
+
+    def __enter__(self):
+        import torch.nn.functional as F
+
+        self.n, self._orig = 0, F.conv2d
+
+        def counted(*a, **k):
+            self.n += 1
+            return self._orig(*a, **k)
+
+        F.conv2d = counted
+        return self
+
+    def __exit__(self, *exc):
+        import torch.nn.functional as F
+
+        F.conv2d = self._orig
+
+
+def _resnet18_shaped_stack(gen):
+    """The conv geometries of a ResNet-18 (stem 7x7/2, 3x3/1, 3x3/2 + 1x1/2 projections), 16-channel
+    aligned and reduced in width, with unfused in-place ReLUs between some layers."""
+    import torch.nn as nn
+
+    def conv(ci, co, k, s, p):
+        m = nn.Conv2d(ci, co, k, s, p)
+        with torch.no_grad():
+            m.weight.copy_(torch.randn(m.weight.shape, generator=gen) * (2.0 / (ci * k * k)) ** 0.5)
+            m.bias.copy_(torch.randn(co, generator=gen) * 0.05)
+        return m
+
+    return nn.Sequential(
+        conv(16, 32, 7, 2, 3), nn.ReLU(inplace=True),
+        conv(32, 32, 3, 1, 1), nn.ReLU(inplace=True), conv(32, 32, 3, 1, 1), nn.ReLU(inplace=True),
+        conv(32, 64, 3, 2, 1), nn.ReLU(inplace=True), conv(64, 64, 3, 1, 1),
+        conv(64, 128, 1, 2, 0), nn.ReLU(inplace=True),
+        conv(128, 128, 3, 2, 1), nn.ReLU(inplace=True),
+    )
+
+
+def test_resnet18_shaped_stack_runs_on_the_integer_path():
+    """Reference gate lucid/test/unit/quantization/test_static_ptq.py:180-199 (a ResNet-18 through
+    prepare / calibrate / convert): every convolution -- strided ones and unfused in-place ReLUs
+    included -- runs the integer kernel (no call of the library's float convolution), and the
+    result equals the reference's float route (engine "reference") up to +-1 code at a tiny rate."""
+    import lucid_b200
+
+    gen = torch.Generator().manual_seed(0)
+    model = _resnet18_shaped_stack(gen).cuda().eval()
+    x = torch.randn(2, 16, 64, 64, generator=gen).cuda()
+    prepared = Q.prepare(model, Q.QConfig(activation=Q.MinMaxObserver, weight=Q.get_default_qconfig().weight))
+    with torch.no_grad():
+        prepared(x)
+    qmodel = Q.convert(prepared)
+    convs = [m for m in qmodel.modules() if isinstance(m, nnq.Conv2d)]
+    assert len(convs) == 7 and all(c._int8_ok() for c in convs)
+    with _CountConv() as counter, torch.no_grad():
+        y = qmodel(x)
+    _sync_status()
+    assert counter.n == 0
+    lucid_b200.backends.quantized.engine = "reference"
+    try:
+        with torch.no_grad():
+            y_ref = qmodel(x)
+    finally:
+        lucid_b200.backends.quantized.engine = "auto"
+    assert y.shape == y_ref.shape
+    step = float(convs[-1].scale)
+    diff = (y - y_ref).abs()
+    assert float((diff > 0).float().mean()) < 5e-3 and float(diff.max()) <= 2.001 * step
+
+
+def test_inplace_relu_invalidates_carried_codes():
+    """quantized Conv2d -> nn.ReLU(inplace=True) -> quantized Conv2d: the in-place op keeps the
+    Python attribute that carries the first layer's codes but changes the values; the second layer
+    must encode what the tensor holds now, as the reference (which only sees floats) does."""
+    import lucid_b200
+    from lucid_b200.nn.quantized._utils import codes_of
+
+    gen = torch.Generator().manual_seed(1)
+    c1 = torch.nn.Conv2d(16, 32, 3, padding=1)
+    c2 = torch.nn.Conv2d(32, 16, 3, padding=1)
+    model = torch.nn.Sequential(c1, torch.nn.ReLU(inplace=True), c2).cuda().eval()
+    x = torch.randn(2, 16, 12, 12, generator=gen).cuda()
+    prepared = Q.prepare(model, Q.QConfig(activation=Q.MinMaxObserver, weight=Q.get_default_qconfig().weight))
+    with torch.no_grad():
+        prepared(x)
+    qmodel = Q.convert(prepared)
+    with torch.no_grad():
+        mid = qmodel[0](x)
+        assert codes_of(mid) is not None and float(mid.min()) < 0
+        mid = qmodel[1](mid)
+        assert codes_of(mid) is None  # stale after relu_()
+        y = qmodel(x)
+        lucid_b200.backends.quantized.engine = "reference"
+        try:
+            y_ref = qmodel(x)
+        finally:
+            lucid_b200.backends.quantized.engine = "auto"
+    _sync_status()
+    diff = (y - y_ref).abs()
+    assert float((diff > 0).float().mean()) < 5e-3 and float(diff.max()) <= 1.001 * float(qmodel[2].scale)

@@ -37,16 +37,26 @@ SHAPES = [(128, 128, 128), (128, 256, 128), (256, 512, 256), (1, 16, 16), (130, 
 
 
 @pytest.fixture(params=["auto", "pair", "single256", "single128", "pair-epi8", "pair-epi16",
-                        "single256-epi8", "single256-epi16"])
+                        "single256-epi8", "single256-epi16", "auto-sk", "pair-sk", "single256-sk",
+                        "single128-sk", "pair-epi16-sk"])
 def tile_shape(request, monkeypatch):
-    """Forces the GEMM's tile policy (CTA pair 256x256 / single 128x256 / single 128x128) and
-    the epilogue build (8 or 16 epilogue warps)."""
-    shape, _, epi = request.param.partition("-epi")
+    """Forces the GEMM's tile policy (CTA pair 256x256 / single 128x256 / single 128x128), the
+    epilogue build (8 or 16 epilogue warps) and the schedule (`-sk`: stream-K, i.e. tiles cut
+    across CTAs and completed from partial sums, even for these small shapes)."""
+    spec = request.param
+    sk = spec.endswith("-sk")
+    if sk:
+        spec = spec[:-3]
+        monkeypatch.setenv("LQ_GEMM_STREAMK", "1")
+    shape, _, epi = spec.partition("-epi")
     if shape != "auto":
         monkeypatch.setenv("LQ_GEMM_SHAPE", shape)
     if epi:
         monkeypatch.setenv("LQ_GEMM_EPI_WARPS", epi)
-    return shape
+    _lib.load().lq_reload_env()
+    yield shape
+    monkeypatch.undo()
+    _lib.load().lq_reload_env()
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
@@ -82,6 +92,38 @@ def test_many_tiles_persistent_schedule(m, n, k, tile_shape):
     acc = QF.gemm_s8(dev(a), dev(b), out_dtype=torch.int32)
     _sync_status()
     assert np.array_equal(host(acc), O.int_gemm_exact(a, b))
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 1280, 8192), (4096, 1024, 8192), (4096, 1024, 28672), (2048, 4096, 4096),
+                                   (4096, 2560, 8192)])
+def test_stream_k_shard_shapes_bit_equal(m, n, k, monkeypatch):
+    """The shapes whose tile count does not fill whole waves of SMs (the per-rank shards of the
+    Llama-2-70B projections at 4 and 8 ranks, config 2): the stream-K schedule the policy picks
+    for them gives the same bits as the tile-by-tile schedule, for raw accumulators and for the
+    bf16 epilogue, and the accumulators equal torch's integer GEMM."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=g)
+    b = torch.randint(-128, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+    sa = torch.rand(m, device="cuda", generator=g) * 1e-2
+    sb = torch.rand(n, device="cuda", generator=g) * 1e-2
+    acc = QF.gemm_s8(a, b, out_dtype=torch.int32)
+    y = QF.gemm_s8(a, b, out_dtype=torch.bfloat16, a_scale=sa, b_scale=sb)
+    monkeypatch.setenv("LQ_GEMM_STREAMK", "0")
+    _lib.load().lq_reload_env()
+    try:
+        acc_dp = QF.gemm_s8(a, b, out_dtype=torch.int32)
+        y_dp = QF.gemm_s8(a, b, out_dtype=torch.bfloat16, a_scale=sa, b_scale=sb)
+    finally:
+        monkeypatch.undo()
+        _lib.load().lq_reload_env()
+    _sync_status()
+    assert torch.equal(acc, acc_dp) and torch.equal(y, y_dp)
+    rows = torch.arange(0, m, 37, device="cuda")
+    ref = (a[rows].double() @ b.double().T).to(torch.int32)
+    assert torch.equal(acc[rows], ref)
+    # the scratch is left clean: a second launch reuses it
+    assert torch.equal(QF.gemm_s8(a, b, out_dtype=torch.int32), acc)
+    _sync_status()
 
 
 def _c2_like(m, k, n, seed=1):

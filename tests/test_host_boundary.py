@@ -51,7 +51,32 @@ def test_host_side_argument_errors_need_no_gpu():
     assert lib.lq_gemm_s8(one, 1, one, 8, 8, 32, ctypes.byref(e), one, 8, None, None) == 3  # scales missing
     assert lib.lq_minmax(one, 0, 0, 4, 0, one, one, one, 1 << 20, None) == 1  # empty has no range
     assert lib.lq_minmax(one, 0, 4, 4, 0, one, one, one, 8, None) == 6  # workspace too small
-    assert lib.lq_conv2d_nhwc_s8(one, 1, one, 1, 8, 8, 16, 16, 3, 3, 2, 1, ctypes.byref(e), one, None, None) == 5
+    assert lib.lq_conv2d_nhwc_s8(one, 1, one, 1, 8, 8, 16, 16, 3, 3, 9, 1, ctypes.byref(e), one, None, None) == 5  # stride > 8
+    assert lib.lq_conv2d_nhwc_s8(one, 1, one, 1, 8, 8, 16, 16, 3, 3, 0, 1, ctypes.byref(e), one, None, None) == 1
+    geo = _lib.ConvGeometry(N=1, H=8, W=8, C=32, K=16, R=3, S=3, P=8, Q=8, stride_h=1, stride_w=1, pad_h=1, pad_w=1,
+                            dil_h=1, dil_w=1, groups=3)
+    conv_ex = lambda: lib.lq_conv2d_nhwc_s8_ex(one, 1, one, ctypes.byref(geo), ctypes.byref(e), one, None, 0, None, None)
+    assert conv_ex() == 1  # groups must divide C and K
+    geo.groups, geo.K = 4, 16
+    assert conv_ex() == 4  # 8 channels per group: not a multiple of 16
+    geo.groups, geo.P = 1, 40
+    assert conv_ex() == 1  # output larger than the padded input allows
+    # workspace-carrying and sharded contraction, exchange flags
+    e.out_dtype = _lib.S32
+    assert lib.lq_gemm_s8_ws(one, 1, one, 8, 8, 32, ctypes.byref(e), one, 8, one, 64, None, None) == 6
+    assert lib.lq_gemm_workspace_bytes() >= 148 * 128 * 256 * 4
+    ptrs = (ctypes.c_void_p * 2)(16, 32)
+    assert lib.lq_gemm_s8_sharded(one, 1, one, 8, 8, 32, ctypes.byref(e), ptrs, 2, 8, 0, ptrs, 2, one, None, 0,
+                                  None, None) == 3  # signalling needs the workspace
+    assert lib.lq_gemm_s8_sharded(one, 1, one, 8, 8, 32, ctypes.byref(e), ptrs, 9, 8, 0, None, 0, None, None, 0,
+                                  None, None) == 1  # at most 8 destinations
+    assert lib.lq_peer_wait(one, 0, one, 0, None, None) == 1
+    assert lib.lq_peer_wait(None, 2, one, 0, None, None) == 3
+    assert lib.lq_peer_signal(ptrs, 9, one, None) == 1
+    assert lib.lq_absmax_rows_bcast(one, 7, 4, 16, 16, ptrs, 2, 0, None) == 2
+    assert lib.lq_quantize_per_token_bcast(one, 1, 4, 24, -128, 127, 1e-8, ptrs, ptrs, 2, None, 0, None) == 4  # cols % 16
+    assert lib.lq_quantize_rows_bcast(one, 1, 4, 16, 16, one, 0, 4, -128, 127, 1e-8, ptrs, 2, 16, 0, None, None) == 1  # parts
+    e.out_dtype = _lib.F32
     hist = (one, 0, 64, 0.0, 1.0, 16, None, 0.0, 0.0, one, None, None, one, 1 << 20, None)
     assert lib.lq_histc(*hist[:5], lib.lq_histc_max_bins() + 1, *hist[6:]) == 5
     assert lib.lq_histc(*hist[:3], 1.0, 1.0, *hist[5:]) == 1  # empty range: the caller derives it
