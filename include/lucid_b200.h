@@ -427,6 +427,16 @@ int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, const uint8_t
                void* out_codes, float* out_f32, const float* out_scale, const float* out_zp,
                int out_signed, void* stream);
 
+/* ---- recurrent cell -------------------------------------------------------------------- */
+
+/* Pointwise part of one LSTM time step on the pre-activations gates (batch, 4 * hidden; row
+ * stride ldg; gate order i, f, g, o):  c_out = sigmoid(f) * c_prev + sigmoid(i) * tanh(g),
+ * h_out = sigmoid(o) * tanh(c_out); h_out has row stride ldh; c_out may alias c_prev.  Float32.
+ * The weight-only quantized LSTM (lucid/nn/quantized/dynamic/rnn.py:67-87) runs the float cell
+ * on dequantized weights; this replaces the element-wise passes of that cell with one kernel. */
+int lq_lstm_cell_f32(const float* gates, size_t ldg, const float* c_prev, float* h_out, size_t ldh,
+                     float* c_out, size_t batch, size_t hidden, void* stream);
+
 /* ---- quantized embedding tables -------------------------------------------------------- */
 
 /* Gather + dequantize of the rows of a per-row int8 table.  Replaces the forward of

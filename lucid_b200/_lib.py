@@ -145,6 +145,8 @@ _SIGNATURES = {
     "lq_gemm_s8_multicast": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                        C.POINTER(Epilogue), C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                        C.c_void_p]),
+    "lq_lstm_cell_f32": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                   C.c_size_t, C.c_size_t, C.c_void_p]),
     "lq_rowsum_s8": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
     "lq_conv2d_nhwc_s8": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p] + [C.c_size_t] * 9 +
                           [C.POINTER(Epilogue), C.c_void_p, C.c_void_p, C.c_void_p]),

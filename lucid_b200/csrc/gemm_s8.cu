@@ -39,6 +39,8 @@ constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128
 constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
 // Epilogue warps per CTA (EW): 8 when the mainloop of a tile outlasts its epilogue (large K:
 // more ring stages, fewer polling warps), 16 when the epilogue is the long pole (small K).
+// The register file is split over the SM's four schedulers (16 K registers each): 10 warps leave
+// at most 3 on one scheduler (168 registers per thread), 18 warps 5 (96 registers).
 constexpr int threads_for(int ew) { return 64 + 32 * ew; }  // producer warp, MMA warp, epilogue warps
 constexpr int kTmemCols = 512;
 constexpr long long kWaitBudgetCycles = 1ll << 31;  // ~1 s: default budget of every device-side wait
@@ -760,7 +762,7 @@ __device__ __forceinline__ bool sched_next(Sched& s, int& tile, int& kb0, int& k
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int BN, bool PAIR, int EW>
-__global__ void __maxnreg__(EW == 16 ? 112 : 200)
+__global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const Geometry g, const Epi ep, const uint32_t idesc) {
   using C = Cfg<BN, PAIR, EW>;

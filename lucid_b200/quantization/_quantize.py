@@ -83,6 +83,10 @@ def _quant_mapping() -> dict:
 
     m[nnqat.Linear] = nnq.Linear.from_float
     m[nnqat.Conv2d] = nnq.Conv2d.from_float
+    from ..nn.intrinsic import qat as nniqat
+
+    m[nniqat.ConvBn2d] = lambda mod: mod.to_quantized()
+    m[nniqat.ConvBnReLU2d] = lambda mod: mod.to_quantized()
     return m
 
 
@@ -165,9 +169,14 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace:
     mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv2d: nnqat.Conv2d.from_float}
     n_matched = 0
 
+    from ..nn.intrinsic import qat as nniqat
+
     def swap(module):
         nonlocal n_matched
         for name, child in list(module.named_children()):
+            if isinstance(child, nniqat.ConvBn2d):  # fused by fuse_modules_qat: already a QAT module
+                n_matched += 1
+                continue
             build = mapping.get(type(child))
             if build is not None:
                 child.qconfig = qcfg
@@ -194,6 +203,7 @@ def _dynamic_mapping() -> dict:
     import lucid_b200.nn.quantized as nnq
 
     return {torch.nn.Linear: nnq.dynamic.Linear.from_float,
+            torch.nn.LSTM: nnq.dynamic.LSTM.from_float,
             torch.nn.Embedding: lambda mod, dtype: nnq.Embedding.from_float(mod),
             torch.nn.EmbeddingBag: lambda mod, dtype: nnq.EmbeddingBag.from_float(mod)}
 

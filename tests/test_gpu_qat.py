@@ -79,3 +79,85 @@ def test_prepare_qat_conv_and_no_match():
     assert y.shape == (2, 16, 8, 8)
     with pytest.warns(UserWarning):
         Q.prepare_qat(torch.nn.Sequential(torch.nn.ReLU()))
+
+
+class _ConvBnNet(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.quant = Q.QuantStub()
+        self.conv1, self.bn1, self.relu1 = torch.nn.Conv2d(16, 32, 3, padding=1, bias=False), torch.nn.BatchNorm2d(32), torch.nn.ReLU()
+        self.conv2, self.bn2 = torch.nn.Conv2d(32, 32, 3, stride=2, padding=1), torch.nn.BatchNorm2d(32)
+        self.dequant = Q.DeQuantStub()
+
+    def forward(self, x):
+        x = self.relu1(self.bn1(self.conv1(self.quant(x))))
+        return self.dequant(self.bn2(self.conv2(x)))
+
+
+def _bn_net():
+    torch.manual_seed(3)
+    net = _ConvBnNet().cuda()
+    with torch.no_grad():
+        for bn in (net.bn1, net.bn2):
+            bn.running_mean.normal_(0, 0.2)
+            bn.running_var.uniform_(0.5, 1.5)
+            bn.weight.uniform_(0.5, 1.5)
+            bn.bias.normal_(0, 0.2)
+    return net
+
+
+def test_static_ptq_with_batchnorm_reaches_the_integer_conv():
+    """fuse_modules -> prepare -> calibrate -> convert on a Conv/BN/ReLU model: BatchNorm is folded
+    (exact at eval time, the reference's gate test_static_ptq.py:90-99) and the converted model
+    runs integer convolutions only (the strided one included)."""
+    net = _bn_net().eval()
+    x = torch.randn(4, 16, 20, 20, device="cuda")
+    y_float = net(x)
+    fused = Q.fuse_modules(net, [["conv1", "bn1", "relu1"], ["conv2", "bn2"]])
+    assert torch.allclose(fused(x), y_float, atol=1e-4)
+    prepared = Q.prepare(fused, Q.QConfig(activation=Q.MinMaxObserver, weight=Q.get_default_qconfig().weight))
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    assert type(qnet.conv1) is nnq.ConvReLU2d and type(qnet.conv2) is nnq.Conv2d
+    assert qnet.conv1._int8_ok() and qnet.conv2._int8_ok() and qnet.conv2.stride == (2, 2)
+    y_q = qnet(x)
+    assert float((y_q - y_float).abs().mean() / y_float.abs().mean()) < 0.05
+
+
+def test_qat_conv_bn_fusion_trains_and_converts():
+    """fuse_modules_qat -> prepare_qat -> a few steps -> convert
+    (lucid/nn/intrinsic/qat/modules.py:30-90, 796-833): BatchNorm stays trainable inside the fused
+    module, the weight grid is that of the FOLDED weight, and the converted integer layers
+    reproduce what QAT simulated."""
+    from lucid_b200.nn.intrinsic import qat as nniqat
+
+    net = _bn_net().train()
+    qcfg = Q.get_default_qat_qconfig()
+    fused = Q.fuse_modules_qat(net, [["conv1", "bn1", "relu1"], ["conv2", "bn2"]], qcfg)
+    assert type(fused.conv1) is nniqat.ConvBnReLU2d and type(fused.conv2) is nniqat.ConvBn2d
+    qat = Q.prepare_qat(fused, qcfg)
+    assert type(qat.conv1) is nniqat.ConvBnReLU2d and type(qat.conv1.conv) is torch.nn.Conv2d
+    x = torch.randn(4, 16, 20, 20, device="cuda")
+    target = torch.randn(4, 32, 10, 10, device="cuda")
+    opt = torch.optim.SGD(qat.parameters(), lr=1e-3)
+    mean0 = qat.conv1.bn.running_mean.clone()
+    for _ in range(3):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(qat(x), target)
+        loss.backward()
+        assert qat.conv1.conv.weight.grad is not None and qat.conv1.bn.weight.grad is not None
+        opt.step()
+    assert not torch.equal(qat.conv1.bn.running_mean, mean0)  # the statistics kept learning
+    qat.eval()
+    with torch.no_grad():
+        y_qat = qat(x)
+    qnet = Q.convert(qat)
+    assert type(qnet.conv1) is nnq.ConvReLU2d and type(qnet.conv2) is nnq.Conv2d
+    w_fold, b_fold = qat.conv1._fold()
+    assert torch.equal(qnet.conv1.bias, b_fold.detach())
+    assert torch.equal(Q.dequantize(qnet.conv1.weight_int8, qnet.conv1.weight_scale, qnet.conv1.weight_zero_point,
+                                    ch_axis=0), qat.conv1.weight_fake_quant(w_fold.detach()))
+    with torch.no_grad():
+        y_q = qnet(x)
+    assert float((y_q - y_qat).abs().mean() / y_qat.abs().mean()) < 0.05

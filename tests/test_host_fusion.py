@@ -1,0 +1,75 @@
+"""Host logic of ``fuse_modules`` / ``fuse_modules_qat`` (CPU; the float model is plain torch):
+the reference's fusion gate lucid/test/unit/quantization/test_static_ptq.py:86-99 (folding
+BatchNorm into the convolution is exact at eval time, atol 1e-4) and its pattern rules
+(lucid/quantization/fuse_modules.py:62-90)."""
+
+import pytest
+import torch
+
+import lucid_b200.quantization as Q
+from lucid_b200.nn.intrinsic import qat as nniqat
+
+
+class _ConvNet(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.conv = torch.nn.Conv2d(3, 8, 3, padding=1)
+        self.bn = torch.nn.BatchNorm2d(8)
+        self.relu = torch.nn.ReLU()
+        self.fc = torch.nn.Linear(8, 4)
+        self.act = torch.nn.ReLU()
+
+    def forward(self, x):
+        y = self.relu(self.bn(self.conv(x)))
+        return self.act(self.fc(y.mean(dim=(2, 3))))
+
+
+def _net():
+    torch.manual_seed(1)
+    net = _ConvNet().eval()
+    with torch.no_grad():
+        net.bn.running_mean.normal_()
+        net.bn.running_var.uniform_(0.5, 2.0)
+        net.bn.weight.normal_()
+        net.bn.bias.normal_()
+    return net
+
+
+def test_conv_bn_fold_matches():
+    net = _net()
+    x = torch.randn(2, 3, 8, 8)
+    y_ref = net(x)
+    fused = Q.fuse_modules(net, [["conv", "bn"]])
+    assert torch.allclose(fused(x), y_ref, atol=1e-4)
+    assert isinstance(fused.bn, torch.nn.Identity) and isinstance(net.bn, torch.nn.BatchNorm2d)  # a copy
+    fused3 = Q.fuse_modules(net, [["conv", "bn", "relu"], ["fc", "act"]])
+    assert type(fused3.conv).__name__ == "ConvReLU2d" and type(fused3.fc).__name__ == "LinearReLU"
+    assert isinstance(fused3.relu, torch.nn.Identity) and isinstance(fused3.act, torch.nn.Identity)
+    assert torch.allclose(fused3(x), y_ref, atol=1e-4)
+    same = Q.fuse_modules(net, [["conv", "relu"]], inplace=True)
+    assert same is net
+
+
+def test_unsupported_patterns_raise():
+    net = _net()
+    with pytest.raises(ValueError):
+        Q.fuse_modules(net, [["bn", "relu"]])
+    with pytest.raises(ValueError):
+        Q.fuse_modules(net, [["fc", "act", "relu"]])
+    with pytest.raises(ValueError):
+        Q.fuse_modules_qat(net, [["bn", "relu"]], Q.get_default_qat_qconfig())
+
+
+def test_qat_fusion_keeps_batchnorm_live():
+    net = _net()
+    qcfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)  # structure only: no kernels on CPU
+    fused = Q.fuse_modules_qat(net, [["conv", "bn", "relu"]], qcfg)
+    assert isinstance(fused.conv, nniqat.ConvBnReLU2d) and isinstance(fused.conv.bn, torch.nn.BatchNorm2d)
+    assert isinstance(fused.bn, torch.nn.Identity)
+    x = torch.randn(2, 3, 8, 8)
+    assert torch.allclose(fused.eval()(x), net(x), atol=1e-4)  # identity "fake-quantizers": the fold alone
+    w, b = fused.conv._fold()
+    ref = Q.fuse_conv_bn_eval(net.conv, net.bn)
+    assert torch.equal(w, ref.weight) and torch.equal(b, ref.bias)
+    with pytest.raises(ValueError):
+        nniqat.ConvBn2d(net.conv, net.bn, qconfig=None)
