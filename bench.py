@@ -429,6 +429,13 @@ def run_b200_arm(args):
         barrier()
     gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
     n_gemm = len(gemm_events)
+    per_proj = {}
+    for i, name in enumerate(("qkv", "o", "gate_up", "down")):
+        ev = gemm_events[i::4]
+        if ev:
+            ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+            ops = 2.0 * M_TOKENS * sum(PROJ[p][0] * PROJ[p][1] for p in (("gate", "up") if name == "gate_up" else (name,)))
+            per_proj[name] = {"ms": ms, "TOPS_this_rank": ops / world / ms / 1e9}
     t = torch.tensor([ms_total, gemm_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -574,6 +581,7 @@ def run_b200_arm(args):
                 "peak_note": f"2 x cuBLAS bf16 sustained ({peaks['source']}); nominal dense int8 "
                              "is 4500 TOPS",
                 "frac_of_nominal_4500": achieved / 4500.0,
+                "per_projection": per_proj,
             },
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": h2d,
@@ -683,9 +691,21 @@ def library_int8_gemm(torch, dev, weights, iters=10):
     block.  Never on the product path."""
     out = {}
     total_ops, total_s = 0.0, 0.0
+    acts = {k: torch.randint(-128, 128, (M_TOKENS, k), dtype=torch.int8, device=dev)
+            for k in {w.shape[1] for w, _ in weights.values()}}
+    try:
+        # about a second of the same load first: the part is power-capped, and a burst after an
+        # idle phase would run at clocks the timed region never sees
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 1.0:
+            for w, _ in weights.values():
+                torch._int_mm(acts[w.shape[1]], w.t())
+            torch.cuda.synchronize()
+    except Exception as exc:  # noqa: BLE001
+        return {"error": f"{type(exc).__name__}: {exc}"[:200]}
     for name, (w, _) in weights.items():
         n, k = w.shape
-        a = torch.randint(-128, 128, (M_TOKENS, k), dtype=torch.int8, device=dev)
+        a = acts[k]
         wt = w.t()  # (K, N) column-major view: the layout _int_mm takes without a copy
         try:
             for _ in range(3):
@@ -707,7 +727,8 @@ def library_int8_gemm(torch, dev, weights, iters=10):
         total_s += sec
     if total_s > 0:
         out["all_four"] = {"TOPS": total_ops / total_s / 1e12}
-    out["what"] = "torch._int_mm (cuBLASLt s8 x s8 -> s32, no epilogue) on the same shapes, same process, after the timed region"
+    out["what"] = ("torch._int_mm (cuBLASLt s8 x s8 -> s32, no epilogue) on the same shapes, same process, after "
+                   "the timed region and one second of the same load")
     return out
 
 

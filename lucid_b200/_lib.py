@@ -8,6 +8,7 @@ library or a non-CUDA tensor raises.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 
@@ -205,6 +206,20 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
         raise DeviceMismatch(
             f"{what} lives on {t.device}; the B200 quantized engine only runs on CUDA tensors "
             "(no CPU fallback)")
+
+
+@contextlib.contextmanager
+def ieee_float32():
+    """The float routes (engine "reference", layers outside the integer path, the weight-only
+    LSTM) restate the reference's binary32 arithmetic: keep the library's convolutions and
+    matrix products off TF32 (19-bit operands) while they run."""
+    old_mm = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+            yield
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old_mm
 
 
 def ptr(t):

@@ -724,39 +724,47 @@ __device__ __forceinline__ void q8_dispatch(int mask, const Epi& ep, const RowCt
 
 // ---- work schedule ------------------------------------------------------------------
 // Tile mode: worker w takes tiles w, w + W, ... whole (M fastest, so neighbouring workers share
-// a B tile in L2).  Stream-K mode: the k-blocks of all tiles form one sequence of
-// total_tiles * num_kb units and worker w takes units [U*w/W, U*(w+1)/W): the tail of one tile,
-// some whole tiles and the head of another.
+// a B tile in L2).  Stream-K mode handles the tiles that do not fill a whole wave: with T tiles
+// and W workers the first T % W tiles form one sequence of k-block units that is dealt out in
+// equal contiguous runs (worker w takes units [U*w/W, U*(w+1)/W): the tail of one tile, maybe
+// whole tiles, the head of another); the other T - T % W tiles follow tile by tile, so every
+// worker ends with the same number of whole tiles and the L2 footprint of the tile-by-tile order
+// is kept.
 struct Sched {
-  int streamk, num_workers, num_kb;
-  int tile, total_tiles;  // tile mode
-  long long u, u_end;     // stream-K
+  int num_workers, num_kb;
+  int tile, total_tiles;  // tile-by-tile part: next tile
+  long long u, u_end;     // stream-K part: next unit, end of the run (empty when not stream-K)
 };
 __device__ __forceinline__ long long run_begin(long long units, int worker, int num_workers) {
   return units * worker / num_workers;
 }
-__device__ __forceinline__ Sched make_sched(const Geometry& g, int worker, int num_workers, int total_tiles) {
+// tiles handled by the stream-K part
+__device__ __forceinline__ int streamk_tiles(const Geometry& g, int total_tiles, int num_workers) {
+  return g.streamk ? total_tiles % num_workers : 0;
+}
+__device__ __forceinline__ Sched make_sched(const Geometry& g, int worker, int raw_worker, int num_workers,
+                                            int total_tiles) {
   Sched s;
-  s.streamk = g.streamk, s.num_workers = num_workers, s.num_kb = g.num_kb;
-  s.tile = worker, s.total_tiles = total_tiles;
-  const long long units = (long long)total_tiles * g.num_kb;
+  s.num_workers = num_workers, s.num_kb = g.num_kb, s.total_tiles = total_tiles;
+  const int sk_tiles = streamk_tiles(g, total_tiles, num_workers);
+  const long long units = (long long)sk_tiles * g.num_kb;
   s.u = run_begin(units, worker, num_workers), s.u_end = run_begin(units, worker + 1, num_workers);
+  s.tile = sk_tiles + raw_worker;
   return s;
 }
 // Next work item: k-blocks [kb0, kb1) of `tile`.  False when the worker is done.
 __device__ __forceinline__ bool sched_next(Sched& s, int& tile, int& kb0, int& kb1) {
-  if (!s.streamk) {
-    if (s.tile >= s.total_tiles) return false;
-    tile = s.tile, kb0 = 0, kb1 = s.num_kb;
-    s.tile += s.num_workers;
+  if (s.u < s.u_end) {
+    tile = (int)(s.u / s.num_kb);
+    kb0 = (int)(s.u - (long long)tile * s.num_kb);
+    const long long left = s.u_end - s.u;
+    kb1 = left < (long long)(s.num_kb - kb0) ? kb0 + (int)left : s.num_kb;
+    s.u += kb1 - kb0;
     return true;
   }
-  if (s.u >= s.u_end) return false;
-  tile = (int)(s.u / s.num_kb);
-  kb0 = (int)(s.u - (long long)tile * s.num_kb);
-  const long long left = s.u_end - s.u;
-  kb1 = left < (long long)(s.num_kb - kb0) ? kb0 + (int)left : s.num_kb;
-  s.u += kb1 - kb0;
+  if (s.tile >= s.total_tiles) return false;
+  tile = s.tile, kb0 = 0, kb1 = s.num_kb;
+  s.tile += s.num_workers;
   return true;
 }
 
@@ -834,7 +842,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   if (warp == 0) {
     // ===== TMA producer (one per CTA) =====
-    Sched sc = make_sched(g, worker, num_workers, total_tiles);
+    Sched sc = make_sched(g, worker, raw_worker, num_workers, total_tiles);
     int stage = 0, tile, kb0, kb1;
     uint32_t phase = 0;
     bool ok = true;
@@ -891,7 +899,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   } else if (warp == 1) {
     // ===== MMA issuer (leader CTA only when paired) =====
     if (leader) {
-      Sched sc = make_sched(g, worker, num_workers, total_tiles);
+      Sched sc = make_sched(g, worker, raw_worker, num_workers, total_tiles);
       int stage = 0, acc = 0, tile, kb0, kb1;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -961,8 +969,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // (arrivals of the writing warps, departures of the reading warps)
     uint8_t* const sk_slots = ep.ws ? ep.ws + kWsHeaderBytes : nullptr;
     unsigned int* const sk_flags = ep.ws ? reinterpret_cast<unsigned int*>(ep.ws + kWsFlagsOffset) : nullptr;
-    const long long units = (long long)total_tiles * g.num_kb;
-    Sched sc = make_sched(g, worker, num_workers, total_tiles);
+    const long long units = (long long)streamk_tiles(g, total_tiles, num_workers) * g.num_kb;
+    Sched sc = make_sched(g, worker, raw_worker, num_workers, total_tiles);
     int acc = 0, tile, kb0, kb1;
     uint32_t acc_phase = 0;
     const uint32_t tempty_target = PAIR ? map_to_cta(bar_tempty, 0) : bar_tempty;
@@ -1062,17 +1070,19 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
 
   // ===== teardown (every role falls through to here) =====
-  __syncwarp();
-  if (*abort_flag) {
+  tc_fence_before();
+  __syncthreads();
+  // read after the barrier: a role that finished early (the producer once it has issued its
+  // last load) must still see an abort that another role raised later
+  const bool aborted = *abort_flag != 0;
+  if (aborted) {
     // give copies / MMAs still in flight time to land before the CTA's shared
     // memory and TMEM are released
     for (int i = 0; i < 50; ++i) __nanosleep(20000);
     if (threadIdx.x == 0 && ep.status) atomicExch(ep.status, (int)LQ_ERR_TIMEOUT);
   }
-  tc_fence_before();
-  __syncthreads();
   if (PAIR) cluster_sync_all();  // the peer may still signal this CTA's barriers / read its tiles
-  if (ep.n_flags > 0 && threadIdx.x == 0 && !*abort_flag) {
+  if (ep.n_flags > 0 && threadIdx.x == 0 && !aborted) {
     // Exchange step: every CTA's stores into the peers' buffers are complete (barrier above) and
     // made visible system-wide before its ticket; the CTA that draws the last ticket publishes
     // this rank's new step count to its flag word on every peer.
@@ -1250,9 +1260,17 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
 // LQ_GEMM_VERBOSE prints each launch's geometry.
 struct Knobs {
   int shape = -1, epi_warps = 0, streamk = -1;
+  // policy thresholds: stream-K when the last wave fills less than this percentage of the
+  // workers and a tile has at least this many k-blocks.  Measured on the Llama-2-70B shard
+  // shapes: +11 % at 4096 x 4096 x 28672 (34 of 74 clusters in the last wave, 224 k-blocks);
+  // within +-2 % or a loss for tiles of 64 k-blocks, where the partial-tile round trip and the
+  // extra exposed epilogue cost what the evened-out wave saves.
+  int streamk_max_fill = 60, streamk_min_kb = 128;
   bool verbose = false;
   void read() {
     shape = -1, epi_warps = 0, streamk = -1;
+    if (const char* f = getenv("LQ_GEMM_STREAMK_MAX_FILL")) streamk_max_fill = atoi(f);
+    if (const char* f = getenv("LQ_GEMM_STREAMK_MIN_KB")) streamk_min_kb = atoi(f);
     if (const char* f = getenv("LQ_GEMM_SHAPE")) {
       if (!strcmp(f, "pair")) shape = 0;
       else if (!strcmp(f, "single256")) shape = 1;
@@ -1281,7 +1299,7 @@ struct LaunchState {
 };
 
 template <int BN, bool PAIR, int EW>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep,
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_in, const Epi& ep,
            uint32_t idesc, cudaStream_t st) {
   static LaunchState<BN, PAIR, EW> state;
   auto kernel = gemm_s8_kernel<BN, PAIR, EW>;
@@ -1309,13 +1327,22 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
     return e;
   });
   if (attr_err != cudaSuccess) return check_cuda(attr_err, "cudaFuncSetAttribute(max dynamic smem)");
-  const int tiles_mw = PAIR ? (g.tiles_m + 1) / 2 : g.tiles_m;
-  const int total_tiles = tiles_mw * g.tiles_n;
-  // workers that get something to do: one per tile, or (stream-K) one per run of k-blocks
+  const int tiles_mw = PAIR ? (g_in.tiles_m + 1) / 2 : g_in.tiles_m;
+  const int total_tiles = tiles_mw * g_in.tiles_n;
+  // workers that get something to do: one per tile, or (stream-K, fewer tiles than workers) one
+  // per run of k-blocks
+  Geometry g = g_in;
+  const int workers_max = PAIR ? state.max_clusters[dev] : sm_count();
   int total = total_tiles;
   if (g.streamk) {
-    const long long runs = (long long)total_tiles * g.num_kb / (knobs().streamk == 1 ? 2 : 8);
-    total = runs < 1 ? 1 : (runs > (1 << 20) ? (1 << 20) : (int)runs);
+    const int min_run = knobs().streamk == 1 ? 2 : 8;
+    if (total_tiles < workers_max) {
+      const long long runs = (long long)total_tiles * g.num_kb / min_run;
+      total = runs < 1 ? 1 : (runs > workers_max ? workers_max : (int)runs);
+      if (total <= total_tiles) g.streamk = 0, total = total_tiles;  // nothing to gain from cutting tiles
+    } else if ((long long)(total_tiles % workers_max) * g.num_kb < (long long)min_run * workers_max) {
+      g.streamk = 0;  // the partial wave is too short to cut into one run per worker
+    }
   }
   if (!PAIR) {
     const int grid = total < sm_count() ? total : sm_count();
@@ -1342,12 +1369,11 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, cons
   return check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, ep, idesc), "gemm_s8_kernel (paired) launch");
 }
 
-// Tile shape and schedule.  Candidates: CTA pairs on 256 x 256 tiles (cta_group::2), single CTAs
-// on 128 x 256 or 128 x 128 tiles; each either tile by tile or stream-K.  The cost of a candidate
-// is the number of k-block steps the busiest CTA runs (a step = one 128-deep k-block of a
-// 256-column CTA tile; a 128-column tile costs a little more than half of it because the MMA
-// re-reads A per column block), plus the exposed epilogue of its last tile; stream-K evens the
-// steps out over all CTAs at the price of one partial-tile round trip through L2.
+// Tile shape and schedule.  CTA pairs (256 x 256 tiles, cta_group::2) when there is enough work
+// to fill the clusters; single CTAs (128 x 256, or 128 x 128 for narrow outputs) otherwise.
+// Stream-K on top of that shape when the last wave of tiles would leave a good part of the SMs
+// idle and a tile is long enough (k-blocks) to be worth cutting: the cut costs one partial-tile
+// round trip through L2 and exposes one more epilogue.
 enum class Shape { kPair256 = 0, kSingle256 = 1, kSingle128 = 2 };
 struct Plan {
   Shape shape;
@@ -1356,39 +1382,35 @@ struct Plan {
 
 Plan pick_plan(size_t m_subtiles, size_t N, bool gated, size_t k_blocks, bool have_ws) {
   const Knobs& kn = knobs();
-  const int sms = sm_count();
-  const bool sk_allowed = have_ws && kn.streamk != 0;
-  Plan best = {Shape::kSingle256, false};
-  double best_cost = 1e300;
-  for (int c = 0; c < 3; ++c) {
-    const Shape sh = (Shape)c;
-    if (kn.shape >= 0 && kn.shape != c && !(c == 1 && kn.shape == 2 && gated)) continue;
-    if (sh == Shape::kSingle128 && gated) continue;
-    if (sh == Shape::kPair256 && m_subtiles < 2 && kn.shape != 0) continue;
-    // With a handful of k-blocks a tile is all epilogue: the pair's saving on operand traffic
-    // buys nothing and its cluster handshakes cost (measured 63 vs 68 us at 50176 x 1024 x 256).
-    if (sh == Shape::kPair256 && k_blocks <= 4 && kn.shape != 0) continue;
-    if (sh == Shape::kSingle128 && N > 128 && kn.shape != 2 && k_blocks <= 4) continue;
+  const size_t sms = (size_t)sm_count();
+  Shape sh;
+  const size_t tiles_n256 = (N + 255) / 256;
+  const size_t pair_tiles = ((m_subtiles + 1) / 2) * tiles_n256;
+  if (kn.shape == 0) sh = Shape::kPair256;
+  else if (kn.shape == 1 || (kn.shape == 2 && gated)) sh = Shape::kSingle256;
+  else if (kn.shape == 2) sh = Shape::kSingle128;
+  else if (N <= 128 && !gated) sh = Shape::kSingle128;
+  // With a handful of k-blocks a tile is all epilogue: the pair's saving on operand traffic buys
+  // nothing and its cluster handshakes cost (measured 63 vs 68 us at 50176 x 1024 x 256).
+  else if (k_blocks <= 4) sh = Shape::kSingle256;
+  // a pair tile on a half-empty M pair wastes a CTA; need about one wave of clusters -- three
+  // quarters of one when K is long, where the pair's halved B traffic outweighs the idle
+  // clusters (measured 2567 vs 2152 TOPS at 4096 x 1024 x 28672: 64 pair tiles on 74 clusters)
+  else if (m_subtiles >= 2 && (pair_tiles >= sms / 2 || (k_blocks >= 128 && pair_tiles * 4 >= (sms / 2) * 3)))
+    sh = Shape::kPair256;
+  else sh = Shape::kSingle256;
+
+  bool sk = false;
+  if (have_ws && kn.streamk != 0) {
     const size_t bn = sh == Shape::kSingle128 ? 128 : 256;
-    const size_t tiles_n = (N + bn - 1) / bn;
-    const size_t tiles = (sh == Shape::kPair256 ? (m_subtiles + 1) / 2 : m_subtiles) * tiles_n;
-    const size_t workers = sh == Shape::kPair256 ? (size_t)(sms / 2) : (size_t)sms;
-    // steps of one tile on one CTA, and the part of its epilogue that nothing hides
-    const double tile_steps = (double)k_blocks * (sh == Shape::kSingle128 ? 0.58 : (sh == Shape::kSingle256 ? 1.03 : 1.0));
-    const double epi_steps = sh == Shape::kSingle128 ? 12.0 : 24.0;
-    const size_t waves = (tiles + workers - 1) / workers;
-    const double dp = (double)waves * (tile_steps > epi_steps ? tile_steps : epi_steps) + epi_steps;
-    if (dp < best_cost) best_cost = dp, best = {sh, false};
-    const size_t units = tiles * k_blocks;
-    if (sk_allowed && kn.streamk == 1 && k_blocks >= 2) {
-      // forced (tests): any shape with something to cut
-      if (best_cost >= 0.0 || dp < -best_cost) best_cost = -dp, best = {sh, true};
-    } else if (sk_allowed && k_blocks >= 16 && tiles * 2 >= workers && units >= 8 * workers && tiles <= 8 * workers) {
-      const double sk = (double)tiles / (double)workers * tile_steps + epi_steps + 16.0;
-      if (sk < best_cost) best_cost = sk, best = {sh, true};
-    }
+    const size_t tiles = (sh == Shape::kPair256 ? (m_subtiles + 1) / 2 : m_subtiles) * ((N + bn - 1) / bn);
+    const size_t workers = sh == Shape::kPair256 ? sms / 2 : sms;
+    const size_t rem = tiles % workers;
+    if (kn.streamk == 1) sk = k_blocks >= 2;  // forced (tests): the launch drops it where nothing can be cut
+    else sk = rem != 0 && rem * 100 < workers * (size_t)kn.streamk_max_fill && k_blocks >= (size_t)kn.streamk_min_kb &&
+              tiles <= workers * 8;
   }
-  return best;
+  return {sh, sk};
 }
 
 int dispatch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,

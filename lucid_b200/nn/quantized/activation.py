@@ -112,3 +112,25 @@ class LeakyReLU(_QuantizedActivation):
 
     def _act(self, x):
         return F.leaky_relu(x, self.negative_slope)
+
+
+class ReLU(torch.nn.ReLU):
+    """``nn.ReLU`` that keeps the codes of its input alive.  On floats it is the plain ReLU (the
+    reference's converted model keeps ``nn.ReLU`` as it is); when the input carries integer codes,
+    the rectified tensor carries ``max(code, zero_point)`` on the same grid -- exactly the codes
+    of the rectified values -- so that a quantized layer behind an unfused (possibly in-place)
+    ReLU consumes codes instead of re-encoding floats.  ``convert`` swaps every ``nn.ReLU`` of
+    the model for this class; it has no state and no observer."""
+
+    def forward(self, x):
+        qc = codes_of(x) if isinstance(x, torch.Tensor) and x.is_cuda else None
+        y = F.relu(x, inplace=self.inplace)
+        if qc is None or qc.scale.dim() != 0:
+            return y
+        floor = qc.zero_point.to(qc.codes.dtype)
+        codes = torch.maximum(qc.codes, floor)
+        return tag(y, QCodes(codes, qc.scale, qc.zero_point, qc.layout, qc.zp_is_zero))
+
+    @classmethod
+    def from_float(cls, mod):
+        return cls(inplace=mod.inplace)

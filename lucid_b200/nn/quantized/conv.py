@@ -137,6 +137,8 @@ class Conv2d(torch.nn.Module):
         qc = codes_of(x)
         if qc is not None and qc.layout == "nhwc":
             a, s, z = qc.codes, qc.scale, qc.zero_point
+        elif qc is not None and qc.codes.dim() == 4 and qc.codes.dtype in (torch.int8, torch.uint8):
+            a, s, z = qc.codes.permute(0, 2, 3, 1).contiguous(), qc.scale, qc.zero_point  # NCHW codes: re-lay, exact
         else:
             a, s, z = encode_activation(x.permute(0, 2, 3, 1))
         if qc is not None and qc.zp_is_zero is not None:
@@ -157,11 +159,12 @@ class Conv2d(torch.nn.Module):
         lo, hi, _ = self._geometry(x.shape[2], x.shape[3])
         x = x.to(torch.float32)
         mode = "constant" if self.padding_mode == "zeros" else self.padding_mode
-        if mode != "constant" or lo != hi:
-            xp = F.pad(x, (lo[1], hi[1], lo[0], hi[0]), mode=mode)
-            y = F.conv2d(xp, w, self.bias, self.stride, 0, self.dilation, self.groups)
-        else:
-            y = F.conv2d(x, w, self.bias, self.stride, lo, self.dilation, self.groups)
+        with _lib.ieee_float32():
+            if mode != "constant" or lo != hi:
+                xp = F.pad(x, (lo[1], hi[1], lo[0], hi[0]), mode=mode)
+                y = F.conv2d(xp, w, self.bias, self.stride, 0, self.dilation, self.groups)
+            else:
+                y = F.conv2d(x, w, self.bias, self.stride, lo, self.dilation, self.groups)
         y = self._activation(y).contiguous()
         return fake_quantize(y, self.scale, self.zero_point, self.out_qdtype.quant_min,
                              self.out_qdtype.quant_max)

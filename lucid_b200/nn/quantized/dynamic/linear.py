@@ -73,7 +73,8 @@ class Linear(torch.nn.Module):
         s, z = calculate_qparams(mn, mx, per_tensor_affine, self.act_qdtype)
         xq = fake_quantize(x32.contiguous(), s, z, self.act_qdtype.quant_min, self.act_qdtype.quant_max)
         w = dequantize(self.weight_int8, self.weight_scale, self.weight_zero_point, ch_axis=self.weight_ch_axis)
-        return F.linear(xq, w, self.bias)
+        with _lib.ieee_float32():
+            return F.linear(xq, w, self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _lib.require_cuda(x, "input")

@@ -78,6 +78,10 @@ class LSTM(torch.nn.Module):
         return out, h, c
 
     def forward(self, x, hx=None):
+        with _lib.ieee_float32():
+            return self._forward(x, hx)
+
+    def _forward(self, x, hx):
         if isinstance(x, torch.nn.utils.rnn.PackedSequence):
             return self._forward_packed(x, hx)
         _lib.require_cuda(x, "input")

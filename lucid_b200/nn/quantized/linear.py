@@ -129,7 +129,8 @@ class Linear(torch.nn.Module):
         """The reference's own sequence, on device (engine ``"reference"``)."""
         w = dequantize(self.weight_int8, self.weight_scale, self.weight_zero_point,
                        ch_axis=self.weight_ch_axis)
-        y = self._activation(F.linear(x.to(torch.float32), w, self.bias))
+        with _lib.ieee_float32():
+            y = self._activation(F.linear(x.to(torch.float32), w, self.bias))
         return fake_quantize(y, self.scale, self.zero_point, self.out_qdtype.quant_min,
                              self.out_qdtype.quant_max)
 

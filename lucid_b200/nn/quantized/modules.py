@@ -13,7 +13,7 @@ class Quantize(torch.nn.Module):
     """Snap a float activation onto a fixed grid; the result is the
     fake-quantized float tensor (as in the reference) carrying its codes."""
 
-    def __init__(self, scale=1.0, zero_point=0.0, qdtype: QDtype = quint8, nhwc: bool = False):
+    def __init__(self, scale=1.0, zero_point=0.0, qdtype: QDtype = quint8, nhwc: bool | None = None):
         super().__init__()
         self.register_buffer("scale", torch.as_tensor(scale, dtype=torch.float32))
         self.register_buffer("zero_point", torch.as_tensor(zero_point, dtype=torch.float32))
@@ -21,14 +21,16 @@ class Quantize(torch.nn.Module):
         self.nhwc = nhwc
 
     def forward(self, x):
-        src = x.permute(0, 2, 3, 1) if self.nhwc else x
+        # image batches (4-D) carry their codes channels-last, the layout the convolution reads
+        nhwc = self.nhwc if self.nhwc is not None else x.dim() == 4
+        src = x.permute(0, 2, 3, 1) if nhwc else x
         store = torch.int8 if self.qdtype.signed else torch.uint8
         codes = quantize_to(src, self.scale, self.zero_point, self.qdtype.quant_min,
                             self.qdtype.quant_max, store)
         y = dequantize(codes, self.scale, self.zero_point)
-        if self.nhwc:
+        if nhwc:
             y = y.permute(0, 3, 1, 2)
-        return tag(y, QCodes(codes, self.scale, self.zero_point, "nhwc" if self.nhwc else "rowmajor"))
+        return tag(y, QCodes(codes, self.scale, self.zero_point, "nhwc" if nhwc else "rowmajor"))
 
     @classmethod
     def from_float(cls, mod):

@@ -64,6 +64,7 @@ def _quant_mapping() -> dict:
         torch.nn.Conv2d: nnq.Conv2d.from_float,
         QuantStub: nnq.Quantize.from_float,
         DeQuantStub: nnq.DeQuantize.from_float,
+        torch.nn.ReLU: nnq.ReLU.from_float,
         nnq.FloatFunctional: nnq.QFunctional.from_float,
         torch.nn.ConvTranspose1d: nnq.ConvTranspose1d.from_float,
         torch.nn.ConvTranspose2d: nnq.ConvTranspose2d.from_float,
@@ -150,7 +151,7 @@ def convert(model: torch.nn.Module, inplace: bool = False):
     model = model if inplace else copy.deepcopy(model)
     model.eval()
     mapping = _quant_mapping()
-    always = (DeQuantStub,)
+    always = (DeQuantStub, torch.nn.ReLU)
     build = mapping.get(type(model))
     if build is not None and hasattr(model, "activation_post_process"):
         return build(model)

@@ -110,11 +110,14 @@ def test_static_ptq_with_batchnorm_reaches_the_integer_conv():
     """fuse_modules -> prepare -> calibrate -> convert on a Conv/BN/ReLU model: BatchNorm is folded
     (exact at eval time, the reference's gate test_static_ptq.py:90-99) and the converted model
     runs integer convolutions only (the strided one included)."""
+    from lucid_b200 import _lib
+
     net = _bn_net().eval()
     x = torch.randn(4, 16, 20, 20, device="cuda")
-    y_float = net(x)
     fused = Q.fuse_modules(net, [["conv1", "bn1", "relu1"], ["conv2", "bn2"]])
-    assert torch.allclose(fused(x), y_float, atol=1e-4)
+    with _lib.ieee_float32(), torch.no_grad():  # the library's convolutions default to TF32
+        y_float = net(x)
+        assert torch.allclose(fused(x), y_float, atol=1e-4)
     prepared = Q.prepare(fused, Q.QConfig(activation=Q.MinMaxObserver, weight=Q.get_default_qconfig().weight))
     with torch.no_grad():
         prepared(x)
