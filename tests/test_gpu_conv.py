@@ -232,20 +232,28 @@ def test_resnet18_shaped_stack_runs_on_the_integer_path():
     with _CountConv() as counter, torch.no_grad():
         y = qmodel(x)
     _sync_status()
-    assert counter.n == 0
-    lucid_b200.backends.quantized.engine = "reference"
-    try:
-        with torch.no_grad():
-            y_ref = qmodel(x)
-    finally:
-        lucid_b200.backends.quantized.engine = "auto"
-    assert y.shape == y_ref.shape
-    # codes travel from the entry stub through every layer (the ReLUs keep them exact), so the two
-    # routes differ only where the float convolution's rounding moves a value across a grid edge,
-    # and such a flip can move a few downstream codes by one step
-    step = float(convs[-1].scale)
-    diff = (y - y_ref).abs()
-    assert float((diff > 0).float().mean()) < 0.02 and float(diff.max()) <= 2.001 * step
+    assert counter.n == 0 and y.shape == (2, 128, 4, 4)
+    # Layer by layer on the same input: the integer kernel against the reference's float route
+    # (engine "reference": decode the weight, float convolution, fake-quantize).  The two differ
+    # only where the float convolution's rounding moves a value across a grid edge: a tiny rate,
+    # one code.  (Across a deep stack such flips compound, so the end-to-end rate says little.)
+    t = x
+    with torch.no_grad():
+        for mod in qmodel:
+            if isinstance(mod, nnq.Conv2d):
+                lucid_b200.backends.quantized.engine = "reference"
+                try:
+                    y_ref = mod(t)
+                finally:
+                    lucid_b200.backends.quantized.engine = "auto"
+                t = mod(t)
+                diff = (t - y_ref).abs()
+                assert float((diff > 0).float().mean()) < 1e-3, mod
+                assert float(diff.max()) <= 1.001 * float(mod.scale), mod
+            else:
+                t = mod(t)
+    assert torch.equal(t, y)
+    _sync_status()
 
 
 def test_inplace_ops_and_carried_codes():

@@ -43,7 +43,8 @@ def test_static_ptq_mlp_and_checkpoint_round_trip():
     buf = io.BytesIO()
     torch.save(qmodel.state_dict(), buf)
     buf.seek(0)
-    clone = torch.nn.Sequential(nnq.Quantize(), nnq.Linear(128, 256), torch.nn.ReLU(),
+    assert type(qmodel[2]) is nnq.ReLU  # plain ReLU on floats; keeps integer codes alive
+    clone = torch.nn.Sequential(nnq.Quantize(), nnq.Linear(128, 256), nnq.ReLU(),
                                 nnq.Linear(256, 64), nnq.DeQuantize()).cuda()
     clone.load_state_dict(torch.load(buf))
     for a, b in ((clone[1], qmodel[1]), (clone[3], qmodel[3])):
