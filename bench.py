@@ -281,7 +281,7 @@ def run_b200_arm(args):
         # The hidden tensor is exchanged as int8 codes from 4 ranks up (half the bytes, and the
         # encode is sharded); at 2 ranks the extra abs-max exchange costs more than the halved
         # bytes save, so the bf16 tensor is exchanged there.
-        if world >= 4:
+        if args.hidden == "codes" or (args.hidden == "auto" and world >= 4):
             hidden = HiddenExchange(M_TOKENS, D_FF, dev)
         else:
             peers["h"] = PeerOutputs(M_TOKENS, D_FF, torch.bfloat16, dev)
@@ -1029,6 +1029,8 @@ def main():
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="N > 1: capture the step in a CUDA graph and replay it (auto: with the p2p exchange, "
                          "whose step holds no collective call)")
+    ap.add_argument("--hidden", default="auto", choices=["auto", "codes", "bf16"],
+                    help="N > 1, p2p: exchange the gate/up output as per-token int8 codes or as bf16 (auto: codes from 4 ranks)")
     ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
                          "(auto: from 4 ranks)")

@@ -409,6 +409,25 @@ int make_params(const float* scale, const float* zp, float sv, float zv, int ch_
   return LQ_OK;
 }
 
+// tuning knobs of the stream kernels (environment, read once; lq_reload_env re-reads)
+struct StreamKnobs {
+  int ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4;
+  void read() {
+    ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4;
+    if (const char* e = getenv("LQ_QUANT_CTAS_PER_SM")) ctas_per_sm = atoi(e);
+    if (const char* e = getenv("LQ_QUANT_UNROLL")) unroll = atoi(e) == 2 ? 2 : 4;
+    if (const char* e = getenv("LQ_MINMAX_CTAS_PER_SM")) minmax_ctas_per_sm = atoi(e) > 0 ? atoi(e) : 4;
+  }
+};
+StreamKnobs& stream_knobs() {
+  static StreamKnobs k = [] {
+    StreamKnobs v;
+    v.read();
+    return v;
+  }();
+  return k;
+}
+
 // ---- range reduction -----------------------------------------------------------
 struct MinMaxWorkspace {
   unsigned int ticket;
@@ -455,7 +474,13 @@ __device__ __forceinline__ void minmax_accumulate(const In* x, size_t n, size_t 
     const uint4 c = ld_stream_u4(xv + i + 2 * stride), d = ld_stream_u4(xv + i + 3 * stride);
     vec_minmax<In>(a, mn, mx), vec_minmax<In>(b, mn, mx), vec_minmax<In>(c, mn, mx), vec_minmax<In>(d, mn, mx);
   }
-  for (; i < nvec; i += stride) vec_minmax<In>(ld_stream_u4(xv + i), mn, mx);
+  if (i < nvec) {
+    // up to three vectors left for this thread: issued together (one latency, not three); a
+    // vector past the end re-reads the first one, which changes no min / max
+    const size_t i1 = i + stride < nvec ? i + stride : i, i2 = i + 2 * stride < nvec ? i + 2 * stride : i;
+    const uint4 a = ld_stream_u4(xv + i), b = ld_stream_u4(xv + i1), c = ld_stream_u4(xv + i2);
+    vec_minmax<In>(a, mn, mx), vec_minmax<In>(b, mn, mx), vec_minmax<In>(c, mn, mx);
+  }
   for (size_t e = nvec * E + first; e < n; e += stride) {
     const float v = Packet<In>::load1(x + e);
     mn = fminf(mn, v), mx = fmaxf(mx, v);
@@ -690,8 +715,22 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
   } else if (vec) {
     // 4 groups per thread at full occupancy (32 registers): measured fastest on B200 -- the
     // encode is latency-bound, so resident warps matter more than loads in flight per thread
-    affine_vec_kernel<OP, In, Out, MASK, 4, 8><<<grid_for((n / 4 + 3) / 4), kThreads, 0, st>>>(
-        (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
+    const StreamKnobs& kn = stream_knobs();
+    if (kn.ctas_per_sm > 0) {
+      // persistent, grid-stride: every CTA slot of the GPU gets one CTA that walks the tensor in
+      // steps of the whole grid, so the last wave is full and the DRAM front still advances in order
+      const size_t spans = kn.unroll == 2 ? (n / 4 + 1) / 2 : (n / 4 + 3) / 4;
+      const int grid = grid_for(spans, (size_t)kn.ctas_per_sm);
+      if (kn.unroll == 2)
+        affine_vec_kernel<OP, In, Out, MASK, 2, 8><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, cols, q,
+                                                                           (float)qmin, (float)qmax);
+      else
+        affine_vec_kernel<OP, In, Out, MASK, 4, 8><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, cols, q,
+                                                                           (float)qmin, (float)qmax);
+    } else {
+      affine_vec_kernel<OP, In, Out, MASK, 4, 8><<<grid_for((n / 4 + 3) / 4), kThreads, 0, st>>>(
+          (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
+    }
   } else {
     affine_scalar_kernel<OP, In, Out, MASK><<<grid_for(n), kThreads, 0, st>>>(
         (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
@@ -700,33 +739,33 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
 }
 
 
-// Per-tensor: per-CTA partials go to the workspace; the CTA that takes the last
-// ticket folds them (min/max are exact in any order) and re-arms the ticket.
+// Order-preserving map of a float onto unsigned integers (and back), so that integer atomics
+// fold float minima / maxima.  -0.0 and +0.0 keep their order.
+__device__ __forceinline__ unsigned int float_key(float f) {
+  const unsigned int b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(unsigned int k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Per-tensor: every CTA folds its pair into two words of the workspace with integer atomics
+// (max of the key for the maximum, max of the complemented key for the minimum, so that the
+// zero-filled workspace is the identity of both); the CTA that takes the last ticket decodes
+// them and re-arms the workspace.  Min / max are exact in any order.
 __device__ __forceinline__ void finish_tensor_minmax(float mn, float mx, MinMaxWorkspace* ws,
                                                      float* out_min, float* out_max) {
   block_minmax(mn, mx);
-  __shared__ bool is_last;
-  if (threadIdx.x == 0) {
-    ws->pmin[blockIdx.x] = mn;
-    ws->pmax[blockIdx.x] = mx;
-    __threadfence();
-    unsigned int t = atomicAdd(&ws->ticket, 1u);
-    is_last = (t == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (!is_last) return;
+  if (threadIdx.x != 0) return;
+  atomicMax(&ws->pad[0], float_key(mx));
+  atomicMax(&ws->pad[1], ~float_key(mn));
   __threadfence();
-  mn = INFINITY, mx = -INFINITY;
-  for (unsigned int i = threadIdx.x; i < gridDim.x; i += kThreads) {
-    mn = fminf(mn, __ldcg(&ws->pmin[i]));
-    mx = fmaxf(mx, __ldcg(&ws->pmax[i]));
-  }
-  block_minmax(mn, mx);
-  if (threadIdx.x == 0) {
-    *out_min = mn;
-    *out_max = mx;
-    ws->ticket = 0;  // leave the workspace zeroed for the next call
-  }
+  if (atomicAdd(&ws->ticket, 1u) != gridDim.x - 1) return;
+  __threadfence();
+  const unsigned int kmax = atomicExch(&ws->pad[0], 0u), kmin = atomicExch(&ws->pad[1], 0u);
+  *out_max = key_float(kmax);
+  *out_min = key_float(~kmin);
+  ws->ticket = 0;  // leave the workspace zeroed for the next call
 }
 
 template <typename In>
@@ -982,6 +1021,10 @@ rowsum_kernel(const int8_t* __restrict__ b, size_t N, size_t K, bool vec_ok,
 
 using namespace lq;
 
+namespace lq {
+void reload_stream_knobs() { stream_knobs().read(); }
+}  // namespace lq
+
 extern "C" size_t lq_minmax_workspace_bytes(void) { return sizeof(MinMaxWorkspace); }
 
 extern "C" int lq_stream_timeouts(unsigned int* count) {
@@ -1013,7 +1056,7 @@ extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, 
     const bool vec_ok = aligned16(x);
     // two packets per thread-iteration; grid in multiples of the SM count
     size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
-    const size_t gcap = (size_t)sm_count() * 4;
+    const size_t gcap = (size_t)sm_count() * stream_knobs().minmax_ctas_per_sm;
     int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
     auto* ws = (MinMaxWorkspace*)workspace;
     if (vec_ok && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
