@@ -617,100 +617,57 @@ __device__ __forceinline__ uint32_t pack4_low_bytes(const float (&c)[4]) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(d, e, 0x0040), 0x5410);
 }
 
-// Exact chain for four columns of one row (the rare group the short form could not certify):
-// t = f32(acc - zp * rowsum) * (s_a * s_w) + bias, ReLU, clip(rint(t / s_o) + z_o), every step a
-// separate binary32 operation.  Out of line: it must not weigh on the hot loop.
-struct ExactParams {  // in shared memory, written once per CTA
-  const float* b_scale;
-  const float* bias;
-  const int32_t* b_rowsum;
-  int zpa, relu;
-  float sa, so, zo, fqmin, fqmax;
-};
-__device__ __noinline__ uint32_t requant4_exact(const ExactParams* p, int a0, int a1, int a2, int a3, int col) {
-  // (few scalar arguments: a reference to the kernel's descriptor or a pointer into the caller's
-  // register array would push those into local memory, and a long argument list costs the hot
-  // loop registers at the call site)
-  const int acc4[4] = {a0, a1, a2, a3};
-  const Divisor d = make_divisor(p->so);
-  float y[4], c[4];
+// Four outputs -> four codes without the division: q~ = y * RN(1 / s_o) is within |q| * 2^-23 of
+// the true quotient, so rint(q~) equals rint(RN(y / s_o)) unless q~ lies within that distance of a
+// half-integer.  q~ + 1.5 * 2^23 rounds to the nearest integer (ties to even) in the mantissa;
+// d = q~ - that integer is exact, and |d| <= 0.499 certifies the rounding for every |q~| <= 4096
+// (beyond that the code is clipped either way: the grid and its zero point lie within +-512).
+// Returns false when some element is not certain (NaN included); the caller then takes the
+// exact division for the group.
+__device__ __forceinline__ bool requant4_certain(const float (&y)[4], const RowCtx& rc, float (&c)[4]) {
+  bool ok = true;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    int a = acc4[i];
-    if (p->b_rowsum != nullptr && p->zpa != 0) a -= p->zpa * __ldg(p->b_rowsum + col + i);
-    y[i] = __fmul_rn((float)a, __fmul_rn(p->sa, p->b_scale ? __ldg(p->b_scale + col + i) : 1.0f));
-    if (p->bias != nullptr) y[i] = __fadd_rn(y[i], __ldg(p->bias + col + i));
-    if (p->relu) y[i] = fmaxf(y[i], 0.0f);
+    const float q = __fmul_rn(y[i], rc.so.y);
+    const float n = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+    ok = ok && (fabsf(__fsub_rn(q, n)) <= 0.499f);
+    c[i] = fminf(fmaxf(__fadd_rn(n, rc.zo), rc.fqmin), rc.fqmax);
   }
-  code4_f32(y, d, p->zo, p->fqmin, p->fqmax, c);
-  return pack4_low_bytes(c);
+  return ok;
 }
 
-// round to nearest even and saturate to the 8-bit storage type, one instruction
-__device__ __forceinline__ uint32_t cvt_sat_u8(float q) {
-  uint32_t r;
-  asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(q));
-  return r;
-}
-__device__ __forceinline__ uint32_t cvt_sat_s8(float q) {
-  uint32_t r;
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(q));
-  return r;
-}
-
-// Lean requantising epilogue: 8-bit codes to one destination, tile inside N, per-tensor
-// activation scale.  The reference chain per output is
-//     y = f32(acc) * (s_a * s_w[n]) + b[n];  y = max(y, 0);  code = clip(rint(y / s_o) + z_o)
-// -- four roundings and a division.  Here the per-column constants are folded once per column of
-// tiles into a table in the warp's staging area, T[n] = (s_a * s_w[n]) / s_o and
-// B[n] = b[n] / s_o + z_o, and an output costs
-//     q = fma(f32(acc), T[n], B[n]);   code = cvt.rni.sat(q)       (round, clip, convert: one
-// instruction; the saturation at 0 is also the ReLU on an unsigned grid with z_o = 0)
-// plus a certificate.  With u = 2^-24, the reference's pre-rounding value (plus z_o) and q differ
-// by at most u * (3 |f p| / s_o + 2 |b| / s_o + |B| + 3 |Q| + ...) <= 8 u * (|q| + Bmax), where
-// Bmax bounds |b[n] / s_o| + 2 |z_o| + 1 over the warp's columns; so the two roundings agree
-// unless q lies within that distance of a half-integer: |q - rint(q)| < 0.5 - 6e-7 * (|q| + Bmax)
-// certifies the code (one fused multiply-add and one compare).  Where the bound no longer holds
-// for large |q| both chains saturate to the same end of the grid (the grid and z_o lie within
-// +-512, Bmax <= 4096 + 1025).  A column whose |b / s_o| exceeds 4096 gets T = NaN, which fails
-// every certificate.  A group of four with an uncertified element is redone by requant4_exact:
-// about one group in ten thousand.
-// Every thread stores its 16 finished bytes straight to global memory (its row's next 16 bytes
-// follow one block later, so L2 merges the sectors) -- no staging pass.
-//   SIGNED: storage int8 / uint8.  HAS_ZP: activation zero-point correction (row-sum table).
-//   CLAMP: the grid is narrower than the storage type, or a ReLU has to hold the value at
-//   z_o != 0 (lower bound max(qmin, z_o)): two more min / max per output.
-template <int BN, int PARTS, bool SIGNED, bool HAS_ZP, bool CLAMP>
+// Lean requantising epilogue: 8-bit codes to one destination, tile inside N.  Compared with
+// epilogue_tile: the per-column parameters of the warp's columns are combined once per column
+// of tiles into a table in the warp's staging area (scale product folded when the activation
+// scale is per tensor; `fill` says the warp moved to another column of tiles) and read back with
+// broadcast 16-byte shared loads, the division is replaced by requant4_certain, and every thread
+// stores its 16 finished bytes straight to global memory (its row's next 16 bytes follow one
+// block later, so L2 merges the sectors) -- no staging pass.  What the epilogue descriptor asks
+// for (bias, ReLU, zero-point correction) is a template argument, so the 16-column loop has no
+// branch on it; signed and unsigned grids share one byte pack (the codes are already clipped
+// into their grid, so the low byte of the integer is the code either way).  Taken for a
+// per-tensor activation scale, whose product with the weight scale folds into the table.
+template <int BN, int PARTS, bool HAS_BIAS, bool RELU, bool HAS_ZP>
 __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc, uint32_t taddr, uint8_t* stg,
                                                  int lane, int part, int n0, bool fill, const Partials& ps,
-                                                 int quad, float lo, float hi, const ExactParams* xp) {
+                                                 int quad) {
   constexpr int WCOLS = BN / PARTS;
   constexpr int NB = WCOLS / 16;
   const int c0 = part * WCOLS;
   float* t_scale = reinterpret_cast<float*>(stg);
   float* t_bias = t_scale + WCOLS;
   int* t_rowsum = reinterpret_cast<int*>(t_bias + WCOLS);
-  float* t_margin = reinterpret_cast<float*>(t_rowsum + WCOLS);  // one word: 0.5 - 6e-7 * Bmax
   if (fill) {
     __syncwarp();
-    float bmax = 0.0f;
     for (int j = lane; j < WCOLS; j += 32) {
       const int col = n0 + c0 + j;
       const float sb = ep.b_scale ? __ldg(ep.b_scale + col) : 1.0f;
-      const float t = __fmul_rn(__fmul_rn(rc.sa, sb), rc.so.y);
-      float bq = ep.bias != nullptr ? __fmul_rn(__ldg(ep.bias + col), rc.so.y) : 0.0f;
-      const bool ok = fabsf(bq) <= 4096.0f;
-      if (ok) bmax = fmaxf(bmax, fabsf(bq));
-      bq = __fadd_rn(bq, rc.zo);
-      t_scale[j] = ok ? t : __int_as_float(0x7fc00000);
-      t_bias[j] = bq;
+      t_scale[j] = __fmul_rn(rc.sa, sb);
+      if (HAS_BIAS) t_bias[j] = __ldg(ep.bias + col);
       if (HAS_ZP) t_rowsum[j] = __ldg(ep.b_rowsum + col);
     }
-    bmax = warp_max(bmax);
-    if (lane == 0) *t_margin = 0.5f - 6e-7f * (bmax + 2.0f * fabsf(rc.zo) + 1.0f);
     __syncwarp();
   }
-  const float margin0 = *t_margin;
   const bool row_ok = (rc.row_mask >> lane) & 1u;
   uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
 #pragma unroll 1
@@ -722,33 +679,31 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       const float4 s4 = *reinterpret_cast<const float4*>(t_scale + blk * 16 + 4 * q4);
-      const float4 b4 = *reinterpret_cast<const float4*>(t_bias + blk * 16 + 4 * q4);
-      const float sc[4] = {s4.x, s4.y, s4.z, s4.w}, bq[4] = {b4.x, b4.y, b4.z, b4.w};
-      int a[4];
+      const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+      float y[4];
       if (HAS_ZP) {
         const int4 r4 = *reinterpret_cast<const int4*>(t_rowsum + blk * 16 + 4 * q4);
         const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = (int)acc[4 * q4 + i] - rc.zpa * rs[i];
+        for (int i = 0; i < 4; ++i) y[i] = (float)((int)acc[4 * q4 + i] - rc.zpa * rs[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = (int)acc[4 * q4 + i];
+        for (int i = 0; i < 4; ++i) y[i] = (float)(int)acc[4 * q4 + i];
       }
-      uint32_t code[4];
-      bool certain = true;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float q = __fmaf_rn((float)a[i], sc[i], bq[i]);
-        if (CLAMP) q = fminf(fmaxf(q, lo), hi);
-        certain = certain && (fabsf(__fsub_rn(q, rintf(q))) < __fmaf_rn(fabsf(q), -6e-7f, margin0));
-        code[i] = SIGNED ? cvt_sat_s8(q) : cvt_sat_u8(q);
+      for (int i = 0; i < 4; ++i) y[i] = __fmul_rn(y[i], sc[i]);
+      if (HAS_BIAS) {
+        const float4 b4 = *reinterpret_cast<const float4*>(t_bias + blk * 16 + 4 * q4);
+        y[0] = __fadd_rn(y[0], b4.x), y[1] = __fadd_rn(y[1], b4.y);
+        y[2] = __fadd_rn(y[2], b4.z), y[3] = __fadd_rn(y[3], b4.w);
       }
-      if (certain) {
-        w[q4] = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
-      } else {
-        w[q4] = requant4_exact(xp, (int)acc[4 * q4], (int)acc[4 * q4 + 1], (int)acc[4 * q4 + 2], (int)acc[4 * q4 + 3],
-                               n0 + c0 + blk * 16 + 4 * q4);
+      if (RELU) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] = fmaxf(y[i], 0.0f);
       }
+      float c[4];
+      if (!requant4_certain(y, rc, c)) code4_f32(y, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
+      w[q4] = pack4_low_bytes(c);
     }
     if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
@@ -757,14 +712,13 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
 // Runtime flags -> template arguments (three uniform branches per tile, none per element).
 template <int BN, int PARTS, bool... Fs>
 __device__ __forceinline__ void q8_dispatch(int mask, const Epi& ep, const RowCtx& rc, uint32_t taddr, uint8_t* stg,
-                                            int lane, int part, int n0, bool fill, const Partials& ps, int quad,
-                                            float lo, float hi, const ExactParams* xp) {
+                                            int lane, int part, int n0, bool fill, const Partials& ps, int quad) {
   if constexpr (sizeof...(Fs) == 3) {
-    epilogue_tile_q8<BN, PARTS, Fs...>(ep, rc, taddr, stg, lane, part, n0, fill, ps, quad, lo, hi, xp);
+    epilogue_tile_q8<BN, PARTS, Fs...>(ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
   } else if (mask & 1) {
-    q8_dispatch<BN, PARTS, Fs..., true>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad, lo, hi, xp);
+    q8_dispatch<BN, PARTS, Fs..., true>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
   } else {
-    q8_dispatch<BN, PARTS, Fs..., false>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad, lo, hi, xp);
+    q8_dispatch<BN, PARTS, Fs..., false>(mask >> 1, ep, rc, taddr, stg, lane, part, n0, fill, ps, quad);
   }
 }
 
@@ -829,7 +783,6 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);  // full[S], empty[S], tfull[2], tempty[2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 256);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 260);
-  ExactParams* exact_params = reinterpret_cast<ExactParams*>(tail + 272);  // for requant4_exact
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -862,12 +815,6 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       mbar_init(bar_tempty + 8 * s, (PAIR ? 2 : 1) * EW);
     }
     *abort_flag = 0;
-    exact_params->b_scale = ep.b_scale, exact_params->bias = ep.bias, exact_params->b_rowsum = ep.b_rowsum;
-    exact_params->zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0, exact_params->relu = ep.act == LQ_ACT_RELU ? 1 : 0;
-    exact_params->sa = (ep.a_scale && ep.a_scale_mode != LQ_PER_ROW) ? __ldg(ep.a_scale) : 1.0f;
-    exact_params->so = ep.out_scale ? __ldg(ep.out_scale) : 1.0f;
-    exact_params->zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
-    exact_params->fqmin = (float)ep.qmin, exact_params->fqmax = (float)ep.qmax;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_b) : "memory");
@@ -1015,15 +962,8 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     rc_launch.fqmin = (float)ep.qmin, rc_launch.fqmax = (float)ep.qmax;
     rc_launch.row_mask = 0u, rc_launch.row0 = 0;
     const bool q8_lean_grid = rc_launch.so.fast && fabsf(rc_launch.zo) <= 512.0f;
-    // lean-epilogue variant: signed storage, zero-point correction, explicit clamp (a grid
-    // narrower than its storage type, or a ReLU that has to hold the value at z_o != 0)
-    const bool q8_signed = ep.out_dtype == LQ_S8;
-    const bool q8_relu_floor = ep.act == LQ_ACT_RELU && (q8_signed || rc_launch.zo != 0.0f);
-    const bool q8_narrow = q8_signed ? (ep.qmin != -128 || ep.qmax != 127) : (ep.qmin != 0 || ep.qmax != 255);
-    const float q8_lo = ep.act == LQ_ACT_RELU ? fmaxf(rc_launch.fqmin, rc_launch.zo) : rc_launch.fqmin;
-    const float q8_hi = rc_launch.fqmax;
-    const int q8_mask = (q8_signed ? 1 : 0) | ((ep.b_rowsum != nullptr && rc_launch.zpa != 0) ? 2 : 0) |
-                        ((q8_relu_floor || q8_narrow) ? 4 : 0);
+    const int q8_mask = (ep.bias != nullptr ? 1 : 0) | (ep.act == LQ_ACT_RELU ? 2 : 0) |
+                        ((ep.b_rowsum != nullptr && rc_launch.zpa != 0) ? 4 : 0);
     int q8_filled_tn = -1;  // column of tiles whose parameters this warp's table holds
     // stream-K scratch of this CTA: its slot for a partial tile and its two flag words
     // (arrivals of the writing warps, departures of the reading warps)
@@ -1097,8 +1037,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         } else if (ep.out_dtype == LQ_S32) {
           epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
         } else if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
-          q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad, q8_lo,
-                                 q8_hi, exact_params);
+          q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
           q8_filled_tn = tn_idx;
         } else {
           epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);

@@ -302,3 +302,67 @@ def test_inplace_ops_and_carried_codes():
         stale = qmodel[3](qmodel[1](qmodel[0](x)))  # what consuming the un-rectified codes would give
         assert float((stale - y_ref).abs().mean() / y_ref.abs().mean()) > 0.1
     _sync_status()
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,opad,dil,groups", [
+    (32, 48, 3, 2, 1, 1, 1, 1),    # the usual 2x up-sampling layer
+    (32, 32, 4, 2, 1, 0, 1, 1),    # even kernel
+    (64, 32, 3, 1, 0, 0, 1, 2),    # groups, stride 1
+    (16, 16, 3, 3, 2, 2, 2, 1),    # stride 3, dilation 2
+])
+def test_conv_transpose2d_integer_route(cin, cout, k, stride, pad, opad, dil, groups):
+    """nn.quantized.ConvTranspose2d (lucid/nn/quantized/conv_transpose.py:45-160) on the integer
+    kernel: exact accumulators against the float transposed convolution of the codes evaluated in
+    float64, and the module output against the reference's float route."""
+    import lucid_b200
+
+    torch.manual_seed(cin + k + stride)
+    ct = torch.nn.ConvTranspose2d(cin, cout, k, stride, pad, opad, groups, True, dil).cuda()
+    x = torch.randn(2, cin, 9, 11, device="cuda")
+    xs, xz = Q.calculate_qparams(float(x.min()), float(x.max()), Q.per_tensor_affine, Q.quint8)
+    xin = nnq.Quantize(xs, xz, Q.quint8)(x)
+    obs = Q.MinMaxObserver()
+    obs(ct(xin).detach().contiguous())
+    ct.activation_post_process = obs
+    qm = nnq.ConvTranspose2d.from_float(ct)
+    assert qm._int8_ok()
+    with _CountConvT() as counter:
+        y = qm(xin)
+    _sync_status()
+    assert counter.n == 0 and y.shape == ct(xin).shape
+    # exact integer accumulators: conv_transpose of (codes - zp) with the weight codes, in float64
+    qc = xin._lq_codes
+    a = (qc.codes.double() - float(xz)).permute(0, 3, 1, 2)
+    acc_ref = torch.nn.functional.conv_transpose2d(a, qm.weight_int8.double(), None, stride, pad, opad, groups, dil)
+    wk, rowsum, wscale = qm._weight_krsc()
+    scale_k = (float(xs) * wscale.double()).reshape(1, -1, 1, 1)
+    y_exact = acc_ref * scale_k + qm.bias.double().reshape(1, -1, 1, 1)
+    codes_ref = torch.clamp(torch.round(y_exact / float(qm.scale)) + float(qm.zero_point), 0, 255)
+    got = y._lq_codes.codes.permute(0, 3, 1, 2).double()
+    assert float((got != codes_ref).double().mean()) < 1e-3 and float((got - codes_ref).abs().max()) <= 1
+    lucid_b200.backends.quantized.engine = "reference"
+    try:
+        y_ref = qm(xin)
+    finally:
+        lucid_b200.backends.quantized.engine = "auto"
+    diff = (y - y_ref).abs()
+    assert float((diff > 0).float().mean()) < 1e-3 and float(diff.max()) <= 1.001 * float(qm.scale)
+
+
+class _CountConvT:
+    def __enter__(self):
+        import torch.nn.functional as F
+
+        self.n, self._orig = 0, F.conv_transpose2d
+
+        def counted(*a, **k):
+            self.n += 1
+            return self._orig(*a, **k)
+
+        F.conv_transpose2d = counted
+        return self
+
+    def __exit__(self, *exc):
+        import torch.nn.functional as F
+
+        F.conv_transpose2d = self._orig
