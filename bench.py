@@ -736,9 +736,10 @@ def config_cases(torch, dev, peaks, iters=20):
     """Device-resident timings of BASELINE configurations 2-4 with their own rooflines:
     config 2 dynamic Linear and config 3 gated MLP against the tensor peak, config 4's conv stack
     per layer (the 1x1 layers against HBM with their algorithmic bytes, the 3x3 against the tensor
-    peak).  Timed as a loop of eager calls with CUDA events; inputs rotate where they would
-    otherwise sit in L2 (config 4's activations are a few MB: they are L2-resident between
-    layers by design, as in a real stack)."""
+    peak).  Each is timed as replays of a CUDA graph of the call (device time of its launches) and,
+    beside it, as a loop of eager calls (`eager_ms`: the host's per-call work included).  Config
+    4's activations are a few MB: they are L2-resident between layers by design, as in a real
+    stack."""
     import lucid_b200.nn.quantized as nnq
     from lucid_b200 import _lib
     from lucid_b200.nn.quantized import functional as QF
@@ -758,10 +759,38 @@ def config_cases(torch, dev, peaks, iters=20):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n
 
-    def tensor_block(ms, ops):
+    def graph_timed(fn, n):
+        """The same call captured once in a CUDA graph and replayed: the device time of the
+        launches without the host's per-call work (allocation, ctypes marshalling), which is what
+        bounds the eager loop for the short configurations."""
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph):
+            fn()
+        for _ in range(3):
+            gph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(n):
+            gph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def tensor_block(ms, ops, eager_ms=None):
         t = ops / ms / 1e9
-        return {"ms": ms, "TOPS": t, "bound": "tensor", "peak_TOPS": tensor_peak, "frac": t / tensor_peak,
-                "frac_of_nominal_4500": t / 4500.0}
+        blk = {"ms": ms, "TOPS": t, "bound": "tensor", "peak_TOPS": tensor_peak, "frac": t / tensor_peak,
+               "frac_of_nominal_4500": t / 4500.0}
+        if eager_ms is not None:
+            blk["timing"] = "CUDA-graph replay of the module forward"
+            blk["eager_ms"] = eager_ms
+        return blk
 
     out = {}
     # config 2: dynamic Linear, f32 in/out (range reduction + qparams + u8 encode + GEMM)
@@ -771,7 +800,8 @@ def config_cases(torch, dev, peaks, iters=20):
         lin.bias.copy_(torch.randn(4096, device=dev, generator=g) * 0.01)
     qlin = nnq.dynamic.Linear.from_float(lin)
     x2 = torch.randn(2048, 4096, device=dev, generator=g)
-    out["c2_dynamic_linear"] = tensor_block(timed(lambda: qlin(x2), iters), 2 * 2048 * 4096 * 4096)
+    out["c2_dynamic_linear"] = tensor_block(graph_timed(lambda: qlin(x2), iters), 2 * 2048 * 4096 * 4096,
+                                            timed(lambda: qlin(x2), iters))
     out["c2_dynamic_linear"]["what"] = "module forward: fused min-max + qparams + u8 encode, GEMM with zero-point correction + bias, f32 out"
     del lin, qlin, x2
     # config 3: gated MLP block, bf16
@@ -780,7 +810,8 @@ def config_cases(torch, dev, peaks, iters=20):
                                           torch.randn(ff, d, device=dev, generator=g) * 0.02,
                                           torch.randn(d, ff, device=dev, generator=g) * 0.02)
     x3 = torch.randn(8, 512, d, device=dev, generator=g).to(torch.bfloat16)
-    out["c3_gated_mlp"] = tensor_block(timed(lambda: mlp(x3), iters), 3 * 2 * 4096 * d * ff)
+    out["c3_gated_mlp"] = tensor_block(graph_timed(lambda: mlp(x3), iters), 3 * 2 * 4096 * d * ff,
+                                       timed(lambda: mlp(x3), iters))
     out["c3_gated_mlp"]["what"] = "2 per-token encodes + gate/up GEMM with SiLU-gate epilogue + down GEMM, bf16"
     del mlp, x3
     # config 4: conv stack on codes, fused bias + ReLU + requantise
@@ -803,14 +834,16 @@ def config_cases(torch, dev, peaks, iters=20):
             t = conv(t, wq, ws, b, pad)
         return t
 
-    ms = timed(conv_stack, iters)
+    ms_eager = timed(conv_stack, iters)
+    ms = graph_timed(conv_stack, iters)
     px = n * h * w
     ops = [2 * px * 512 * 256, 2 * px * 9 * 256 * 256, 2 * px * 256 * 1024]
     nbytes = [px * 512 + 512 * 256 + px * 256, px * 256 + 9 * 256 * 256 + px * 256, px * 256 + 256 * 1024 + px * 1024]
-    stack = {"ms": ms, "TOPS": sum(ops) / ms / 1e9, "layers": []}
+    stack = {"ms": ms, "TOPS": sum(ops) / ms / 1e9, "timing": "CUDA-graph replay of the three launches",
+             "eager_ms": ms_eager, "layers": []}
     t = a
     for i, (wq, ws, b, pad) in enumerate(layers):
-        lms = timed(lambda t=t, wq=wq, ws=ws, b=b, pad=pad: conv(t, wq, ws, b, pad), iters)
+        lms = graph_timed(lambda t=t, wq=wq, ws=ws, b=b, pad=pad: conv(t, wq, ws, b, pad), iters)
         if i == 1:
             blk = tensor_block(lms, ops[i])
         else:
@@ -1006,6 +1039,76 @@ def run_single_kernel_case(args):
     return 0
 
 
+def run_tile_sweep(args):
+    """`--case tiles`: the per-rank shard shapes of the workload at 1 / 2 / 4 / 8 ranks (and config
+    2 / 3 shapes) under every forced tile shape and schedule of the contraction (`LQ_GEMM_SHAPE`,
+    `LQ_GEMM_STREAMK`), bf16 epilogue with per-token scales.  The table behind the tile policy."""
+    import torch
+
+    from lucid_b200 import _lib
+    from lucid_b200.nn.quantized import functional as QF
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+
+    def force(shape, sk):
+        for k in ("LQ_GEMM_SHAPE", "LQ_GEMM_STREAMK"):
+            os.environ.pop(k, None)
+        if shape != "auto":
+            os.environ["LQ_GEMM_SHAPE"] = shape
+        if sk is not None:
+            os.environ["LQ_GEMM_STREAMK"] = str(sk)
+        lib.lq_reload_env()
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    shapes = {"qkv_w1": (4096, 10240, 8192), "o_w1": (4096, 8192, 8192), "down_w1": (4096, 8192, 28672),
+              "qkv_w2": (4096, 5120, 8192), "o_w2": (4096, 4096, 8192), "down_w2": (4096, 4096, 28672),
+              "qkv_w4": (4096, 2560, 8192), "o_w4": (4096, 2048, 8192), "down_w4": (4096, 2048, 28672),
+              "qkv_w8": (4096, 1280, 8192), "o_w8": (4096, 1024, 8192), "down_w8": (4096, 1024, 28672),
+              "config2": (2048, 4096, 4096), "config3_down": (4096, 4096, 11008)}
+    variants = [("auto", None), ("pair", 0), ("pair", 1), ("single256", 0), ("single256", 1), ("single128", 0),
+                ("single128", 1)]
+    # about a second of load first: the part is power-capped
+    a = torch.randint(-128, 128, (4096, 8192), dtype=torch.int8, device=dev)
+    b = torch.randint(-128, 128, (8192, 8192), dtype=torch.int8, device=dev)
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < 1.0:
+        QF.gemm_s8(a, b, out_dtype=torch.int32)
+        torch.cuda.synchronize()
+    out = {}
+    for name, (m, n, k) in shapes.items():
+        a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device=dev)
+        b = torch.randint(-128, 128, (n, k), dtype=torch.int8, device=dev)
+        sa, sb = torch.rand(m, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-2
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        row, ref = {}, None
+        for rep in range(2):  # the second pass is the one kept (clocks settled)
+            for shape, sk in variants:
+                force(shape, sk)
+                ms = min(timed(lambda: QF.gemm_s8(a, b, a_scale=sa, b_scale=sb, out=y), args.steps) for _ in range(2))
+                if ref is None:
+                    ref = y.clone()
+                assert torch.equal(y, ref), (name, shape, sk)  # every variant computes the same bits
+                row[shape + ("+streamk" if sk else "")] = {"us": ms * 1e3, "TOPS": 2.0 * m * n * k / ms / 1e9}
+        out[name] = {"shape": [m, n, k], "variants": row}
+    force("auto", None)
+    _lib.check_device_status(dev)
+    print(json.dumps({"case": "tiles", "tiles": out}))
+    return 0
+
+
 def run_config_cases(args):
     """`--case configs`: configurations 2-4 alone (the default run carries the same block)."""
     import torch
@@ -1018,7 +1121,7 @@ def run_config_cases(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs", "histc"])
+    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs", "histc", "tiles"])
     ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm; element count for --case histc")
     ap.add_argument("--epi", default="bf16", choices=["bf16", "u8"], help="epilogue of --case gemm")
     ap.add_argument("--gpus", type=int, default=1)
@@ -1043,6 +1146,8 @@ def main():
         return run_reference_arm(args)
     if args.case == "configs":
         return run_config_cases(args)
+    if args.case == "tiles":
+        return run_tile_sweep(args)
     if args.case != "full":
         return run_single_kernel_case(args)
     return run_b200_arm(args)

@@ -1262,10 +1262,11 @@ struct Knobs {
   int shape = -1, epi_warps = 0, streamk = -1, bcast_epi_warps = 0;
   // policy thresholds: stream-K when the last wave fills less than this percentage of the
   // workers and a tile has at least this many k-blocks.  Measured on the Llama-2-70B shard
-  // shapes: +11 % at 4096 x 4096 x 28672 (34 of 74 clusters in the last wave, 224 k-blocks);
-  // within +-2 % or a loss for tiles of 64 k-blocks, where the partial-tile round trip and the
-  // extra exposed epilogue cost what the evened-out wave saves.
-  int streamk_max_fill = 60, streamk_min_kb = 128;
+  // shapes: +14 % at 4096 x 4096 x 28672 (34 of 74 clusters in the last wave, 224 k-blocks),
+  // +3-4 % with 64-86 k-blocks and a last wave under half full; a loss where the last wave is
+  // mostly full or a run would be a few k-blocks (the partial-tile round trip and the extra
+  // exposed epilogue then cost more than the evened-out wave saves).
+  int streamk_max_fill = 50, streamk_min_kb = 64;
   bool verbose = false;
   void read() {
     shape = -1, epi_warps = 0, streamk = -1, bcast_epi_warps = 0;

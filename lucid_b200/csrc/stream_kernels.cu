@@ -739,6 +739,32 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
 }
 
 
+// (scale, zero_point) of one observed range: the op sequence of calculate_qparams
+// (lucid/quantization/_qparams.py:197-215).
+__device__ __forceinline__ void qparams_one(float mn, float mx, int symmetric, int is_signed, int qmin, int qmax,
+                                            float eps, float* scale, float* zp) {
+  const float lo = fminf(mn, 0.0f), hi = fmaxf(mx, 0.0f);
+  if (symmetric) {
+    const float m = fmaxf(fabsf(lo), fabsf(hi));
+    const float half = (float)((double)(qmax - qmin) / 2.0);
+    *scale = fmaxf(__fdiv_rn(m, half), eps);
+    *zp = is_signed ? 0.0f : (float)((qmax + qmin + 1) / 2);
+  } else {
+    const float s = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), (float)((double)qmax - (double)qmin)), eps);
+    *scale = s;
+    const float t = __fsub_rn((float)qmin, rintf(__fdiv_rn(lo, s)));
+    const float fq0 = (float)qmin, fq1 = (float)qmax;
+    *zp = t < fq0 ? fq0 : (t > fq1 ? fq1 : t);
+  }
+}
+// What the reducing kernel may do with the final range before it returns: derive the grid.
+struct FusedQParams {
+  float* scale;  // null: nothing to derive
+  float* zp;
+  int symmetric, is_signed, qmin, qmax;
+  float eps;
+};
+
 // Order-preserving map of a float onto unsigned integers (and back), so that integer atomics
 // fold float minima / maxima.  -0.0 and +0.0 keep their order.
 __device__ __forceinline__ unsigned int float_key(float f) {
@@ -754,7 +780,8 @@ __device__ __forceinline__ float key_float(unsigned int k) {
 // zero-filled workspace is the identity of both); the CTA that takes the last ticket decodes
 // them and re-arms the workspace.  Min / max are exact in any order.
 __device__ __forceinline__ void finish_tensor_minmax(float mn, float mx, MinMaxWorkspace* ws,
-                                                     float* out_min, float* out_max) {
+                                                     float* out_min, float* out_max,
+                                                     const FusedQParams& fq = FusedQParams{}) {
   block_minmax(mn, mx);
   if (threadIdx.x != 0) return;
   atomicMax(&ws->pad[0], float_key(mx));
@@ -765,17 +792,19 @@ __device__ __forceinline__ void finish_tensor_minmax(float mn, float mx, MinMaxW
   const unsigned int kmax = atomicExch(&ws->pad[0], 0u), kmin = atomicExch(&ws->pad[1], 0u);
   *out_max = key_float(kmax);
   *out_min = key_float(~kmin);
+  if (fq.scale != nullptr)
+    qparams_one(key_float(~kmin), key_float(kmax), fq.symmetric, fq.is_signed, fq.qmin, fq.qmax, fq.eps, fq.scale, fq.zp);
   ws->ticket = 0;  // leave the workspace zeroed for the next call
 }
 
 template <typename In>
 __global__ void __launch_bounds__(kThreads)
 minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWorkspace* ws,
-                     float* out_min, float* out_max) {
+                     float* out_min, float* out_max, FusedQParams fq) {
   float mn = INFINITY, mx = -INFINITY;
   minmax_accumulate(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
                     (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
-  finish_tensor_minmax(mn, mx, ws, out_min, out_max);
+  finish_tensor_minmax(mn, mx, ws, out_min, out_max, fq);
 }
 
 // Per-tensor range reduction through the ring (same partial / ticket scheme as below).
@@ -870,19 +899,7 @@ __global__ void qparams_kernel(const float* __restrict__ mn, const float* __rest
                                float* __restrict__ scale, float* __restrict__ zp) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const float lo = fminf(mn[i], 0.0f), hi = fmaxf(mx[i], 0.0f);
-  if (symmetric) {
-    const float m = fmaxf(fabsf(lo), fabsf(hi));
-    const float half = (float)((double)(qmax - qmin) / 2.0);
-    scale[i] = fmaxf(__fdiv_rn(m, half), eps);
-    zp[i] = is_signed ? 0.0f : (float)((qmax + qmin + 1) / 2);
-  } else {
-    const float s = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), (float)((double)qmax - (double)qmin)), eps);
-    scale[i] = s;
-    const float t = __fsub_rn((float)qmin, rintf(__fdiv_rn(lo, s)));
-    const float fq0 = (float)qmin, fq1 = (float)qmax;
-    zp[i] = t < fq0 ? fq0 : (t > fq1 ? fq1 : t);
-  }
+  qparams_one(mn[i], mx[i], symmetric, is_signed, qmin, qmax, eps, scale + i, zp + i);
 }
 
 // Fused per-token encode: abs-max of the row, symmetric scale, codes.  The row
@@ -1022,6 +1039,45 @@ rowsum_kernel(const int8_t* __restrict__ b, size_t N, size_t K, bool vec_ok,
 using namespace lq;
 
 namespace lq {
+namespace {
+// Per-tensor range reduction (and, optionally, the grid derived from it by the kernel's last
+// CTA): shared by lq_minmax, lq_minmax_noalloc and lq_quantize_dynamic.
+int minmax_tensor_launch(const void* x, int in_dtype, size_t n, MinMaxWorkspace* ws, float* out_min, float* out_max,
+                         const FusedQParams& fq, cudaStream_t st) {
+  const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
+  const bool vec_ok = aligned16(x);
+  // two packets per thread-iteration; grid in multiples of the SM count
+  size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
+  const size_t gcap = (size_t)sm_count() * stream_knobs().minmax_ctas_per_sm;
+  int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
+  if (vec_ok && fq.scale == nullptr && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
+    // bulk-copy ring variant (kept for comparison; the register-staged kernel is faster)
+    constexpr int stages = kRingBytes / kChunkBytes;
+    constexpr size_t smem = kRingHeader + kRingBytes;
+    static PerDeviceOnce once;
+    const cudaError_t attr = once.run([&] {
+      const cudaError_t a32 = enable_ring(minmax_pipe_kernel<float>, smem);
+      return a32 != cudaSuccess ? a32 : enable_ring(minmax_pipe_kernel<__nv_bfloat16>, smem);
+    });
+    if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
+    const size_t nchunks = (n * esz + kChunkBytes - 1) / kChunkBytes;
+    const size_t pcap = (size_t)sm_count() * 3;
+    const int pgrid = (int)(nchunks < pcap ? nchunks : pcap);
+    if (in_dtype == LQ_F32)
+      minmax_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, n, ws, out_min, out_max, stages);
+    else
+      minmax_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, n, ws, out_min, out_max, stages);
+  } else if (in_dtype == LQ_F32) {
+    minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max, fq);
+  } else {
+    minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max, fq);
+  }
+  return check_cuda(cudaGetLastError(), "range reduction launch");
+}
+}  // namespace
+}  // namespace lq
+
+namespace lq {
 void reload_stream_knobs() { stream_knobs().read(); }
 }  // namespace lq
 
@@ -1052,34 +1108,9 @@ extern "C" int lq_minmax(const void* x, int in_dtype, size_t rows, size_t cols, 
     if (workspace_bytes < sizeof(MinMaxWorkspace))
       return fail(LQ_ERR_WORKSPACE, "lq_minmax: workspace smaller than lq_minmax_workspace_bytes()");
     if (!aligned16(workspace)) return fail(LQ_ERR_ALIGNMENT, "lq_minmax: workspace alignment");
-    const size_t n = rows * cols;
-    const bool vec_ok = aligned16(x);
-    // two packets per thread-iteration; grid in multiples of the SM count
-    size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
-    const size_t gcap = (size_t)sm_count() * stream_knobs().minmax_ctas_per_sm;
-    int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
-    auto* ws = (MinMaxWorkspace*)workspace;
-    if (vec_ok && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
-      // bulk-copy ring variant (kept for comparison; the register-staged kernel is faster)
-      constexpr int stages = kRingBytes / kChunkBytes;
-      constexpr size_t smem = kRingHeader + kRingBytes;
-      static PerDeviceOnce once;
-      const cudaError_t attr = once.run([&] {
-        const cudaError_t a32 = enable_ring(minmax_pipe_kernel<float>, smem);
-        return a32 != cudaSuccess ? a32 : enable_ring(minmax_pipe_kernel<__nv_bfloat16>, smem);
-      });
-      if (attr != cudaSuccess) return check_cuda(attr, "cudaFuncSetAttribute(ring)");
-      const size_t nchunks = (n * esz + kChunkBytes - 1) / kChunkBytes;
-      const size_t pcap = (size_t)sm_count() * 3;
-      const int pgrid = (int)(nchunks < pcap ? nchunks : pcap);
-      if (in_dtype == LQ_F32)
-        minmax_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, n, ws, out_min, out_max, stages);
-      else
-        minmax_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, n, ws, out_min, out_max, stages);
-    } else if (in_dtype == LQ_F32)
-      minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max);
-    else
-      minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max);
+    const int rc = minmax_tensor_launch(x, in_dtype, rows * cols, (MinMaxWorkspace*)workspace, out_min, out_max,
+                                        FusedQParams{}, st);
+    if (rc != LQ_OK) return rc;
   } else if (mode == LQ_PER_ROW) {
     const bool vec_ok = aligned16(x) && ((cols * esz) % 16 == 0);
     if (cols <= 2048) {
@@ -1287,16 +1318,7 @@ extern "C" int lq_minmax_noalloc(const void* x, int in_dtype, size_t n, float* o
   cudaStream_t st = (cudaStream_t)stream;
   // the array keeps whatever the previous call left: re-arm the arrival counter
   LQ_CUDA(cudaMemsetAsync(scratch, 0, 16, st));
-  const bool vec_ok = aligned16(x);
-  size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
-  const size_t gcap = (size_t)sm_count() * 4;
-  int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
-  auto* ws = (MinMaxWorkspace*)scratch;
-  if (in_dtype == LQ_F32)
-    minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max);
-  else
-    minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max);
-  return check_cuda(cudaGetLastError(), "lq_minmax_noalloc launch");
+  return minmax_tensor_launch(x, in_dtype, n, (MinMaxWorkspace*)scratch, out_min, out_max, FusedQParams{}, st);
 }
 
 // Dynamic per-tensor encode in one call: range reduction -> qparams -> codes (three launches,
@@ -1307,11 +1329,19 @@ extern "C" int lq_quantize_dynamic(const void* x, int in_dtype, size_t rows, siz
                                    float* out_zp, float* out_minmax, void* stream) {
   if (rows == 0 || cols == 0) return fail(LQ_ERR_SHAPE, "lq_quantize_dynamic: empty input has no range");
   if (!out_scale || !out_zp || !out_minmax) return fail(LQ_ERR_DEVICE, "lq_quantize_dynamic: null pointer");
-  int rc = lq_minmax(x, in_dtype, 1, rows * cols, LQ_PER_TENSOR, out_minmax, out_minmax + 1, workspace,
-                     workspace_bytes, stream);
-  if (rc != LQ_OK) return rc;
-  rc = lq_calculate_qparams(out_minmax, out_minmax + 1, 1, symmetric, is_signed, qmin, qmax, eps, out_scale,
-                            out_zp, stream);
+  if (!x) return fail(LQ_ERR_DEVICE, "lq_quantize_dynamic: null pointer");
+  if (in_dtype != LQ_F32 && in_dtype != LQ_BF16) return fail(LQ_ERR_DTYPE, "lq_quantize_dynamic: in_dtype");
+  if (qmax <= qmin) return fail(LQ_ERR_SHAPE, "lq_quantize_dynamic: qmax must exceed qmin");
+  if (!workspace) return fail(LQ_ERR_DEVICE, "lq_quantize_dynamic: needs the range-reduction workspace");
+  if (workspace_bytes < sizeof(MinMaxWorkspace))
+    return fail(LQ_ERR_WORKSPACE, "lq_quantize_dynamic: workspace smaller than lq_minmax_workspace_bytes()");
+  if (!aligned16(workspace)) return fail(LQ_ERR_ALIGNMENT, "lq_quantize_dynamic: workspace alignment");
+  // two launches: the range reduction, whose last CTA also derives (scale, zero_point), and the encode
+  FusedQParams fq;
+  fq.scale = out_scale, fq.zp = out_zp, fq.symmetric = symmetric, fq.is_signed = is_signed;
+  fq.qmin = qmin, fq.qmax = qmax, fq.eps = eps;
+  int rc = minmax_tensor_launch(x, in_dtype, rows * cols, (MinMaxWorkspace*)workspace, out_minmax, out_minmax + 1, fq,
+                                (cudaStream_t)stream);
   if (rc != LQ_OK) return rc;
   return lq_quantize(x, in_dtype, rows, cols, out_scale, out_zp, 0.0f, 0.0f, LQ_PER_TENSOR, qmin, qmax, out,
                      out_dtype, stream);
