@@ -944,9 +944,16 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
             # a quantized activation on 8-bit codes: one table lookup per byte
             _lib.check(lib.lq_lut_u8(_lib.ptr(qs[j]), n * n, _lib.ptr(table), _lib.ptr(q2[j % 2]), _lib.stream_ptr(dev)))
 
+        fq_out = [torch.empty(n, n, device=dev) for _ in range(2)]
+
+        def f_fake(j):
+            # the QAT forward on an activation: snap to the grid, float out (no mask)
+            _lib.check(lib.lq_fake_quantize(_lib.ptr(xs[j]), n, n, None, None, 0.03, 0.0, 0, -128, 127,
+                                            _lib.ptr(fq_out[j % 2]), None, _lib.stream_ptr(dev)))
+
         block = {}
         # dequantize last: it overwrites the normal samples with 255 grid values
-        for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("minmax_f32", f_minmax, 4),
+        for name, fn, bpe in (("quantize_f32_s8", f_quant, 5), ("fake_quantize_f32", f_fake, 8), ("minmax_f32", f_minmax, 4),
                               ("histogram_observe_f32", f_hist, 4), ("qmerge_add_relu_s8", f_merge, 3),
                               ("qmerge_add_relu_s8_table", f_merge_table, 3), ("lut_activation_u8", f_lut, 2), ("dequantize_s8_f32", f_dequant, 5)):
             sec = graph_time(fn, sets, reps)
@@ -954,8 +961,26 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
             block[name] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
                            "frac_of_nominal_8000": gbs / 8000.0}
         out[label] = block
-        del xs, qs, q2
-    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 4 B/elem range and histogram, 3 B/elem code merge, 2 B/elem table lookup)"
+        del xs, qs, q2, fq_out
+    # the per-token encodes of the timed step (bf16 rows in, s8 codes + one f32 scale per row out)
+    block = {}
+    for cols, sets in ((8192, 4), (28672, 2)):
+        rows = 4096
+        xs = [torch.randn(rows, cols, device=dev).to(torch.bfloat16) for _ in range(sets)]
+        qs = [torch.empty(rows, cols, dtype=torch.int8, device=dev) for _ in range(sets)]
+        ss = [torch.empty(rows, dtype=torch.float32, device=dev) for _ in range(sets)]
+
+        def f_token(j):
+            _lib.check(lib.lq_quantize_per_token(_lib.ptr(xs[j]), _lib.BF16, rows, cols, -128, 127, 1e-8,
+                                                 _lib.ptr(qs[j]), _lib.ptr(ss[j]), _lib.stream_ptr(dev)))
+
+        sec = graph_time(f_token, sets, iters)
+        gbs = (rows * cols * 3 + rows * 4) / sec / 1e9
+        block[f"{rows}x{cols}"] = {"us": sec * 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                   "frac_of_nominal_8000": gbs / 8000.0}
+        del xs, qs, ss
+    out["per_token_bf16_s8"] = block
+    out["how"] = "CUDA-graph replays over rotating buffer sets larger than L2; bytes = algorithmic (5 B/elem encode/decode, 8 B/elem fake-quantize, 4 B/elem range and histogram, 3 B/elem code merge, 2 B/elem table lookup, 3 B/elem per-token encode)"
     return out
 
 

@@ -67,7 +67,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {s}")
     for lib, sources, defs, tag in todo:
         objs = [obj for l, s, obj, p in procs if l == lib]
-        subprocess.check_call([nvcc, "-arch=sm_100a", "-shared", "-o", lib, *objs, "-lcudart"])
+        # link beside the target and rename, so a reader never sees a half-written library
+        tmp = lib + ".tmp"
+        subprocess.check_call([nvcc, "-arch=sm_100a", "-shared", "-o", tmp, *objs, "-lcudart"])
+        os.replace(tmp, lib)
     return LIB
 
 

@@ -92,6 +92,45 @@ __device__ __forceinline__ float div_rn(float x, const Divisor& d) {
   return div_full(x, d.s);
 }
 
+// Two-wide float arithmetic (sm_100 packed f32x2 instructions): one issue slot carries two
+// multiply-adds, each rounded exactly like its scalar form.  The stream encodes are issue-bound,
+// so halving the slots of the division chain is what these buy.
+struct F2 {
+  unsigned long long b;
+};
+__device__ __forceinline__ F2 f2_pack(float lo, float hi) {
+  F2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.b) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(F2 a, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.b));
+}
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+  F2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.b) : "l"(a.b), "l"(b.b));
+  return r;
+}
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
+  F2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.b) : "l"(a.b), "l"(b.b));
+  return r;
+}
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+  F2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.b) : "l"(a.b), "l"(b.b), "l"(c.b));
+  return r;
+}
+// The short division of div_rn4 on a pair: x * y corrected twice by the residual (`ns` = -s).
+// Returns the quotient pair; `q0` receives the first estimate (the domain check reads it).
+__device__ __forceinline__ F2 f2_div_short(F2 x, F2 y, F2 ns, F2& q0) {
+  q0 = f2_mul(x, y);
+  F2 r = f2_fma(q0, ns, x);
+  const F2 q1 = f2_fma(r, y, q0);
+  r = f2_fma(q1, ns, x);
+  return f2_fma(r, y, q1);
+}
+
 // Four quotients by the same divisor.  The short form runs unconditionally on all four (no
 // per-element branch, so the four dependency chains overlap); the rare elements outside its
 // domain are redone with the full-range division afterwards.
@@ -177,6 +216,33 @@ __device__ __forceinline__ void code4_int(const float (&x)[4], const Divisor& d,
       const float t = __fadd_rn(rintf(q[i]), z);
       c[i] = __float2int_rz(t < qmin ? qmin : (t > qmax ? qmax : t));
     }
+  }
+}
+// code4_int without the domain check, on the packed pipe: for callers that know every quotient is
+// below 2^22 in magnitude (a per-token symmetric encode: |x| <= abs-max = s * half) and whose
+// divisor is in the short division's range (d.fast) with an integral zero point (g.fast).
+struct ShortDiv {
+  F2 y2, ns2;
+};
+__device__ __forceinline__ ShortDiv make_short_div(const Divisor& d) {
+  ShortDiv sd;
+  sd.y2 = f2_pack(d.y, d.y), sd.ns2 = f2_pack(-d.s, -d.s);
+  return sd;
+}
+__device__ __forceinline__ void code4_short(const float (&x)[4], const ShortDiv& sd, const IntGrid& g, int (&c)[4]) {
+  const F2 magic2 = f2_pack(12582912.0f, 12582912.0f);
+#pragma unroll
+  for (int i = 0; i < 4; i += 2) {
+    F2 q0;
+    const F2 qq = f2_div_short(f2_pack(x[i], x[i + 1]), sd.y2, sd.ns2, q0);
+    float t0, t1;
+    f2_unpack(f2_add(qq, magic2), t0, t1);
+    c[i] = __float_as_int(t0) + g.zofs;
+    c[i + 1] = __float_as_int(t1) + g.zofs;
+  }
+  if (g.clamp) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = min(max(c[i], g.qmin), g.qmax);
   }
 }
 // four ints -> four packed 8-bit codes (saturating to the storage type)

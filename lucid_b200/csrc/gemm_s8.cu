@@ -1569,11 +1569,13 @@ using namespace lq;
 
 namespace lq {
 void reload_stream_knobs();
+void reload_hist_knobs();
 }
 extern "C" void lq_reload_env(void) {
   knobs_storage().read();
 #ifndef LQ_TESTING  // the test-only library holds the contraction alone
   lq::reload_stream_knobs();
+  lq::reload_hist_knobs();
 #endif
 }
 

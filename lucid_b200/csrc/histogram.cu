@@ -610,6 +610,11 @@ observe_pass2(const In* __restrict__ x, size_t n, bool vec_ok, int bins, bool al
 }
 
 }  // namespace
+// LQ_HIST_BINARY64 (diagnostic: force the binary64 binning tier), read once and again by
+// lq_reload_env().
+static bool g_hist_binary64 = getenv("LQ_HIST_BINARY64") != nullptr;
+static bool hist_force_binary64() { return g_hist_binary64; }
+void reload_hist_knobs() { g_hist_binary64 = getenv("LQ_HIST_BINARY64") != nullptr; }
 }  // namespace lq
 
 using namespace lq;
@@ -650,7 +655,7 @@ extern "C" int lq_histogram_observe(const void* x, int in_dtype, size_t n, int b
   if (!min_val || !max_val || !hist) return fail(LQ_ERR_DEVICE, "lq_histogram_observe: null state pointer");
   const size_t esz = in_dtype == LQ_F32 ? 4 : 2;
   const bool vec_ok = aligned16(x);
-  const bool allow_tier1 = !getenv("LQ_HIST_BINARY64");
+  const bool allow_tier1 = !hist_force_binary64();
   const int grid = hist_grid(n, esz);
   const size_t smem = hist_smem_bytes(bins);
   auto* ws = (HistWorkspace*)workspace;
@@ -685,7 +690,7 @@ extern "C" int lq_histc(const void* x, int in_dtype, size_t n, double lo, double
                               "range from the data, as the reference's histc does)");
 
   HistArgs a{};
-  if (!derive_binning(lo, hi, bins, !getenv("LQ_HIST_BINARY64"), a))
+  if (!derive_binning(lo, hi, bins, !hist_force_binary64(), a))
     return fail(LQ_ERR_SHAPE, "lq_histc: (hi - lo) / bins is not a positive finite number");
   a.prev = prev_hist;
   a.out = hist_out;

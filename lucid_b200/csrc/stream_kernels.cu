@@ -324,30 +324,42 @@ __device__ __forceinline__ Divisor group_divisor(float s) {
 }
 
 // Vector kernel: kUnroll coalesced 4-element groups per thread-iteration, grid-stride.
-template <Op OP, typename In, typename Out, bool MASK, int kUnroll, int kMinBlocks>
+// MODE = LQ_PER_TENSOR compiles the per-tensor case on its own (parameters, divisor and integer
+// grid live in registers for the whole thread; a group costs its load, the arithmetic and its
+// store), MODE < 0 reads the mode at run time.  The encode is issue-bound, so the instructions a
+// group does not need are what the specialisation buys.
+template <Op OP, typename In, typename Out, bool MASK, int kUnroll, int kMinBlocks, int MODE>
 __global__ void __launch_bounds__(kThreads, kMinBlocks)
 affine_vec_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __restrict__ mask,
                   size_t rows, size_t cols, QParamRef q, float qmin, float qmax) {
+  const int mode = MODE >= 0 ? MODE : q.mode;
   const size_t ngroups = rows * cols / 4;
   const size_t span = (size_t)kThreads * kUnroll;
-  Divisor dt = group_divisor<OP>(1.0f);
-  if (q.mode == LQ_PER_TENSOR) dt = group_divisor<OP>(q.s != nullptr ? __ldg(q.s) : q.sv);
-  const IntGrid igt = make_int_grid(q.mode == LQ_PER_TENSOR ? (q.z != nullptr ? __ldg(q.z) : q.zv) : 0.0f, qmin, qmax,
-                                    StoreRange<Out>::lo, StoreRange<Out>::hi);
+  float st = 1.0f, zt = 0.0f;
+  if (mode == LQ_PER_TENSOR) {
+    st = q.s != nullptr ? __ldg(q.s) : q.sv;
+    zt = q.z != nullptr ? __ldg(q.z) : q.zv;
+  }
+  const Divisor dt = group_divisor<OP>(st);
+  const IntGrid igt = make_int_grid(zt, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
   for (size_t base = (size_t)blockIdx.x * span; base < ngroups; base += (size_t)gridDim.x * span) {
+    // one pointer per stream; the groups of a thread sit at compile-time offsets from it
+    const size_t g0 = base + threadIdx.x;
+    const In* xp = x + g0 * 4;
+    Out* op = out + g0 * 4;
+    const bool whole = base + span <= ngroups;
     float v[kUnroll][4];
-    size_t gidx[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (whole || g0 + (size_t)u * kThreads < ngroups) Quad<In>::load(xp + (size_t)u * kThreads * 4, v[u]);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      gidx[u] = base + (size_t)u * kThreads + threadIdx.x;
-      if (gidx[u] < ngroups) Quad<In>::load(x + gidx[u] * 4, v[u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      if (gidx[u] >= ngroups) continue;
-      float s[4], z[4], m[4];
-      quad_params(q, gidx[u] * 4, cols, s, z);
-      if (q.mode == LQ_PER_COL) {
+      if (!whole && g0 + (size_t)u * kThreads >= ngroups) continue;
+      constexpr size_t kStep = (size_t)kThreads * 4;
+      float m[4];
+      if (mode == LQ_PER_COL) {
+        float s[4], z[4];
+        quad_params(q, (g0 + (size_t)u * kThreads) * 4, cols, s, z);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           Divisor d;
@@ -356,19 +368,116 @@ affine_vec_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __rest
           v[u][i] = apply<OP>(v[u][i], d, z[i], qmin, qmax, MASK ? &m[i] : nullptr);
         }
       } else {
-        const Divisor d = q.mode == LQ_PER_TENSOR ? dt : group_divisor<OP>(s[0]);
+        Divisor d = dt;
+        IntGrid ig = igt;
+        float z0 = zt;
+        if (mode != LQ_PER_TENSOR) {
+          float s[4], z[4];
+          quad_params(q, (g0 + (size_t)u * kThreads) * 4, cols, s, z);
+          d = group_divisor<OP>(s[0]);
+          z0 = z[0];
+          if (OP == Op::kQuantize) ig = make_int_grid(z0, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
+        }
         if (OP == Op::kQuantize) {
-          const IntGrid ig = q.mode == LQ_PER_TENSOR ? igt : make_int_grid(z[0], qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
           int c[4];
-          code4_int(v[u], d, ig, z[0], qmin, qmax, c);
-          store_codes(out + gidx[u] * 4, c);
+          code4_int(v[u], d, ig, z0, qmin, qmax, c);
+          store_codes(op + u * kStep, c);
           continue;
         }
-        apply4<OP, MASK>(v[u], d, z[0], qmin, qmax, m);
+        apply4<OP, MASK>(v[u], d, z0, qmin, qmax, m);
       }
-      Quad<Out>::store(out + gidx[u] * 4, v[u]);
-      if (MASK) Quad<float>::store(mask + gidx[u] * 4, m);
+      Quad<Out>::store(op + u * kStep, v[u]);
+      if (MASK) Quad<float>::store(mask + g0 * 4 + u * kStep, m);
     }
+  }
+}
+
+// Per-tensor encode, the lean form.  The encode is issue-bound, so a group costs only its
+// load, five multiply-adds per element (reciprocal estimate + two correction steps = the correctly
+// rounded quotient), the magic-number rounding and its store.  An element outside the short
+// division's domain (|q| >= 2^22, infinity, NaN) only raises a flag; the thread then redoes its
+// whole span through the full-range sequence, out of line and from memory, so that the hot loop
+// keeps no registers alive for the rare case.
+template <typename In, typename Out>
+static __device__ __noinline__ void encode_span_full(const In* __restrict__ x, Out* __restrict__ out, size_t g0,
+                                                     size_t ngroups, int unroll, const float* sp, const float* zp,
+                                                     float sv, float zv, float qmin, float qmax) {
+  const float z = zp != nullptr ? __ldg(zp) : zv;
+  Divisor d;
+  d.s = sp != nullptr ? __ldg(sp) : sv, d.y = 0.0f, d.fast = false;
+  for (int u = 0; u < unroll; ++u) {
+    const size_t g = g0 + (size_t)u * kThreads;
+    if (g >= ngroups) break;
+    for (int i = 0; i < 4; ++i) {
+      const size_t e = g * 4 + i;
+      Packet<Out>::store1(out + e, apply<Op::kQuantize>(Packet<In>::load1(x + e), d, z, qmin, qmax, nullptr));
+    }
+  }
+}
+
+template <typename In, typename Out, int kUnroll, int kMinBlocks, bool PACKED>
+__global__ void __launch_bounds__(kThreads, kMinBlocks)
+quantize_tensor_kernel(const In* __restrict__ x, Out* __restrict__ out, size_t ngroups, QParamRef q, float qmin,
+                       float qmax) {
+  const Divisor d = make_divisor(q.s != nullptr ? __ldg(q.s) : q.sv);
+  const IntGrid ig = make_int_grid(q.z != nullptr ? __ldg(q.z) : q.zv, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
+  const bool lean = d.fast && ig.fast;
+  constexpr size_t kSpan = (size_t)kThreads * kUnroll;
+  constexpr size_t kStep = (size_t)kThreads * 4;
+  for (size_t base = (size_t)blockIdx.x * kSpan; base < ngroups; base += (size_t)gridDim.x * kSpan) {
+    const size_t g0 = base + threadIdx.x;
+    bool bad = !lean;
+    if (lean) {
+      const In* xp = x + g0 * 4;
+      Out* op = out + g0 * 4;
+      const bool whole = base + kSpan <= ngroups;
+      float v[kUnroll][4];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (whole || g0 + (size_t)u * kThreads < ngroups) Quad<In>::load(xp + u * kStep, v[u]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (!whole && g0 + (size_t)u * kThreads >= ngroups) continue;
+        int c[4];
+        if (PACKED) {
+          const F2 y2 = f2_pack(d.y, d.y), ns2 = f2_pack(-d.s, -d.s), magic2 = f2_pack(12582912.0f, 12582912.0f);
+          float big = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 4; i += 2) {
+            F2 q0;
+            const F2 qq = f2_div_short(f2_pack(v[u][i], v[u][i + 1]), y2, ns2, q0);
+            float a, b, t0, t1;
+            f2_unpack(q0, a, b);
+            // (a NaN input is out of contract -- the reference's integer cast of it is undefined --
+            // and is the one value this maximum does not see)
+            big = fmaxf(big, fmaxf(fabsf(a), fabsf(b)));
+            f2_unpack(f2_add(qq, magic2), t0, t1);
+            c[i] = __float_as_int(t0) + ig.zofs;
+            c[i + 1] = __float_as_int(t1) + ig.zofs;
+          }
+          bad |= !(big < 0x1p22f);
+          if (ig.clamp) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[i] = min(max(c[i], ig.qmin), ig.qmax);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float q0 = __fmul_rn(v[u][i], d.y);
+            float r = __fmaf_rn(-q0, d.s, v[u][i]);
+            const float q1 = __fmaf_rn(r, d.y, q0);
+            r = __fmaf_rn(-q1, d.s, v[u][i]);
+            const float qq = __fmaf_rn(r, d.y, q1);
+            bad |= !(fabsf(q0) < 0x1p22f);
+            int t = __float_as_int(__fadd_rn(qq, 12582912.0f)) + ig.zofs;
+            if (ig.clamp) t = min(max(t, ig.qmin), ig.qmax);
+            c[i] = t;
+          }
+        }
+        store_codes(op + u * kStep, c);
+      }
+    }
+    if (bad) encode_span_full(x, out, g0, ngroups, kUnroll, q.s, q.z, q.sv, q.zv, qmin, qmax);
   }
 }
 
@@ -411,9 +520,16 @@ int make_params(const float* scale, const float* zp, float sv, float zv, int ch_
 
 // tuning knobs of the stream kernels (environment, read once; lq_reload_env re-reads)
 struct StreamKnobs {
-  int ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4;
+  int ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4, lean = 1, minmax_pipe = 0;
+  int token_pipe_min_row = 16 * 1024, token_ring_kb = 0, token_reg_threads = 256;
   void read() {
-    ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4;
+    ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4, lean = 1, minmax_pipe = 0;
+    token_pipe_min_row = 16 * 1024, token_ring_kb = 0, token_reg_threads = 256;
+    if (const char* e = getenv("LQ_TOKEN_REG_THREADS")) token_reg_threads = atoi(e) == 128 ? 128 : 256;
+    if (const char* e = getenv("LQ_TOKEN_PIPE_MIN_ROW")) token_pipe_min_row = atoi(e);
+    if (const char* e = getenv("LQ_TOKEN_RING_KB")) token_ring_kb = atoi(e) > 0 && atoi(e) <= 96 ? atoi(e) : 0;
+    if (const char* e = getenv("LQ_MINMAX_PIPE")) minmax_pipe = atoi(e);
+    if (const char* e = getenv("LQ_QUANT_LEAN")) lean = atoi(e);
     if (const char* e = getenv("LQ_QUANT_CTAS_PER_SM")) ctas_per_sm = atoi(e);
     if (const char* e = getenv("LQ_QUANT_UNROLL")) unroll = atoi(e) == 2 ? 2 : 4;
     if (const char* e = getenv("LQ_MINMAX_CTAS_PER_SM")) minmax_ctas_per_sm = atoi(e) > 0 ? atoi(e) : 4;
@@ -459,6 +575,32 @@ __device__ __forceinline__ void vec_minmax<__nv_bfloat16>(uint4 u, float& mn, fl
     mx = fmaxf(mx, fmaxf(a, b));
   }
 }
+
+// Abs-max over 16-byte vectors.  bf16 stays packed: the sign bits are masked off and pairs are
+// folded with the two-wide bf16 maximum (one mask + one maximum per two elements).
+template <typename In>
+struct AbsMax;
+template <>
+struct AbsMax<float> {
+  float m = 0.0f;
+  __device__ __forceinline__ void add(uint4 u) {
+    const float a = __uint_as_float(u.x), b = __uint_as_float(u.y), c = __uint_as_float(u.z), d = __uint_as_float(u.w);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(a), fabsf(b)), fmaxf(fabsf(c), fabsf(d))));
+  }
+  __device__ __forceinline__ float get() const { return m; }
+};
+template <>
+struct AbsMax<__nv_bfloat16> {
+  uint32_t m = 0u;
+  __device__ __forceinline__ void add(uint4 u) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) asm("max.bf16x2 %0, %0, %1;" : "+r"(m) : "r"(w[j] & 0x7fff7fffu));
+  }
+  __device__ __forceinline__ float get() const {
+    return fmaxf(bf16_bits_to_f32(m & 0xffffu), bf16_bits_to_f32(m >> 16));
+  }
+};
 
 // x[0..n): lane `first` of `stride` cooperating threads.  16-byte vectors, consecutive
 // threads on consecutive vectors, four loads in flight per thread.
@@ -713,24 +855,32 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
     const int grid = (int)(nchunks < cap ? nchunks : cap);
     kernel<<<grid, kThreads, smem, st>>>((const In*)x, (Out*)out, mask, n, cols, q, (float)qmin, (float)qmax, stages);
   } else if (vec) {
-    // 4 groups per thread at full occupancy (32 registers): measured fastest on B200 -- the
-    // encode is latency-bound, so resident warps matter more than loads in flight per thread
+    // 4 groups per thread at full occupancy (32 registers): measured fastest on B200
     const StreamKnobs& kn = stream_knobs();
-    if (kn.ctas_per_sm > 0) {
-      // persistent, grid-stride: every CTA slot of the GPU gets one CTA that walks the tensor in
-      // steps of the whole grid, so the last wave is full and the DRAM front still advances in order
-      const size_t spans = kn.unroll == 2 ? (n / 4 + 1) / 2 : (n / 4 + 3) / 4;
-      const int grid = grid_for(spans, (size_t)kn.ctas_per_sm);
-      if (kn.unroll == 2)
-        affine_vec_kernel<OP, In, Out, MASK, 2, 8><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, cols, q,
-                                                                           (float)qmin, (float)qmax);
-      else
-        affine_vec_kernel<OP, In, Out, MASK, 4, 8><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, cols, q,
-                                                                           (float)qmin, (float)qmax);
-    } else {
-      affine_vec_kernel<OP, In, Out, MASK, 4, 8><<<grid_for((n / 4 + 3) / 4), kThreads, 0, st>>>(
-          (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
+    const size_t groups = n / 4;
+    const int unroll = kn.unroll == 2 ? 2 : 4;
+    const size_t spans = (groups + unroll - 1) / unroll;
+    const int grid = kn.ctas_per_sm > 0 ? grid_for(spans, (size_t)kn.ctas_per_sm) : grid_for(spans);
+    const bool tensor = q.mode == LQ_PER_TENSOR;
+    if (kn.lean && OP == Op::kQuantize && tensor && !MASK && StoreRange<Out>::lo != StoreRange<Out>::hi) {
+      // measured on B200 (config 1, 64 MB): 4 groups per thread at 6 CTAs/SM (40 registers, no
+      // spill) 14.6 us; at 8 CTAs/SM (32 registers, 32 B spilled) 15.4 us; scalar multiply-adds
+      // instead of the packed ones 15.4 us; the run-time-mode kernel 17.2 us
+      quantize_tensor_kernel<In, Out, 4, 6, true><<<grid_for((groups + 3) / 4), kThreads, 0, st>>>(
+          (const In*)x, (Out*)out, groups, q, (float)qmin, (float)qmax);
+      return check_cuda(cudaGetLastError(), "affine kernel launch");
     }
+#define LQ_LAUNCH_VEC(U, M)                                                                              \
+  affine_vec_kernel<OP, In, Out, MASK, U, 8, M><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, \
+                                                                           cols, q, (float)qmin, (float)qmax)
+    if (unroll == 2) {
+      if (tensor) LQ_LAUNCH_VEC(2, LQ_PER_TENSOR);
+      else LQ_LAUNCH_VEC(2, -1);
+    } else {
+      if (tensor) LQ_LAUNCH_VEC(4, LQ_PER_TENSOR);
+      else LQ_LAUNCH_VEC(4, -1);
+    }
+#undef LQ_LAUNCH_VEC
   } else {
     affine_scalar_kernel<OP, In, Out, MASK><<<grid_for(n), kThreads, 0, st>>>(
         (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax);
@@ -840,11 +990,21 @@ per_token_pipe_kernel(const In* __restrict__ x, size_t rows, size_t cols, float 
   const uint32_t row_bytes = (uint32_t)(cols * sizeof(In));
   const bool ok = run_chunks(reinterpret_cast<const uint8_t*>(x), rows * (size_t)row_bytes, row_bytes, stages, ring,
                              [&](uint32_t slot, size_t r, uint32_t) {
-    float mn = INFINITY, mx = -INFINITY;
-    smem_vec_minmax<In>(slot, row_bytes, threadIdx.x, kThreads, mn, mx);
-    block_minmax(mn, mx);
+    constexpr uint32_t E = VecOf<In>::kElems;
+    const uint32_t nvec = row_bytes / 16;
+    AbsMax<In> am;
+    for (uint32_t i = threadIdx.x; i < nvec; i += kThreads) am.add(lds_u4(slot + i * 16));
+    float m = am.get();
+    // cols % 4 == 0: at most one 4-element group lies past the last whole vector
+    const uint32_t groups = (uint32_t)(cols / 4), tail_g = nvec * (E / 4);
+    if (threadIdx.x == 0 && tail_g < groups) {
+      float v[4];
+      lds_quad<In>(slot + tail_g * (4 * sizeof(In)), v);
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+    }
+    float lo = 0.0f;  // block_minmax folds a (min, max) pair; only the maximum is used
+    block_minmax(lo, m);
     if (threadIdx.x == 0) {
-      const float m = fmaxf(fabsf(fminf(mn, 0.0f)), fabsf(fmaxf(mx, 0.0f)));
       const float sc = fmaxf(__fdiv_rn(m, half), eps);
       s_scale = sc;
       out_scale[r] = sc;
@@ -852,14 +1012,44 @@ per_token_pipe_kernel(const In* __restrict__ x, size_t rows, size_t cols, float 
     __syncthreads();
     const Divisor d = make_divisor(s_scale);
     const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    const ShortDiv sd = make_short_div(d);
     int8_t* outr = out + r * cols;
-    const uint32_t groups = (uint32_t)(cols / 4);
-    for (uint32_t g = threadIdx.x; g < groups; g += kThreads) {
-      float v[4];
-      int c[4];
-      lds_quad<In>(slot + g * (4 * sizeof(In)), v);
-      code4_int(v, d, ig, 0.0f, qmin, qmax, c);
-      store_codes(outr + (size_t)g * 4, c);
+    if (d.fast) {
+      // every |x| <= abs-max = scale * half, so the short division covers the whole row
+      for (uint32_t i = threadIdx.x; i < nvec; i += kThreads) {
+        const uint4 u = lds_u4(slot + i * 16);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        if (E == 4) {
+          const float f[4] = {__uint_as_float(w[0]), __uint_as_float(w[1]), __uint_as_float(w[2]), __uint_as_float(w[3])};
+          int c[4];
+          code4_short(f, sd, ig, c);
+          st_stream_u1(outr + (size_t)i * 4, pack4i_s8(c));
+        } else {
+          const float f0[4] = {bf16_bits_to_f32(w[0] & 0xffffu), bf16_bits_to_f32(w[0] >> 16),
+                               bf16_bits_to_f32(w[1] & 0xffffu), bf16_bits_to_f32(w[1] >> 16)};
+          const float f1[4] = {bf16_bits_to_f32(w[2] & 0xffffu), bf16_bits_to_f32(w[2] >> 16),
+                               bf16_bits_to_f32(w[3] & 0xffffu), bf16_bits_to_f32(w[3] >> 16)};
+          int c0[4], c1[4];
+          code4_short(f0, sd, ig, c0);
+          code4_short(f1, sd, ig, c1);
+          st_stream_u2(outr + (size_t)i * 8, make_uint2(pack4i_s8(c0), pack4i_s8(c1)));
+        }
+      }
+      if (threadIdx.x == 0 && tail_g < groups) {
+        float v[4];
+        int c[4];
+        lds_quad<In>(slot + tail_g * (4 * sizeof(In)), v);
+        code4_short(v, sd, ig, c);
+        store_codes(outr + (size_t)tail_g * 4, c);
+      }
+    } else {
+      for (uint32_t g = threadIdx.x; g < groups; g += kThreads) {
+        float v[4];
+        int c[4];
+        lds_quad<In>(slot + g * (4 * sizeof(In)), v);
+        code4_int(v, d, ig, 0.0f, qmin, qmax, c);
+        store_codes(outr + (size_t)g * 4, c);
+      }
     }
   });
   if (!ok && threadIdx.x == 0) atomicAdd(&g_pipe_timeouts, 1u);
@@ -945,21 +1135,21 @@ per_token_kernel(const In* __restrict__ x, size_t rows, size_t cols, bool vec_ok
 // Fused per-token encode for rows of at most 16 KB: the row lives in registers (four 16-byte
 // vectors per thread, consecutive lanes on consecutive vectors), so HBM is read exactly once
 // and nothing is re-read from L2.
-template <typename In>
-__global__ void __launch_bounds__(kThreads, 4)
+template <typename In, int kT, int kV, int kMinBlocks>
+__global__ void __launch_bounds__(kT, kMinBlocks)
 per_token_reg_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps,
                      float qmin, float qmax, int8_t* __restrict__ out, float* __restrict__ out_scale) {
   constexpr int E = VecOf<In>::kElems;  // elements per 16-byte vector
-  __shared__ float s_part[2][kThreads / 32];
+  __shared__ float s_part[2][kT / 32];
   const uint32_t nvec = (uint32_t)(cols / E);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   int flip = 0;
-  uint4 v[4], vn[4];
-  auto load_row = [&](size_t r, uint4 (&dst)[4]) {
+  uint4 v[kV], vn[kV];
+  auto load_row = [&](size_t r, uint4 (&dst)[kV]) {
     const uint4* xv = reinterpret_cast<const uint4*>(x + r * cols);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t i = threadIdx.x + k * kThreads;
+    for (int k = 0; k < kV; ++k) {
+      const uint32_t i = threadIdx.x + k * kT;
       dst[k] = i < nvec ? ld_stream_u4(xv + i) : make_uint4(0, 0, 0, 0);  // zeros do not move an abs-max
     }
   };
@@ -968,30 +1158,33 @@ per_token_reg_kernel(const In* __restrict__ x, size_t rows, size_t cols, float h
     // the next row's loads are in flight while this one is encoded
     const size_t rn = r + gridDim.x;
     if (rn < rows) load_row(rn, vn);
-    float mn = 0.0f, mx = 0.0f;  // the range is extended to include 0 anyway
+    AbsMax<In> acc;  // zero-filled vectors past the row do not move an abs-max
 #pragma unroll
-    for (int k = 0; k < 4; ++k) vec_minmax<In>(v[k], mn, mx);
-    float am = fmaxf(fabsf(mn), fabsf(mx));
-    am = warp_max(am);
+    for (int k = 0; k < kV; ++k) acc.add(v[k]);
+    float am = warp_max(acc.get());
     if (l == 0) s_part[flip][w] = am;
     __syncthreads();  // the only block barrier per row (partials are double-buffered)
     float m = s_part[flip][0];
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, s_part[flip][i]);
+    for (int i = 1; i < kT / 32; ++i) m = fmaxf(m, s_part[flip][i]);
     const float sc = fmaxf(__fdiv_rn(m, half), eps);
     if (threadIdx.x == 0) out_scale[r] = sc;
     const Divisor d = make_divisor(sc);
     const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    const ShortDiv sd = make_short_div(d);
     int8_t* outr = out + r * cols;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t i = threadIdx.x + k * kThreads;
+    for (int k = 0; k < kV; ++k) {
+      const uint32_t i = threadIdx.x + k * kT;
       if (i >= nvec) continue;
       const uint32_t wv[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+      // every |x| <= abs-max = scale * half: with a divisor in the short division's range the
+      // whole row takes it (row-uniform branch)
       if (E == 4) {
         const float f[4] = {__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3])};
         int c[4];
-        code4_int(f, d, ig, 0.0f, qmin, qmax, c);
+        if (d.fast) code4_short(f, sd, ig, c);
+        else code4_int(f, d, ig, 0.0f, qmin, qmax, c);
         st_stream_u1(outr + (size_t)i * 4, pack4i_s8(c));
       } else {
         const float f0[4] = {bf16_bits_to_f32(wv[0] & 0xffffu), bf16_bits_to_f32(wv[0] >> 16),
@@ -999,13 +1192,18 @@ per_token_reg_kernel(const In* __restrict__ x, size_t rows, size_t cols, float h
         const float f1[4] = {bf16_bits_to_f32(wv[2] & 0xffffu), bf16_bits_to_f32(wv[2] >> 16),
                              bf16_bits_to_f32(wv[3] & 0xffffu), bf16_bits_to_f32(wv[3] >> 16)};
         int c0[4], c1[4];
-        code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
-        code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        if (d.fast) {
+          code4_short(f0, sd, ig, c0);
+          code4_short(f1, sd, ig, c1);
+        } else {
+          code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
+          code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        }
         st_stream_u2(outr + (size_t)i * 8, make_uint2(pack4i_s8(c0), pack4i_s8(c1)));
       }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = vn[k];
+    for (int k = 0; k < kV; ++k) v[k] = vn[k];
   }
 }
 
@@ -1050,7 +1248,7 @@ int minmax_tensor_launch(const void* x, int in_dtype, size_t n, MinMaxWorkspace*
   size_t want = (n / 16 + 2 * kThreads - 1) / (2 * kThreads);
   const size_t gcap = (size_t)sm_count() * stream_knobs().minmax_ctas_per_sm;
   int grid = (int)(want < 1 ? 1 : (want > gcap ? gcap : want));
-  if (vec_ok && fq.scale == nullptr && getenv("LQ_MINMAX_PIPE") && n * esz >= pipe_min_bytes()) {
+  if (vec_ok && fq.scale == nullptr && stream_knobs().minmax_pipe && n * esz >= pipe_min_bytes()) {
     // bulk-copy ring variant (kept for comparison; the register-staged kernel is faster)
     constexpr int stages = kRingBytes / kChunkBytes;
     constexpr size_t smem = kRingHeader + kRingBytes;
@@ -1222,9 +1420,16 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     return fail(LQ_ERR_DTYPE, "lq_quantize_per_token: in_dtype must be f32|bf16");
   const size_t row_bytes = cols * esz;
   constexpr size_t kRowRing = 96 * 1024;
-  if (vec_ok && row_bytes >= 20 * 1024 && row_bytes <= kRowRing && rows * row_bytes >= pipe_min_bytes()) {
-    // rows held in shared memory: one HBM read per element, rows prefetched through the ring
-    int stages = (int)(kRowRing / row_bytes);
+  const StreamKnobs& kn = stream_knobs();
+  if (vec_ok && row_bytes >= (size_t)kn.token_pipe_min_row && row_bytes <= kRowRing && rows * row_bytes >= pipe_min_bytes()) {
+    // rows held in shared memory: one HBM read per element, rows prefetched through the ring.
+    // Measured on B200 (4096 x 8192 bf16): resident CTAs matter more than ring depth -- 6 stages
+    // at 2 CTAs/SM 28.2 us, 3 stages at 4 CTAs/SM 24.0 us, 2 stages at 6 CTAs/SM 22.3 us (the
+    // register-staged kernel: 24.1 us) -- so the ring holds two rows, or `LQ_TOKEN_RING_KB`.
+    size_t ring = kn.token_ring_kb > 0 ? (size_t)kn.token_ring_kb * 1024 : 2 * row_bytes;
+    if (ring < row_bytes) ring = row_bytes;
+    if (ring > kRowRing) ring = kRowRing;
+    int stages = (int)(ring / row_bytes);
     if (stages > 8) stages = 8;
     const size_t smem = kRingHeader + (size_t)stages * row_bytes;
     static PerDeviceOnce once;
@@ -1245,10 +1450,21 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
   }
   if (vec_ok && row_bytes <= 16 * 1024) {
-    if (in_dtype == LQ_F32)
-      per_token_reg_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale);
-    else
-      per_token_reg_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale);
+    // one row per CTA-iteration, held in registers; narrow CTAs (more rows in flight per SM)
+    // when LQ_TOKEN_REG_THREADS=128
+    const int t = kn.token_reg_threads;
+    const size_t cap = (size_t)sm_count() * (t == 128 ? 6 : 4);
+    const int rgrid = (int)(rows < cap ? rows : cap);
+#define LQ_LAUNCH_REG(T, KT, KV, MB) \
+  per_token_reg_kernel<T, KT, KV, MB><<<rgrid, KT, 0, st>>>((const T*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale)
+    if (in_dtype == LQ_F32) {
+      if (t == 128) LQ_LAUNCH_REG(float, 128, 8, 6);
+      else LQ_LAUNCH_REG(float, 256, 4, 4);
+    } else {
+      if (t == 128) LQ_LAUNCH_REG(__nv_bfloat16, 128, 8, 6);
+      else LQ_LAUNCH_REG(__nv_bfloat16, 256, 4, 4);
+    }
+#undef LQ_LAUNCH_REG
     return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
   }
   if (in_dtype == LQ_F32)
@@ -1747,6 +1963,7 @@ per_token_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, float
     if (threadIdx.x < n_dst) sdst.p[threadIdx.x][row0 + r] = sc;
     const Divisor d = make_divisor(sc);
     const IntGrid ig = make_int_grid(0.0f, qmin, qmax, -128, 127);
+    const ShortDiv sd = make_short_div(d);  // |x| <= this row's abs-max: no quotient leaves its domain
     const uint4* xv = reinterpret_cast<const uint4*>(xr);
     const size_t obase = (row0 + r) * cols;
     for (uint32_t i = threadIdx.x; i < nvec; i += kThreads) {
@@ -1755,7 +1972,8 @@ per_token_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, float
       if (E == 4) {
         const float f[4] = {__uint_as_float(wv[0]), __uint_as_float(wv[1]), __uint_as_float(wv[2]), __uint_as_float(wv[3])};
         int c[4];
-        code4_int(f, d, ig, 0.0f, qmin, qmax, c);
+        if (d.fast) code4_short(f, sd, ig, c);
+        else code4_int(f, d, ig, 0.0f, qmin, qmax, c);
         const uint32_t w = pack4i_s8(c);
         if (multicast)
           asm volatile("multimem.st.weak.global.b32 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 4), "r"(w) : "memory");
@@ -1767,8 +1985,13 @@ per_token_bcast_kernel(const In* __restrict__ x, size_t rows, size_t cols, float
         const float f1[4] = {bf16_bits_to_f32(wv[2] & 0xffffu), bf16_bits_to_f32(wv[2] >> 16),
                              bf16_bits_to_f32(wv[3] & 0xffffu), bf16_bits_to_f32(wv[3] >> 16)};
         int c0[4], c1[4];
-        code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
-        code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        if (d.fast) {
+          code4_short(f0, sd, ig, c0);
+          code4_short(f1, sd, ig, c1);
+        } else {
+          code4_int(f0, d, ig, 0.0f, qmin, qmax, c0);
+          code4_int(f1, d, ig, 0.0f, qmin, qmax, c1);
+        }
         const uint2 w = make_uint2(pack4i_s8(c0), pack4i_s8(c1));
         if (multicast)
           asm volatile("multimem.st.weak.global.b64 [%0], %1;" ::"l"(dst.p[0] + obase + (size_t)i * 8),

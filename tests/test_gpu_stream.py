@@ -276,6 +276,24 @@ def test_extreme_scales_and_values_take_the_full_division():
         assert np.array_equal(got, ref), scale
 
 
+def test_outliers_inside_a_large_tensor_and_ragged_last_span():
+    """The per-tensor encode redoes only the spans that hold a value outside the short division's
+    domain; the rest of the tensor, the spans next to them and a last span that is not whole must
+    all equal the oracle."""
+    rng = np.random.default_rng(23)
+    for shape in ((37, 1028), (1024, 4096), (3, 16)):
+        x = (rng.standard_normal(shape) * 3).astype(np.float32)
+        flat = x.reshape(-1)
+        pos = rng.choice(flat.size, size=min(64, flat.size // 2), replace=False)
+        flat[pos] = rng.choice(np.array([1e30, -1e30, np.inf, -np.inf, 3e38, 1e9, -4.2e6 * 0.05, 4194304.0 * 0.05],
+                                        np.float32), size=pos.size)
+        for qd, oqd, z in ((Q.qint8, O.QINT8, 0.0), (Q.quint8, O.QUINT8, 131.0)):
+            got = host(Q.quantize(dev(x), 0.05, z, qd))
+            with np.errstate(over="ignore", invalid="ignore"):
+                ref = O.quantize(x, 0.05, z, oqd)
+            assert np.array_equal(got, ref), (shape, qd)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_shard_encode_with_broadcast_equals_unsharded_per_token_encode(dtype):
     """Column shards encoded separately with the all-reduced abs-max and stored into the
