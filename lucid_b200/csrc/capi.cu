@@ -1,4 +1,5 @@
 // Error plumbing and version query of the C ABI.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -39,6 +40,14 @@ int sm_count() {
   }
   return count[dev];
 }
+
+static bool read_pdl_knob() {
+  const char* e = getenv("LQ_PDL");
+  return e == nullptr || atoi(e) != 0;
+}
+static bool g_pdl = read_pdl_knob();
+bool pdl_enabled() { return g_pdl; }
+void reload_pdl_knob() { g_pdl = read_pdl_knob(); }
 
 }  // namespace lq
 

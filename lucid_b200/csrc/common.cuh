@@ -53,6 +53,31 @@ struct PerDeviceOnce {
   }
 };
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// Kernels launched through launch_pdl() may become resident while the kernel before them in
+// the stream is still draining: their CTAs run their set-up (barrier initialisation, TMEM
+// allocation, parameter derivation from kernel arguments), then pdl_wait() holds them until
+// that kernel has completed and its writes are visible.  Such a kernel must execute pdl_wait()
+// on every thread before its first access to global memory; pdl_launch_dependents() right after
+// lets the kernel behind it do the same.  After a kernel that does not take part (or with
+// LQ_PDL=0) the launch is an ordinary one and both calls are no-ops.
+bool pdl_enabled();
+void reload_pdl_knob();
+template <typename... P, typename... A>
+cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at, cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // ---- device-side exact arithmetic ---------------------------------------
 // Every step is a separate IEEE binary32 operation; the intrinsics keep the
 // compiler from contracting or approximating them.
@@ -94,7 +119,10 @@ __device__ __forceinline__ float div_rn(float x, const Divisor& d) {
 
 // Two-wide float arithmetic (sm_100 packed f32x2 instructions): one issue slot carries two
 // multiply-adds, each rounded exactly like its scalar form.  The stream encodes are issue-bound,
-// so halving the slots of the division chain is what these buy.
+// so halving the slots of the division chain is what these buy.  One trap, found by a parity
+// test: ptxas contracts an f2_mul whose result feeds an f2_add into one fused multiply-add
+// (`.rn` on both notwithstanding), so a product that must be rounded before an addition is
+// computed with the scalar intrinsics.  The division chain below has no such pair.
 struct F2 {
   unsigned long long b;
 };

@@ -374,6 +374,10 @@ struct RowCtx {
   Divisor so;        // output grid: scale (with its hoisted reciprocal)
   float zo;          // ... and zero point
   float fqmin, fqmax;
+  // the requantising epilogue's integer tail: code = bits(q + 1.5 * 2^23) + zofs, clamped to
+  // [clo, chi] (a ReLU is folded into clo) unless the saturating pack already does that
+  int zofs, clo, chi;
+  bool need_clamp, out_signed;
   uint32_t row_mask; // valid rows of this warp (bit r = tile row quad*32 + r)
   long long row0;    // global output row of the warp's first row
 };
@@ -617,31 +621,13 @@ __device__ __forceinline__ uint32_t pack4_low_bytes(const float (&c)[4]) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(d, e, 0x0040), 0x5410);
 }
 
-// Four outputs -> four codes without the division: q~ = y * RN(1 / s_o) is within |q| * 2^-23 of
-// the true quotient, so rint(q~) equals rint(RN(y / s_o)) unless q~ lies within that distance of a
-// half-integer.  q~ + 1.5 * 2^23 rounds to the nearest integer (ties to even) in the mantissa;
-// d = q~ - that integer is exact, and |d| <= 0.499 certifies the rounding for every |q~| <= 4096
-// (beyond that the code is clipped either way: the grid and its zero point lie within +-512).
-// Returns false when some element is not certain (NaN included); the caller then takes the
-// exact division for the group.
-__device__ __forceinline__ bool requant4_certain(const float (&y)[4], const RowCtx& rc, float (&c)[4]) {
-  bool ok = true;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float q = __fmul_rn(y[i], rc.so.y);
-    const float n = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
-    ok = ok && (fabsf(__fsub_rn(q, n)) <= 0.499f);
-    c[i] = fminf(fmaxf(__fadd_rn(n, rc.zo), rc.fqmin), rc.fqmax);
-  }
-  return ok;
-}
-
 // Lean requantising epilogue: 8-bit codes to one destination, tile inside N.  Compared with
 // epilogue_tile: the per-column parameters of the warp's columns are combined once per column
 // of tiles into a table in the warp's staging area (scale product folded when the activation
 // scale is per tensor; `fill` says the warp moved to another column of tiles) and read back with
-// broadcast 16-byte shared loads, the division is replaced by requant4_certain, and every thread
-// stores its 16 finished bytes straight to global memory (its row's next 16 bytes follow one
+// broadcast 16-byte shared loads, scale / bias / division run on the packed f32x2 pipe with the
+// integer tail of the stream encodes (no float-to-int conversion, no clip in float), and every
+// thread stores its 16 finished bytes straight to global memory (its row's next 16 bytes follow one
 // block later, so L2 merges the sectors) -- no staging pass.  What the epilogue descriptor asks
 // for (bias, ReLU, zero-point correction) is a template argument, so the 16-column loop has no
 // branch on it; signed and unsigned grids share one byte pack (the codes are already clipped
@@ -670,43 +656,88 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
   }
   const bool row_ok = (rc.row_mask >> lane) & 1u;
   uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
+  const F2 y2 = f2_pack(rc.so.y, rc.so.y), ns2 = f2_pack(-rc.so.s, -rc.so.s);
+  const F2 magic2 = f2_pack(12582912.0f, 12582912.0f);
 #pragma unroll 1
   for (int blk = 0; blk < NB; ++blk) {
     uint32_t acc[16];
     tc_ld16_sync(taddr + c0 + blk * 16, acc);
     if (ps.n) add_partials16<BN>(acc, ps, quad, (c0 >> 4) + blk, lane);
     uint32_t w[4];
+    float big = 0.0f;
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       const float4 s4 = *reinterpret_cast<const float4*>(t_scale + blk * 16 + 4 * q4);
-      const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
-      float y[4];
+      float a[4];
       if (HAS_ZP) {
         const int4 r4 = *reinterpret_cast<const int4*>(t_rowsum + blk * 16 + 4 * q4);
         const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) y[i] = (float)((int)acc[4 * q4 + i] - rc.zpa * rs[i]);
+        for (int i = 0; i < 4; ++i) a[i] = (float)((int)acc[4 * q4 + i] - rc.zpa * rs[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) y[i] = (float)(int)acc[4 * q4 + i];
+        for (int i = 0; i < 4; ++i) a[i] = (float)(int)acc[4 * q4 + i];
       }
+      // acc * scale (+ bias): scalar, two roundings.  (Packed, ptxas contracts mul.rn.f32x2 +
+      // add.rn.f32x2 into one fused multiply-add -- one rounding, codes off by one at ties.)
+      const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+      float v[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) y[i] = __fmul_rn(y[i], sc[i]);
+      for (int i = 0; i < 4; ++i) v[i] = __fmul_rn(a[i], sc[i]);
       if (HAS_BIAS) {
         const float4 b4 = *reinterpret_cast<const float4*>(t_bias + blk * 16 + 4 * q4);
-        y[0] = __fadd_rn(y[0], b4.x), y[1] = __fadd_rn(y[1], b4.y);
-        y[2] = __fadd_rn(y[2], b4.z), y[3] = __fadd_rn(y[3], b4.w);
+        v[0] = __fadd_rn(v[0], b4.x), v[1] = __fadd_rn(v[1], b4.y);
+        v[2] = __fadd_rn(v[2], b4.z), v[3] = __fadd_rn(v[3], b4.w);
       }
-      if (RELU) {
+      const F2 v01 = f2_pack(v[0], v[1]), v23 = f2_pack(v[2], v[3]);
+      // correctly rounded quotient by the output scale, rounded to the nearest integer (ties to
+      // even) in the mantissa of q + 1.5 * 2^23; the ReLU is the lower clamp of the code
+      // (rint(max(y, 0) / s) == max(rint(y / s), 0) for s > 0)
+      F2 e01, e23;
+      const F2 q01 = f2_div_short(v01, y2, ns2, e01), q23 = f2_div_short(v23, y2, ns2, e23);
+      float e[4], t[4];
+      f2_unpack(e01, e[0], e[1]), f2_unpack(e23, e[2], e[3]);
+      big = fmaxf(fmaxf(big, fmaxf(fabsf(e[0]), fabsf(e[1]))), fmaxf(fabsf(e[2]), fabsf(e[3])));
+      f2_unpack(f2_add(q01, magic2), t[0], t[1]), f2_unpack(f2_add(q23, magic2), t[2], t[3]);
+      int c[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) y[i] = fmaxf(y[i], 0.0f);
+      for (int i = 0; i < 4; ++i) c[i] = __float_as_int(t[i]) + rc.zofs;
+      if (rc.need_clamp) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[i] = min(max(c[i], rc.clo), rc.chi);
       }
-      float c[4];
-      if (!requant4_certain(y, rc, c)) code4_f32(y, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
-      w[q4] = pack4_low_bytes(c);
+      w[q4] = rc.out_signed ? pack4i_s8(c) : pack4i_u8(c);
+    }
+    if (!(big < 0x1p22f)) {
+      // a quotient outside the short division's domain (never for sane scales): the whole block
+      // again through the full-range sequence
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float y[4], c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = blk * 16 + 4 * q4 + i;
+          const int v = HAS_ZP ? (int)acc[4 * q4 + i] - rc.zpa * t_rowsum[col] : (int)acc[4 * q4 + i];
+          y[i] = __fmul_rn((float)v, t_scale[col]);
+          if (HAS_BIAS) y[i] = __fadd_rn(y[i], t_bias[col]);
+          if (RELU) y[i] = fmaxf(y[i], 0.0f);
+        }
+        code4_f32(y, rc.so, rc.zo, rc.fqmin, rc.fqmax, c);
+        w[q4] = pack4_low_bytes(c);
+      }
     }
     if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
   }
+}
+
+// The general 8-bit epilogue (ragged last column of tiles, per-row activation scales, several
+// destinations), out of line: it is the rare path of the 8-bit kernels, and inlined it would
+// set the register budget of their tile loop.
+template <int BN, int PARTS>
+static __device__ __noinline__ void epilogue_q8_generic(const Epi& ep, const Geometry& g, const RowCtx& rc, uint32_t taddr,
+                                                        uint8_t* stg, int lane, int part, int n0, const Partials& ps,
+                                                        int quad) {
+  epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
 }
 
 // Runtime flags -> template arguments (three uniform branches per tile, none per element).
@@ -769,10 +800,14 @@ __device__ __forceinline__ bool sched_next(Sched& s, int& tile, int& kb0, int& k
 }
 
 // ---- the kernel ---------------------------------------------------------------------
-template <int BN, bool PAIR, int EW>
+// FAM selects the epilogue family compiled into the kernel: 0 = float / s32 outputs (plain and
+// gated), 1 = 8-bit codes (the requantising epilogues).  One kernel with both spilled the state
+// of its tile loop (96 registers with 16 epilogue warps) and reloaded it from L2 inside the
+// requantising loop, which is what bounded the small-K layers.
+template <int BN, bool PAIR, int EW, int FAM>
 __global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const Geometry g, const Epi ep, const uint32_t idesc) {
+               const __grid_constant__ Geometry g, const __grid_constant__ Epi ep, const uint32_t idesc) {
   using C = Cfg<BN, PAIR, EW>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -839,6 +874,11 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only kernel arguments, shared memory and TMEM, and may have run
+  // while the kernel before this one in the stream was still draining; global memory (operands,
+  // scales, workspace, outputs) is touched from here on.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ===== TMA producer (one per CTA) =====
@@ -955,13 +995,25 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                          ep.a_scale_mode != LQ_PER_ROW && (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8);
     // what does not change from tile to tile is read once
     RowCtx rc_launch;
-    rc_launch.sa = (ep.a_scale && ep.a_scale_mode != LQ_PER_ROW) ? __ldg(ep.a_scale) : 1.0f;
-    rc_launch.zpa = ep.a_zp ? (int)__ldg(ep.a_zp) : 0;
-    rc_launch.so = make_divisor(ep.out_scale ? __ldg(ep.out_scale) : 1.0f);
-    rc_launch.zo = ep.out_zp ? __ldg(ep.out_zp) : 0.0f;
+    rc_launch.sa = (ep.a_scale && ep.a_scale_mode != LQ_PER_ROW) ? __ldcg(ep.a_scale) : 1.0f;
+    rc_launch.zpa = ep.a_zp ? (int)__ldcg(ep.a_zp) : 0;
+    rc_launch.so = make_divisor(ep.out_scale ? __ldcg(ep.out_scale) : 1.0f);
+    rc_launch.zo = ep.out_zp ? __ldcg(ep.out_zp) : 0.0f;
     rc_launch.fqmin = (float)ep.qmin, rc_launch.fqmax = (float)ep.qmax;
     rc_launch.row_mask = 0u, rc_launch.row0 = 0;
-    const bool q8_lean_grid = rc_launch.so.fast && fabsf(rc_launch.zo) <= 512.0f;
+    {
+      const bool relu = ep.act == LQ_ACT_RELU;
+      const int zo_i = (int)rc_launch.zo;
+      rc_launch.zofs = zo_i - 0x4B400000;
+      rc_launch.clo = relu && zo_i > ep.qmin ? zo_i : ep.qmin;
+      rc_launch.chi = ep.qmax;
+      rc_launch.out_signed = ep.out_dtype == LQ_S8;
+      const int store_lo = rc_launch.out_signed ? -128 : 0, store_hi = rc_launch.out_signed ? 127 : 255;
+      rc_launch.need_clamp = !(rc_launch.clo <= store_lo && rc_launch.chi >= store_hi);
+    }
+    // a positive output scale in the short division's range and an integral zero point
+    const bool q8_lean_grid = rc_launch.so.fast && rc_launch.so.s > 0.0f && fabsf(rc_launch.zo) <= 512.0f &&
+                              rc_launch.zo == rintf(rc_launch.zo);
     const int q8_mask = (ep.bias != nullptr ? 1 : 0) | (ep.act == LQ_ACT_RELU ? 2 : 0) |
                         ((ep.b_rowsum != nullptr && rc_launch.zpa != 0) ? 4 : 0);
     int q8_filled_tn = -1;  // column of tiles whose parameters this warp's table holds
@@ -995,7 +1047,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         row_ok = m_global < g.M;
       }
       RowCtx rc = rc_launch;
-      if (ep.a_scale && ep.a_scale_mode == LQ_PER_ROW) rc.sa = row_ok ? __ldg(ep.a_scale + m_global) : 1.0f;
+      if (ep.a_scale && ep.a_scale_mode == LQ_PER_ROW) rc.sa = row_ok ? __ldcg(ep.a_scale + m_global) : 1.0f;
       rc.row_mask = __ballot_sync(0xffffffffu, row_ok);
       rc.row0 = (long long)__shfl_sync(0xffffffffu, m_global, 0);
 
@@ -1026,22 +1078,26 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
               ready = flag_wait_eq(sk_flags + 2 * (ps.cta0 + i * ps.cta_step), (unsigned)EW, abort_flag, budget) ? 1 : 0;
           if (!__shfl_sync(0xffffffffu, ready, 0)) break;
         }
-        if (gated) {
-          const int on0 = tn_idx * (BN / 2);
-          if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
-          else epilogue_tile<BN, KIND_BF16, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
-        } else if (ep.out_dtype == LQ_BF16) {
-          epilogue_tile<BN, KIND_BF16, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
-        } else if (ep.out_dtype == LQ_F32) {
-          epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
-        } else if (ep.out_dtype == LQ_S32) {
-          epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
-        } else if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
-          q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
-          q8_filled_tn = tn_idx;
+        if constexpr (FAM == 0) {
+          if (gated) {
+            const int on0 = tn_idx * (BN / 2);
+            if (ep.out_dtype == LQ_F32) epilogue_tile<BN, KIND_F32, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
+            else epilogue_tile<BN, KIND_BF16, true, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, on0, ps, quad);
+          } else if (ep.out_dtype == LQ_BF16) {
+            epilogue_tile<BN, KIND_BF16, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+          } else if (ep.out_dtype == LQ_F32) {
+            epilogue_tile<BN, KIND_F32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+          } else {
+            epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
+          }
         } else {
-          epilogue_tile<BN, KIND_Q8, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
-          q8_filled_tn = -1;  // the generic path stages through the table's memory
+          if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
+            q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
+            q8_filled_tn = tn_idx;
+          } else {
+            epilogue_q8_generic<BN, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, ps, quad);
+            q8_filled_tn = -1;  // the generic path stages through the table's memory
+          }
         }
         if (ps.n) {
           // the last reading warp re-arms the contributors' flags for the next launch
@@ -1294,17 +1350,17 @@ Knobs& knobs_storage() {
 const Knobs& knobs() { return knobs_storage(); }
 
 // CTA pairs that can be resident at once, per device.
-template <int BN, bool PAIR, int EW>
+template <int BN, bool PAIR, int EW, int FAM>
 struct LaunchState {
   PerDeviceOnce once;
   int max_clusters[kMaxDevices] = {};
 };
 
-template <int BN, bool PAIR, int EW>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_in, const Epi& ep,
-           uint32_t idesc, cudaStream_t st) {
-  static LaunchState<BN, PAIR, EW> state;
-  auto kernel = gemm_s8_kernel<BN, PAIR, EW>;
+template <int BN, bool PAIR, int EW, int FAM>
+int launch_fam(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_in, const Epi& ep,
+               uint32_t idesc, cudaStream_t st) {
+  static LaunchState<BN, PAIR, EW, FAM> state;
+  auto kernel = gemm_s8_kernel<BN, PAIR, EW, FAM>;
   constexpr int smem = Cfg<BN, PAIR, EW>::kSmemBytes;
   constexpr int kGemmThreads = threads_for(EW);
   const int dev = current_device();
@@ -1351,8 +1407,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_in, c
     if (knobs().verbose)
       fprintf(stderr, "[lq] launch BN=%d EW=%d: %d tiles x %d k-blocks on %d CTAs%s\n", BN, EW, total_tiles, g.num_kb, grid,
               g.streamk ? " (stream-K)" : "");
-    kernel<<<grid, kGemmThreads, smem, st>>>(ta, tb, g, ep, idesc);
-    return check_cuda(cudaGetLastError(), "gemm_s8_kernel launch");
+    return check_cuda(launch_pdl(kernel, dim3(grid), dim3(kGemmThreads), smem, st, ta, tb, g, ep, idesc),
+                      "gemm_s8_kernel launch");
   }
   const int max_clusters = state.max_clusters[dev];
   const int clusters = total < max_clusters ? total : max_clusters;
@@ -1364,11 +1420,20 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_in, c
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
-  cfg.attrs = at, cfg.numAttrs = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at, cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return check_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, g, ep, idesc), "gemm_s8_kernel (paired) launch");
+}
+
+template <int BN, bool PAIR, int EW>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep, uint32_t idesc,
+           cudaStream_t st) {
+  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) return launch_fam<BN, PAIR, EW, 1>(ta, tb, g, ep, idesc, st);
+  return launch_fam<BN, PAIR, EW, 0>(ta, tb, g, ep, idesc, st);
 }
 
 // Tile shape and schedule.  CTA pairs (256 x 256 tiles, cta_group::2) when there is enough work
@@ -1419,6 +1484,10 @@ int dispatch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, Geo
              int a_signed, cudaStream_t st) {
   // tiles whose mainloop (k-blocks x ~0.28 us) is shorter than their epilogue get 16 epilogue warps
   bool wide_epi = g.num_kb <= 32;
+  // ... except 8-bit outputs: at 96 registers per thread (18 warps) the requantising loop spills
+  // and reloads through L2; 8 warps at 168 registers measured 51.7 us against 65.7 us on
+  // 50176 x 1024 x 256 and 33.4 against 37.8 us on 50176 x 256 x 2304
+  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) wide_epi = false;
   // tiles that also travel to peer GPUs: their stores take longer to issue
   if ((ep.n_dst > 1 || ep.multicast) && knobs().bcast_epi_warps) wide_epi = knobs().bcast_epi_warps == 16;
   if (knobs().epi_warps) wide_epi = knobs().epi_warps == 16;
@@ -1573,6 +1642,7 @@ void reload_hist_knobs();
 }
 extern "C" void lq_reload_env(void) {
   knobs_storage().read();
+  lq::reload_pdl_knob();
 #ifndef LQ_TESTING  // the test-only library holds the contraction alone
   lq::reload_stream_knobs();
   lq::reload_hist_knobs();

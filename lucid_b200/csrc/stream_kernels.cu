@@ -332,13 +332,15 @@ template <Op OP, typename In, typename Out, bool MASK, int kUnroll, int kMinBloc
 __global__ void __launch_bounds__(kThreads, kMinBlocks)
 affine_vec_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __restrict__ mask,
                   size_t rows, size_t cols, QParamRef q, float qmin, float qmax) {
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
   const int mode = MODE >= 0 ? MODE : q.mode;
   const size_t ngroups = rows * cols / 4;
   const size_t span = (size_t)kThreads * kUnroll;
   float st = 1.0f, zt = 0.0f;
   if (mode == LQ_PER_TENSOR) {
-    st = q.s != nullptr ? __ldg(q.s) : q.sv;
-    zt = q.z != nullptr ? __ldg(q.z) : q.zv;
+    st = q.s != nullptr ? __ldcg(q.s) : q.sv;
+    zt = q.z != nullptr ? __ldcg(q.z) : q.zv;
   }
   const Divisor dt = group_divisor<OP>(st);
   const IntGrid igt = make_int_grid(zt, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
@@ -402,9 +404,9 @@ template <typename In, typename Out>
 static __device__ __noinline__ void encode_span_full(const In* __restrict__ x, Out* __restrict__ out, size_t g0,
                                                      size_t ngroups, int unroll, const float* sp, const float* zp,
                                                      float sv, float zv, float qmin, float qmax) {
-  const float z = zp != nullptr ? __ldg(zp) : zv;
+  const float z = zp != nullptr ? __ldcg(zp) : zv;
   Divisor d;
-  d.s = sp != nullptr ? __ldg(sp) : sv, d.y = 0.0f, d.fast = false;
+  d.s = sp != nullptr ? __ldcg(sp) : sv, d.y = 0.0f, d.fast = false;
   for (int u = 0; u < unroll; ++u) {
     const size_t g = g0 + (size_t)u * kThreads;
     if (g >= ngroups) break;
@@ -419,8 +421,11 @@ template <typename In, typename Out, int kUnroll, int kMinBlocks, bool PACKED>
 __global__ void __launch_bounds__(kThreads, kMinBlocks)
 quantize_tensor_kernel(const In* __restrict__ x, Out* __restrict__ out, size_t ngroups, QParamRef q, float qmin,
                        float qmax) {
-  const Divisor d = make_divisor(q.s != nullptr ? __ldg(q.s) : q.sv);
-  const IntGrid ig = make_int_grid(q.z != nullptr ? __ldg(q.z) : q.zv, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
+  // (scale, zero point) usually come from the kernel just before this one: read them through L2
+  const Divisor d = make_divisor(q.s != nullptr ? __ldcg(q.s) : q.sv);
+  const IntGrid ig = make_int_grid(q.z != nullptr ? __ldcg(q.z) : q.zv, qmin, qmax, StoreRange<Out>::lo, StoreRange<Out>::hi);
   const bool lean = d.fast && ig.fast;
   constexpr size_t kSpan = (size_t)kThreads * kUnroll;
   constexpr size_t kStep = (size_t)kThreads * 4;
@@ -763,6 +768,8 @@ template <Op OP, typename In, typename Out, bool MASK>
 __global__ void __launch_bounds__(kThreads)
 affine_pipe_kernel(const In* __restrict__ x, Out* __restrict__ out, float* __restrict__ mask,
                    size_t n, size_t cols, QParamRef q, float qmin, float qmax, int stages) {
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t ring[];
   // the 16-byte multiple part goes through the ring; at most 15 bytes of elements are left
   const size_t main_bytes = (n * sizeof(In)) & ~(size_t)15;
@@ -853,7 +860,8 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
     const size_t nchunks = (n * sizeof(In) + kChunkBytes - 1) / kChunkBytes;
     const size_t cap = (size_t)sm_count() * 3;
     const int grid = (int)(nchunks < cap ? nchunks : cap);
-    kernel<<<grid, kThreads, smem, st>>>((const In*)x, (Out*)out, mask, n, cols, q, (float)qmin, (float)qmax, stages);
+    return check_cuda(launch_pdl(kernel, dim3(grid), dim3(kThreads), smem, st, (const In*)x, (Out*)out, mask, n, cols, q,
+                                 (float)qmin, (float)qmax, stages), "affine kernel launch");
   } else if (vec) {
     // 4 groups per thread at full occupancy (32 registers): measured fastest on B200
     const StreamKnobs& kn = stream_knobs();
@@ -866,13 +874,14 @@ int launch_affine(const void* x, void* out, float* mask, size_t rows, size_t col
       // measured on B200 (config 1, 64 MB): 4 groups per thread at 6 CTAs/SM (40 registers, no
       // spill) 14.6 us; at 8 CTAs/SM (32 registers, 32 B spilled) 15.4 us; scalar multiply-adds
       // instead of the packed ones 15.4 us; the run-time-mode kernel 17.2 us
-      quantize_tensor_kernel<In, Out, 4, 6, true><<<grid_for((groups + 3) / 4), kThreads, 0, st>>>(
-          (const In*)x, (Out*)out, groups, q, (float)qmin, (float)qmax);
-      return check_cuda(cudaGetLastError(), "affine kernel launch");
+      return check_cuda(launch_pdl(quantize_tensor_kernel<In, Out, 4, 6, true>, dim3(grid_for((groups + 3) / 4)),
+                                   dim3(kThreads), 0, st, (const In*)x, (Out*)out, groups, q, (float)qmin, (float)qmax),
+                        "affine kernel launch");
     }
-#define LQ_LAUNCH_VEC(U, M)                                                                              \
-  affine_vec_kernel<OP, In, Out, MASK, U, 8, M><<<grid, kThreads, 0, st>>>((const In*)x, (Out*)out, mask, rows, \
-                                                                           cols, q, (float)qmin, (float)qmax)
+#define LQ_LAUNCH_VEC(U, M)                                                                                   \
+  return check_cuda(launch_pdl(affine_vec_kernel<OP, In, Out, MASK, U, 8, M>, dim3(grid), dim3(kThreads), 0, st, \
+                               (const In*)x, (Out*)out, mask, rows, cols, q, (float)qmin, (float)qmax),           \
+                    "affine kernel launch")
     if (unroll == 2) {
       if (tensor) LQ_LAUNCH_VEC(2, LQ_PER_TENSOR);
       else LQ_LAUNCH_VEC(2, -1);
@@ -951,6 +960,8 @@ template <typename In>
 __global__ void __launch_bounds__(kThreads)
 minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWorkspace* ws,
                      float* out_min, float* out_max, FusedQParams fq) {
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
   float mn = INFINITY, mx = -INFINITY;
   minmax_accumulate(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
                     (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
@@ -985,6 +996,8 @@ __global__ void __launch_bounds__(kThreads)
 per_token_pipe_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps,
                       float qmin, float qmax, int8_t* __restrict__ out, float* __restrict__ out_scale,
                       int stages) {
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ float s_scale;
   const uint32_t row_bytes = (uint32_t)(cols * sizeof(In));
@@ -1139,6 +1152,8 @@ template <typename In, int kT, int kV, int kMinBlocks>
 __global__ void __launch_bounds__(kT, kMinBlocks)
 per_token_reg_kernel(const In* __restrict__ x, size_t rows, size_t cols, float half, float eps,
                      float qmin, float qmax, int8_t* __restrict__ out, float* __restrict__ out_scale) {
+  pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
+  pdl_launch_dependents();
   constexpr int E = VecOf<In>::kElems;  // elements per 16-byte vector
   __shared__ float s_part[2][kT / 32];
   const uint32_t nvec = (uint32_t)(cols / E);
@@ -1266,9 +1281,11 @@ int minmax_tensor_launch(const void* x, int in_dtype, size_t n, MinMaxWorkspace*
     else
       minmax_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, n, ws, out_min, out_max, stages);
   } else if (in_dtype == LQ_F32) {
-    minmax_tensor_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, n, vec_ok, ws, out_min, out_max, fq);
+    return check_cuda(launch_pdl(minmax_tensor_kernel<float>, dim3(grid), dim3(kThreads), 0, st, (const float*)x, n, vec_ok,
+                                 ws, out_min, out_max, fq), "minmax launch");
   } else {
-    minmax_tensor_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max, fq);
+    return check_cuda(launch_pdl(minmax_tensor_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), 0, st,
+                                 (const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max, fq), "minmax launch");
   }
   return check_cuda(cudaGetLastError(), "range reduction launch");
 }
@@ -1444,9 +1461,13 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     const size_t cap = (size_t)sm_count() * ctas_per_sm;
     const int pgrid = (int)(rows < cap ? rows : cap);
     if (in_dtype == LQ_F32)
-      per_token_pipe_kernel<float><<<pgrid, kThreads, smem, st>>>((const float*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
+      return check_cuda(launch_pdl(per_token_pipe_kernel<float>, dim3(pgrid), dim3(kThreads), smem, st, (const float*)x, rows,
+                                   cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages),
+                        "lq_quantize_per_token launch");
     else
-      per_token_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale, stages);
+      return check_cuda(launch_pdl(per_token_pipe_kernel<__nv_bfloat16>, dim3(pgrid), dim3(kThreads), smem, st,
+                                   (const __nv_bfloat16*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale,
+                                   stages), "lq_quantize_per_token launch");
     return check_cuda(cudaGetLastError(), "lq_quantize_per_token launch");
   }
   if (vec_ok && row_bytes <= 16 * 1024) {
@@ -1456,7 +1477,8 @@ extern "C" int lq_quantize_per_token(const void* x, int in_dtype, size_t rows, s
     const size_t cap = (size_t)sm_count() * (t == 128 ? 6 : 4);
     const int rgrid = (int)(rows < cap ? rows : cap);
 #define LQ_LAUNCH_REG(T, KT, KV, MB) \
-  per_token_reg_kernel<T, KT, KV, MB><<<rgrid, KT, 0, st>>>((const T*)x, rows, cols, half, eps, (float)qmin, (float)qmax, out, out_scale)
+  return check_cuda(launch_pdl(per_token_reg_kernel<T, KT, KV, MB>, dim3(rgrid), dim3(KT), 0, st, (const T*)x, rows, cols, \
+                               half, eps, (float)qmin, (float)qmax, out, out_scale), "lq_quantize_per_token launch")
     if (in_dtype == LQ_F32) {
       if (t == 128) LQ_LAUNCH_REG(float, 128, 8, 6);
       else LQ_LAUNCH_REG(float, 256, 4, 4);
