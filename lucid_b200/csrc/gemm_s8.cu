@@ -658,10 +658,8 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
   uint8_t* dst = reinterpret_cast<uint8_t*>(ep.out) + (rc.row0 + lane) * ep.ldo + ep.col0 + n0 + c0;
   const F2 y2 = f2_pack(rc.so.y, rc.so.y), ns2 = f2_pack(-rc.so.s, -rc.so.s);
   const F2 magic2 = f2_pack(12582912.0f, 12582912.0f);
-#pragma unroll 1
-  for (int blk = 0; blk < NB; ++blk) {
-    uint32_t acc[16];
-    tc_ld16_sync(taddr + c0 + blk * 16, acc);
+  // one 16-column block: accumulators in registers -> 16 finished bytes in global memory
+  auto finish_block = [&](uint32_t (&acc)[16], int blk) {
     if (ps.n) add_partials16<BN>(acc, ps, quad, (c0 >> 4) + blk, lane);
     uint32_t w[4];
     float big = 0.0f;
@@ -727,6 +725,31 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
       }
     }
     if (row_ok) *reinterpret_cast<uint4*>(dst + blk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  };
+  if constexpr (PARTS <= 2) {
+    // 8 epilogue warps (168 registers)
+    static_assert(NB % 2 == 0, "blocks are taken in pairs");
+    // two blocks per iteration, finished in one basic block: eight independent chains of four
+    // outputs for the scheduler to interleave (two epilogue warps per scheduler hide little)
+    uint32_t acc_a[16], acc_b[16];
+#pragma unroll 1
+    for (int blk = 0; blk < NB; blk += 2) {
+      tc_ld16(taddr + c0 + blk * 16, acc_a);
+      tc_ld16(taddr + c0 + (blk + 1) * 16, acc_b);
+      tc_wait_ld_dep16(acc_a);
+      tc_wait_ld_dep16(acc_b);
+      finish_block(acc_a, blk);
+      finish_block(acc_b, blk + 1);
+    }
+  } else {
+    // 16 epilogue warps (96 registers): one register set, read and wait in one statement (a
+    // register that a read in flight will write must never be spilled)
+#pragma unroll 1
+    for (int blk = 0; blk < NB; ++blk) {
+      uint32_t acc[16];
+      tc_ld16_sync(taddr + c0 + blk * 16, acc);
+      finish_block(acc, blk);
+    }
   }
 }
 
@@ -1483,6 +1506,9 @@ Plan pick_plan(size_t m_subtiles, size_t N, bool gated, size_t k_blocks, bool ha
 int dispatch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, Geometry& g, const Epi& ep,
              int a_signed, cudaStream_t st) {
   // tiles whose mainloop (k-blocks x ~0.28 us) is shorter than their epilogue get 16 epilogue warps
+  // (16 against 8 warps: bf16 out, K = 2048 76.6 / 88.6 us at 4096 x 10240, K = 4096 54.5 / 53.3 us
+  // at 4096 x 4096; f32 out with the zero-point correction, K = 4096: 63 / 74 us for the whole
+  // dynamic Linear)
   bool wide_epi = g.num_kb <= 32;
   // ... except 8-bit outputs: at 96 registers per thread (18 warps) the requantising loop spills
   // and reloads through L2; 8 warps at 168 registers measured 51.7 us against 65.7 us on
