@@ -276,6 +276,29 @@ def test_extreme_scales_and_values_take_the_full_division():
         assert np.array_equal(got, ref), scale
 
 
+def test_back_to_back_dependent_launches_see_each_others_results():
+    """The encode reads the grid that the range reduction launched just before it derived, and
+    both kernels may become resident while their predecessor drains.  A long unsynchronised chain
+    over inputs of alternating magnitude (all links share the reduction's workspace) must give
+    every link the grid of ITS input."""
+    rng = np.random.default_rng(29)
+    shapes = [(1024, 1024), (96, 4096), (2048, 512)]
+    xs = [(rng.standard_normal(shapes[i % 3]) * (0.01 if i % 2 else 37.0)).astype(np.float32) for i in range(6)]
+    dx = [dev(x) for x in xs]
+    outs = []
+    for rep in range(40):
+        for i, x in enumerate(dx):
+            outs.append((i, *Q.quantize_dynamic_per_tensor(x, Q.quint8)))
+    torch.cuda.synchronize()
+    refs = {}
+    for i, x in enumerate(xs):
+        s, z = O.calculate_qparams(x.min(), x.max(), False, O.QUINT8)
+        refs[i] = (O.quantize(x, s, z, O.QUINT8), np.float32(s), np.float32(z))
+    for i, codes, s, z in outs:
+        assert float(s) == refs[i][1] and float(z) == refs[i][2]
+        assert np.array_equal(host(codes), refs[i][0])
+
+
 def test_outliers_inside_a_large_tensor_and_ragged_last_span():
     """The per-tensor encode redoes only the spans that hold a value outside the short division's
     domain; the rest of the tensor, the spans next to them and a last span that is not whole must
