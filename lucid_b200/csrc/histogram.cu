@@ -614,7 +614,17 @@ observe_pass2(const In* __restrict__ x, size_t n, bool vec_ok, int bins, bool al
 // lq_reload_env().
 static bool g_hist_binary64 = getenv("LQ_HIST_BINARY64") != nullptr;
 static bool hist_force_binary64() { return g_hist_binary64; }
-void reload_hist_knobs() { g_hist_binary64 = getenv("LQ_HIST_BINARY64") != nullptr; }
+// LQ_HIST_CTAS_PER_SM (1..4): resident CTAs per SM of the binning kernels (measurement knob).
+static int read_hist_ctas() {
+  const char* e = getenv("LQ_HIST_CTAS_PER_SM");
+  const int v = e ? atoi(e) : 0;
+  return v >= 1 && v <= kHistCtasPerSm ? v : kHistCtasPerSm;
+}
+static int g_hist_ctas = read_hist_ctas();
+void reload_hist_knobs() {
+  g_hist_binary64 = getenv("LQ_HIST_BINARY64") != nullptr;
+  g_hist_ctas = read_hist_ctas();
+}
 }  // namespace lq
 
 using namespace lq;
@@ -628,7 +638,7 @@ size_t hist_smem_bytes(int bins) {
 int hist_grid(size_t n, size_t esz) {
   const size_t per_cta = (size_t)kHistThreads * 4 * (16 / esz);
   const size_t want = (n + per_cta - 1) / per_cta;
-  size_t cap = (size_t)sm_count() * kHistCtasPerSm;
+  size_t cap = (size_t)sm_count() * g_hist_ctas;
   if (cap > (size_t)kHistMaxCtas) cap = (size_t)kHistMaxCtas;  // slots of the workspace
   return (int)(want < 1 ? 1 : (want > cap ? cap : want));
 }
