@@ -285,8 +285,12 @@ def run_b200_arm(args):
             hidden = HiddenExchange(M_TOKENS, D_FF, dev)
         else:
             peers["h"] = PeerOutputs(M_TOKENS, D_FF, torch.bfloat16, dev)
-        # the three replicated input activations: each rank encodes 1/w of the token rows
-        shard_inputs = args.shard_encode == "on" or (args.shard_encode == "auto" and world >= 4)
+        # the three replicated input activations: every rank encodes all token rows (auto), or
+        # each rank encodes 1/w of them and stores codes + scales into every rank's buffers (on).
+        # Measured at 4 ranks: replicated 1.024 ms / step, sharded 1.129 ms -- a whole-tensor
+        # encode is ~22 us, less than the flag round trip and the code exchange cost.  The
+        # end-to-end path always shards (each rank copies only its rows from the host).
+        shard_inputs = args.shard_encode == "on"
         encoders = [TokenShardedEncoder(M_TOKENS, D_MODEL, dev) for _ in range(3)]
 
     # NVSwitch multicast stores when the buffers are bound to a multicast object
@@ -1161,7 +1165,7 @@ def main():
                     help="N > 1, p2p: exchange the gate/up output as per-token int8 codes or as bf16 (auto: codes from 4 ranks)")
     ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
-                         "(auto: from 4 ranks)")
+                         "(auto: off on the device-timed path; the end-to-end path always shards)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-unicast", "nccl"],
                     help="N > 1: fused epilogue stores into every rank's buffer (default; through NVSwitch "
                          "multicast when the buffers are bound to a multicast object, 'p2p-unicast' forces one "
