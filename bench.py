@@ -294,7 +294,8 @@ def run_b200_arm(args):
         encoders = [TokenShardedEncoder(M_TOKENS, D_MODEL, dev) for _ in range(3)]
 
     # NVSwitch multicast stores when the buffers are bound to a multicast object
-    use_mc = bool(peers) and world >= 8 and args.exchange != "p2p-unicast" and \
+    mc_wanted = args.multicast == "on" or (args.multicast == "auto" and world >= 8)
+    use_mc = bool(peers) and mc_wanted and args.exchange != "p2p-unicast" and \
         all(p.has_multicast for p in peers.values())
 
     def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, wait=False, gather=True):
@@ -1166,6 +1167,8 @@ def main():
     ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
                          "(auto: off on the device-timed path; the end-to-end path always shards)")
+    ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
+                    help="N > 1, p2p: store through the NVSwitch multicast address of the buffers (auto: at 8 ranks)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-unicast", "nccl"],
                     help="N > 1: fused epilogue stores into every rank's buffer (default; through NVSwitch "
                          "multicast when the buffers are bound to a multicast object, 'p2p-unicast' forces one "
