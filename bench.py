@@ -577,12 +577,12 @@ def run_b200_arm(args):
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS",
                 "frac": achieved / peak,
                 # DRAM bytes per average GEMM launch: an ncu capture of 4096 x 16384 x 8192
-                # (dram__bytes_read.sum + dram__bytes_write.sum) moved 318.6 MB for 302.0 MB
+                # (dram__bytes_read.sum + dram__bytes_write.sum) moved 321.5 MB for 302.0 MB
                 # of algorithmic bytes (A + B read once, output written once); the same factor is
                 # applied to this workload's average launch (381.7 MB algorithmic at one GPU)
-                "traffic": 381.7e6 / world * (318.6 / 302.0),
+                "traffic": 381.7e6 / world * (321.5 / 302.0),
                 "traffic_note": "scaled from an ncu capture of a smaller case by algorithmic bytes",
-                "kernel": "gemm_s8_kernel<256, PAIR, 8>",
+                "kernel": "gemm_s8_kernel<256, PAIR, 8, float outputs>",
                 "peak_note": f"2 x cuBLAS bf16 sustained ({peaks['source']}); nominal dense int8 "
                              "is 4500 TOPS",
                 "frac_of_nominal_4500": achieved / 4500.0,
