@@ -325,14 +325,39 @@ def run_b200_arm(args):
             return encoders[i](xs[i], multicast=use_mc, local=local)
         return Q.quantize_per_token(xs[i], Q.qint8)
 
+    # The QKV, O and MLP chains of a step have no data in common.  Sharded, each GEMM ends by
+    # waiting until its tiles have reached the peers; on one stream the next chain's kernels
+    # would wait behind that.  Forked over three streams (joined before the end-of-step waits)
+    # the link drain of one chain overlaps the arithmetic of the others; every chain's
+    # contractions run on a workspace of their own.
+    n_chains = 3 if (args.chains == "3" or (args.chains == "auto" and world > 1 and p2p)) else 1
+    side_streams = [torch.cuda.Stream(dev) for _ in range(2)] if n_chains == 3 else []
+
     def step(xs, record=False, local=False):
         """One pass of the hot path; returns the QKV, O and down-projection outputs.  `local`:
         `xs` holds only this rank's 1/w of the token rows (the end-to-end path, where each rank
         copies its rows in from the host)."""
-        a, s = encode(0, xs, local)
-        qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"))
-        a, s = encode(1, xs, local)
-        o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"))
+        forked = n_chains == 3 and not record
+        if forked:
+            cur = torch.cuda.current_stream(dev)
+            fork = torch.cuda.Event()
+            fork.record(cur)
+            joins = []
+            for i, (sd, nm, w_, s_, out_) in enumerate(((side_streams[0], "qkv", w_qkv, s_qkv, out_qkv),
+                                                        (side_streams[1], "o", w_o, s_o, out_o))):
+                with torch.cuda.stream(sd), _lib.workspace_tag(nm):
+                    sd.wait_event(fork)
+                    a, s = encode(i, xs, local)
+                    res = gemm(a, s, w_, s_, out_, peer=peers.get(nm))
+                    ev = torch.cuda.Event()
+                    ev.record(sd)
+                    joins.append((ev, res))
+            qkv, o = joins[0][1], joins[1][1]
+        else:
+            a, s = encode(0, xs, local)
+            qkv = gemm(a, s, w_qkv, s_qkv, out_qkv, record=record, peer=peers.get("qkv"))
+            a, s = encode(1, xs, local)
+            o = gemm(a, s, w_o, s_o, out_o, record=record, peer=peers.get("o"))
         a, s = encode(2, xs, local)
         if hidden is not None:
             # The gate/up output only feeds the per-token encode of the down projection: keep the
@@ -346,6 +371,9 @@ def run_b200_arm(args):
             a, s = Q.quantize_per_token(h, Q.qint8)
         # the down projection contracts over the full ffn width: K is not sharded
         d = gemm(a, s, w_d, s_d, out_d, record=record, peer=peers.get("d"))
+        if forked:
+            for ev, _ in joins:
+                cur.wait_event(ev)
         for name in ("qkv", "o", "d"):
             if name in peers:
                 peers[name].sync.wait()
@@ -1167,6 +1195,9 @@ def main():
     ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
                          "(auto: off on the device-timed path; the end-to-end path always shards)")
+    ap.add_argument("--chains", default="auto", choices=["auto", "1", "3"],
+                    help="issue the QKV, O and MLP chains of a step on one stream or forked over three "
+                         "(auto: three when the step is sharded with the p2p exchange)")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: store through the NVSwitch multicast address of the buffers (auto: at 8 ranks)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-unicast", "nccl"],

@@ -11,6 +11,7 @@ from __future__ import annotations
 import contextlib
 import ctypes as C
 import os
+import threading
 
 import torch
 
@@ -245,23 +246,37 @@ def minmax_workspace(device: torch.device) -> torch.Tensor:
 
 
 _gemm_ws: dict = {}
+_ws_tag = threading.local()
+
+
+@contextlib.contextmanager
+def workspace_tag(tag):
+    """Contractions issued inside run on a workspace of their own when they are captured in a
+    CUDA graph.  Launches that may run concurrently (branches of a graph, i.e. independent chains
+    of a step forked over several streams) must not share the scratch: give each branch its tag."""
+    prev = getattr(_ws_tag, "value", None)
+    _ws_tag.value = tag
+    try:
+        yield
+    finally:
+        _ws_tag.value = prev
 
 
 def gemm_workspace(device: torch.device) -> torch.Tensor:
     """Zero-initialised scratch of the integer contraction (stream-K partial tiles, exchange
     ticket) for the current (device, stream); the kernels leave it zeroed."""
+    cap_key = (device.index, "capture", getattr(_ws_tag, "value", None))
     if torch.cuda.is_current_stream_capturing():
         # A capture runs on a stream of its own; allocating (and zero-filling) a workspace there
-        # would put a 24 MB fill into every replay.  Captured steps share one workspace per device,
-        # created eagerly below, so run the step once before capturing it.
-        ws = _gemm_ws.get((device.index, "capture"))
+        # would put a 24 MB fill into every replay.  Captured launches use one workspace per
+        # device and tag, created eagerly below, so run the step once before capturing it.
+        ws = _gemm_ws.get(cap_key)
         if ws is None:
             raise LucidError("run the step once eagerly before capturing it in a CUDA graph "
                              "(the contraction's workspace is created on first use)")
         return ws
-    if (device.index, "capture") not in _gemm_ws:
-        _gemm_ws[(device.index, "capture")] = torch.zeros(int(load().lq_gemm_workspace_bytes()),
-                                                          dtype=torch.uint8, device=device)
+    if cap_key not in _gemm_ws:
+        _gemm_ws[cap_key] = torch.zeros(int(load().lq_gemm_workspace_bytes()), dtype=torch.uint8, device=device)
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _gemm_ws.get(key)
     if ws is None:
@@ -308,8 +323,8 @@ def check_device_status(device: torch.device) -> None:
     if code != 0 or n.value != 0:
         if w is not None:
             w.zero_()
-        for (dev_index, _), ws in _gemm_ws.items():
-            if dev_index == device.index:
+        for key, ws in _gemm_ws.items():
+            if key[0] == device.index:
                 ws.zero_()
         what = f"status {code}" if code else f"{n.value} pipelined stream launch(es) gave up"
         raise _STATUS_EXC.get(code or ERR_TIMEOUT, LucidError)(f"lucid_b200: device-side {what}")
