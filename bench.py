@@ -298,6 +298,11 @@ def run_b200_arm(args):
     use_mc = bool(peers) and mc_wanted and args.exchange != "p2p-unicast" and \
         all(p.has_multicast for p in peers.values())
 
+    # default: a kernel of its own when the chains are forked (that is where freeing the SMs early
+    # pays: 8 ranks 0.868 -> 0.804 ms, 4 ranks unchanged), fused into the GEMM on one stream
+    split_signal = args.exchange_signal == "kernel" or (
+        args.exchange_signal == "auto" and (args.chains == "3" or (args.chains == "auto" and world > 1)))
+
     def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, wait=False, gather=True):
         if record:
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
@@ -306,8 +311,16 @@ def run_b200_arm(args):
             QF.gemm_s8(a, w, a_scale=a_s, b_scale=w_s, act=act, out=out)
         else:
             buf, ptrs = peer.next(multicast=use_mc)
-            QF.gemm_s8_bcast(a, w, ptrs, (peer.rows, peer.cols), rank * out.shape[1], a_scale=a_s,
-                             b_scale=w_s, act=act, signal=peer.sync.signal_arg)
+            if split_signal:
+                # The kernel's CTAs leave as soon as their stores are issued -- the SMs go to the
+                # other chains while the link drains -- and a one-thread kernel behind it on the
+                # stream (which starts once the GEMM's writes are complete) publishes the flag.
+                QF.gemm_s8_bcast(a, w, ptrs, (peer.rows, peer.cols), rank * out.shape[1], a_scale=a_s,
+                                 b_scale=w_s, act=act)
+                peer.sync.signal()
+            else:
+                QF.gemm_s8_bcast(a, w, ptrs, (peer.rows, peer.cols), rank * out.shape[1], a_scale=a_s,
+                                 b_scale=w_s, act=act, signal=peer.sync.signal_arg)
         if record:
             e1.record()
             gemm_events.append((e0, e1))
@@ -385,6 +398,8 @@ def run_b200_arm(args):
         launches_per_step = 8
     else:
         launches_per_step = 4 + 3 + (3 * 3 if shard_inputs else 3) + (6 if hidden is not None else 2)
+        if split_signal:
+            launches_per_step += 3 if hidden is not None else 4  # one signal kernel per exchanging GEMM
 
     def barrier():
         if world > 1:
@@ -1195,6 +1210,9 @@ def main():
     ap.add_argument("--shard-encode", default="auto", choices=["auto", "on", "off"],
                     help="N > 1, p2p: shard the per-token encodes of the replicated inputs over token rows "
                          "(auto: off on the device-timed path; the end-to-end path always shards)")
+    ap.add_argument("--exchange-signal", default="auto", choices=["auto", "fused", "kernel"],
+                    help="N > 1, p2p: the GEMM publishes its step count itself after a system-wide fence in "
+                         "every CTA (fused), or a one-thread kernel behind it does (kernel; auto: with forked chains)")
     ap.add_argument("--chains", default="auto", choices=["auto", "1", "3"],
                     help="issue the QKV, O and MLP chains of a step on one stream or forked over three "
                          "(auto: three when the step is sharded with the p2p exchange)")

@@ -126,6 +126,48 @@ def test_stream_k_shard_shapes_bit_equal(m, n, k, monkeypatch):
     _sync_status()
 
 
+def test_concurrent_contractions_in_one_graph_use_their_own_scratch():
+    """Two stream-K contractions forked over two streams inside one CUDA graph may run at the
+    same time; each branch names its own workspace (`workspace_tag`), and the replayed results
+    equal the eager ones."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    ops = []
+    for m, n, k in ((4096, 1280, 8192), (4096, 1024, 8192)):  # both cut their partial wave across CTAs
+        a = torch.randint(-128, 128, (m, k), dtype=torch.int8, device="cuda", generator=g)
+        b = torch.randint(-128, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+        ops.append((a, b, QF.gemm_s8(a, b, out_dtype=torch.int32), torch.empty((m, n), dtype=torch.int32, device="cuda")))
+    side = torch.cuda.Stream()
+
+    def both():
+        cur = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        with torch.cuda.stream(side), _lib.workspace_tag("side"):
+            side.wait_event(fork)
+            QF.gemm_s8(ops[1][0], ops[1][1], out_dtype=torch.int32, out=ops[1][3])
+            join = torch.cuda.Event()
+            join.record(side)
+        QF.gemm_s8(ops[0][0], ops[0][1], out_dtype=torch.int32, out=ops[0][3])
+        cur.wait_event(join)
+
+    warm = torch.cuda.Stream()
+    warm.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(warm):
+        both()  # creates the workspaces eagerly
+    torch.cuda.current_stream().wait_stream(warm)
+    torch.cuda.synchronize()
+    gph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gph):
+        both()
+    for _ in range(5):
+        for _, _, _, out in ops:
+            out.zero_()
+        gph.replay()
+        torch.cuda.synchronize()
+        assert all(torch.equal(out, ref) for _, _, ref, out in ops)
+    _sync_status()
+
+
 def _c2_like(m, k, n, seed=1):
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((m, k)).astype(np.float32)
