@@ -525,21 +525,19 @@ int make_params(const float* scale, const float* zp, float sv, float zv, int ch_
 
 // tuning knobs of the stream kernels (environment, read once; lq_reload_env re-reads)
 struct StreamKnobs {
-  int ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4, lean = 1, minmax_pipe = 0, minmax_deep = 0;
+  int ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 6, lean = 1, minmax_pipe = 0;
   int token_pipe_min_row = 16 * 1024, token_ring_kb = 0, token_reg_threads = 256;
   void read() {
-    ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 4, lean = 1, minmax_pipe = 0;
+    ctas_per_sm = 0, unroll = 4, minmax_ctas_per_sm = 6, lean = 1, minmax_pipe = 0;
     token_pipe_min_row = 16 * 1024, token_ring_kb = 0, token_reg_threads = 256;
     if (const char* e = getenv("LQ_TOKEN_REG_THREADS")) token_reg_threads = atoi(e) == 128 ? 128 : 256;
     if (const char* e = getenv("LQ_TOKEN_PIPE_MIN_ROW")) token_pipe_min_row = atoi(e);
     if (const char* e = getenv("LQ_TOKEN_RING_KB")) token_ring_kb = atoi(e) > 0 && atoi(e) <= 96 ? atoi(e) : 0;
     if (const char* e = getenv("LQ_MINMAX_PIPE")) minmax_pipe = atoi(e);
-    minmax_deep = 0;
-    if (const char* e = getenv("LQ_MINMAX_DEEP")) minmax_deep = atoi(e);
     if (const char* e = getenv("LQ_QUANT_LEAN")) lean = atoi(e);
     if (const char* e = getenv("LQ_QUANT_CTAS_PER_SM")) ctas_per_sm = atoi(e);
     if (const char* e = getenv("LQ_QUANT_UNROLL")) unroll = atoi(e) == 2 ? 2 : 4;
-    if (const char* e = getenv("LQ_MINMAX_CTAS_PER_SM")) minmax_ctas_per_sm = atoi(e) > 0 ? atoi(e) : 4;
+    if (const char* e = getenv("LQ_MINMAX_CTAS_PER_SM")) minmax_ctas_per_sm = atoi(e) > 0 ? atoi(e) : 6;
   }
 };
 StreamKnobs& stream_knobs() {
@@ -611,23 +609,13 @@ struct AbsMax<__nv_bfloat16> {
 
 // x[0..n): lane `first` of `stride` cooperating threads.  16-byte vectors, consecutive
 // threads on consecutive vectors, four loads in flight per thread.
-template <typename In, bool kDeep = false>
+template <typename In>
 __device__ __forceinline__ void minmax_accumulate(const In* x, size_t n, size_t first, size_t stride,
                                                   bool vec_ok, float& mn, float& mx) {
   constexpr int E = VecOf<In>::kElems;
   const size_t nvec = vec_ok ? n / E : 0;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   size_t i = first;
-  if (kDeep) {
-    // eight loads in flight per thread (fewer, longer iterations)
-    for (; i + 7 * stride < nvec; i += 8 * stride) {
-      uint4 v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = ld_stream_u4(xv + i + j * stride);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) vec_minmax<In>(v[j], mn, mx);
-    }
-  }
   for (; i + 3 * stride < nvec; i += 4 * stride) {
     const uint4 a = ld_stream_u4(xv + i), b = ld_stream_u4(xv + i + stride);
     const uint4 c = ld_stream_u4(xv + i + 2 * stride), d = ld_stream_u4(xv + i + 3 * stride);
@@ -968,15 +956,15 @@ __device__ __forceinline__ void finish_tensor_minmax(float mn, float mx, MinMaxW
   ws->ticket = 0;  // leave the workspace zeroed for the next call
 }
 
-template <typename In, bool kDeep>
+template <typename In>
 __global__ void __launch_bounds__(kThreads)
 minmax_tensor_kernel(const In* __restrict__ x, size_t n, bool vec_ok, MinMaxWorkspace* ws,
                      float* out_min, float* out_max, FusedQParams fq) {
   pdl_wait();  // launched through launch_pdl(): nothing above touches global memory
   pdl_launch_dependents();
   float mn = INFINITY, mx = -INFINITY;
-  minmax_accumulate<In, kDeep>(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
-                               (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
+  minmax_accumulate(x, n, (size_t)blockIdx.x * kThreads + threadIdx.x,
+                    (size_t)gridDim.x * kThreads, vec_ok, mn, mx);
   finish_tensor_minmax(mn, mx, ws, out_min, out_max, fq);
 }
 
@@ -1293,14 +1281,10 @@ int minmax_tensor_launch(const void* x, int in_dtype, size_t n, MinMaxWorkspace*
     else
       minmax_pipe_kernel<__nv_bfloat16><<<pgrid, kThreads, smem, st>>>((const __nv_bfloat16*)x, n, ws, out_min, out_max, stages);
   } else if (in_dtype == LQ_F32) {
-    return check_cuda(stream_knobs().minmax_deep
-                          ? launch_pdl(minmax_tensor_kernel<float, true>, dim3(grid), dim3(kThreads), 0, st,
-                                       (const float*)x, n, vec_ok, ws, out_min, out_max, fq)
-                          : launch_pdl(minmax_tensor_kernel<float, false>, dim3(grid), dim3(kThreads), 0, st,
-                                       (const float*)x, n, vec_ok, ws, out_min, out_max, fq),
-                      "minmax launch");
+    return check_cuda(launch_pdl(minmax_tensor_kernel<float>, dim3(grid), dim3(kThreads), 0, st, (const float*)x, n, vec_ok,
+                                 ws, out_min, out_max, fq), "minmax launch");
   } else {
-    return check_cuda(launch_pdl(minmax_tensor_kernel<__nv_bfloat16, false>, dim3(grid), dim3(kThreads), 0, st,
+    return check_cuda(launch_pdl(minmax_tensor_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), 0, st,
                                  (const __nv_bfloat16*)x, n, vec_ok, ws, out_min, out_max, fq), "minmax launch");
   }
   return check_cuda(cudaGetLastError(), "range reduction launch");
