@@ -298,10 +298,10 @@ def run_b200_arm(args):
     use_mc = bool(peers) and mc_wanted and args.exchange != "p2p-unicast" and \
         all(p.has_multicast for p in peers.values())
 
-    # default: a kernel of its own when the chains are forked (that is where freeing the SMs early
-    # pays: 8 ranks 0.868 -> 0.804 ms, 4 ranks unchanged), fused into the GEMM on one stream
+    # default: a kernel of its own at 8 ranks with forked chains (that is where freeing the SMs
+    # early pays: 0.868 -> 0.804 ms; 4 ranks unchanged, 2 ranks 2 % slower), fused otherwise
     split_signal = args.exchange_signal == "kernel" or (
-        args.exchange_signal == "auto" and (args.chains == "3" or (args.chains == "auto" and world > 1)))
+        args.exchange_signal == "auto" and world >= 8 and args.chains in ("auto", "3"))
 
     def gemm(a, a_s, w, w_s, out, act=_lib.ACT_NONE, record=False, peer=None, wait=False, gather=True):
         if record:
@@ -1282,7 +1282,7 @@ def main():
                          "(auto: off on the device-timed path; the end-to-end path always shards)")
     ap.add_argument("--exchange-signal", default="auto", choices=["auto", "fused", "kernel"],
                     help="N > 1, p2p: the GEMM publishes its step count itself after a system-wide fence in "
-                         "every CTA (fused), or a one-thread kernel behind it does (kernel; auto: with forked chains)")
+                         "every CTA (fused), or a one-thread kernel behind it does (kernel; auto: at 8 ranks with forked chains)")
     ap.add_argument("--mlp-chunks", default="auto", choices=["auto", "1", "2", "4"],
                     help="N > 1, forked chains, hidden tensor as codes: split the MLP chain into blocks of token "
                          "rows on two streams (auto: 2 at 8 ranks)")
