@@ -378,6 +378,7 @@ struct RowCtx {
   // [clo, chi] (a ReLU is folded into clo) unless the saturating pack already does that
   int zofs, clo, chi;
   bool need_clamp, out_signed;
+  bool grid_ok;  // the output grid is inside the short division's domain (else: full-range blocks)
   uint32_t row_mask; // valid rows of this warp (bit r = tile row quad*32 + r)
   long long row0;    // global output row of the warp's first row
 };
@@ -662,7 +663,7 @@ __device__ __forceinline__ void epilogue_tile_q8(const Epi& ep, const RowCtx& rc
   auto finish_block = [&](uint32_t (&acc)[16], int blk) {
     if (ps.n) add_partials16<BN>(acc, ps, quad, (c0 >> 4) + blk, lane);
     uint32_t w[4];
-    float big = 0.0f;
+    float big = rc.grid_ok ? 0.0f : INFINITY;
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       const float4 s4 = *reinterpret_cast<const float4*>(t_scale + blk * 16 + 4 * q4);
@@ -1037,6 +1038,7 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // a positive output scale in the short division's range and an integral zero point
     const bool q8_lean_grid = rc_launch.so.fast && rc_launch.so.s > 0.0f && fabsf(rc_launch.zo) <= 512.0f &&
                               rc_launch.zo == rintf(rc_launch.zo);
+    rc_launch.grid_ok = q8_lean_grid;
     const int q8_mask = (ep.bias != nullptr ? 1 : 0) | (ep.act == LQ_ACT_RELU ? 2 : 0) |
                         ((ep.b_rowsum != nullptr && rc_launch.zpa != 0) ? 4 : 0);
     int q8_filled_tn = -1;  // column of tiles whose parameters this warp's table holds
@@ -1113,6 +1115,12 @@ gemm_s8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           } else {
             epilogue_tile<BN, KIND_S32, false, PARTS>(ep, g, rc, taddr, stg, lane, part, n0, n0, ps, quad);
           }
+        } else if constexpr (FAM == 2) {
+          // every tile is eligible for the requantising loop (checked by the launcher); an output
+          // grid outside the short division's domain sends every block through its full-range
+          // sequence (rc.grid_ok)
+          q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
+          q8_filled_tn = tn_idx;
         } else {
           if (q8_lean && q8_lean_grid && n0 + BN <= g.N) {
             q8_dispatch<BN, PARTS>(q8_mask, ep, rc, taddr, stg, lane, part, n0, q8_filled_tn != tn_idx, ps, quad);
@@ -1338,7 +1346,7 @@ void fill_epi(Epi* d, const lq_epilogue_t* e, void* out, size_t ldo, size_t n_ou
 // schedule (the tests cover every variant this way; all of them compute the same numbers),
 // LQ_GEMM_VERBOSE prints each launch's geometry.
 struct Knobs {
-  int shape = -1, epi_warps = 0, streamk = -1, bcast_epi_warps = 0;
+  int shape = -1, epi_warps = 0, streamk = -1, bcast_epi_warps = 0, q8_lean_only = 1, q8_epi_warps = 8;
   // policy thresholds: stream-K when the last wave fills less than this percentage of the
   // workers and a tile has at least this many k-blocks.  Measured on the Llama-2-70B shard
   // shapes: +14 % at 4096 x 4096 x 28672 (34 of 74 clusters in the last wave, 224 k-blocks),
@@ -1350,6 +1358,9 @@ struct Knobs {
   void read() {
     shape = -1, epi_warps = 0, streamk = -1, bcast_epi_warps = 0;
     if (const char* f = getenv("LQ_GEMM_BCAST_EPI_WARPS")) bcast_epi_warps = atoi(f);
+    q8_lean_only = 1, q8_epi_warps = 8;
+    if (const char* f = getenv("LQ_GEMM_Q8_LEAN_ONLY")) q8_lean_only = atoi(f);
+    if (const char* f = getenv("LQ_GEMM_Q8_EPI_WARPS")) q8_epi_warps = atoi(f) == 16 ? 16 : 8;
     if (const char* f = getenv("LQ_GEMM_STREAMK_MAX_FILL")) streamk_max_fill = atoi(f);
     if (const char* f = getenv("LQ_GEMM_STREAMK_MIN_KB")) streamk_min_kb = atoi(f);
     if (const char* f = getenv("LQ_GEMM_SHAPE")) {
@@ -1455,7 +1466,13 @@ int launch_fam(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g_i
 template <int BN, bool PAIR, int EW>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Geometry& g, const Epi& ep, uint32_t idesc,
            cudaStream_t st) {
-  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) return launch_fam<BN, PAIR, EW, 1>(ta, tb, g, ep, idesc, st);
+  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) {
+    // every tile eligible for the requantising loop: the kernel that holds nothing else
+    const bool lean_only = ep.n_dst == 1 && !ep.multicast && ep.vec_ok && ep.par_vec && ep.a_scale_mode != LQ_PER_ROW &&
+                           g.N % BN == 0 && knobs().q8_lean_only;
+    if (lean_only) return launch_fam<BN, PAIR, EW, 2>(ta, tb, g, ep, idesc, st);
+    return launch_fam<BN, PAIR, EW, 1>(ta, tb, g, ep, idesc, st);
+  }
   return launch_fam<BN, PAIR, EW, 0>(ta, tb, g, ep, idesc, st);
 }
 
@@ -1513,7 +1530,7 @@ int dispatch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, Geo
   // ... except 8-bit outputs: at 96 registers per thread (18 warps) the requantising loop spills
   // and reloads through L2; 8 warps at 168 registers measured 51.7 us against 65.7 us on
   // 50176 x 1024 x 256 and 33.4 against 37.8 us on 50176 x 256 x 2304
-  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) wide_epi = false;
+  if (ep.out_dtype == LQ_S8 || ep.out_dtype == LQ_U8) wide_epi = knobs().q8_epi_warps == 16;
   // tiles that also travel to peer GPUs: their stores take longer to issue
   if ((ep.n_dst > 1 || ep.multicast) && knobs().bcast_epi_warps) wide_epi = knobs().bcast_epi_warps == 16;
   if (knobs().epi_warps) wide_epi = knobs().epi_warps == 16;
