@@ -4,7 +4,7 @@ the dynamic Linear family, the boundary stubs, the element-wise merges and the a
 
 from . import dynamic, functional  # noqa: F401
 from .activation import ELU, Hardsigmoid, Hardswish, LeakyReLU, ReLU, Sigmoid, Tanh  # noqa: F401
-from .conv import Conv2d, ConvReLU2d  # noqa: F401
+from .conv import Conv1d, Conv2d, Conv3d, ConvReLU1d, ConvReLU2d, ConvReLU3d  # noqa: F401
 from .conv_transpose import ConvTranspose1d, ConvTranspose2d, ConvTranspose3d  # noqa: F401
 from .functional_module import FloatFunctional, QFunctional  # noqa: F401
 from .linear import Linear, LinearReLU  # noqa: F401

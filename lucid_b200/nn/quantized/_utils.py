@@ -19,7 +19,7 @@ class QCodes:
     codes: torch.Tensor       # int8 or uint8, same shape as the float tensor (NHWC for conv)
     scale: torch.Tensor       # 0-d f32
     zero_point: torch.Tensor  # 0-d f32
-    layout: str = "rowmajor"  # "rowmajor" | "nhwc"
+    layout: str = "rowmajor"  # "rowmajor" | "nhwc" | "nlc" (1-D convolutions: (N, L, C))
     zp_is_zero: bool | None = None  # known on the host without a sync, when not None
     # identity of the float tensor at tag time (set by `tag`): an in-place op on the tensor
     # (relu_(), `y += identity`, nn.ReLU(inplace=True)) keeps the Python attribute but bumps

@@ -59,6 +59,8 @@ class _QuantizedActivation(torch.nn.Module):
             y = dequantize(out, self.scale, self.zero_point)
             if qc.layout == "nhwc":
                 y = y.permute(0, 3, 1, 2)
+            elif qc.layout == "nlc":
+                y = y.permute(0, 2, 1)
             return tag(y, QCodes(out, self.scale, self.zero_point, qc.layout))
         return fake_quantize(self._act(x.to(torch.float32)).contiguous(), self.scale, self.zero_point,
                              self.qdtype.quant_min, self.qdtype.quant_max)

@@ -199,3 +199,156 @@ class ConvReLU2d(Conv2d):
     """Quantized Conv2d with the ReLU fused ahead of the output grid."""
 
     _RELU = True
+
+
+class Conv1d(Conv2d):
+    """Quantized Conv1d (lucid/nn/quantized/conv.py:232-385) on the same implicit GEMM: an
+    ``(N, C, L)`` signal is an ``(N, C, 1, L)`` image and the ``(Cout, Cin/g, k)`` kernel a
+    ``1 x k`` one.  Buffers keep the reference's shapes in ``state_dict`` (the weight is stored
+    3-D); inside the module it carries the unit height."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0,
+                 dilation=1, groups: int = 1, bias: bool = True) -> None:
+        def one(v):
+            return int(v[0]) if isinstance(v, (tuple, list)) else int(v)
+        super().__init__(in_channels, out_channels, (1, one(kernel_size)), (1, one(stride)), (0, one(padding)),
+                         (1, one(dilation)), groups, bias)
+        self._register_state_dict_hook(self._squeeze_weight)
+        self._register_load_state_dict_pre_hook(self._unsqueeze_weight)
+
+    @staticmethod
+    def _squeeze_weight(module, state, prefix, _meta):
+        key = prefix + "weight_int8"
+        if key in state and state[key].dim() == 4:
+            state[key] = state[key].squeeze(2)
+        return state
+
+    def _unsqueeze_weight(self, state, prefix, *_):
+        key = prefix + "weight_int8"
+        if key in state and state[key].dim() == 3:
+            state[key] = state[key].unsqueeze(2)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() != 3:
+            raise _lib.ShapeMismatch(f"{type(self).__name__} expects (N, C, L), got {tuple(x.shape)}")
+        # codes ride along as (N, L, C) ("nlc") between 1-D layers, or arrive (N, C, L) from a stub
+        qc = codes_of(x)
+        x4 = x.unsqueeze(2)
+        if qc is not None and qc.codes.dim() == 3 and qc.codes.dtype in (torch.int8, torch.uint8):
+            nlc = qc.codes if qc.layout == "nlc" else qc.codes.permute(0, 2, 1).contiguous()
+            x4 = tag(x4, QCodes(nlc.unsqueeze(1), qc.scale, qc.zero_point, "nhwc", qc.zp_is_zero))
+        y4 = super().forward(x4)
+        y = y4.squeeze(2)
+        q4 = codes_of(y4)
+        if q4 is not None and q4.layout == "nhwc":
+            y = tag(y, QCodes(q4.codes.squeeze(1), q4.scale, q4.zero_point, "nlc", q4.zp_is_zero))
+        return y
+
+    @classmethod
+    def from_float(cls, mod: torch.nn.Module) -> "Conv1d":
+        inner = mod[0] if isinstance(mod, torch.nn.Sequential) else mod
+        padding = inner.padding if not isinstance(inner.padding, str) else 0
+        qmod = cls(inner.in_channels, inner.out_channels, inner.kernel_size, inner.stride, padding,
+                   inner.dilation, inner.groups, bias=inner.bias is not None)
+        if not hasattr(inner, "qconfig") and hasattr(mod, "qconfig"):
+            inner.qconfig = mod.qconfig
+        codes, w_scale, w_zp, ch_axis = quantize_weight(inner)
+        qmod.weight_int8, qmod.weight_scale, qmod.weight_zero_point = codes.unsqueeze(2), w_scale, w_zp
+        qmod.weight_ch_axis = ch_axis
+        qmod.padding_str = inner.padding if isinstance(inner.padding, str) else \
+            getattr(inner, "_padding_str", None)
+        qmod.padding_mode = getattr(inner, "padding_mode", "zeros")
+        if inner.bias is not None:
+            qmod.bias = inner.bias.detach().to(torch.float32)
+        src = mod if hasattr(mod, "activation_post_process") else inner
+        a_scale, a_zp, a_qdtype = activation_qparams(src)
+        qmod.scale, qmod.zero_point, qmod.out_qdtype = a_scale, a_zp, a_qdtype
+        return qmod
+
+    def extra_repr(self) -> str:
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size[1:]}, "
+                f"stride={self.stride[1:]}, qdtype={self.out_qdtype.name}")
+
+
+class ConvReLU1d(Conv1d):
+    """Quantized Conv1d with the ReLU fused ahead of the output grid
+    (lucid/nn/quantized/intrinsic.py)."""
+
+    _RELU = True
+
+
+class Conv3d(torch.nn.Module):
+    """Quantized Conv3d (lucid/nn/quantized/conv.py:545-700): the reference's sequence --
+    dequantize the weight, float convolution, activation, fake-quantize onto the output grid --
+    around the library's float kernel with TF32 off.  (The implicit-GEMM kernel walks two spatial
+    axes; volumes take this route.)"""
+
+    _RELU = False
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0,
+                 dilation=1, groups: int = 1, bias: bool = True) -> None:
+        super().__init__()
+
+        def triple(v):
+            return (v, v, v) if isinstance(v, int) else tuple(v)
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size = triple(kernel_size)
+        self.stride, self.padding, self.dilation = triple(stride), triple(padding), triple(dilation)
+        self.groups = groups
+        self.padding_str: str | None = None
+        self.padding_mode = "zeros"
+        self.weight_ch_axis = 0
+        self.out_qdtype: QDtype = quint8
+        self.register_buffer("weight_int8", torch.zeros((out_channels, in_channels // groups, *self.kernel_size),
+                                                        dtype=torch.int8))
+        self.register_buffer("weight_scale", torch.ones(out_channels))
+        self.register_buffer("weight_zero_point", torch.zeros(out_channels))
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_channels))
+        else:
+            self.bias = None
+        self.register_buffer("scale", torch.tensor(1.0))
+        self.register_buffer("zero_point", torch.tensor(0.0))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        _lib.require_cuda(x, "input")
+        w = dequantize(self.weight_int8, self.weight_scale, self.weight_zero_point, ch_axis=self.weight_ch_axis)
+        x = x.to(torch.float32)
+        pad = self.padding_str if self.padding_str is not None else self.padding
+        with _lib.ieee_float32():
+            if self.padding_mode != "zeros" and not isinstance(pad, str):
+                rev = [p for d in reversed(pad) for p in (d, d)]
+                y = F.conv3d(F.pad(x, rev, mode=self.padding_mode), w, self.bias, self.stride, 0, self.dilation,
+                             self.groups)
+            else:
+                y = F.conv3d(x, w, self.bias, self.stride, pad, self.dilation, self.groups)
+        y = (F.relu(y) if self._RELU else y).contiguous()
+        return fake_quantize(y, self.scale, self.zero_point, self.out_qdtype.quant_min, self.out_qdtype.quant_max)
+
+    @classmethod
+    def from_float(cls, mod: torch.nn.Module) -> "Conv3d":
+        inner = mod[0] if isinstance(mod, torch.nn.Sequential) else mod
+        padding = inner.padding if not isinstance(inner.padding, str) else 0
+        qmod = cls(inner.in_channels, inner.out_channels, inner.kernel_size, inner.stride, padding,
+                   inner.dilation, inner.groups, bias=inner.bias is not None)
+        if not hasattr(inner, "qconfig") and hasattr(mod, "qconfig"):
+            inner.qconfig = mod.qconfig
+        codes, w_scale, w_zp, ch_axis = quantize_weight(inner)
+        qmod.weight_int8, qmod.weight_scale, qmod.weight_zero_point = codes, w_scale, w_zp
+        qmod.weight_ch_axis = ch_axis
+        qmod.padding_str = inner.padding if isinstance(inner.padding, str) else None
+        qmod.padding_mode = getattr(inner, "padding_mode", "zeros")
+        if inner.bias is not None:
+            qmod.bias = inner.bias.detach().to(torch.float32)
+        src = mod if hasattr(mod, "activation_post_process") else inner
+        a_scale, a_zp, a_qdtype = activation_qparams(src)
+        qmod.scale, qmod.zero_point, qmod.out_qdtype = a_scale, a_zp, a_qdtype
+        return qmod
+
+    def extra_repr(self) -> str:
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, "
+                f"stride={self.stride}, qdtype={self.out_qdtype.name}")
+
+
+class ConvReLU3d(Conv3d):
+    _RELU = True

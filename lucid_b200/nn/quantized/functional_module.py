@@ -151,6 +151,8 @@ def qmerge(op: int, x, y, scale, zero_point, qdtype: QDtype = quint8, cache: _Ta
         _launch_qmerge(op, xa, xd, xs, xz, ya, yd, ys, yz, scalar, s, z, qdtype, codes, out)
     if layout == "nhwc":  # codes are NHWC; the float carrier is the logical NCHW view of them
         out = out.permute(0, 3, 1, 2)
+    elif layout == "nlc":  # 1-D convolutions: codes (N, L, C), carrier (N, C, L)
+        out = out.permute(0, 2, 1)
     if codes is None:
         return out
     return tag(out, QCodes(codes, s, z, layout))

@@ -52,8 +52,9 @@ def _observed_types() -> tuple:
     from ..nn.quantized.functional_module import FloatFunctional
 
     nni = _intrinsic()
-    fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
-    return (torch.nn.Linear, torch.nn.Conv2d, QuantStub, FloatFunctional) + _ACTIVATIONS + _CONV_TRANSPOSE + fused
+    fused = (nni.LinearReLU, nni.ConvReLU1d, nni.ConvReLU2d, nni.ConvReLU3d) if nni is not None else ()
+    return (torch.nn.Linear, torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d, QuantStub, FloatFunctional) + \
+        _ACTIVATIONS + _CONV_TRANSPOSE + fused
 
 
 def _quant_mapping() -> dict:
@@ -61,7 +62,9 @@ def _quant_mapping() -> dict:
 
     m = {
         torch.nn.Linear: nnq.Linear.from_float,
+        torch.nn.Conv1d: nnq.Conv1d.from_float,
         torch.nn.Conv2d: nnq.Conv2d.from_float,
+        torch.nn.Conv3d: nnq.Conv3d.from_float,
         QuantStub: nnq.Quantize.from_float,
         DeQuantStub: nnq.DeQuantize.from_float,
         torch.nn.ReLU: nnq.ReLU.from_float,
@@ -79,7 +82,9 @@ def _quant_mapping() -> dict:
     nni = _intrinsic()
     if nni is not None:
         m[nni.LinearReLU] = nnq.LinearReLU.from_float
+        m[nni.ConvReLU1d] = nnq.ConvReLU1d.from_float
         m[nni.ConvReLU2d] = nnq.ConvReLU2d.from_float
+        m[nni.ConvReLU3d] = nnq.ConvReLU3d.from_float
     from ..nn import qat as nnqat
 
     m[nnqat.Linear] = nnq.Linear.from_float
@@ -109,7 +114,7 @@ def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: boo
     model.eval()
     observed = _observed_types()
     nni = _intrinsic()
-    fused = (nni.LinearReLU, nni.ConvReLU2d) if nni is not None else ()
+    fused = (nni.LinearReLU, nni.ConvReLU1d, nni.ConvReLU2d, nni.ConvReLU3d) if nni is not None else ()
     inside_fused = set()
     n_matched = 0
     for name, mod in model.named_modules():

@@ -366,3 +366,57 @@ class _CountConvT:
         import torch.nn.functional as F
 
         F.conv_transpose2d = self._orig
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,groups", [(32, 48, 3, 1, 1, 1, 1), (64, 64, 5, 2, 2, 1, 2),
+                                                              (16, 32, 3, 1, "same", 2, 1)])
+def test_conv1d_integer_route_equals_float_form(cin, cout, k, stride, pad, dil, groups):
+    """Conv1d on the implicit GEMM (a signal is a one-row image): the integer route and the
+    reference's dequantize -> float conv -> fake-quantize route agree up to one output step at a
+    few positions, and the state dict keeps the reference's 3-D weight."""
+    import lucid_b200.backends as backends
+
+    g = torch.Generator(device="cuda").manual_seed(cin + k)
+    conv = torch.nn.Conv1d(cin, cout, k, stride=stride, padding=pad, dilation=dil, groups=groups).cuda()
+    x0 = torch.randn(3, cin, 97, device="cuda", generator=g)
+    xs, xz = Q.calculate_qparams(float(x0.min()), float(x0.max()), Q.per_tensor_affine, Q.quint8)
+    x = nnq.Quantize(xs, xz, Q.quint8)(x0)  # on a grid, carrying its codes, like a stub's output
+    with _lib.ieee_float32(), torch.no_grad():
+        y_float = torch.relu(conv(x))
+    obs = Q.MinMaxObserver()
+    obs(y_float.contiguous())
+    conv.activation_post_process = obs
+    qm = nnq.ConvReLU1d.from_float(conv)
+    assert qm.state_dict()["weight_int8"].shape == (cout, cin // groups, k)
+    clone = nnq.ConvReLU1d(cin, cout, k, stride=stride, padding=0 if isinstance(pad, str) else pad, dilation=dil,
+                           groups=groups).cuda()
+    clone.load_state_dict(qm.state_dict())
+    clone.padding_str, clone.out_qdtype = qm.padding_str, qm.out_qdtype
+    y = qm(x)
+    _sync_status()
+    assert y.shape == y_float.shape and torch.equal(clone(x), y)
+    old = backends.quantized.engine
+    backends.quantized.engine = "reference"
+    try:
+        y_ref = qm(x)
+    finally:
+        backends.quantized.engine = old
+    diff = (y - y_ref).abs()
+    assert float((diff > 0).float().mean()) < 0.02 and float(diff.max()) <= float(qm.scale) * 1.001
+    assert float((y - y_float).abs().max()) <= float(qm.scale) * 3
+
+
+def test_conv3d_float_route_and_convert_mapping():
+    g = torch.Generator(device="cuda").manual_seed(3)
+    model = torch.nn.Sequential(Q.QuantStub(), torch.nn.Conv3d(8, 16, 3, padding=1), torch.nn.ReLU(), Q.DeQuantStub()).cuda()
+    x = torch.randn(2, 8, 6, 10, 10, device="cuda", generator=g)
+    prepared = Q.prepare(model)
+    prepared(x)
+    qmodel = Q.convert(prepared)
+    assert isinstance(qmodel[1], nnq.Conv3d)
+    with _lib.ieee_float32():
+        y_float = model(x)
+    y = qmodel(x)
+    _sync_status()
+    assert y.shape == y_float.shape
+    assert float((y - y_float).abs().max()) <= 4 * float(qmodel[1].scale) + 4 * float(qmodel[0].scale)
