@@ -249,6 +249,36 @@ def test_requantising_epilogue_bit_exact(unsigned_out, relu, tile_shape):
     assert np.array_equal(host(out).astype(np.int32), ref.astype(np.int32))
 
 
+@pytest.mark.parametrize("case", ["narrow_grid_relu", "zp_above_qmin_relu", "fractional_zp", "tiny_scale"])
+def test_requantising_epilogue_corners_full_tiles(case):
+    """N a multiple of the tile width (the kernel that holds the requantising loop alone): a grid
+    narrower than the storage type, a ReLU whose floor is the zero point, and output grids outside
+    the short division's domain (fractional zero point, subnormal scale), which every block
+    answers through the full-range sequence."""
+    x, w, b = _c2_like(300, 256, 512, seed=11)
+    wq, ws, _ = O.quantize_weight_per_channel(w)
+    xs, xz = O.calculate_qparams(x.min(), x.max(), False, O.QUINT8)
+    xq = O.quantize(x, xs, xz, O.QUINT8).astype(np.uint8)
+    acc = O.int_gemm_exact(xq, wq)
+    rowsum = wq.astype(np.int64).sum(axis=1).astype(np.int32)
+    relu = case in ("narrow_grid_relu", "zp_above_qmin_relu")
+    y = O.epilogue_f32(acc, xs, xz, rowsum, ws, b, relu=relu)
+    span = float(np.abs(y).max())
+    os_, oz, qmin, qmax, store = {
+        "narrow_grid_relu": (np.float32(span / 90), np.float32(0.0), -100, 100, torch.int8),
+        "zp_above_qmin_relu": (np.float32(span / 100), np.float32(-20.0), -128, 127, torch.int8),
+        "fractional_zp": (np.float32(span / 100), np.float32(2.5), -128, 127, torch.int8),
+        "tiny_scale": (np.float32(3e-41), np.float32(0.0), 0, 255, torch.uint8),
+    }[case]
+    with np.errstate(over="ignore", invalid="ignore"):
+        ref = O.requantize_f32(y, os_, oz, qmin, qmax)
+    out = QF.gemm_s8(dev(xq), dev(wq), out_dtype=store, a_scale=dev(xs), a_zp=dev(xz), b_rowsum=dev(rowsum),
+                     b_scale=dev(ws), bias=dev(b), act=_lib.ACT_RELU if relu else _lib.ACT_NONE,
+                     out_scale=dev(os_), out_zp=dev(oz), qmin=qmin, qmax=qmax)
+    _sync_status()
+    assert np.array_equal(host(out).astype(np.int32), ref.astype(np.int32))
+
+
 def test_static_linear_module_vs_reference_float_form(golden):
     """Module-level: mismatch rate against the reference's float path must be tiny
     and every mismatch +-1 code (the float GEMM's rounding, not ours)."""
