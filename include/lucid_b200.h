@@ -437,6 +437,28 @@ int lq_lut2_u8(const void* x_codes, const void* y_codes, size_t n, const uint8_t
 int lq_lstm_cell_f32(const float* gates, size_t ldg, const float* c_prev, float* h_out, size_t ldh,
                      float* c_out, size_t batch, size_t hidden, void* stream);
 
+/* ---- group-wise weight-only codes (4 / 8 bits) ------------------------------------------- */
+
+/* The reference's low-precision weight route (lucid/quantization/_qgemm.py:69-152 `quantize`,
+ * :155-225 `dequantize`, :228-320 `quantized_matmul`; engine ops
+ * lucid/_C/ops/quantized/QuantizedMatmul.cpp:47-109): the input axis of a float32 (N, K) weight
+ * is cut into groups of group_size (32 | 64 | 128) elements, each with
+ * scale = (max - min) / (2^bits - 1) and bias = min (a constant group takes scale 1);
+ * code = clip(rint((w - bias) / scale), 0, 2^bits - 1), bits = 4 | 8, packed little-endian into
+ * 32-bit words: packed (N, K * bits / 32), scales / biases (N, K / group_size). */
+int lq_groupwise_quantize(const float* w, size_t N, size_t K, int group_size, int bits, uint32_t* packed,
+                          float* scales, float* biases, void* stream);
+/* w_hat = code * scale + bias, float32 (N, K). */
+int lq_groupwise_dequantize(const uint32_t* packed, const float* scales, const float* biases, size_t N,
+                            size_t K, int group_size, int bits, float* out, void* stream);
+/* out (M, N) = x (M, K) * w_hat^T (+ bias[N]) (ReLU when relu != 0), the weight decoded inside the
+ * kernel; x and out share a dtype (LQ_F32 | LQ_BF16), float32 accumulation; row strides ldx / ldo
+ * in elements; x rows and `packed` 16-byte aligned.  Built for decode shapes (a few activation
+ * rows): the packed weight is streamed once per block of four rows. */
+int lq_groupwise_matmul(const void* x, int x_dtype, size_t M, size_t ldx, const uint32_t* packed,
+                        const float* scales, const float* biases, size_t N, size_t K, int group_size,
+                        int bits, const float* bias, int relu, void* out, size_t ldo, void* stream);
+
 /* ---- quantized embedding tables -------------------------------------------------------- */
 
 /* Gather + dequantize of the rows of a per-row int8 table.  Replaces the forward of

@@ -133,6 +133,13 @@ _SIGNATURES = {
     "lq_lut2_u8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                              C.c_void_p, C.c_int, C.c_void_p]),
     "lq_lut_u8": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_groupwise_quantize": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq_groupwise_dequantize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int,
+                                          C.c_int, C.c_void_p, C.c_void_p]),
+    "lq_groupwise_matmul": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                      C.c_void_p, C.c_size_t, C.c_void_p]),
     "lq_embedding_s8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int,
                                   C.c_size_t, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_longlong, C.c_void_p,
                                   C.c_int, C.c_void_p, C.c_void_p]),

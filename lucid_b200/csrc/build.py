@@ -15,7 +15,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ["capi.cu", "stream_kernels.cu", "histogram.cu", "embedding.cu", "exchange.cu", "lstm.cu", "gemm_s8.cu"]
+SOURCES = ["capi.cu", "stream_kernels.cu", "histogram.cu", "embedding.cu", "exchange.cu", "lstm.cu", "groupwise.cu",
+           "gemm_s8.cu"]
 # the test-only library: the GEMM with its wait-expiry hook compiled in (-DLQ_TESTING)
 TEST_SOURCES = ["capi.cu", "gemm_s8.cu"]
 HEADERS = ["common.cuh", os.path.join(ROOT, "include", "lucid_b200.h")]

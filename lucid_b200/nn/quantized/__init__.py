@@ -8,6 +8,7 @@ from .conv import Conv1d, Conv2d, Conv3d, ConvReLU1d, ConvReLU2d, ConvReLU3d  # 
 from .conv_transpose import ConvTranspose1d, ConvTranspose2d, ConvTranspose3d  # noqa: F401
 from .functional_module import FloatFunctional, QFunctional  # noqa: F401
 from .linear import Linear, LinearReLU  # noqa: F401
+from .mlx_linear import QuantizedLinearMLX  # noqa: F401
 from .modules import DeQuantize, Quantize  # noqa: F401
 from .sharded import ColumnShardedLinear  # noqa: F401
 from .sparse import Embedding, EmbeddingBag  # noqa: F401

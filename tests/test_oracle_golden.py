@@ -308,3 +308,23 @@ def test_c_restatement_of_histogram_and_merges(golden):
             assert np.array_equal(CO.qfunctional(op, xf, yf, sc, zp, int(qmin), int(qmax)), golden[f"qf_{tag}_{op}"])
         assert np.array_equal(CO.qfunctional("add", xf, 0.75, sc, zp, int(qmin), int(qmax)),
                               golden[f"qf_{tag}_add_scalar"])
+
+
+def test_groupwise_codes_round_trip_and_packing():
+    """Group-wise weight codes (formulas of lucid/quantization/_qgemm.py:84-97): the round-trip
+    error stays within half a step, a constant group is exact, and the packing is little-endian."""
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((6, 256)).astype(np.float32)
+    w[2, :64] = -0.75
+    for bits in (4, 8):
+        packed, s, b = O.groupwise_quantize(w, 64, bits)
+        assert packed.shape == (6, 256 * bits // 32) and s.shape == (6, 4)
+        w_hat = O.groupwise_dequantize(packed, s, b, 64, bits)
+        assert np.all(np.abs(w_hat - w) <= np.repeat(s, 64, axis=1) * 0.5000001 + 1e-7)
+        assert np.all(w_hat[2, :64] == np.float32(-0.75))
+        codes = O.groupwise_codes(packed, bits)
+        assert codes.max() <= (1 << bits) - 1
+        assert int(packed[0, 0] & ((1 << bits) - 1)) == int(codes[0, 0])
+        x = rng.standard_normal((3, 256)).astype(np.float32)
+        ref = O.groupwise_matmul_f64(x, packed, s, b, 64, bits)
+        assert np.allclose(ref, x.astype(np.float64) @ w_hat.astype(np.float64).T, atol=1e-5)
