@@ -1102,6 +1102,56 @@ def bench_streams(torch, Q, _lib, dev, peaks, iters=40):
     return out
 
 
+def bench_groupwise(torch, dev, peaks, iters=20):
+    """Decode-shape matmul on group-wise 4 / 8-bit weight codes: bf16 activations of 1 and 4 rows
+    against the Llama-2-70B projection shapes; weights rotate over copies larger than L2.  Bytes =
+    packed codes + scales + biases (+ activations and outputs, negligible): the weight is streamed
+    once per launch."""
+    from lucid_b200.quantization import _qgemm
+
+    out = {}
+    for name, n, k in (("o_8192x8192", 8192, 8192), ("gate_28672x8192", 28672, 8192), ("down_8192x28672", 8192, 28672)):
+        w = torch.randn(n, k, device=dev) * 0.02
+        for bits in (4, 8):
+            packed, scales, biases = _qgemm.quantize(w, group_size=64, bits=bits)
+            wbytes = packed.numel() * 4 + scales.numel() * 8
+            copies = max(2, int(300e6 // wbytes) + 1)
+            sets = [(packed.clone(), scales.clone(), biases.clone()) for _ in range(copies)]
+            for m in (1, 4):
+                x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+
+                def run():
+                    for p_, s_, b_ in sets:
+                        _qgemm.quantized_matmul(x, p_, s_, b_, group_size=64, bits=bits)
+                # replayed from a CUDA graph: a launch lasts a few microseconds, less than the
+                # host needs to issue it
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    run()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize()
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph):
+                    run()
+                gph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+                e0.record()
+                for _ in range(iters):
+                    gph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                sec = e0.elapsed_time(e1) * 1e-3 / (iters * copies)
+                del gph
+                nbytes = wbytes + m * k * 2 + m * n * 2
+                out[f"{name}_w{bits}_m{m}"] = {"us": sec * 1e6, "GB/s": nbytes / sec / 1e9,
+                                               "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
+            del sets
+        del w
+    return out
+
+
 def run_single_kernel_case(args):
     """Small single-kernel runs for profiler captures: `--case gemm` launches one
     integer GEMM shape (operands larger than L2), `--case streams` the config-1
@@ -1117,6 +1167,9 @@ def run_single_kernel_case(args):
     peaks = load_peaks()
     if args.case == "streams":
         print(json.dumps({"case": "streams", "streams": bench_streams(torch, Q, _lib, dev, peaks, iters=args.steps)}))
+        return 0
+    if args.case == "groupwise":
+        print(json.dumps({"case": "groupwise", "groupwise": bench_groupwise(torch, dev, peaks, iters=args.steps)}))
         return 0
     if args.case == "histc":
         # one histogram-observer batch per launch on `--shape N` normal samples (default 2^28);
@@ -1264,7 +1317,7 @@ def run_config_cases(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs", "histc", "tiles"])
+    ap.add_argument("--case", default="full", choices=["full", "gemm", "streams", "configs", "histc", "tiles", "groupwise"])
     ap.add_argument("--shape", default="4096,16384,8192", help="M,N,K for --case gemm; element count for --case histc")
     ap.add_argument("--epi", default="bf16", choices=["bf16", "u8"], help="epilogue of --case gemm")
     ap.add_argument("--gpus", type=int, default=1)

@@ -11,8 +11,8 @@
 //
 // The matmul is the bandwidth-bound decode shape (few activation rows): one warp per output
 // row, 16 bytes of packed codes per lane and step, activations read through L1 (they are a few
-// KB), float32 accumulation as  sum_g scale_g * (sum_k x_k * code_k) + bias_g * (sum_k x_k),
-// which keeps the decode to one integer-to-float conversion per code.
+// KB), each code decoded once per step to w_hat = fma(code, scale, bias) without a conversion
+// instruction and multiplied into a float32 accumulator per activation row.
 #include "common.cuh"
 
 namespace lq {
@@ -100,63 +100,116 @@ __device__ __forceinline__ void store1<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store1<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// One warp per output row n; MT activation rows at a time.  Per step a lane takes one 16-byte
-// piece of the row's packed codes (128 / BITS consecutive input positions, inside one group as
-// group % (128 / BITS) == 0) and accumulates  scale * sum(x * code) + bias * sum(x)  per
-// activation row; lanes are reduced with shuffles at the end.
-template <int BITS, int MT, typename T>
+// Codes of one 32-bit word as float32 without a conversion instruction: a byte permute drops the
+// code into the mantissa of 2^23 (0x4B000000 | code == 2^23 + code exactly), one subtraction
+// brings it back.  The conversion unit runs at an eighth of the arithmetic rate and was what
+// bounded the first form of this kernel.
+template <int BITS>
+__device__ __forceinline__ void decode_word(uint32_t word, float (&c)[32 / BITS]);
+template <>
+__device__ __forceinline__ void decode_word<8>(uint32_t word, float (&c)[4]) {
+  c[0] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7440)) - 8388608.0f;
+  c[1] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7441)) - 8388608.0f;
+  c[2] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7442)) - 8388608.0f;
+  c[3] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7443)) - 8388608.0f;
+}
+template <>
+__device__ __forceinline__ void decode_word<4>(uint32_t word, float (&c)[8]) {
+  const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;  // even / odd nibbles
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    c[2 * i] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7440 + i)) - 8388608.0f;
+    c[2 * i + 1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7440 + i)) - 8388608.0f;
+  }
+}
+
+// One CTA per R consecutive output rows; MT activation rows at a time.  Per step a lane takes
+// the same 16-byte piece (128 / BITS consecutive input positions, inside one group as
+// group % (128 / BITS) == 0) of each of its R rows: the activations of those positions are
+// loaded once into registers and reused for all R rows, every code is decoded once to
+// w_hat = fma(code, scale, bias) and multiplied into one float32 accumulator per (row,
+// activation row); lanes are reduced with shuffles at the end.
+template <int BITS, int MT, int R, typename T>
 __global__ void __launch_bounds__(kGwThreads)
 gw_matvec_kernel(const T* __restrict__ x, size_t ldx, const uint32_t* __restrict__ packed,
                  const float* __restrict__ scales, const float* __restrict__ biases, size_t N, size_t K, int group,
                  const float* __restrict__ bias, int relu, T* __restrict__ out, size_t ldo) {
   constexpr int kPerPiece = 128 / BITS;  // codes per 16-byte piece: 32 (4 bits) or 16 (8 bits)
-  constexpr uint32_t kMask = (1u << BITS) - 1u;
-  const size_t n = ((size_t)blockIdx.x * kGwThreads + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (n >= N) return;
+  constexpr int kPerWord = 32 / BITS;
+  // one CTA per R rows; its eight warps split the input axis (a decode-shape launch has too few
+  // rows to fill the GPU with one warp per row group) and add up through shared memory
+  constexpr int kWarps = kGwThreads / 32;
+  __shared__ float s_part[kWarps][R][MT];
+  const size_t n0 = (size_t)blockIdx.x * R;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const size_t pieces = K / kPerPiece;
-  const uint4* wrow = reinterpret_cast<const uint4*>(packed + n * (K * BITS / 32));
-  const size_t groups_per_row = K / (size_t)group;
-  float acc[MT];
+  const size_t row_words = K * BITS / 32;
+  const int gshift = 31 - __clz(group);  // group sizes are powers of two
+  const size_t groups_per_row = K >> gshift;
+  float acc[R][MT];
 #pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
-  for (size_t p = lane; p < pieces; p += 32) {
-    uint4 u;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
-                 : "l"(wrow + p));
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
+  for (size_t p = (size_t)warp * 32 + lane; p < pieces; p += kGwThreads) {
     const size_t k0 = p * kPerPiece;
-    const size_t g = n * groups_per_row + k0 / (size_t)group;
-    const float s = __ldg(scales + g), b = __ldg(biases + g);
-    const uint32_t words[4] = {u.x, u.y, u.z, u.w};
+    // the R rows' pieces first (independent loads in flight), then the activations
+    uint4 u[R];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      float dot = 0.0f, sum = 0.0f;
+    for (int r = 0; r < R; ++r) {
+      const size_t n = n0 + r < N ? n0 + r : N - 1;  // a row past the end repeats the last one (not stored)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(u[r].x), "=r"(u[r].y), "=r"(u[r].z), "=r"(u[r].w)
+                   : "l"(reinterpret_cast<const uint4*>(packed + n * row_words) + p));
+    }
+    float xv[MT][kPerPiece];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
       for (int q = 0; q < kPerPiece / 8; ++q) {
-        float xv[8];
-        load8<T>(x + (size_t)m * ldx + k0 + q * 8, xv);
+        float t[8];
+        load8<T>(x + (size_t)m * ldx + k0 + q * 8, t);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int idx = q * 8 + e;
-          const uint32_t word = words[idx / (32 / BITS)];
-          const float c = (float)((word >> ((idx % (32 / BITS)) * BITS)) & kMask);
-          dot = fmaf(xv[e], c, dot);
-          sum += xv[e];
+        for (int e = 0; e < 8; ++e) xv[m][q * 8 + e] = t[e];
+      }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const size_t n = n0 + r < N ? n0 + r : N - 1;
+      const size_t g = n * groups_per_row + (k0 >> gshift);
+      const float s = __ldg(scales + g), b = __ldg(biases + g);
+      const uint32_t words[4] = {u[r].x, u[r].y, u[r].z, u[r].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float c[kPerWord];
+        decode_word<BITS>(words[j], c);
+#pragma unroll
+        for (int e = 0; e < kPerWord; ++e) {
+          const float wh = fmaf(c[e], s, b);
+#pragma unroll
+          for (int m = 0; m < MT; ++m) acc[r][m] = fmaf(xv[m][j * kPerWord + e], wh, acc[r][m]);
         }
       }
-      acc[m] = fmaf(s, dot, fmaf(b, sum, acc[m]));
     }
   }
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
-    float v = acc[m];
+  for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) {
-      if (bias) v += __ldg(bias + n);
+    for (int m = 0; m < MT; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) s_part[warp][r][m] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < R * MT) {
+    const int r = threadIdx.x / MT, m = threadIdx.x % MT;
+    if (n0 + r < N) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) v += s_part[w][r][m];
+      if (bias) v += __ldg(bias + n0 + r);
       if (relu) v = fmaxf(v, 0.0f);
-      store1<T>(out + (size_t)m * ldo + n, v);
+      store1<T>(out + (size_t)m * ldo + n0 + r, v);
     }
   }
 }
@@ -172,22 +225,19 @@ int check_gw(const char* who, size_t K, int group, int bits) {
 template <int BITS, typename T>
 int launch_matvec(const T* x, size_t M, size_t ldx, const uint32_t* packed, const float* scales, const float* biases,
                   size_t N, size_t K, int group, const float* bias, int relu, T* out, size_t ldo, cudaStream_t st) {
-  const int grid = (int)((N * 32 + kGwThreads - 1) / kGwThreads);
+  constexpr int R = 4;  // output rows per warp: the activations of a step are loaded once for all of them
+  const int grid = (int)((N + R - 1) / R);
   size_t m0 = 0;
-  // activation rows in blocks of 4, then 2, then 1 (every block re-reads the packed weight: the
-  // kernel is for decode shapes; larger batches are better served by dequantize + a library GEMM)
+  // activation rows in pairs, then one (every block re-reads the packed weight: the kernel is for
+  // decode shapes; larger batches are better served by dequantize + a library GEMM)
   while (m0 < M) {
-    const size_t left = M - m0;
     const T* xm = x + m0 * ldx;
     T* om = out + m0 * ldo;
-    if (left >= 4) {
-      gw_matvec_kernel<BITS, 4, T><<<grid, kGwThreads, 0, st>>>(xm, ldx, packed, scales, biases, N, K, group, bias, relu, om, ldo);
-      m0 += 4;
-    } else if (left >= 2) {
-      gw_matvec_kernel<BITS, 2, T><<<grid, kGwThreads, 0, st>>>(xm, ldx, packed, scales, biases, N, K, group, bias, relu, om, ldo);
+    if (M - m0 >= 2) {
+      gw_matvec_kernel<BITS, 2, R, T><<<grid, kGwThreads, 0, st>>>(xm, ldx, packed, scales, biases, N, K, group, bias, relu, om, ldo);
       m0 += 2;
     } else {
-      gw_matvec_kernel<BITS, 1, T><<<grid, kGwThreads, 0, st>>>(xm, ldx, packed, scales, biases, N, K, group, bias, relu, om, ldo);
+      gw_matvec_kernel<BITS, 1, R, T><<<grid, kGwThreads, 0, st>>>(xm, ldx, packed, scales, biases, N, K, group, bias, relu, om, ldo);
       m0 += 1;
     }
   }
