@@ -4,8 +4,12 @@ The reference's values are ``"auto" | "mlx_group" | "reference"``; this build
 adds ``"b200_i8"`` (the integer tcgen05 path) and makes ``"auto"`` select it.
 ``"reference"`` keeps its meaning -- dequantize the weight, run the float
 contraction, fake-quantize the result -- evaluated on the GPU with this
-package's streaming kernels around a library float GEMM.  ``"mlx_group"`` names
-a Metal kernel that does not exist on this platform and is rejected when used.
+package's streaming kernels around a library float GEMM.  ``"mlx_group"`` keeps
+the reference's meaning too: ``convert`` / ``quantize_dynamic`` route the Linear
+family to the weight-only group-wise layer (``QuantizedLinearMLX``, here on this
+library's CUDA kernels), everything else takes the dequantize-to-float route.
+Unlike the reference, ``"auto"`` does not pick that route: it selects the integer
+W8A8 path.
 """
 
 from __future__ import annotations
@@ -37,15 +41,12 @@ class _QuantizedBackend:
 
     def use_int8(self) -> bool:
         """Whether modules run the integer GEMM given the current mode."""
-        if self._engine == "reference":
-            return False
-        if self._engine == "mlx_group":
-            raise _lib.EngineUnavailable("the MLX group-wise kernel is unavailable on this platform")
-        return True
+        return self._engine in ("auto", "b200_i8")
 
-    # name kept for callers written against the reference
     def use_mlx(self) -> bool:
-        return False
+        """Whether ``convert`` / ``quantize_dynamic`` route Linear layers to the group-wise
+        weight-only kernel (lucid/backends/__init__.py:90-96)."""
+        return self._engine == "mlx_group"
 
 
 quantized = _QuantizedBackend()

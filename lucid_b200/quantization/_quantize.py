@@ -93,7 +93,64 @@ def _quant_mapping() -> dict:
 
     m[nniqat.ConvBn2d] = lambda mod: mod.to_quantized()
     m[nniqat.ConvBnReLU2d] = lambda mod: mod.to_quantized()
+    from .. import backends
+
+    if backends.quantized.use_mlx():  # the Linear family on the group-wise weight-only kernel
+        m[torch.nn.Linear] = _mlx_linear_builder(False)
+        if nni is not None:
+            m[nni.LinearReLU] = _mlx_linear_builder(True)
     return m
+
+
+def _mlx_weight_bits(mod) -> int:
+    """Weight bit-width (4 / 8) of the group-wise route, read from the module's qconfig
+    (lucid/quantization/_quantize.py:116-124)."""
+    qcfg = getattr(mod, "qconfig", None)
+    if qcfg is not None and hasattr(qcfg, "weight"):
+        bits = getattr(getattr(qcfg.weight(), "qdtype", None), "bits", None)
+        if isinstance(bits, int) and bits in (4, 8):
+            return bits
+    return 8
+
+
+def _mlx_group_size(in_features: int):
+    """Largest preferred group size (64, 128, 32) dividing ``in_features``, or None
+    (lucid/quantization/_quantize.py:127-140)."""
+    for gs in (64, 128, 32):
+        if in_features % gs == 0:
+            return gs
+    return None
+
+
+def _mlx_linear_builder(relu: bool):
+    """``convert`` builder of the group-wise route (lucid/quantization/_quantize.py:143-165):
+    weight-only codes, float activations; a layer no group size divides falls back to the
+    calibrated layer."""
+    import lucid_b200.nn.quantized as nnq
+
+    fallback = nnq.LinearReLU.from_float if relu else nnq.Linear.from_float
+
+    def build(child):
+        inner = child[0] if relu else child
+        gs = _mlx_group_size(inner.in_features)
+        if gs is None:
+            return fallback(child)
+        return nnq.QuantizedLinearMLX.from_float(inner, bits=_mlx_weight_bits(child), group_size=gs, relu=relu)
+
+    return build
+
+
+def _mlx_dynamic_builder():
+    """``quantize_dynamic`` builder of the group-wise route (lucid/quantization/_quantize.py:168-179)."""
+    import lucid_b200.nn.quantized as nnq
+
+    def build(child, dtype):
+        gs = _mlx_group_size(child.in_features)
+        if gs is None or dtype.bits not in (4, 8):
+            return nnq.dynamic.Linear.from_float(child, dtype)
+        return nnq.QuantizedLinearMLX.from_float(child, bits=dtype.bits, group_size=gs, relu=False)
+
+    return build
 
 
 def _make_observer_hook(obs):
@@ -208,7 +265,10 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace:
 def _dynamic_mapping() -> dict:
     import lucid_b200.nn.quantized as nnq
 
-    return {torch.nn.Linear: nnq.dynamic.Linear.from_float,
+    from .. import backends
+
+    linear = _mlx_dynamic_builder() if backends.quantized.use_mlx() else nnq.dynamic.Linear.from_float
+    return {torch.nn.Linear: linear,
             torch.nn.LSTM: nnq.dynamic.LSTM.from_float,
             torch.nn.Embedding: lambda mod, dtype: nnq.Embedding.from_float(mod),
             torch.nn.EmbeddingBag: lambda mod, dtype: nnq.EmbeddingBag.from_float(mod)}

@@ -86,3 +86,33 @@ def test_bad_arguments_raise():
         _qgemm.quantize(torch.randn(8, 128, device="cuda"), group_size=64, bits=2)
     with pytest.raises(_lib.DeviceMismatch):
         _qgemm.quantize(torch.randn(8, 128), group_size=64, bits=8)
+
+
+def test_convert_routes_linear_layers_under_the_group_wise_engine():
+    """`backends.quantized.engine = "mlx_group"`: `convert` and `quantize_dynamic` turn Linear
+    layers into the weight-only group-wise layer (test_real_gemm.py:95-140), a layer whose width
+    no group size divides keeps its calibrated / dynamic form."""
+    import lucid_b200.backends as backends
+    import lucid_b200.quantization as Q
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.ReLU(), torch.nn.Linear(256, 80),
+                                torch.nn.ReLU(), torch.nn.Linear(80, 16)).cuda().eval()
+    x = torch.randn(8, 128, device="cuda")
+    with torch.no_grad(), _lib.ieee_float32():
+        y_float = model(x)
+    old = backends.quantized.engine
+    backends.quantized.engine = "mlx_group"
+    try:
+        prepared = Q.prepare(model)
+        prepared(x)
+        qmodel = Q.convert(prepared)
+        dmodel = Q.quantize_dynamic(model)
+    finally:
+        backends.quantized.engine = old
+    assert isinstance(qmodel[0], nnq.QuantizedLinearMLX) and isinstance(qmodel[2], nnq.QuantizedLinearMLX)
+    assert isinstance(qmodel[4], nnq.Linear) and qmodel[0].group_size == 64 and qmodel[2].group_size == 64
+    assert isinstance(dmodel[0], nnq.QuantizedLinearMLX) and isinstance(dmodel[4], nnq.dynamic.Linear)
+    for m in (qmodel, dmodel):
+        y = m(x)
+        assert float((y - y_float).abs().max() / y_float.abs().max()) < 0.05

@@ -162,10 +162,20 @@ def test_engine_switch():
         b.engine = "fastest"
     b.engine = "reference"
     assert not b.use_int8()
-    b.engine = "mlx_group"
-    with pytest.raises(lucid_b200.EngineUnavailable):
-        b.use_int8()
-    b.engine = "auto"
+    assert not b.use_mlx()
+    b.engine = "mlx_group"  # the Linear family on the group-wise weight-only layer, the rest float
+    assert b.use_mlx() and not b.use_int8()
+    try:
+        import torch
+
+        from lucid_b200.quantization import _quantize
+
+        assert _quantize._quant_mapping()[torch.nn.Linear].__name__ == "build"
+        assert _quantize._mlx_group_size(4096) == 64 and _quantize._mlx_group_size(96) == 32
+        assert _quantize._mlx_group_size(100) is None
+    finally:
+        b.engine = "auto"
+    assert not b.use_mlx()
     assert lucid_b200.device("cuda:0").type == "cuda"
     with pytest.raises(RuntimeError):
         lucid_b200.device("metal")
