@@ -6,8 +6,9 @@ convolution weight, fake-quantizes the FOLDED weight per output channel, convolv
 the optional ReLU and fake-quantizes the output -- so the weight grid the model trains against
 is the grid ``convert`` will bake.  BatchNorm stays a live sub-module: its parameters keep
 learning and the fold is recomputed every step.  The float convolution under the fake-quantize
-ops is the library's (training path); ``convert`` turns the module into the integer
-``nn.quantized.Conv2d`` / ``ConvReLU2d``."""
+ops is the library's (training path); ``convert`` turns the module into the inference layer
+of its rank: the integer ``nn.quantized.Conv2d`` / ``ConvReLU2d`` and ``Conv1d`` / ``ConvReLU1d``,
+or ``Conv3d`` / ``ConvReLU3d`` (which keep the reference's float sequence)."""
 
 from __future__ import annotations
 
@@ -28,13 +29,19 @@ def fold_conv_bn(conv_w, conv_b, bn: torch.nn.modules.batchnorm._BatchNorm):
     return w, b
 
 
-class ConvBn2d(torch.nn.Module):
+class _ConvBnNd(torch.nn.Module):
     _RELU = False
+    _RANK = 2
 
-    def __init__(self, conv: torch.nn.Conv2d, bn: torch.nn.BatchNorm2d, qconfig=None) -> None:
+    def __init__(self, conv: torch.nn.Module, bn: torch.nn.Module, qconfig=None) -> None:
         super().__init__()
         if qconfig is None:
             raise ValueError(f"{type(self).__name__} requires a qconfig")
+        conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[self._RANK - 1]
+        bn_t = (torch.nn.BatchNorm1d, torch.nn.BatchNorm2d, torch.nn.BatchNorm3d)[self._RANK - 1]
+        if not isinstance(conv, conv_t) or not isinstance(bn, bn_t):
+            raise TypeError(f"{type(self).__name__} fuses {conv_t.__name__} + {bn_t.__name__}, got "
+                            f"{type(conv).__name__} + {type(bn).__name__}")
         self.conv, self.bn = conv, bn
         self.relu = self._RELU
         self.qconfig = qconfig
@@ -74,8 +81,11 @@ class ConvBn2d(torch.nn.Module):
             codes = quantize(weight, w_scale.to(dev), w_zp.to(dev), wfq.qdtype, ch_axis=wfq.ch_axis)
             conv = self.conv
             padding = conv.padding if not isinstance(conv.padding, str) else 0
-            cls = nnq.ConvReLU2d if self.relu else nnq.Conv2d
-            q = cls(conv.in_channels, conv.out_channels, conv.kernel_size, conv.stride, padding, conv.dilation,
+            plain = (nnq.Conv1d, nnq.Conv2d, nnq.Conv3d)[self._RANK - 1]
+            fused = (nnq.ConvReLU1d, nnq.ConvReLU2d, nnq.ConvReLU3d)[self._RANK - 1]
+            if self._RANK == 1:
+                codes = codes.unsqueeze(2)  # the 1-D layer keeps its kernel as 1 x k
+            q = (fused if self.relu else plain)(conv.in_channels, conv.out_channels, conv.kernel_size, conv.stride, padding, conv.dilation,
                     conv.groups, bias=True)
             q.weight_int8, q.weight_scale, q.weight_zero_point = codes, w_scale.to(dev), w_zp.to(dev)
             q.weight_ch_axis = ch_axis
@@ -88,5 +98,25 @@ class ConvBn2d(torch.nn.Module):
         return q
 
 
+class ConvBn1d(_ConvBnNd):
+    _RANK = 1
+
+
+class ConvBn2d(_ConvBnNd):
+    _RANK = 2
+
+
+class ConvBn3d(_ConvBnNd):
+    _RANK = 3
+
+
+class ConvBnReLU1d(ConvBn1d):
+    _RELU = True
+
+
 class ConvBnReLU2d(ConvBn2d):
+    _RELU = True
+
+
+class ConvBnReLU3d(ConvBn3d):
     _RELU = True

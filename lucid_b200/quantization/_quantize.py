@@ -91,8 +91,9 @@ def _quant_mapping() -> dict:
     m[nnqat.Conv2d] = nnq.Conv2d.from_float
     from ..nn.intrinsic import qat as nniqat
 
-    m[nniqat.ConvBn2d] = lambda mod: mod.to_quantized()
-    m[nniqat.ConvBnReLU2d] = lambda mod: mod.to_quantized()
+    for cls in (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d,
+                nniqat.ConvBnReLU1d, nniqat.ConvBnReLU2d, nniqat.ConvBnReLU3d):
+        m[cls] = lambda mod: mod.to_quantized()
     from .. import backends
 
     if backends.quantized.use_mlx():  # the Linear family on the group-wise weight-only kernel
@@ -237,7 +238,7 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace:
     def swap(module):
         nonlocal n_matched
         for name, child in list(module.named_children()):
-            if isinstance(child, nniqat.ConvBn2d):  # fused by fuse_modules_qat: already a QAT module
+            if isinstance(child, nniqat._ConvBnNd):  # fused by fuse_modules_qat: already a QAT module
                 n_matched += 1
                 continue
             build = mapping.get(type(child))

@@ -14,8 +14,18 @@ import copy
 
 import torch
 
-_CONV_TYPES = (torch.nn.Conv2d,)
-_BN_TYPES = (torch.nn.BatchNorm2d,)
+_CONV_TYPES = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)
+_BN_TYPES = (torch.nn.BatchNorm1d, torch.nn.BatchNorm2d, torch.nn.BatchNorm3d)
+
+
+def _rank(conv: torch.nn.Module) -> int:
+    return conv.weight.dim() - 2
+
+
+def _check_pair(who: str, conv: torch.nn.Module, bn: torch.nn.Module) -> None:
+    """A convolution folds with the BatchNorm of its own rank only."""
+    if not isinstance(conv, _CONV_TYPES) or type(bn) is not _BN_TYPES[_rank(conv) - 1]:
+        raise TypeError(f"{who}: unsupported pair {type(conv).__name__}, {type(bn).__name__}")
 
 
 def _get_module(root: torch.nn.Module, dotted: str) -> torch.nn.Module:
@@ -37,14 +47,13 @@ def _set_module(root: torch.nn.Module, dotted: str, value: torch.nn.Module) -> N
         setattr(parent, parts[-1], value)
 
 
-def fuse_conv_bn_eval(conv: torch.nn.Conv2d, bn: torch.nn.BatchNorm2d) -> torch.nn.Conv2d:
+def fuse_conv_bn_eval(conv: torch.nn.Module, bn: torch.nn.Module) -> torch.nn.Module:
     """A copy of ``conv`` computing ``bn(conv(x))`` at eval time
     (lucid/nn/utils/fusion.py:100-135): ``W' = W * g / sqrt(var + eps)``,
     ``b' = (b - mean) * g / sqrt(var + eps) + beta``."""
     from ..nn.intrinsic.qat import fold_conv_bn
 
-    if not isinstance(conv, _CONV_TYPES) or not isinstance(bn, _BN_TYPES):
-        raise TypeError(f"fuse_conv_bn_eval: unsupported pair {type(conv).__name__}, {type(bn).__name__}")
+    _check_pair("fuse_conv_bn_eval", conv, bn)
     fused = copy.deepcopy(conv)
     with torch.no_grad():
         w, b = fold_conv_bn(conv.weight.detach(), None if conv.bias is None else conv.bias.detach(), bn)
@@ -56,7 +65,7 @@ def fuse_conv_bn_eval(conv: torch.nn.Conv2d, bn: torch.nn.BatchNorm2d) -> torch.
 def _conv_relu(conv):
     import torch.ao.nn.intrinsic as nni
 
-    return nni.ConvReLU2d(conv, torch.nn.ReLU())
+    return (nni.ConvReLU1d, nni.ConvReLU2d, nni.ConvReLU3d)[_rank(conv) - 1](conv, torch.nn.ReLU())
 
 
 def _fuse_run(mods):
@@ -103,8 +112,9 @@ def _fuse_run_qat(mods, qconfig):
             bn = rest.pop(0)
             relu = bool(rest and isinstance(rest[0], torch.nn.ReLU))
             if len(rest) == (1 if relu else 0):
-                cls = nniqat.ConvBnReLU2d if relu else nniqat.ConvBn2d
-                return [cls(first, bn, qconfig=qconfig), *ids]
+                plain = (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d)[_rank(first) - 1]
+                fused = (nniqat.ConvBnReLU1d, nniqat.ConvBnReLU2d, nniqat.ConvBnReLU3d)[_rank(first) - 1]
+                return [(fused if relu else plain)(first, bn, qconfig=qconfig), *ids]
         elif len(rest) == 1 and isinstance(rest[0], torch.nn.ReLU):
             return [_conv_relu(first), *ids]
         elif not rest:
@@ -116,7 +126,7 @@ def _fuse_run_qat(mods, qconfig):
 
 def fuse_modules_qat(model: torch.nn.Module, modules_to_fuse, qconfig, inplace: bool = False) -> torch.nn.Module:
     """QAT fusion, run before ``prepare_qat``: ``[Conv, BN]`` / ``[Conv, BN, ReLU]`` runs become
-    trainable ``ConvBn2d`` / ``ConvBnReLU2d`` modules that fold BatchNorm per forward (the
+    trainable ``ConvBn{1,2,3}d`` / ``ConvBnReLU{1,2,3}d`` modules that fold BatchNorm per forward (the
     qconfig is needed here: they fake-quantize from their first forward)."""
     model = model if inplace else copy.deepcopy(model)
     for group in modules_to_fuse:

@@ -128,6 +128,51 @@ def test_static_ptq_with_batchnorm_reaches_the_integer_conv():
     assert float((y_q - y_float).abs().mean() / y_float.abs().mean()) < 0.05
 
 
+@pytest.mark.parametrize("rank", [1, 3])
+def test_qat_conv_bn_fusion_of_the_other_ranks(rank):
+    """ConvBn1d / ConvBn3d (lucid/nn/intrinsic/qat/modules.py:30-90, 796-833;
+    lucid/quantization/fuse_modules.py:190-205): the fused module trains, keeps its BatchNorm
+    live, and converts to the inference layer of its rank, which reproduces what QAT simulated."""
+    from lucid_b200.nn.intrinsic import qat as nniqat
+
+    conv_t = (torch.nn.Conv1d, None, torch.nn.Conv3d)[rank - 1]
+    bn_t = (torch.nn.BatchNorm1d, None, torch.nn.BatchNorm3d)[rank - 1]
+    torch.manual_seed(5 + rank)
+    net = torch.nn.Sequential(Q.QuantStub(), conv_t(16, 32, 3, padding=1, bias=False), bn_t(32), torch.nn.ReLU(),
+                              conv_t(32, 32, 3, stride=2, padding=1), bn_t(32), Q.DeQuantStub()).cuda().train()
+    with torch.no_grad():
+        for bn in (net[2], net[5]):
+            bn.running_mean.normal_(0, 0.2)
+            bn.running_var.uniform_(0.5, 1.5)
+            bn.weight.uniform_(0.5, 1.5)
+            bn.bias.normal_(0, 0.2)
+    qcfg = Q.get_default_qat_qconfig()
+    fused = Q.fuse_modules_qat(net, [["1", "2", "3"], ["4", "5"]], qcfg)
+    assert type(fused[1]) is getattr(nniqat, f"ConvBnReLU{rank}d") and type(fused[4]) is getattr(nniqat, f"ConvBn{rank}d")
+    qat = Q.prepare_qat(fused, qcfg)
+    assert type(qat[1]) is getattr(nniqat, f"ConvBnReLU{rank}d") and type(qat[1].conv) is conv_t
+    x = torch.randn(4, 16, *([12] * rank), device="cuda")
+    opt = torch.optim.SGD(qat.parameters(), lr=1e-3)
+    mean0 = qat[1].bn.running_mean.clone()
+    for _ in range(2):
+        opt.zero_grad()
+        qat(x).square().mean().backward()
+        assert qat[1].conv.weight.grad is not None and qat[1].bn.weight.grad is not None
+        opt.step()
+    assert not torch.equal(qat[1].bn.running_mean, mean0)
+    qat.eval()
+    with torch.no_grad():
+        y_qat = qat(x)
+    qnet = Q.convert(qat)
+    assert type(qnet[1]) is getattr(nnq, f"ConvReLU{rank}d") and type(qnet[4]) is getattr(nnq, f"Conv{rank}d")
+    _, b_fold = qat[1]._fold()
+    assert torch.equal(qnet[1].bias, b_fold.detach())
+    with torch.no_grad():
+        y_q = qnet(x)
+    assert y_q.shape == y_qat.shape
+    assert float((y_q - y_qat).abs().mean() / y_qat.abs().mean()) < 0.05
+
+
 def test_qat_conv_bn_fusion_trains_and_converts():
     """fuse_modules_qat -> prepare_qat -> a few steps -> convert
     (lucid/nn/intrinsic/qat/modules.py:30-90, 796-833): BatchNorm stays trainable inside the fused

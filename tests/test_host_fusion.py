@@ -73,3 +73,52 @@ def test_qat_fusion_keeps_batchnorm_live():
     assert torch.equal(w, ref.weight) and torch.equal(b, ref.bias)
     with pytest.raises(ValueError):
         nniqat.ConvBn2d(net.conv, net.bn, qconfig=None)
+
+
+def _ranked(rank):
+    """Conv + BatchNorm + ReLU of one rank with non-trivial statistics, and an input for it."""
+    torch.manual_seed(10 + rank)
+    conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
+    bn_t = (torch.nn.BatchNorm1d, torch.nn.BatchNorm2d, torch.nn.BatchNorm3d)[rank - 1]
+    net = torch.nn.Sequential(conv_t(3, 8, 3, padding=1, bias=rank != 2), bn_t(8), torch.nn.ReLU()).eval()
+    with torch.no_grad():
+        net[1].running_mean.normal_()
+        net[1].running_var.uniform_(0.5, 2.0)
+        net[1].weight.normal_()
+        net[1].bias.normal_()
+    return net, torch.randn(2, 3, *([6] * rank))
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+def test_fusion_covers_the_three_ranks(rank):
+    """The rank picks the fused type (lucid/quantization/fuse_modules.py:62-90, 190-205): static
+    fusion folds BatchNorm{1,2,3}d exactly and wraps the ReLU in ConvReLU{1,2,3}d; QAT fusion
+    builds ConvBn{1,2,3}d / ConvBnReLU{1,2,3}d with the BatchNorm kept live."""
+    net, x = _ranked(rank)
+    y_ref = net(x)
+    fused = Q.fuse_modules(net, [["0", "1", "2"]])
+    assert type(fused[0]).__name__ == f"ConvReLU{rank}d"
+    assert isinstance(fused[1], torch.nn.Identity) and isinstance(fused[2], torch.nn.Identity)
+    assert torch.allclose(fused(x), y_ref, atol=1e-4)
+    plain = Q.fuse_modules(net, [["0", "1"]])
+    assert type(plain[0]) is type(net[0]) and torch.allclose(plain(x), y_ref, atol=1e-4)
+    qcfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)  # structure only: no kernels on CPU
+    qat = Q.fuse_modules_qat(net, [["0", "1", "2"]], qcfg)
+    assert type(qat[0]) is getattr(nniqat, f"ConvBnReLU{rank}d") and type(qat[0].bn) is type(net[1])
+    assert torch.allclose(qat.eval()(x), y_ref, atol=1e-4)
+    qat2 = Q.fuse_modules_qat(net, [["0", "1"]], qcfg)
+    assert type(qat2[0]) is getattr(nniqat, f"ConvBn{rank}d")
+    w, b = qat2[0]._fold()
+    ref = Q.fuse_conv_bn_eval(net[0], net[1])
+    assert torch.equal(w, ref.weight) and torch.equal(b, ref.bias)
+
+
+def test_fusion_rejects_a_batchnorm_of_another_rank():
+    net, _ = _ranked(1)
+    other = torch.nn.BatchNorm2d(8)
+    with pytest.raises(TypeError):
+        Q.fuse_conv_bn_eval(net[0], other)
+    with pytest.raises(TypeError):
+        nniqat.ConvBn1d(net[0], other, qconfig=Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity))
+    with pytest.raises(TypeError):
+        nniqat.ConvBn3d(net[0], net[1], qconfig=Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity))
