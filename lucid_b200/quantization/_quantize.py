@@ -88,7 +88,13 @@ def _quant_mapping() -> dict:
     from ..nn import qat as nnqat
 
     m[nnqat.Linear] = nnq.Linear.from_float
+    m[nnqat.LinearReLU] = nnq.LinearReLU.from_float
+    m[nnqat.Conv1d] = nnq.Conv1d.from_float
     m[nnqat.Conv2d] = nnq.Conv2d.from_float
+    m[nnqat.Conv3d] = nnq.Conv3d.from_float
+    m[nnqat.ConvReLU1d] = nnq.ConvReLU1d.from_float
+    m[nnqat.ConvReLU2d] = nnq.ConvReLU2d.from_float
+    m[nnqat.ConvReLU3d] = nnq.ConvReLU3d.from_float
     from ..nn.intrinsic import qat as nniqat
 
     for cls in (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d,
@@ -223,14 +229,20 @@ def convert(model: torch.nn.Module, inplace: bool = False):
 
 
 def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
-    """Swap every float ``Linear`` / ``Conv2d`` for its QAT form (weight and output each behind a
+    """Swap every float ``Linear`` / ``Conv{1,2,3}d`` and every fused ``LinearReLU`` /
+    ``ConvReLU{1,2,3}d`` container for its QAT form (weight and output each behind a
     ``FakeQuantize``) and leave the model in training mode
-    (lucid/quantization/_quantize.py:575-640)."""
+    (lucid/quantization/_quantize.py:557-572, 575-640)."""
     from ..nn import qat as nnqat
 
     qcfg = qconfig if qconfig is not None else get_default_qat_qconfig()
     model = model if inplace else copy.deepcopy(model)
-    mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv2d: nnqat.Conv2d.from_float}
+    mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv1d: nnqat.Conv1d.from_float,
+               torch.nn.Conv2d: nnqat.Conv2d.from_float, torch.nn.Conv3d: nnqat.Conv3d.from_float}
+    nni = _intrinsic()
+    if nni is not None:
+        mapping.update({nni.LinearReLU: nnqat.LinearReLU.from_float, nni.ConvReLU1d: nnqat.ConvReLU1d.from_float,
+                        nni.ConvReLU2d: nnqat.ConvReLU2d.from_float, nni.ConvReLU3d: nnqat.ConvReLU3d.from_float})
     n_matched = 0
 
     from ..nn.intrinsic import qat as nniqat

@@ -24,7 +24,7 @@ def _rank(conv: torch.nn.Module) -> int:
 
 def _check_pair(who: str, conv: torch.nn.Module, bn: torch.nn.Module) -> None:
     """A convolution folds with the BatchNorm of its own rank only."""
-    if not isinstance(conv, _CONV_TYPES) or type(bn) is not _BN_TYPES[_rank(conv) - 1]:
+    if not isinstance(conv, _CONV_TYPES) or not isinstance(bn, _BN_TYPES[_rank(conv) - 1]):
         raise TypeError(f"{who}: unsupported pair {type(conv).__name__}, {type(bn).__name__}")
 
 

@@ -209,3 +209,37 @@ def test_qat_conv_bn_fusion_trains_and_converts():
     with torch.no_grad():
         y_q = qnet(x)
     assert float((y_q - y_qat).abs().mean() / y_qat.abs().mean()) < 0.05
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+def test_qat_fused_relu_layers_of_every_rank_convert(rank):
+    """[Conv, ReLU] / [Linear, ReLU] runs under QAT (lucid/quantization/_quantize.py:557-572,
+    lucid/nn/qat/conv.py:469-800): prepare_qat builds nn.qat.ConvReLU{rank}d / LinearReLU, they
+    train through the straight-through mask, and convert produces the fused inference layers."""
+    conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
+    torch.manual_seed(20 + rank)
+    net = torch.nn.Sequential(Q.QuantStub(), conv_t(16, 32, 3, padding=1), torch.nn.ReLU(), conv_t(32, 16, 1),
+                              torch.nn.Flatten(), torch.nn.LazyLinear(8), torch.nn.ReLU(), Q.DeQuantStub()).cuda()
+    x = torch.randn(4, 16, *([8] * rank), device="cuda")
+    net(x)  # materialise the lazy layer
+    qcfg = Q.get_default_qat_qconfig()
+    qat = Q.prepare_qat(Q.fuse_modules_qat(net, [["1", "2"], ["5", "6"]], qcfg), qcfg)
+    assert type(qat[1]) is getattr(nnqat, f"ConvReLU{rank}d") and type(qat[3]) is getattr(nnqat, f"Conv{rank}d")
+    assert type(qat[5]) is nnqat.LinearReLU
+    opt = torch.optim.SGD(qat.parameters(), lr=1e-3)
+    for _ in range(2):
+        opt.zero_grad()
+        qat(x).square().mean().backward()
+        assert qat[1].weight.grad is not None and qat[5].weight.grad is not None
+        opt.step()
+    qat.eval()
+    with torch.no_grad():
+        y_qat = qat(x)
+        assert float(y_qat.min()) >= 0.0  # the fused ReLU sits ahead of the output grid
+    qnet = Q.convert(qat)
+    assert type(qnet[1]) is getattr(nnq, f"ConvReLU{rank}d") and type(qnet[3]) is getattr(nnq, f"Conv{rank}d")
+    assert type(qnet[5]) is nnq.LinearReLU
+    with torch.no_grad():
+        y_q = qnet(x)
+    assert y_q.shape == y_qat.shape and bool(torch.isfinite(y_q).all())
+    assert float((y_q - y_qat).abs().mean() / y_qat.abs().mean().clamp_min(1e-6)) < 0.15

@@ -122,3 +122,34 @@ def test_fusion_rejects_a_batchnorm_of_another_rank():
         nniqat.ConvBn1d(net[0], other, qconfig=Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity))
     with pytest.raises(TypeError):
         nniqat.ConvBn3d(net[0], net[1], qconfig=Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity))
+
+
+def test_prepare_qat_maps_every_rank_and_fused_container():
+    """The QAT map of lucid/quantization/_quantize.py:557-572: Linear, Conv{1,2,3}d and the fused
+    LinearReLU / ConvReLU{1,2,3}d containers each become the ``nn.qat`` layer of the same name; the
+    fused forms apply their ReLU before the output fake-quantize.  Identity "fake-quantizers"
+    keep this on the CPU: the forward must then equal the float model's."""
+    import lucid_b200.nn.qat as nnqat
+
+    torch.manual_seed(4)
+    qcfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    for rank in (1, 2, 3):
+        conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
+        net = torch.nn.Sequential(conv_t(3, 8, 3, padding=1), torch.nn.ReLU(), conv_t(8, 4, 1, bias=False)).eval()
+        x = torch.randn(2, 3, *([6] * rank))
+        y_ref = net(x)
+        fused = Q.fuse_modules_qat(net, [["0", "1"]], qcfg)
+        qat = Q.prepare_qat(fused, qcfg)
+        assert type(qat[0]) is getattr(nnqat, f"ConvReLU{rank}d") and type(qat[2]) is getattr(nnqat, f"Conv{rank}d")
+        assert isinstance(qat[0], conv_t) and qat.training
+        assert qat[0].weight is fused[0][0].weight or torch.equal(qat[0].weight, net[0].weight)
+        assert torch.allclose(qat.eval()(x), y_ref, atol=1e-6)
+    lin = torch.nn.Sequential(torch.nn.Linear(8, 4), torch.nn.ReLU(), torch.nn.Linear(4, 2)).eval()
+    x = torch.randn(5, 8)
+    qat = Q.prepare_qat(Q.fuse_modules_qat(lin, [["0", "1"]], qcfg), qcfg)
+    assert type(qat[0]) is nnqat.LinearReLU and type(qat[2]) is nnqat.Linear
+    assert torch.allclose(qat.eval()(x), lin(x), atol=1e-6)
+    with pytest.raises(ValueError):
+        nnqat.ConvReLU1d(3, 8, 3, qconfig=None)
+    with pytest.raises(ValueError):
+        nnqat.LinearReLU(3, 8, qconfig=None)
