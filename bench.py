@@ -661,6 +661,13 @@ def run_b200_arm(args):
         configs = config_cases(torch, dev, peaks, iters=20)
         library_ref = library_int8_gemm(torch, dev, {"qkv": (w_qkv, None), "o": (w_o, None), "gate_up": (w_gu, None),
                                                       "down": (w_d, None)})
+    # ---- the weight-only decode matmul (one GPU only; an extra: a failure never costs the line) ----
+    groupwise = None
+    if rank == 0 and world == 1:
+        try:
+            groupwise = bench_groupwise(torch, dev, peaks, iters=10)
+        except Exception as exc:
+            groupwise = {"error": repr(exc)}
 
     if rank == 0:
         gemm_ops_per_launch = OPS_PER_STEP / 4 / world
@@ -702,6 +709,7 @@ def run_b200_arm(args):
             "parity_check": parity,
             "streams": streams,
             "configs": configs,
+            "groupwise": groupwise,
         }
         line["roofline"]["library_ref"] = library_ref
         print(json.dumps(line), flush=True)
