@@ -8,6 +8,7 @@ from .modules import (  # noqa: F401
     ConvReLU1d,
     ConvReLU2d,
     ConvReLU3d,
+    Embedding,
     Linear,
     LinearReLU,
 )

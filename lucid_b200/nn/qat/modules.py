@@ -107,3 +107,25 @@ class ConvReLU2d(Conv2d):
 
 class ConvReLU3d(Conv3d):
     _RELU = True
+
+
+class Embedding(torch.nn.Embedding):
+    """Lookup in the fake-quantized table (lucid/nn/qat/sparse.py:21-132): one
+    ``weight_fake_quant`` and no output fake-quantizer, as the rows are read back unchanged."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, padding_idx=None, *, qconfig=None, **kw) -> None:
+        super().__init__(num_embeddings, embedding_dim, padding_idx, **kw)
+        if qconfig is None:
+            raise ValueError("qat.Embedding requires a qconfig")
+        self.qconfig = qconfig
+        self.weight_fake_quant = qconfig.weight()
+
+    def forward(self, x):
+        return F.embedding(x, self.weight_fake_quant(self.weight), self.padding_idx)
+
+    @classmethod
+    def from_float(cls, mod) -> "Embedding":
+        qat = cls(mod.num_embeddings, mod.embedding_dim, mod.padding_idx, qconfig=mod.qconfig,
+                  device=mod.weight.device, dtype=mod.weight.dtype)
+        qat.weight = mod.weight
+        return qat

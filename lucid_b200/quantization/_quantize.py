@@ -78,6 +78,8 @@ def _quant_mapping() -> dict:
         torch.nn.Tanh: nnq.Tanh.from_float,
         torch.nn.ELU: nnq.ELU.from_float,
         torch.nn.LeakyReLU: nnq.LeakyReLU.from_float,
+        torch.nn.Embedding: nnq.Embedding.from_float,
+        torch.nn.EmbeddingBag: nnq.EmbeddingBag.from_float,
     }
     nni = _intrinsic()
     if nni is not None:
@@ -95,6 +97,7 @@ def _quant_mapping() -> dict:
     m[nnqat.ConvReLU1d] = nnq.ConvReLU1d.from_float
     m[nnqat.ConvReLU2d] = nnq.ConvReLU2d.from_float
     m[nnqat.ConvReLU3d] = nnq.ConvReLU3d.from_float
+    m[nnqat.Embedding] = nnq.Embedding.from_float
     from ..nn.intrinsic import qat as nniqat
 
     for cls in (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d,
@@ -220,7 +223,8 @@ def convert(model: torch.nn.Module, inplace: bool = False):
     model = model if inplace else copy.deepcopy(model)
     model.eval()
     mapping = _quant_mapping()
-    always = (DeQuantStub, torch.nn.ReLU)
+    # tables need no calibration (lucid/quantization/_quantize.py:416)
+    always = (DeQuantStub, torch.nn.ReLU, torch.nn.Embedding, torch.nn.EmbeddingBag)
     build = mapping.get(type(model))
     if build is not None and hasattr(model, "activation_post_process"):
         return build(model)
@@ -238,7 +242,8 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace:
     qcfg = qconfig if qconfig is not None else get_default_qat_qconfig()
     model = model if inplace else copy.deepcopy(model)
     mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv1d: nnqat.Conv1d.from_float,
-               torch.nn.Conv2d: nnqat.Conv2d.from_float, torch.nn.Conv3d: nnqat.Conv3d.from_float}
+               torch.nn.Conv2d: nnqat.Conv2d.from_float, torch.nn.Conv3d: nnqat.Conv3d.from_float,
+               torch.nn.Embedding: nnqat.Embedding.from_float}
     nni = _intrinsic()
     if nni is not None:
         mapping.update({nni.LinearReLU: nnqat.LinearReLU.from_float, nni.ConvReLU1d: nnqat.ConvReLU1d.from_float,

@@ -101,3 +101,28 @@ def test_embedding_large_table_gather_only_reads_rows():
     sel = idx.cpu().numpy()
     want = O.dequantize(host(q.weight_int8[idx]), host(q.weight_scale[idx]), np.zeros(4096, dtype=F32), ch_axis=0)
     assert np.array_equal(host(out), want) and sel.shape == (4096,)
+
+
+def test_static_convert_and_qat_swap_embeddings():
+    """Tables convert without calibration (the always-convert set of
+    lucid/quantization/_quantize.py:416), and ``prepare_qat`` routes them through
+    ``nn.qat.Embedding`` (lucid/nn/qat/sparse.py:21-132), whose trained table converts to the same
+    inference layer."""
+    import lucid_b200.nn.qat as nnqat
+
+    torch.manual_seed(9)
+    model = torch.nn.Sequential(torch.nn.Embedding(500, 64, padding_idx=0), torch.nn.Linear(64, 32)).cuda()
+    idx = torch.randint(0, 500, (4, 10), device="cuda")
+    y = model(idx).detach()
+    qstatic = Q.convert(model)  # no observers anywhere: only the table converts
+    assert type(qstatic[0]) is nnq.Embedding and type(qstatic[1]) is torch.nn.Linear
+    assert float((y - qstatic(idx)).abs().mean() / y.abs().mean()) < 0.05
+    qat = Q.prepare_qat(model)
+    assert type(qat[0]) is nnqat.Embedding and type(qat[1]) is nnqat.Linear
+    qat(idx).square().mean().backward()
+    assert qat[0].weight.grad is not None
+    qnet = Q.convert(qat.eval())
+    assert type(qnet[0]) is nnq.Embedding and type(qnet[1]) is nnq.Linear
+    assert qnet[0].padding_idx == 0
+    assert list(qnet[0].state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point"]
+    assert float((y - qnet(idx)).abs().mean() / y.abs().mean()) < 0.1

@@ -153,3 +153,21 @@ def test_prepare_qat_maps_every_rank_and_fused_container():
         nnqat.ConvReLU1d(3, 8, 3, qconfig=None)
     with pytest.raises(ValueError):
         nnqat.LinearReLU(3, 8, qconfig=None)
+
+
+def test_prepare_qat_swaps_embedding_tables():
+    """``nn.qat.Embedding`` (lucid/nn/qat/sparse.py:21-132): the table is looked up through its
+    weight fake-quantizer, there is no output fake-quantizer, and a qconfig is mandatory."""
+    import lucid_b200.nn.qat as nnqat
+
+    torch.manual_seed(6)
+    qcfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    net = torch.nn.Sequential(torch.nn.Embedding(20, 8, padding_idx=0), torch.nn.Linear(8, 4)).eval()
+    idx = torch.tensor([[1, 0, 5], [19, 3, 3]])
+    qat = Q.prepare_qat(net, qcfg)
+    assert type(qat[0]) is nnqat.Embedding and isinstance(qat[0], torch.nn.Embedding)
+    assert qat[0].padding_idx == 0 and not hasattr(qat[0], "activation_post_process")
+    assert qat[0].weight is net[0].weight or torch.equal(qat[0].weight, net[0].weight)
+    assert torch.equal(qat.eval()(idx), net(idx))
+    with pytest.raises(ValueError):
+        nnqat.Embedding(20, 8)
