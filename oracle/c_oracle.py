@@ -126,3 +126,25 @@ def qfunctional(op, x, y, scale, zp, qmin, qmax):
     lib().lo_qfunctional_f32(C.c_int({"add": 0, "mul": 1, "add_relu": 2}[op]), _p(x), _p(y), C.c_size_t(x.size),
                              C.c_float(scale), C.c_float(zp), C.c_int(qmin), C.c_int(qmax), _p(out))
     return out
+
+
+def groupwise_quantize(w, group_size=64, bits=8):
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    packed = np.empty((n, k * bits // 32), dtype=np.uint32)
+    scales = np.empty((n, k // group_size), dtype=np.float32)
+    biases = np.empty((n, k // group_size), dtype=np.float32)
+    lib().lo_groupwise_quantize(_p(w), C.c_size_t(n), C.c_size_t(k), C.c_int(group_size), C.c_int(bits),
+                                _p(packed), _p(scales), _p(biases))
+    return packed, scales, biases
+
+
+def groupwise_dequantize(packed, scales, biases, group_size=64, bits=8):
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    biases = np.ascontiguousarray(biases, dtype=np.float32)
+    n, k = packed.shape[0], packed.shape[1] * 32 // bits
+    out = np.empty((n, k), dtype=np.float32)
+    lib().lo_groupwise_dequantize(_p(packed), _p(scales), _p(biases), C.c_size_t(n), C.c_size_t(k),
+                                  C.c_int(group_size), C.c_int(bits), _p(out))
+    return out

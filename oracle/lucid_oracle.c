@@ -206,3 +206,49 @@ void lo_qfunctional_f32(int op, const float* x, const float* y, size_t n, float 
     out[i] = d * scale;
   }
 }
+
+/* ---- group-wise weight-only codes --------------------------------------------------------
+ * Formulas the reference documents for its MLX route (lucid/quantization/_qgemm.py:84-97):
+ * per group of `group` consecutive input positions, scale = (max - min) / (2^bits - 1),
+ * bias = min, code = clip(rint((w - bias) / scale), 0, 2^bits - 1), codes packed
+ * little-endian into 32-bit words; a constant group takes scale 1.  The engine that implements
+ * them (MLX) is absent here: parity unpinned, like the NumPy form. */
+void lo_groupwise_quantize(const float* w, size_t n, size_t k, int group, int bits, uint32_t* packed,
+                           float* scales, float* biases) {
+  const float top = (float)((1 << bits) - 1);
+  const size_t per = (size_t)(32 / bits), groups = k / (size_t)group;
+  for (size_t r = 0; r < n; ++r) {
+    for (size_t g = 0; g < groups; ++g) {
+      const float* wg = w + r * k + g * (size_t)group;
+      float mn = wg[0], mx = wg[0];
+      for (int i = 1; i < group; ++i) {
+        mn = wg[i] < mn ? wg[i] : mn;
+        mx = wg[i] > mx ? wg[i] : mx;
+      }
+      float s = (mx - mn) / top;
+      if (!(s > 0.0f)) s = 1.0f;
+      scales[r * groups + g] = s;
+      biases[r * groups + g] = mn;
+      for (int i = 0; i < group; ++i) {
+        const size_t e = g * (size_t)group + (size_t)i;
+        const float q = clipf(rintf((wg[i] - mn) / s), 0.0f, top);
+        uint32_t* word = packed + r * (k / per) + e / per;
+        if (e % per == 0) *word = 0u;
+        *word |= (uint32_t)q << ((e % per) * (size_t)bits);
+      }
+    }
+  }
+}
+
+void lo_groupwise_dequantize(const uint32_t* packed, const float* scales, const float* biases, size_t n, size_t k,
+                             int group, int bits, float* out) {
+  const size_t per = (size_t)(32 / bits), groups = k / (size_t)group;
+  const uint32_t mask = (1u << bits) - 1u;
+  for (size_t r = 0; r < n; ++r)
+    for (size_t e = 0; e < k; ++e) {
+      const uint32_t code = (packed[r * (k / per) + e / per] >> ((e % per) * (size_t)bits)) & mask;
+      const size_t g = r * groups + e / (size_t)group;
+      const float prod = (float)code * scales[g]; /* two roundings: product, then sum */
+      out[r * k + e] = prod + biases[g];
+    }
+}

@@ -328,3 +328,20 @@ def test_groupwise_codes_round_trip_and_packing():
         x = rng.standard_normal((3, 256)).astype(np.float32)
         ref = O.groupwise_matmul_f64(x, packed, s, b, 64, bits)
         assert np.allclose(ref, x.astype(np.float64) @ w_hat.astype(np.float64).T, atol=1e-5)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_c_restatement_of_groupwise_codes(bits, group):
+    """The two restatements of the group-wise codes (NumPy and plain C) agree bit for bit,
+    constant groups and ties included."""
+    rng = np.random.default_rng(100 * bits + group)
+    w = rng.standard_normal((9, 4 * group)).astype(np.float32)
+    w[1, :group] = 0.5                                   # constant group: scale 1, codes 0
+    w[2, group:2 * group] = np.linspace(0, 1, group)     # an evenly spaced group
+    w[3] = np.round(w[3] * 8) / 8                        # coarse values: exact ties after the divide
+    packed, s, b = O.groupwise_quantize(w, group, bits)
+    cpacked, cs, cb = CO.groupwise_quantize(w, group, bits)
+    assert np.array_equal(packed, cpacked) and np.array_equal(s, cs) and np.array_equal(b, cb)
+    assert np.array_equal(O.groupwise_dequantize(packed, s, b, group, bits),
+                          CO.groupwise_dequantize(cpacked, cs, cb, group, bits))
