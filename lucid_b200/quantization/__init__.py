@@ -15,4 +15,11 @@ from ._quantize import DeQuantStub, QuantStub, convert, prepare, quantize_dynami
 from ._fake_quantize import FakeQuantize  # noqa: F401,E402
 from ._quantize import prepare_qat  # noqa: F401,E402
 from .fuse_modules import fuse_conv_bn_eval, fuse_modules, fuse_modules_qat  # noqa: F401,E402
-from .qconfig import QConfig, get_default_qat_qconfig, get_default_qconfig  # noqa: F401,E402
+from .qconfig import (  # noqa: F401,E402
+    QConfig,
+    QConfigMapping,
+    get_default_qat_qconfig,
+    get_default_qat_qconfig_mapping,
+    get_default_qconfig,
+    get_default_qconfig_mapping,
+)

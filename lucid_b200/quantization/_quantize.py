@@ -15,7 +15,12 @@ import warnings
 import torch
 
 from ._qscheme import QDtype, qint8
-from .qconfig import QConfig, get_default_qat_qconfig, get_default_qconfig
+from .qconfig import (
+    QConfig,
+    QConfigMapping,
+    get_default_qat_qconfig_mapping,
+    get_default_qconfig_mapping,
+)
 
 
 class QuantStub(torch.nn.Module):
@@ -171,12 +176,23 @@ def _make_observer_hook(obs):
     return hook
 
 
-def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
-    """Attach an activation observer (forward hook) to every quantizable module; nothing
-    numeric changes.  Fused containers are observed as a unit, not their children."""
+def _as_mapping(qconfig, default) -> QConfigMapping:
+    """A bare ``QConfig`` is the global tier of a mapping, ``None`` the default mapping
+    (lucid/quantization/_quantize.py:195-201)."""
+    if qconfig is None:
+        return default()
+    if isinstance(qconfig, QConfig):
+        return QConfigMapping().set_global(qconfig)
+    return qconfig
+
+
+def prepare(model: torch.nn.Module, qconfig: QConfig | QConfigMapping | None = None, inplace: bool = False):
+    """Attach an activation observer (forward hook) to every quantizable module the mapping
+    gives a qconfig; nothing numeric changes.  Fused containers are observed as a unit, not
+    their children (an excluded container keeps its children in float too)."""
     from ..nn.quantized.functional_module import FloatFunctional
 
-    qcfg = qconfig if qconfig is not None else get_default_qconfig()
+    qmap = _as_mapping(qconfig, get_default_qconfig_mapping)
     model = model if inplace else copy.deepcopy(model)
     model.eval()
     observed = _observed_types()
@@ -191,6 +207,9 @@ def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: boo
             continue
         if isinstance(mod, fused):
             inside_fused.add(name)
+        qcfg = qmap.get_qconfig(type(mod), name)
+        if qcfg is None:
+            continue
         mod.qconfig = qcfg
         obs = qcfg.activation()
         mod.activation_post_process = obs
@@ -198,7 +217,7 @@ def prepare(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: boo
             mod._lq_hook = mod.register_forward_hook(_make_observer_hook(obs))
         n_matched += 1
     if n_matched == 0:
-        warnings.warn("prepare(): the qconfig matched no quantizable modules -- convert() will "
+        warnings.warn("prepare(): the QConfigMapping matched no quantizable modules -- convert() will "
                       "leave this model unchanged.", stacklevel=2)
     return model
 
@@ -232,14 +251,14 @@ def convert(model: torch.nn.Module, inplace: bool = False):
     return model
 
 
-def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace: bool = False):
+def prepare_qat(model: torch.nn.Module, qconfig: QConfig | QConfigMapping | None = None, inplace: bool = False):
     """Swap every float ``Linear`` / ``Conv{1,2,3}d`` and every fused ``LinearReLU`` /
     ``ConvReLU{1,2,3}d`` container for its QAT form (weight and output each behind a
     ``FakeQuantize``) and leave the model in training mode
     (lucid/quantization/_quantize.py:557-572, 575-640)."""
     from ..nn import qat as nnqat
 
-    qcfg = qconfig if qconfig is not None else get_default_qat_qconfig()
+    qmap = _as_mapping(qconfig, get_default_qat_qconfig_mapping)
     model = model if inplace else copy.deepcopy(model)
     mapping = {torch.nn.Linear: nnqat.Linear.from_float, torch.nn.Conv1d: nnqat.Conv1d.from_float,
                torch.nn.Conv2d: nnqat.Conv2d.from_float, torch.nn.Conv3d: nnqat.Conv3d.from_float,
@@ -252,29 +271,32 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | None = None, inplace:
 
     from ..nn.intrinsic import qat as nniqat
 
-    def swap(module):
+    def swap(module, prefix):
         nonlocal n_matched
         for name, child in list(module.named_children()):
+            full = f"{prefix}.{name}" if prefix else name
             if isinstance(child, nniqat._ConvBnNd):  # fused by fuse_modules_qat: already a QAT module
                 n_matched += 1
                 continue
             build = mapping.get(type(child))
-            if build is not None:
+            qcfg = qmap.get_qconfig(type(child), full)
+            if build is not None and qcfg is not None:
                 child.qconfig = qcfg
                 module._modules[name] = build(child)
                 n_matched += 1
             else:
-                swap(child)
+                swap(child, full)
 
     build = mapping.get(type(model))
-    if build is not None:
+    qcfg = qmap.get_qconfig(type(model), "")
+    if build is not None and qcfg is not None:
         model.qconfig = qcfg
         model = build(model)
         n_matched += 1
     else:
-        swap(model)
+        swap(model, "")
     if n_matched == 0:
-        warnings.warn("prepare_qat(): the qconfig matched no quantizable modules -- convert() will "
+        warnings.warn("prepare_qat(): the QConfigMapping matched no quantizable modules -- convert() will "
                       "leave this model unchanged.", stacklevel=2)
     model.train()
     return model

@@ -171,3 +171,47 @@ def test_prepare_qat_swaps_embedding_tables():
     assert torch.equal(qat.eval()(idx), net(idx))
     with pytest.raises(ValueError):
         nnqat.Embedding(20, 8)
+
+
+def test_qconfig_mapping_resolution_and_routing():
+    """``QConfigMapping`` (lucid/quantization/qconfig.py:261-425): per-name beats per-type beats
+    global, ``None`` excludes; ``prepare`` / ``prepare_qat`` observe or swap only what the mapping
+    gives a qconfig (lucid/quantization/_quantize.py:195-201, 291-305, 661-681)."""
+    import lucid_b200.nn.qat as nnqat
+
+    a = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    b = Q.QConfig(activation=torch.nn.ReLU, weight=torch.nn.Identity)
+    m = Q.QConfigMapping().set_global(a).set_object_type(torch.nn.Conv2d, b).set_module_name("head", None)
+    assert m.get_qconfig(torch.nn.Linear, "body.fc") is a
+    assert m.get_qconfig(torch.nn.Conv2d, "body.conv") is b
+    assert m.get_qconfig(torch.nn.Conv2d, "head") is None          # the name wins over the type
+    assert Q.QConfigMapping().get_qconfig(torch.nn.Linear, "x") is None
+    assert isinstance(Q.get_default_qconfig_mapping().get_qconfig(torch.nn.Linear, "x"), Q.QConfig)
+    assert isinstance(Q.get_default_qat_qconfig_mapping().get_qconfig(torch.nn.Linear, "x"), Q.QConfig)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.body = torch.nn.Sequential(torch.nn.Conv2d(3, 4, 1), torch.nn.Flatten(), torch.nn.Linear(64, 8))
+            self.head = torch.nn.Linear(8, 2)
+
+        def forward(self, x):
+            return self.head(self.body(x))
+
+    net = Net().eval()
+    mapping = Q.QConfigMapping().set_global(a).set_object_type(torch.nn.Conv2d, b).set_module_name("head", None)
+    prepared = Q.prepare(net, mapping)
+    assert isinstance(prepared.body[0].activation_post_process, torch.nn.ReLU)       # by type
+    assert isinstance(prepared.body[2].activation_post_process, torch.nn.Identity)   # global
+    assert not hasattr(prepared.head, "activation_post_process")                     # excluded by name
+    x = torch.randn(2, 3, 4, 4)
+    assert torch.equal(prepared(x), net(x))  # observers change nothing
+    qat = Q.prepare_qat(net, mapping)
+    assert type(qat.body[0]) is nnqat.Conv2d and type(qat.body[2]) is nnqat.Linear
+    assert type(qat.head) is torch.nn.Linear
+    with pytest.warns(UserWarning):
+        Q.prepare(net, Q.QConfigMapping().set_object_type(torch.nn.Conv3d, a))
+    with pytest.warns(UserWarning):
+        Q.prepare_qat(net, Q.QConfigMapping())
+    # a bare QConfig is the global tier
+    assert hasattr(Q.prepare(net, a).head, "activation_post_process")
