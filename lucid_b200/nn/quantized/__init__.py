@@ -9,6 +9,6 @@ from .conv_transpose import ConvTranspose1d, ConvTranspose2d, ConvTranspose3d  #
 from .functional_module import FloatFunctional, QFunctional  # noqa: F401
 from .linear import Linear, LinearReLU  # noqa: F401
 from .mlx_linear import QuantizedLinearMLX  # noqa: F401
-from .modules import DeQuantize, Quantize  # noqa: F401
+from .modules import DeQuantize, DeQuantStub, Quantize, QuantStub, QuantWrapper  # noqa: F401
 from .sharded import ColumnShardedLinear  # noqa: F401
 from .sparse import Embedding, EmbeddingBag  # noqa: F401

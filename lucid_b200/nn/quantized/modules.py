@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from ...quantization import QDtype, dequantize, quantize_to, quint8
+from ...quantization._quantize import DeQuantStub, QuantStub, QuantWrapper  # noqa: F401  (the reference exports them here)
 from ._utils import QCodes, activation_qparams, codes_of, tag
 
 

@@ -24,17 +24,49 @@ from .qconfig import (
 
 
 class QuantStub(torch.nn.Module):
-    """Marks where float activations enter the quantized region (identity until converted)."""
+    """Marks where float activations enter the quantized region
+    (lucid/nn/quantized/modules.py:29-123): an identity under static PTQ, where a forward hook
+    feeds the observer; a ``FakeQuantize`` attached as ``activation_post_process`` is applied."""
+
+    def __init__(self, qconfig=None) -> None:
+        super().__init__()
+        if qconfig is not None:
+            self.qconfig = qconfig
 
     def forward(self, x):
+        from ._fake_quantize import FakeQuantize
+
+        app = getattr(self, "activation_post_process", None)
+        if isinstance(app, FakeQuantize) and torch.is_floating_point(x):
+            return app(x)
         return x
 
 
 class DeQuantStub(torch.nn.Module):
-    """Marks where activations leave the quantized region (identity)."""
+    """Marks where activations leave the quantized region (identity;
+    lucid/nn/quantized/modules.py:126-183)."""
+
+    def __init__(self, qconfig=None) -> None:
+        super().__init__()
+        if qconfig is not None:
+            self.qconfig = qconfig
 
     def forward(self, x):
         return x
+
+
+class QuantWrapper(torch.nn.Module):
+    """``quant -> module -> dequant`` around a model that has no stubs of its own
+    (lucid/nn/quantized/modules.py:351-424)."""
+
+    def __init__(self, module: torch.nn.Module) -> None:
+        super().__init__()
+        self.quant = QuantStub()
+        self.module = module
+        self.dequant = DeQuantStub()
+
+    def forward(self, x):
+        return self.dequant(self.module(self.quant(x)))
 
 
 def _intrinsic():
@@ -284,6 +316,11 @@ def prepare_qat(model: torch.nn.Module, qconfig: QConfig | QConfigMapping | None
                 child.qconfig = qcfg
                 module._modules[name] = build(child)
                 n_matched += 1
+            elif qcfg is not None and isinstance(child, QuantStub):
+                # the entry grid is trained too: the stub fake-quantizes its input, and convert
+                # bakes that grid into nn.quantized.Quantize (lucid/quantization/_quantize.py:677-679)
+                child.qconfig = qcfg
+                child.activation_post_process = qcfg.activation()
             else:
                 swap(child, full)
 

@@ -226,6 +226,7 @@ def test_qat_fused_relu_layers_of_every_rank_convert(rank):
     qat = Q.prepare_qat(Q.fuse_modules_qat(net, [["1", "2"], ["5", "6"]], qcfg), qcfg)
     assert type(qat[1]) is getattr(nnqat, f"ConvReLU{rank}d") and type(qat[3]) is getattr(nnqat, f"Conv{rank}d")
     assert type(qat[5]) is nnqat.LinearReLU
+    assert isinstance(qat[0].activation_post_process, Q.FakeQuantize)  # the entry grid is trained too
     opt = torch.optim.SGD(qat.parameters(), lr=1e-3)
     for _ in range(2):
         opt.zero_grad()
@@ -238,7 +239,8 @@ def test_qat_fused_relu_layers_of_every_rank_convert(rank):
         assert float(y_qat.min()) >= 0.0  # the fused ReLU sits ahead of the output grid
     qnet = Q.convert(qat)
     assert type(qnet[1]) is getattr(nnq, f"ConvReLU{rank}d") and type(qnet[3]) is getattr(nnq, f"Conv{rank}d")
-    assert type(qnet[5]) is nnq.LinearReLU
+    assert type(qnet[5]) is nnq.LinearReLU and type(qnet[0]) is nnq.Quantize
+    assert float(qnet[0].scale) == float(qat[0].activation_post_process.scale)
     with torch.no_grad():
         y_q = qnet(x)
     assert y_q.shape == y_qat.shape and bool(torch.isfinite(y_q).all())

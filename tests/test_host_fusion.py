@@ -209,9 +209,34 @@ def test_qconfig_mapping_resolution_and_routing():
     qat = Q.prepare_qat(net, mapping)
     assert type(qat.body[0]) is nnqat.Conv2d and type(qat.body[2]) is nnqat.Linear
     assert type(qat.head) is torch.nn.Linear
+    stubbed = Q.prepare_qat(Q.QuantWrapper(net), a)
+    assert isinstance(stubbed.quant.activation_post_process, torch.nn.Identity) and stubbed.quant.qconfig is a
+    assert not hasattr(stubbed.dequant, "activation_post_process")
+    assert torch.equal(stubbed.eval()(x), net(x))  # only a FakeQuantize is applied by the stub
+    skipped = Q.prepare_qat(Q.QuantWrapper(net), Q.QConfigMapping().set_global(a).set_module_name("quant", None))
+    assert not hasattr(skipped.quant, "activation_post_process")
     with pytest.warns(UserWarning):
         Q.prepare(net, Q.QConfigMapping().set_object_type(torch.nn.Conv3d, a))
     with pytest.warns(UserWarning):
         Q.prepare_qat(net, Q.QConfigMapping())
     # a bare QConfig is the global tier
     assert hasattr(Q.prepare(net, a).head, "activation_post_process")
+
+
+def test_stubs_and_wrapper_are_exported_where_the_reference_has_them():
+    """``QuantStub`` / ``DeQuantStub`` / ``QuantWrapper`` (lucid/nn/quantized/modules.py:29-183,
+    351-424; exported by lucid/nn/quantized/__init__.py:36-42): optional ``qconfig`` argument,
+    identity forwards, wrapper = quant -> module -> dequant."""
+    import lucid_b200.nn.quantized as nnq
+
+    assert nnq.QuantStub is Q.QuantStub and nnq.DeQuantStub is Q.DeQuantStub and nnq.QuantWrapper is Q.QuantWrapper
+    cfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    assert nnq.QuantStub(cfg).qconfig is cfg and not hasattr(nnq.QuantStub(), "qconfig")
+    assert nnq.DeQuantStub(cfg).qconfig is cfg
+    x = torch.randn(3, 5)
+    assert nnq.QuantStub()(x) is x and nnq.DeQuantStub()(x) is x
+    w = nnq.QuantWrapper(torch.nn.Linear(5, 2))
+    assert [n for n, _ in w.named_children()] == ["quant", "module", "dequant"]
+    assert torch.equal(w(x), w.module(x))
+    prepared = Q.prepare(w.eval(), cfg)
+    assert hasattr(prepared.quant, "activation_post_process") and hasattr(prepared.module, "activation_post_process")
