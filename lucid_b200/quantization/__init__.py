@@ -14,6 +14,7 @@ from .observer import (FixedQParamsObserver, HistogramObserver, MinMaxObserver, 
 from ._quantize import DeQuantStub, QuantStub, QuantWrapper, convert, prepare, quantize_dynamic  # noqa: F401,E402
 from ._fake_quantize import FakeQuantize  # noqa: F401,E402
 from ._quantize import prepare_qat  # noqa: F401,E402
+from ._quantize_fx import convert_fx, prepare_fx  # noqa: F401,E402
 from .fuse_modules import fuse_conv_bn_eval, fuse_modules, fuse_modules_qat  # noqa: F401,E402
 from .qconfig import (  # noqa: F401,E402
     QConfig,

@@ -240,3 +240,16 @@ def test_stubs_and_wrapper_are_exported_where_the_reference_has_them():
     assert torch.equal(w(x), w.module(x))
     prepared = Q.prepare(w.eval(), cfg)
     assert hasattr(prepared.quant, "activation_post_process") and hasattr(prepared.module, "activation_post_process")
+
+
+def test_graph_mode_entry_points_wrap_the_model():
+    """``prepare_fx`` (lucid/quantization/_quantize_fx.py:21-92; gate test_graph_mode.py:20-25): no
+    hand-placed stubs, the model comes back inside a ``QuantWrapper`` with observers attached."""
+    cfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 4), torch.nn.ReLU(), torch.nn.Linear(4, 2)).eval()
+    prepared = Q.prepare_fx(net, cfg, example_inputs=torch.randn(1, 6))
+    assert isinstance(prepared, Q.QuantWrapper) and prepared.module is not net
+    assert hasattr(prepared.quant, "activation_post_process") and hasattr(prepared.module[0], "activation_post_process")
+    x = torch.randn(3, 6)
+    assert torch.equal(prepared(x), net(x))
+    assert Q.convert_fx.__module__.endswith("_quantize_fx")
