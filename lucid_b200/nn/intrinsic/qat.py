@@ -110,13 +110,30 @@ class ConvBn3d(_ConvBnNd):
     _RANK = 3
 
 
-class ConvBnReLU1d(ConvBn1d):
+class _WithReLU:
+    """The fused-ReLU forms take the reference's ``(conv, bn, relu=True, qconfig=None)``
+    (lucid/nn/intrinsic/qat/modules.py:553-561)."""
+
     _RELU = True
 
+    def __init__(self, conv, bn, relu: bool = True, qconfig=None) -> None:
+        super().__init__(conv, bn, qconfig=qconfig)
+        self.relu = bool(relu)
 
-class ConvBnReLU2d(ConvBn2d):
-    _RELU = True
+
+class ConvBnReLU1d(_WithReLU, ConvBn1d):
+    pass
 
 
-class ConvBnReLU3d(ConvBn3d):
-    _RELU = True
+class ConvBnReLU2d(_WithReLU, ConvBn2d):
+    pass
+
+
+class ConvBnReLU3d(_WithReLU, ConvBn3d):
+    pass
+
+
+def convbnrelu2d_to_quantized(mod: _ConvBnNd):
+    """Rank-generic bake of a trained ``ConvBn*`` module into its inference layer
+    (lucid/nn/intrinsic/qat/modules.py:796-837)."""
+    return mod.to_quantized()

@@ -18,9 +18,19 @@ from ....quantization import PerChannelMinMaxObserver, QDtype, dequantize, per_c
 
 
 class LSTM(torch.nn.Module):
-    def __init__(self, input_size: int, hidden_size: int, num_layers: int = 1, bias: bool = True,
+    def __init__(self, input_size, hidden_size: int | None = None, num_layers: int = 1, bias: bool = True,
                  batch_first: bool = False, bidirectional: bool = False) -> None:
         super().__init__()
+        if isinstance(input_size, torch.nn.LSTM):
+            # the reference's constructor takes the float layer as a configuration "shell"
+            # (lucid/nn/quantized/dynamic/rnn.py:54-64); the buffers are filled by from_float
+            shell = input_size
+            if getattr(shell, "proj_size", 0):
+                raise NotImplementedError("dynamic LSTM: proj_size is not supported")
+            input_size, hidden_size, num_layers = shell.input_size, shell.hidden_size, shell.num_layers
+            bias, batch_first, bidirectional = shell.bias, shell.batch_first, shell.bidirectional
+        elif hidden_size is None:
+            raise TypeError("dynamic LSTM: hidden_size is required")
         self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
         self.bias, self.batch_first, self.bidirectional = bias, batch_first, bidirectional
         self._weight_names: list[str] = []

@@ -253,3 +253,27 @@ def test_graph_mode_entry_points_wrap_the_model():
     x = torch.randn(3, 6)
     assert torch.equal(prepared(x), net(x))
     assert Q.convert_fx.__module__.endswith("_quantize_fx")
+
+
+def test_reference_constructor_forms():
+    """``ConvBnReLU*d(conv, bn, relu=True, qconfig=None)`` (lucid/nn/intrinsic/qat/modules.py:553-561)
+    and the dynamic ``LSTM(shell)`` (lucid/nn/quantized/dynamic/rnn.py:54-64) take the reference's
+    positional forms."""
+    import lucid_b200.nn.quantized as nnq
+
+    cfg = Q.QConfig(activation=torch.nn.Identity, weight=torch.nn.Identity)
+    conv, bn = torch.nn.Conv2d(3, 4, 3), torch.nn.BatchNorm2d(4)
+    x = torch.randn(2, 3, 8, 8)
+    with torch.no_grad():
+        assert float(nniqat.ConvBnReLU2d(conv, bn, True, cfg).eval()(x).min()) >= 0.0
+        assert float(nniqat.ConvBnReLU2d(conv, bn, relu=False, qconfig=cfg).eval()(x).min()) < 0.0
+    assert nniqat.ConvBnReLU2d(conv, bn, qconfig=cfg).relu is True
+    with pytest.raises(ValueError):
+        nniqat.ConvBnReLU2d(conv, bn, True)
+    assert callable(nniqat.convbnrelu2d_to_quantized)
+    shell = torch.nn.LSTM(8, 16, 2, bidirectional=True, batch_first=True)
+    q = nnq.dynamic.LSTM(shell)
+    assert (q.input_size, q.hidden_size, q.num_layers, q.bidirectional, q.batch_first) == (8, 16, 2, True, True)
+    assert sorted(q.state_dict()) == sorted(nnq.dynamic.LSTM(8, 16, 2, True, True, True).state_dict())
+    with pytest.raises(TypeError):
+        nnq.dynamic.LSTM(8)
