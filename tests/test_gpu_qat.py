@@ -50,7 +50,9 @@ def test_qat_workflow_trains_and_converts():
     assert type(qat[1]) is nnqat.Linear and isinstance(qat[1].weight_fake_quant, Q.FakeQuantize)
     assert qat.training
     x = torch.randn(256, 64, device="cuda")
-    target = model(x).detach()
+    # a target the copied weights do not already meet: the loss starts far above the rounding
+    # noise of the grids, so its descent does not depend on that noise
+    target = model(x).detach() * 1.5
     opt = torch.optim.SGD(qat.parameters(), lr=1e-2)
     losses = []
     for _ in range(5):
@@ -60,14 +62,15 @@ def test_qat_workflow_trains_and_converts():
         assert qat[1].weight.grad is not None and torch.isfinite(qat[1].weight.grad).all()
         opt.step()
         losses.append(loss.item())
-    assert losses[-1] <= losses[0]
+    assert losses[-1] < losses[0]
     qat.eval()
     y_qat = qat(x)
     qmodel = Q.convert(qat)
+    assert type(qmodel[0]) is nnq.Quantize  # the entry grid trained by the stub's fake-quantizer
     assert type(qmodel[1]) is nnq.Linear and type(qmodel[3]) is nnq.Linear
     assert qmodel[1].weight_int8.dtype == torch.int8
     y_q = qmodel(x)
-    # the converted model reproduces what QAT simulated, up to the input grid it adds
+    # the converted model reproduces what QAT simulated
     err = float((y_q - y_qat).abs().mean() / y_qat.abs().mean())
     assert err < 0.05, err
 
