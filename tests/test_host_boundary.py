@@ -288,3 +288,34 @@ def test_workflow_routing_needs_no_gpu():
     ct = nnq.ConvTranspose2d(4, 6, 3, stride=2)
     assert tuple(ct.weight_int8.shape) == (4, 6, 3, 3) and ct.weight_ch_axis == 1
     assert list(ct.state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point", "bias", "scale", "zero_point"]
+
+
+def test_public_names_of_the_reference_are_all_present():
+    """The drop-in surface: every name the reference's packages export for this path
+    (``__all__`` of lucid/quantization/__init__.py, lucid/nn/quantized/__init__.py:45-73,
+    lucid/nn/quantized/dynamic, lucid/nn/qat, lucid/nn/intrinsic, lucid/nn/intrinsic/qat)
+    exists under the same package here."""
+    import importlib
+
+    surface = {
+        "lucid_b200.quantization": """FakeQuantize FixedQParamsObserver HistogramObserver MinMaxObserver
+            MovingAverageMinMaxObserver MovingAveragePerChannelMinMaxObserver NoopObserver ObserverBase
+            PerChannelMinMaxObserver PlaceholderObserver QConfig QConfigMapping QDtype QParams QScheme
+            calculate_qparams convert convert_fx dequantize fake_quantize fuse_modules fuse_modules_qat
+            get_default_qat_qconfig get_default_qat_qconfig_mapping get_default_qconfig
+            get_default_qconfig_mapping per_channel_affine per_channel_symmetric per_tensor_affine
+            per_tensor_symmetric prepare prepare_fx prepare_qat qint32 qint4 qint8 quantize quantize_dynamic
+            quint8""",
+        "lucid_b200.nn.quantized": """Conv1d Conv2d Conv3d ConvReLU1d ConvReLU2d ConvReLU3d ConvTranspose1d
+            ConvTranspose2d ConvTranspose3d DeQuantStub DeQuantize ELU Embedding EmbeddingBag FloatFunctional
+            Hardsigmoid Hardswish LeakyReLU Linear LinearReLU QFunctional QuantStub QuantWrapper Quantize
+            QuantizedLinearMLX Sigmoid Tanh""",
+        "lucid_b200.nn.quantized.dynamic": "LSTM Linear",
+        "lucid_b200.nn.qat": "Conv1d Conv2d Conv3d ConvReLU1d ConvReLU2d ConvReLU3d Embedding Linear LinearReLU",
+        "lucid_b200.nn.intrinsic": "ConvReLU1d ConvReLU2d ConvReLU3d LinearReLU",
+        "lucid_b200.nn.intrinsic.qat": "ConvBn1d ConvBn2d ConvBn3d ConvBnReLU1d ConvBnReLU2d ConvBnReLU3d",
+    }
+    for package, names in surface.items():
+        mod = importlib.import_module(package)
+        missing = [n for n in names.split() if not hasattr(mod, n)]
+        assert not missing, (package, missing)
