@@ -148,3 +148,40 @@ def groupwise_dequantize(packed, scales, biases, group_size=64, bits=8):
     lib().lo_groupwise_dequantize(_p(packed), _p(scales), _p(biases), C.c_size_t(n), C.c_size_t(k),
                                   C.c_int(group_size), C.c_int(bits), _p(out))
     return out
+
+
+def per_token_quantize(x, eps=1e-8):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, cols = x.shape
+    q = np.empty((rows, cols), dtype=np.int8)
+    s = np.empty(rows, dtype=np.float32)
+    lib().lo_per_token_quantize_f32_s8(_p(x), C.c_size_t(rows), C.c_size_t(cols), C.c_float(eps), _p(q), _p(s))
+    return q, s
+
+
+def int_gemm(a, w):
+    a, w = np.ascontiguousarray(a), np.ascontiguousarray(w, dtype=np.int8)
+    (m, k), n = a.shape, w.shape[0]
+    acc = np.empty((m, n), dtype=np.int32)
+    lib().lo_gemm_i8_i32(_p(a), C.c_int(int(a.dtype == np.int8)), _p(w), C.c_size_t(m), C.c_size_t(n), C.c_size_t(k), _p(acc))
+    return acc
+
+
+def linear_epilogue(acc, a_scale, w_scale, bias=None, relu=False, out_bf16=False):
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    m, n = acc.shape
+    a_s = np.ascontiguousarray(np.broadcast_to(np.asarray(a_scale, dtype=np.float32).reshape(-1), (m,)))
+    w_s = np.ascontiguousarray(w_scale, dtype=np.float32)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    y = np.empty((m, n), dtype=np.float32)
+    lib().lo_linear_epilogue_f32(_p(acc), C.c_size_t(m), C.c_size_t(n), _p(a_s), _p(w_s),
+                                 None if b is None else _p(b), C.c_int(int(relu)), C.c_int(int(out_bf16)), _p(y))
+    return y
+
+
+def requantize(y, out_scale, out_zp, qmin, qmax):
+    y = np.ascontiguousarray(y, dtype=np.float32)
+    out = np.empty(y.shape, dtype=np.float32)
+    lib().lo_requantize_f32(_p(y), C.c_size_t(y.size), C.c_float(out_scale), C.c_float(out_zp), C.c_int(qmin),
+                            C.c_int(qmax), _p(out))
+    return out

@@ -252,3 +252,50 @@ void lo_groupwise_dequantize(const uint32_t* packed, const float* scales, const 
       out[r * k + e] = prod + biases[g];
     }
 }
+
+/* ---- the integer form of a quantized Linear, end to end --------------------------------
+ * Per-token symmetric activation encode (the reference's primitives composed:
+ * PerChannelMinMaxObserver(ch_axis=0) -> calculate_qparams -> quantize(ch_axis=0),
+ * lucid/quantization/observer.py:635-648, _qparams.py:197-215, _functional.py:175-182),
+ * exact int32 accumulation, then the epilogue in the kernels' operation order:
+ *   y = f32(acc) * (a_scale[m] * w_scale[n]); y += bias[n]; optional ReLU;
+ * then either the bfloat16 rounding of y (out_bf16, nearest even, lucid/_C/core/Half.h:37-48)
+ * or its requantisation clip(rint(y / out_scale) + out_zp, qmin, qmax). */
+void lo_per_token_quantize_f32_s8(const float* x, size_t rows, size_t cols, float eps, int8_t* q, float* scale) {
+  for (size_t r = 0; r < rows; ++r) {
+    float mn = 0.0f, mx = 0.0f; /* the range always contains 0 */
+    for (size_t c = 0; c < cols; ++c) {
+      const float v = x[r * cols + c];
+      mn = v < mn ? v : mn;
+      mx = v > mx ? v : mx;
+    }
+    const float a = fabsf(mn), b = fabsf(mx);
+    float s = (a > b ? a : b) / 127.5f; /* (qmax - qmin) / 2 for the signed 8-bit grid */
+    s = s > eps ? s : eps;
+    scale[r] = s;
+    for (size_t c = 0; c < cols; ++c) q[r * cols + c] = (int8_t)clipf(rintf(x[r * cols + c] / s), -128.0f, 127.0f);
+  }
+}
+
+static inline float bf16_round_f32(float v) {
+  union { float f; uint32_t u; } w;
+  w.f = v;
+  w.u = (uint32_t)((((uint64_t)w.u + 0x7FFFu + ((w.u >> 16) & 1u)) >> 16) << 16);
+  return w.f;
+}
+
+void lo_linear_epilogue_f32(const int32_t* acc, size_t M, size_t N, const float* a_scale, const float* w_scale,
+                            const float* bias, int relu, int out_bf16, float* y) {
+  for (size_t m = 0; m < M; ++m)
+    for (size_t n = 0; n < N; ++n) {
+      const float sc = a_scale[m] * w_scale[n];
+      float v = (float)acc[m * N + n] * sc;
+      if (bias) v = v + bias[n];
+      if (relu) v = v > 0.0f ? v : 0.0f;
+      y[m * N + n] = out_bf16 ? bf16_round_f32(v) : v;
+    }
+}
+
+void lo_requantize_f32(const float* y, size_t n, float out_scale, float out_zp, int qmin, int qmax, float* codes) {
+  for (size_t i = 0; i < n; ++i) codes[i] = clipf(rintf(y[i] / out_scale) + out_zp, (float)qmin, (float)qmax);
+}

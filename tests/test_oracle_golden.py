@@ -345,3 +345,28 @@ def test_c_restatement_of_groupwise_codes(bits, group):
     assert np.array_equal(packed, cpacked) and np.array_equal(s, cs) and np.array_equal(b, cb)
     assert np.array_equal(O.groupwise_dequantize(packed, s, b, group, bits),
                           CO.groupwise_dequantize(cpacked, cs, cb, group, bits))
+
+
+@pytest.mark.parametrize("relu", [False, True])
+def test_c_restatement_of_the_integer_linear(relu):
+    """The north-star composition (per-token encode -> exact int32 accumulation -> f32 epilogue ->
+    bf16 rounding or requantisation) in plain C equals the NumPy restatement bit for bit."""
+    rng = np.random.default_rng(41 + relu)
+    m, n, k = 37, 29, 96
+    x = (rng.standard_normal((m, k)) * 3).astype(np.float32)
+    x[3] = 0.0                                            # an all-zero token: scale = eps
+    x[5, :8] = [127.5, -127.5, 0.5, -0.5, 1.5, 2.5, -1.5, 63.75]  # ties after the divide (scale 1)
+    x[5, 8:] = 0.0
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    w_scale = (rng.random(n) * 0.01 + 1e-3).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    q, s = O.per_token_quantize(x, O.QINT8)
+    cq, cs = CO.per_token_quantize(x)
+    assert np.array_equal(np.asarray(q, dtype=np.int8), cq) and np.array_equal(np.asarray(s, dtype=np.float32).reshape(-1), cs)
+    acc = O.int_gemm_exact(cq, w)
+    assert np.array_equal(acc, CO.int_gemm(cq, w))
+    y = O.epilogue_f32(acc, cs, 0, None, w_scale, bias, relu=relu)
+    assert np.array_equal(y, CO.linear_epilogue(acc, cs, w_scale, bias, relu=relu))
+    assert np.array_equal(O.bf16_round(y), CO.linear_epilogue(acc, cs, w_scale, bias, relu=relu, out_bf16=True))
+    for scale, zp, qmin, qmax in ((0.05, 128.0, 0, 255), (0.11, 0.0, -128, 127)):
+        assert np.array_equal(O.requantize_f32(y, scale, zp, qmin, qmax), CO.requantize(y, scale, zp, qmin, qmax))
