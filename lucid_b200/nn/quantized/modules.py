@@ -20,6 +20,14 @@ class Quantize(torch.nn.Module):
         self.register_buffer("zero_point", torch.as_tensor(zero_point, dtype=torch.float32))
         self.qdtype = qdtype
         self.nhwc = nhwc
+        self._zp0 = None  # (key of the zero-point buffer, "it is zero"): read back once, not per call
+
+    def _zp_is_zero(self) -> bool:
+        z = self.zero_point
+        key = (z.data_ptr(), z._version)
+        if self._zp0 is None or self._zp0[0] != key:
+            self._zp0 = (key, bool((z == 0).all().item()))
+        return self._zp0[1]
 
     def forward(self, x):
         # image batches (4-D) carry their codes channels-last, the layout the convolution reads
@@ -31,7 +39,7 @@ class Quantize(torch.nn.Module):
         y = dequantize(codes, self.scale, self.zero_point)
         if nhwc:
             y = y.permute(0, 3, 1, 2)
-        return tag(y, QCodes(codes, self.scale, self.zero_point, "nhwc" if nhwc else "rowmajor"))
+        return tag(y, QCodes(codes, self.scale, self.zero_point, "nhwc" if nhwc else "rowmajor", self._zp_is_zero()))
 
     @classmethod
     def from_float(cls, mod):
