@@ -222,7 +222,7 @@ def test_qat_fused_relu_layers_of_every_rank_convert(rank):
     conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
     torch.manual_seed(20 + rank)
     net = torch.nn.Sequential(Q.QuantStub(), conv_t(16, 32, 3, padding=1), torch.nn.ReLU(), conv_t(32, 16, 1),
-                              torch.nn.Flatten(), torch.nn.LazyLinear(8), torch.nn.ReLU(), Q.DeQuantStub()).cuda()
+                              torch.nn.Flatten(), torch.nn.LazyLinear(16), torch.nn.ReLU(), Q.DeQuantStub()).cuda()
     x = torch.randn(4, 16, *([8] * rank), device="cuda")
     net(x)  # materialise the lazy layer
     qcfg = Q.get_default_qat_qconfig()
