@@ -1,0 +1,142 @@
+"""A NumPy stand-in for a handful of C-ABI entry points -- TEST INFRASTRUCTURE ONLY.
+
+The package has no CPU path: without the CUDA library every call raises.  The CPU test suite
+still wants to exercise the HOST logic of the workflows (what ``prepare_qat`` swaps, what
+``convert`` builds from a trained module, which grid ends up where).  ``install`` replaces, for
+the duration of one test, ``lucid_b200._lib.load`` by an object that implements the streaming
+entry points those workflows touch (``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``,
+``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather) in NumPy on host
+pointers, lifts the device checks, and switches the engine to ``"reference"`` so that layers run
+the reference's float sequence (the integer kernels are not stood in for).  The arithmetic is the
+oracle's (same operation order); nothing here is importable from the package and nothing in the
+package knows about it."""
+
+from __future__ import annotations
+
+import contextlib
+import ctypes as C
+
+import numpy as np
+import torch
+
+_NP = {0: np.float32, 2: np.int8, 3: np.uint8, 4: np.int16, 5: np.int32}
+
+
+def _addr(p):
+    if p is None:
+        return None
+    return p.value if isinstance(p, C.c_void_p) else int(p)
+
+
+def _arr(p, code, n):
+    a = _addr(p)
+    if a is None or n == 0:
+        return None
+    dt = np.dtype(_NP[code])
+    return np.frombuffer((C.c_char * (n * dt.itemsize)).from_address(a), dtype=dt)
+
+
+def _f(v):
+    return float(v.value) if isinstance(v, C.c_float) else float(v)
+
+
+def _grid(sp, zp, sv, zv, rows, cols, mode):
+    """(scale, zero_point) broadcastable over a (rows, cols) view: scalars passed by value, or
+    one entry per tensor / row / column behind the pointers."""
+    if _addr(sp) is None:
+        return np.float32(_f(sv)), np.float32(_f(zv))
+    n = 1 if mode == 0 else (rows if mode == 1 else cols)
+    s, z = _arr(sp, 0, n), _arr(zp, 0, n)
+    if mode == 0:
+        return s[0], z[0]
+    return (s[:, None], z[:, None]) if mode == 1 else (s[None, :], z[None, :])
+
+
+class StandIn:
+    """The operation order of lucid/quantization/_functional.py:175-182, 269-281, 299-331 and
+    _qparams.py:197-215, on host memory."""
+
+    def lq_quantize(self, x, xcode, rows, cols, sp, zp, sv, zv, mode, qmin, qmax, out, ocode, stream):
+        X = _arr(x, xcode, rows * cols).reshape(rows, cols)
+        s, z = _grid(sp, zp, sv, zv, rows, cols, mode)
+        q = np.clip(np.rint((X / s).astype(np.float32)) + z, qmin, qmax)
+        _arr(out, ocode, rows * cols).reshape(rows, cols)[...] = q.astype(_NP[ocode])
+        return 0
+
+    def lq_dequantize(self, q, qcode, rows, cols, sp, zp, sv, zv, mode, out, ocode, stream):
+        codes = _arr(q, qcode, rows * cols).reshape(rows, cols).astype(np.float32)
+        s, z = _grid(sp, zp, sv, zv, rows, cols, mode)
+        _arr(out, ocode, rows * cols).reshape(rows, cols)[...] = ((codes - z) * s).astype(np.float32)
+        return 0
+
+    def lq_fake_quantize(self, x, rows, cols, sp, zp, sv, zv, mode, qmin, qmax, out, mask, stream):
+        X = _arr(x, 0, rows * cols).reshape(rows, cols)
+        s, z = _grid(sp, zp, sv, zv, rows, cols, mode)
+        t = np.rint((X / s).astype(np.float32)) + z
+        _arr(out, 0, rows * cols).reshape(rows, cols)[...] = ((np.clip(t, qmin, qmax) - z) * s).astype(np.float32)
+        if _addr(mask) is not None:
+            _arr(mask, 0, rows * cols).reshape(rows, cols)[...] = ((t >= qmin) & (t <= qmax)).astype(np.float32)
+        return 0
+
+    def lq_minmax(self, x, code, rows, cols, mode, mn, mx, ws, ws_bytes, stream):
+        X = _arr(x, code, rows * cols).reshape(rows, cols)
+        if mode == 1:
+            _arr(mn, 0, rows)[...] = X.min(axis=1)
+            _arr(mx, 0, rows)[...] = X.max(axis=1)
+        else:
+            _arr(mn, 0, 1)[0] = X.min()
+            _arr(mx, 0, 1)[0] = X.max()
+        return 0
+
+    def lq_minmax_workspace_bytes(self):
+        return 64
+
+    def lq_calculate_qparams(self, mn, mx, n, symmetric, is_signed, qmin, qmax, eps, scale, zp, stream):
+        lo = np.minimum(_arr(mn, 0, n), np.float32(0))
+        hi = np.maximum(_arr(mx, 0, n), np.float32(0))
+        e = np.float32(_f(eps))
+        if symmetric:
+            m = np.maximum(np.abs(lo), np.abs(hi))
+            _arr(scale, 0, n)[...] = np.maximum(m / np.float32((qmax - qmin) / 2.0), e)
+            _arr(zp, 0, n)[...] = 0.0 if is_signed else float((qmax + qmin + 1) // 2)
+        else:
+            s = np.maximum(((hi - lo) / np.float32(qmax - qmin)).astype(np.float32), e)
+            _arr(scale, 0, n)[...] = s
+            _arr(zp, 0, n)[...] = np.clip(np.float32(qmin) - np.rint((lo / s).astype(np.float32)), qmin, qmax)
+        return 0
+
+    def lq_embedding_s8(self, w, w_scale, w_zp, rows, dim, idx, idx_bits, n, offsets, n_bags, include_last, mode,
+                        padding_idx, out, ocode, status, stream):
+        if _addr(offsets) is not None:
+            raise NotImplementedError("the stand-in gathers rows only (no bags)")
+        table = _arr(w, 2, rows * dim).reshape(rows, dim).astype(np.float32)
+        s, z = _arr(w_scale, 0, rows), _arr(w_zp, 0, rows)
+        index = np.frombuffer((C.c_char * (n * idx_bits // 8)).from_address(_addr(idx)),
+                              dtype=np.int64 if idx_bits == 64 else np.int32)
+        got = ((table[index] - z[index][:, None]) * s[index][:, None]).astype(np.float32)
+        if padding_idx >= 0:
+            got[index == padding_idx] = 0.0
+        _arr(out, ocode, n * dim).reshape(n, dim)[...] = got
+        return 0
+
+
+def install(monkeypatch) -> StandIn:
+    """Stand the NumPy object in for the library until the end of the calling test."""
+    from lucid_b200 import _lib, backends
+
+    fake = StandIn()
+
+    @contextlib.contextmanager
+    def plain_float32():
+        yield
+
+    monkeypatch.setattr(_lib, "load", lambda: fake)
+    monkeypatch.setattr(_lib, "require_cuda", lambda t, what: None)
+    monkeypatch.setattr(_lib, "stream_ptr", lambda device=None: None)
+    monkeypatch.setattr(_lib, "check_device_status_lazily", lambda device, every=256: None)
+    monkeypatch.setattr(_lib, "minmax_workspace", lambda device: torch.zeros(64, dtype=torch.uint8))
+    monkeypatch.setattr(_lib, "status_word", lambda device: torch.zeros(1, dtype=torch.int32))
+    monkeypatch.setattr(_lib, "ieee_float32", plain_float32)
+    monkeypatch.setattr(torch.cuda, "device", lambda dev: contextlib.nullcontext())
+    monkeypatch.setattr(backends.quantized, "_engine", "reference")
+    return fake

@@ -1,0 +1,218 @@
+"""Host logic of the quantization workflows on the CPU: what ``prepare`` / ``prepare_qat`` swap,
+what ``convert`` builds from calibrated and trained modules, where each grid ends up.
+
+The C ABI is replaced for the duration of each test by the NumPy stand-in of
+``tests/abi_standin.py`` and the engine is ``"reference"`` (layers run the reference's float
+sequence), so these tests say nothing about the kernels -- the GPU tests do that through the
+real library -- and everything about the Python that surrounds them.  Gates follow the
+reference's own tests: lucid/test/unit/quantization/test_qat.py, test_qat_fused.py,
+test_qat_convbn_ranks.py, test_static_ptq.py, test_graph_mode.py."""
+
+import pytest
+import torch
+
+import abi_standin
+import lucid_b200.nn.qat as nnqat
+import lucid_b200.nn.quantized as nnq
+import lucid_b200.quantization as Q
+from lucid_b200.nn.intrinsic import qat as nniqat
+
+
+@pytest.fixture(autouse=True)
+def standin(monkeypatch):
+    return abi_standin.install(monkeypatch)
+
+
+def _rel(a, b):
+    a, b = a.detach(), b.detach()
+    return float((a - b).abs().mean() / b.abs().mean().clamp_min(1e-6))
+
+
+def _minmax_qconfig():
+    return Q.QConfig(activation=Q.MinMaxObserver, weight=Q.get_default_qconfig().weight)
+
+
+def test_qat_trains_through_the_grids_and_converts():
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(Q.QuantStub(), torch.nn.Linear(64, 128), torch.nn.ReLU(),
+                                torch.nn.Linear(128, 32), Q.DeQuantStub())
+    qat = Q.prepare_qat(model)
+    assert type(qat[1]) is nnqat.Linear and isinstance(qat[1].weight_fake_quant, Q.FakeQuantize)
+    assert isinstance(qat[0].activation_post_process, Q.FakeQuantize) and qat.training
+    x = torch.randn(256, 64)
+    target = model(x).detach() * 1.5
+    opt = torch.optim.SGD(qat.parameters(), lr=1e-2)
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(qat(x), target)
+        loss.backward()
+        assert torch.isfinite(qat[1].weight.grad).all()
+        opt.step()
+        losses.append(loss.item())
+    assert all(b < a for a, b in zip(losses, losses[1:]))
+    qat.eval()
+    y_qat = qat(x)
+    qmodel = Q.convert(qat)
+    assert [type(m) for m in qmodel] == [nnq.Quantize, nnq.Linear, nnq.ReLU, nnq.Linear, nnq.DeQuantize]
+    assert qmodel[1].weight_int8.dtype == torch.int8 and "weight" not in qmodel[1].state_dict()
+    assert float(qmodel[0].scale) == float(qat[0].activation_post_process.scale)
+    assert float(qmodel[1].scale) == float(qat[1].activation_post_process.scale)
+    # under the reference engine the converted model IS what QAT simulated
+    assert _rel(qmodel(x), y_qat) < 1e-6
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+def test_conv_bn_fusion_trains_and_converts(rank):
+    conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
+    bn_t = (torch.nn.BatchNorm1d, torch.nn.BatchNorm2d, torch.nn.BatchNorm3d)[rank - 1]
+    torch.manual_seed(5 + rank)
+    net = torch.nn.Sequential(Q.QuantStub(), conv_t(16, 32, 3, padding=1, bias=False), bn_t(32), torch.nn.ReLU(),
+                              conv_t(32, 32, 3, stride=2, padding=1), bn_t(32), Q.DeQuantStub()).train()
+    with torch.no_grad():
+        for bn in (net[2], net[5]):
+            bn.running_mean.normal_(0, 0.2)
+            bn.running_var.uniform_(0.5, 1.5)
+            bn.weight.uniform_(0.5, 1.5)
+            bn.bias.normal_(0, 0.2)
+    qcfg = Q.get_default_qat_qconfig()
+    qat = Q.prepare_qat(Q.fuse_modules_qat(net, [["1", "2", "3"], ["4", "5"]], qcfg), qcfg)
+    assert type(qat[1]) is getattr(nniqat, f"ConvBnReLU{rank}d") and type(qat[4]) is getattr(nniqat, f"ConvBn{rank}d")
+    x = torch.randn(4, 16, *([10] * rank))
+    opt = torch.optim.SGD(qat.parameters(), lr=1e-3)
+    mean0 = qat[1].bn.running_mean.clone()
+    for _ in range(2):
+        opt.zero_grad()
+        qat(x).square().mean().backward()
+        assert qat[1].conv.weight.grad is not None and qat[1].bn.weight.grad is not None
+        opt.step()
+    assert not torch.equal(qat[1].bn.running_mean, mean0)  # the statistics kept learning
+    qat.eval()
+    with torch.no_grad():
+        y_qat = qat(x)
+    qnet = Q.convert(qat)
+    assert type(qnet[1]) is getattr(nnq, f"ConvReLU{rank}d") and type(qnet[4]) is getattr(nnq, f"Conv{rank}d")
+    w_fold, b_fold = qat[1]._fold()
+    assert torch.equal(qnet[1].bias, b_fold.detach())
+    w_hat = Q.dequantize(qnet[1].weight_int8, qnet[1].weight_scale, qnet[1].weight_zero_point, ch_axis=0)
+    assert torch.equal(w_hat.reshape(w_fold.shape), qat[1].weight_fake_quant(w_fold.detach()))  # the FOLDED weight's grid
+    assert qnet[1].state_dict()["weight_int8"].shape == w_fold.shape  # the reference's buffer shape
+    with torch.no_grad():
+        assert _rel(qnet(x), y_qat) < 1e-6
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+def test_fused_relu_layers_train_and_convert(rank):
+    conv_t = (torch.nn.Conv1d, torch.nn.Conv2d, torch.nn.Conv3d)[rank - 1]
+    torch.manual_seed(20 + rank)
+    net = torch.nn.Sequential(Q.QuantStub(), conv_t(16, 32, 3, padding=1), torch.nn.ReLU(), conv_t(32, 16, 1),
+                              torch.nn.Flatten(), torch.nn.LazyLinear(16), torch.nn.ReLU(), Q.DeQuantStub())
+    x = torch.randn(4, 16, *([6] * rank))
+    net(x)
+    qcfg = Q.get_default_qat_qconfig()
+    qat = Q.prepare_qat(Q.fuse_modules_qat(net, [["1", "2"], ["5", "6"]], qcfg), qcfg)
+    assert [type(qat[i]) for i in (1, 3, 5)] == [getattr(nnqat, f"ConvReLU{rank}d"), getattr(nnqat, f"Conv{rank}d"),
+                                                 nnqat.LinearReLU]
+    qat(x).square().mean().backward()
+    assert qat[1].weight.grad is not None and qat[5].weight.grad is not None
+    qat.eval()
+    with torch.no_grad():
+        y_qat = qat(x)
+    assert float(y_qat.min()) >= 0.0  # the fused ReLU sits ahead of the output grid
+    assert float(qat[5].activation_post_process.zero_point) == 0.0  # so the grid covers [0, max] only
+    qnet = Q.convert(qat)
+    assert [type(qnet[i]) for i in (0, 1, 3, 5)] == [nnq.Quantize, getattr(nnq, f"ConvReLU{rank}d"),
+                                                    getattr(nnq, f"Conv{rank}d"), nnq.LinearReLU]
+    with torch.no_grad():
+        assert _rel(qnet(x), y_qat) < 1e-6
+
+
+def test_embedding_tables_convert_without_calibration_and_through_qat():
+    torch.manual_seed(9)
+    model = torch.nn.Sequential(torch.nn.Embedding(500, 64, padding_idx=0), torch.nn.Linear(64, 32))
+    idx = torch.randint(0, 500, (4, 10))
+    y = model(idx).detach()
+    qstatic = Q.convert(model)
+    assert type(qstatic[0]) is nnq.Embedding and type(qstatic[1]) is torch.nn.Linear
+    assert _rel(qstatic(idx), y) < 0.02
+    assert bool((qstatic[0](torch.tensor([0, 0])) == 0).all())  # the padding row reads as zeros
+    qat = Q.prepare_qat(model)
+    assert type(qat[0]) is nnqat.Embedding and type(qat[1]) is nnqat.Linear
+    qat(idx).square().mean().backward()
+    assert qat[0].weight.grad is not None
+    qnet = Q.convert(qat.eval())
+    assert type(qnet[0]) is nnq.Embedding and qnet[0].padding_idx == 0
+    assert list(qnet[0].state_dict()) == ["weight_int8", "weight_scale", "weight_zero_point"]
+    assert qnet[0].weight_scale.shape == (500,)  # one scale per row
+    assert _rel(qnet(idx), y) < 0.05
+
+
+def test_static_ptq_with_a_mapping_leaves_the_excluded_head_in_float():
+    """prepare -> calibrate -> convert with a QConfigMapping (lucid/quantization/_quantize.py:291-305;
+    gates of test_static_ptq.py:60-99): stubs become Quantize / DeQuantize, the mapped layers become
+    integer layers with the observed grids, the excluded one stays float, the checkpoint round-trips."""
+    torch.manual_seed(3)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.quant, self.dequant = Q.QuantStub(), Q.DeQuantStub()
+            self.fc1, self.act, self.fc2 = torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 16)
+            self.head = torch.nn.Linear(16, 4)
+
+        def forward(self, x):
+            return self.head(self.dequant(self.fc2(self.act(self.fc1(self.quant(x))))))
+
+    net = Net().eval()
+    x = torch.randn(64, 32)
+    mapping = Q.QConfigMapping().set_global(_minmax_qconfig()).set_module_name("head", None)
+    fused = Q.fuse_modules(net, [["fc1", "act"]])
+    prepared = Q.prepare(fused, mapping)
+    with torch.no_grad():
+        assert torch.equal(prepared(x), net(x))  # observers change nothing
+    qnet = Q.convert(prepared)
+    assert type(qnet.quant) is nnq.Quantize and type(qnet.dequant) is nnq.DeQuantize
+    assert type(qnet.fc1) is nnq.LinearReLU and type(qnet.fc2) is nnq.Linear and type(qnet.head) is torch.nn.Linear
+    lo, hi = float(x.min()), float(x.max())
+    assert float(qnet.quant.scale) == pytest.approx((max(hi, 0) - min(lo, 0)) / 255, rel=1e-6)
+    with torch.no_grad():
+        y, y_q = net(x), qnet(x)
+    assert _rel(y_q, y) < 0.05
+    state = qnet.state_dict()
+    assert {"fc1.weight_int8", "fc1.weight_scale", "fc1.weight_zero_point", "fc1.scale", "fc1.zero_point",
+            "fc1.bias", "head.weight"} <= set(state)
+    other = Q.prepare(Q.fuse_modules(Net().eval(), [["fc1", "act"]]), mapping)  # different weights and grids
+    with torch.no_grad():
+        other(x * 3)
+    clone = Q.convert(other)
+    with torch.no_grad():
+        assert not torch.equal(clone(x), y_q)
+    clone.load_state_dict(state)
+    with torch.no_grad():
+        assert torch.equal(clone(x), y_q)
+
+
+def test_graph_mode_needs_no_hand_placed_stubs():
+    """prepare_fx -> calibrate -> convert_fx (lucid/quantization/_quantize_fx.py; gates of
+    test_graph_mode.py:20-60)."""
+    torch.manual_seed(4)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8)).eval()
+    x = torch.randn(128, 32)
+    prepared = Q.prepare_fx(net, _minmax_qconfig(), example_inputs=x[:1])
+    assert isinstance(prepared, nnq.QuantWrapper)
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert_fx(prepared)
+    assert type(qnet.quant) is nnq.Quantize and type(qnet.dequant) is nnq.DeQuantize
+    assert type(qnet.module[0]) is nnq.Linear and qnet.module[0].weight_int8.dtype == torch.int8
+    with torch.no_grad():
+        assert _rel(qnet(x), net(x)) < 0.05
+
+
+def test_the_package_itself_has_no_cpu_path(monkeypatch):
+    """Without the stand-in a CPU tensor is refused: the fixture is what makes the tests above run."""
+    from lucid_b200 import _lib
+
+    monkeypatch.undo()
+    with pytest.raises(_lib.LucidError):
+        Q.quantize(torch.randn(4, 4), 0.1, 0.0, Q.qint8)
