@@ -5,9 +5,10 @@ still wants to exercise the HOST logic of the workflows (what ``prepare_qat`` sw
 ``convert`` builds from a trained module, which grid ends up where).  ``install`` replaces, for
 the duration of one test, ``lucid_b200._lib.load`` by an object that implements the streaming
 entry points those workflows touch (``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``,
-``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather) in NumPy on host
-pointers, lifts the device checks, and switches the engine to ``"reference"`` so that layers run
-the reference's float sequence (the integer kernels are not stood in for).  The arithmetic is the
+``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather, and for the Linear
+family ``lq_rowsum_s8`` / ``lq_quantize_dynamic`` / ``lq_gemm_s8_ws``) in NumPy on host pointers,
+lifts the device checks, and switches the engine to ``"reference"`` by default so that layers run
+the reference's float sequence (the convolution kernels are not stood in for).  The arithmetic is the
 oracle's (same operation order); nothing here is importable from the package and nothing in the
 package knows about it."""
 
@@ -120,8 +121,62 @@ class StandIn:
         return 0
 
 
-def install(monkeypatch) -> StandIn:
-    """Stand the NumPy object in for the library until the end of the calling test."""
+    # ---- the integer Linear: row sums, dynamic encode, contraction + epilogue -----------------
+    def lq_rowsum_s8(self, b, n, k, out, stream):
+        _arr(out, 5, n)[...] = _arr(b, 2, n * k).reshape(n, k).astype(np.int32).sum(axis=1)
+        return 0
+
+    def lq_quantize_dynamic(self, x, code, rows, cols, symmetric, is_signed, qmin, qmax, eps, ws, ws_bytes, out,
+                            ocode, out_scale, out_zp, out_minmax, stream):
+        X = _arr(x, code, rows * cols)
+        mm = _arr(out_minmax, 0, 2)
+        mm[0], mm[1] = X.min(), X.max()
+        self.lq_calculate_qparams(C.c_void_p(_addr(out_minmax)), C.c_void_p(_addr(out_minmax) + 4), 1, symmetric,
+                                  is_signed, qmin, qmax, eps, out_scale, out_zp, None)
+        s, z = _arr(out_scale, 0, 1)[0], _arr(out_zp, 0, 1)[0]
+        _arr(out, ocode, rows * cols)[...] = np.clip(np.rint((X / s).astype(np.float32)) + z, qmin, qmax).astype(_NP[ocode])
+        return 0
+
+    def lq_gemm_s8_ws(self, a, a_signed, b, m, n, k, e_ref, out, ldo, ws, ws_bytes, status, stream):
+        """acc = a b^T exactly; t = acc - a_zp * rowsum(b); y = f32(t) * (a_scale * b_scale) + bias;
+        optional ReLU; float output, or clip(rint(y / out_scale) + out_zp, qmin, qmax) for 8-bit."""
+        e = e_ref._obj
+        if e.act not in (0, 1):
+            raise NotImplementedError("the stand-in has no gated activation")
+        A = _arr(a, 2 if a_signed else 3, m * k).reshape(m, k).astype(np.int64)
+        B = _arr(b, 2, n * k).reshape(n, k).astype(np.int64)
+        acc = A @ B.T
+        if e.a_zp and e.b_rowsum:
+            acc = acc - np.int64(_arr(e.a_zp, 0, 1)[0]) * _arr(e.b_rowsum, 5, n).astype(np.int64)[None, :]
+        if e.out_dtype == 5:  # raw int32 accumulators
+            got = acc.astype(np.int32)
+        else:
+            a_s = _arr(e.a_scale, 0, m if e.a_scale_mode == 1 else 1).reshape(-1, 1) if e.a_scale else np.float32(1)
+            b_s = _arr(e.b_scale, 0, n).reshape(1, -1) if e.b_scale else np.float32(1)
+            y = acc.astype(np.int32).astype(np.float32) * (a_s * b_s).astype(np.float32)
+            if e.bias:
+                y = (y + _arr(e.bias, 0, n).reshape(1, -1)).astype(np.float32)
+            if e.act == 1:
+                y = np.maximum(y, np.float32(0))
+            if e.out_dtype in (2, 3):
+                s, z = _arr(e.out_scale, 0, 1)[0], _arr(e.out_zp, 0, 1)[0]
+                y = np.clip(np.rint((y / s).astype(np.float32)) + z, e.qmin, e.qmax)
+            elif e.out_dtype != 0:
+                raise NotImplementedError("the stand-in writes f32, s32 and 8-bit outputs")
+            got = y.astype(_NP[e.out_dtype])
+        if ldo != n:
+            raise NotImplementedError("the stand-in writes dense outputs")
+        _arr(out, e.out_dtype, m * n).reshape(m, n)[...] = got
+        return 0
+
+    def lq_gemm_workspace_bytes(self):
+        return 64
+
+
+def install(monkeypatch, engine: str = "reference", pose_as_cuda: bool = False) -> StandIn:
+    """Stand the NumPy object in for the library until the end of the calling test.
+    ``pose_as_cuda`` makes CPU tensors answer ``is_cuda`` with True, for the modules that only
+    read carried codes off device tensors."""
     from lucid_b200 import _lib, backends
 
     fake = StandIn()
@@ -138,5 +193,8 @@ def install(monkeypatch) -> StandIn:
     monkeypatch.setattr(_lib, "status_word", lambda device: torch.zeros(1, dtype=torch.int32))
     monkeypatch.setattr(_lib, "ieee_float32", plain_float32)
     monkeypatch.setattr(torch.cuda, "device", lambda dev: contextlib.nullcontext())
-    monkeypatch.setattr(backends.quantized, "_engine", "reference")
+    monkeypatch.setattr(_lib, "gemm_workspace", lambda device: torch.zeros(64, dtype=torch.uint8))
+    monkeypatch.setattr(backends.quantized, "_engine", engine)
+    if pose_as_cuda:
+        monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
     return fake

@@ -216,3 +216,63 @@ def test_the_package_itself_has_no_cpu_path(monkeypatch):
     monkeypatch.undo()
     with pytest.raises(_lib.LucidError):
         Q.quantize(torch.randn(4, 4), 0.1, 0.0, Q.qint8)
+
+
+def _steps_apart(y_a, y_b, scale):
+    """Distance of two tensors on one output grid, in grid steps."""
+    return torch.round((y_a - y_b) / scale).abs()
+
+
+@pytest.mark.parametrize("fuse", [False, True])
+def test_integer_linear_wiring_against_the_float_form(monkeypatch, fuse):
+    """Engine "auto" over the stand-in: the stub's codes feed the first contraction, its output
+    codes ride through the (code-preserving) ReLU into the second one, and what comes out equals
+    the reference's float sequence on the same converted model up to isolated one-step
+    differences -- i.e. scales, zero points, row sums and bias reach the epilogue in the right
+    places.  (The rate and size of the differences is the gate the GPU tests apply to the
+    kernels, lucid/test/unit/quantization/test_static_ptq.py:86.)"""
+    from lucid_b200 import backends
+    from lucid_b200.nn.quantized._utils import codes_of
+
+    abi_standin.install(monkeypatch, pose_as_cuda=True)  # the code-preserving ReLU reads codes off device tensors
+    torch.manual_seed(11)
+    model = torch.nn.Sequential(Q.QuantStub(), torch.nn.Linear(64, 128), torch.nn.ReLU(),
+                                torch.nn.Linear(128, 32), Q.DeQuantStub()).eval()
+    x = torch.randn(200, 64) + 0.3  # an asymmetric input range: a non-zero activation zero point
+    if fuse:
+        model = Q.fuse_modules(model, [["1", "2"]])
+    prepared = Q.prepare(model, _minmax_qconfig())
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    assert float(qnet[0].zero_point) != 0.0
+    with torch.no_grad():
+        y_float_form = qnet(x)
+        monkeypatch.setattr(backends.quantized, "_engine", "auto")
+        assert qnet[1]._int8_ok() and qnet[3]._int8_ok()
+        h = qnet[1](qnet[0](x))
+        carried = codes_of(h)
+        assert carried is not None and carried.codes.dtype == torch.uint8  # the layer hands its codes on
+        assert torch.equal(Q.dequantize(carried.codes, carried.scale, carried.zero_point), h)
+        y_int = qnet(x)
+    steps = _steps_apart(y_int, y_float_form, qnet[3].scale)
+    assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
+    assert _rel(y_int, model(x)) < 0.05
+
+
+def test_dynamic_linear_wiring_against_the_float_form(monkeypatch):
+    """``quantize_dynamic`` under engine "auto": the live-range encode, the contraction and the
+    float epilogue reproduce the reference's float sequence (lucid/nn/quantized/dynamic/linear.py:84-99)."""
+    from lucid_b200 import backends
+
+    torch.manual_seed(12)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 96), torch.nn.ReLU(), torch.nn.Linear(96, 16)).eval()
+    x = torch.randn(50, 64)
+    qnet = Q.quantize_dynamic(model)
+    assert type(qnet[0]) is nnq.dynamic.Linear and type(qnet[2]) is nnq.dynamic.Linear
+    with torch.no_grad():
+        y_float_form = qnet(x)
+        monkeypatch.setattr(backends.quantized, "_engine", "auto")
+        y_int = qnet(x)
+        assert float((y_int - y_float_form).abs().max() / y_float_form.abs().max()) < 1e-5
+        assert _rel(y_int, model(x)) < 0.03
