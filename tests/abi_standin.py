@@ -6,9 +6,10 @@ still wants to exercise the HOST logic of the workflows (what ``prepare_qat`` sw
 the duration of one test, ``lucid_b200._lib.load`` by an object that implements the streaming
 entry points those workflows touch (``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``,
 ``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather, and for the Linear
-family ``lq_rowsum_s8`` / ``lq_quantize_dynamic`` / ``lq_gemm_s8_ws``) in NumPy on host pointers,
+family and the convolutions ``lq_rowsum_s8`` / ``lq_quantize_dynamic`` / ``lq_gemm_s8_ws`` /
+``lq_conv2d_nhwc_s8_ex``) in NumPy on host pointers,
 lifts the device checks, and switches the engine to ``"reference"`` by default so that layers run
-the reference's float sequence (the convolution kernels are not stood in for).  The arithmetic is the
+the reference's float sequence.  The arithmetic is the
 oracle's (same operation order); nothing here is importable from the package and nothing in the
 package knows about it."""
 
@@ -137,36 +138,56 @@ class StandIn:
         _arr(out, ocode, rows * cols)[...] = np.clip(np.rint((X / s).astype(np.float32)) + z, qmin, qmax).astype(_NP[ocode])
         return 0
 
-    def lq_gemm_s8_ws(self, a, a_signed, b, m, n, k, e_ref, out, ldo, ws, ws_bytes, status, stream):
-        """acc = a b^T exactly; t = acc - a_zp * rowsum(b); y = f32(t) * (a_scale * b_scale) + bias;
-        optional ReLU; float output, or clip(rint(y / out_scale) + out_zp, qmin, qmax) for 8-bit."""
-        e = e_ref._obj
+    @staticmethod
+    def _epilogue(acc, e, m, n):
+        """The epilogue of include/lucid_b200.h on exact accumulators ``acc (m, n)`` (int64):
+        t = acc - a_zp * rowsum(b); S32: out = t; otherwise y = f32(t) * (a_scale * b_scale) + bias,
+        optional ReLU, then float, or clip(rint(y / out_scale) + out_zp, qmin, qmax) for 8-bit."""
         if e.act not in (0, 1):
             raise NotImplementedError("the stand-in has no gated activation")
-        A = _arr(a, 2 if a_signed else 3, m * k).reshape(m, k).astype(np.int64)
-        B = _arr(b, 2, n * k).reshape(n, k).astype(np.int64)
-        acc = A @ B.T
         if e.a_zp and e.b_rowsum:
             acc = acc - np.int64(_arr(e.a_zp, 0, 1)[0]) * _arr(e.b_rowsum, 5, n).astype(np.int64)[None, :]
-        if e.out_dtype == 5:  # raw int32 accumulators
-            got = acc.astype(np.int32)
-        else:
-            a_s = _arr(e.a_scale, 0, m if e.a_scale_mode == 1 else 1).reshape(-1, 1) if e.a_scale else np.float32(1)
-            b_s = _arr(e.b_scale, 0, n).reshape(1, -1) if e.b_scale else np.float32(1)
-            y = acc.astype(np.int32).astype(np.float32) * (a_s * b_s).astype(np.float32)
-            if e.bias:
-                y = (y + _arr(e.bias, 0, n).reshape(1, -1)).astype(np.float32)
-            if e.act == 1:
-                y = np.maximum(y, np.float32(0))
-            if e.out_dtype in (2, 3):
-                s, z = _arr(e.out_scale, 0, 1)[0], _arr(e.out_zp, 0, 1)[0]
-                y = np.clip(np.rint((y / s).astype(np.float32)) + z, e.qmin, e.qmax)
-            elif e.out_dtype != 0:
-                raise NotImplementedError("the stand-in writes f32, s32 and 8-bit outputs")
-            got = y.astype(_NP[e.out_dtype])
+        if e.out_dtype == 5:
+            return acc.astype(np.int32)
+        a_s = _arr(e.a_scale, 0, m if e.a_scale_mode == 1 else 1).reshape(-1, 1) if e.a_scale else np.float32(1)
+        b_s = _arr(e.b_scale, 0, n).reshape(1, -1) if e.b_scale else np.float32(1)
+        y = acc.astype(np.int32).astype(np.float32) * (a_s * b_s).astype(np.float32)
+        if e.bias:
+            y = (y + _arr(e.bias, 0, n).reshape(1, -1)).astype(np.float32)
+        if e.act == 1:
+            y = np.maximum(y, np.float32(0))
+        if e.out_dtype in (2, 3):
+            s, z = _arr(e.out_scale, 0, 1)[0], _arr(e.out_zp, 0, 1)[0]
+            y = np.clip(np.rint((y / s).astype(np.float32)) + z, e.qmin, e.qmax)
+        elif e.out_dtype != 0:
+            raise NotImplementedError("the stand-in writes f32, s32 and 8-bit outputs")
+        return y.astype(_NP[e.out_dtype])
+
+    def lq_gemm_s8_ws(self, a, a_signed, b, m, n, k, e_ref, out, ldo, ws, ws_bytes, status, stream):
+        e = e_ref._obj
+        A = _arr(a, 2 if a_signed else 3, m * k).reshape(m, k).astype(np.int64)
+        B = _arr(b, 2, n * k).reshape(n, k).astype(np.int64)
         if ldo != n:
             raise NotImplementedError("the stand-in writes dense outputs")
-        _arr(out, e.out_dtype, m * n).reshape(m, n)[...] = got
+        _arr(out, e.out_dtype, m * n).reshape(m, n)[...] = self._epilogue(A @ B.T, e, m, n)
+        return 0
+
+    def lq_conv2d_nhwc_s8_ex(self, x, a_signed, w, g_ref, e_ref, out, ws, ws_bytes, status, stream):
+        """NHWC codes * KRSC codes; out-of-image taps read code 0; the output extent (P, Q) is the
+        caller's (a larger one than the leading padding alone gives means trailing padding)."""
+        from oracle import lucid_oracle as O
+
+        g, e = g_ref._obj, e_ref._obj
+        cg = g.C // g.groups
+        X = _arr(x, 2 if a_signed else 3, g.N * g.H * g.W * g.C).reshape(g.N, g.H, g.W, g.C)
+        Wt = _arr(w, 2, g.K * g.R * g.S * cg).reshape(g.K, g.R, g.S, cg)
+        hi_h = max(0, (g.P - 1) * g.stride_h + g.dil_h * (g.R - 1) + 1 - g.H - g.pad_h)
+        hi_w = max(0, (g.Q - 1) * g.stride_w + g.dil_w * (g.S - 1) + 1 - g.W - g.pad_w)
+        acc = O.int_conv2d_nhwc_general(X, Wt, (g.stride_h, g.stride_w), (g.pad_h, g.pad_w), (hi_h, hi_w),
+                                        (g.dil_h, g.dil_w), g.groups, zp=0)[:, :g.P, :g.Q, :]
+        m = g.N * g.P * g.Q
+        got = self._epilogue(np.ascontiguousarray(acc).reshape(m, g.K).astype(np.int64), e, m, g.K)
+        _arr(out, e.out_dtype, m * g.K).reshape(m, g.K)[...] = got
         return 0
 
     def lq_gemm_workspace_bytes(self):

@@ -276,3 +276,36 @@ def test_dynamic_linear_wiring_against_the_float_form(monkeypatch):
         y_int = qnet(x)
         assert float((y_int - y_float_form).abs().max() / y_float_form.abs().max()) < 1e-5
         assert _rel(y_int, model(x)) < 0.03
+
+
+@pytest.mark.parametrize("rank,stride,padding", [(2, 1, 1), (2, 2, "same1"), (1, 2, 2), (2, 1, 0)])
+def test_integer_conv_wiring_against_the_float_form(monkeypatch, rank, stride, padding):
+    """The convolution modules under engine "auto" over the stand-in: a stub with a non-zero zero
+    point feeds NHWC (or, for 1-D, N-L-C) codes, padded taps hold the code of 0.0, grouped and
+    strided geometries reach the kernel as the module states them, and the result equals the
+    float sequence on the same converted model up to isolated one-step differences."""
+    from lucid_b200 import backends
+
+    abi_standin.install(monkeypatch, pose_as_cuda=True)
+    conv_t = (torch.nn.Conv1d, torch.nn.Conv2d)[rank - 1]
+    same = padding == "same1"
+    torch.manual_seed(30 + rank + stride)
+    first = conv_t(16, 32, 3, stride=1 if same else stride, padding="same" if same else padding)
+    net = torch.nn.Sequential(Q.QuantStub(), first, torch.nn.ReLU(),
+                              conv_t(32, 32, 3, stride=stride, padding=1, groups=2), Q.DeQuantStub()).eval()
+    x = torch.randn(3, 16, *([11] * rank)) + 0.4
+    prepared = Q.prepare(Q.fuse_modules(net, [["1", "2"]]), _minmax_qconfig())
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    assert float(qnet[0].zero_point) != 0.0
+    with torch.no_grad():
+        y_float_form = qnet(x)
+        monkeypatch.setattr(backends.quantized, "_engine", "auto")
+        assert qnet[1]._int8_ok() and qnet[3]._int8_ok()
+        y_int = qnet(x)
+        y = net(x)
+    assert y_int.shape == y.shape
+    steps = _steps_apart(y_int, y_float_form, qnet[3].scale)
+    assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
+    assert _rel(y_int, y) < 0.06
