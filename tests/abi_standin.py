@@ -15,6 +15,7 @@ package knows about it."""
 
 from __future__ import annotations
 
+import collections
 import contextlib
 import ctypes as C
 
@@ -56,7 +57,11 @@ def _grid(sp, zp, sv, zv, rows, cols, mode):
 
 class StandIn:
     """The operation order of lucid/quantization/_functional.py:175-182, 269-281, 299-331 and
-    _qparams.py:197-215, on host memory."""
+    _qparams.py:197-215, on host memory.  ``calls`` counts the contractions that ran (a test can
+    tell the integer route from the float one by it)."""
+
+    def __init__(self) -> None:
+        self.calls = collections.Counter()
 
     def lq_quantize(self, x, xcode, rows, cols, sp, zp, sv, zv, mode, qmin, qmax, out, ocode, stream):
         X = _arr(x, xcode, rows * cols).reshape(rows, cols)
@@ -165,6 +170,7 @@ class StandIn:
 
     def lq_gemm_s8_ws(self, a, a_signed, b, m, n, k, e_ref, out, ldo, ws, ws_bytes, status, stream):
         e = e_ref._obj
+        self.calls["gemm"] += 1
         A = _arr(a, 2 if a_signed else 3, m * k).reshape(m, k).astype(np.int64)
         B = _arr(b, 2, n * k).reshape(n, k).astype(np.int64)
         if ldo != n:
@@ -178,6 +184,7 @@ class StandIn:
         from oracle import lucid_oracle as O
 
         g, e = g_ref._obj, e_ref._obj
+        self.calls["conv"] += 1
         cg = g.C // g.groups
         X = _arr(x, 2 if a_signed else 3, g.N * g.H * g.W * g.C).reshape(g.N, g.H, g.W, g.C)
         Wt = _arr(w, 2, g.K * g.R * g.S * cg).reshape(g.K, g.R, g.S, cg)

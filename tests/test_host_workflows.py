@@ -234,7 +234,7 @@ def test_integer_linear_wiring_against_the_float_form(monkeypatch, fuse):
     from lucid_b200 import backends
     from lucid_b200.nn.quantized._utils import codes_of
 
-    abi_standin.install(monkeypatch, pose_as_cuda=True)  # the code-preserving ReLU reads codes off device tensors
+    fake = abi_standin.install(monkeypatch, pose_as_cuda=True)  # the code-preserving ReLU reads codes off device tensors
     torch.manual_seed(11)
     model = torch.nn.Sequential(Q.QuantStub(), torch.nn.Linear(64, 128), torch.nn.ReLU(),
                                 torch.nn.Linear(128, 32), Q.DeQuantStub()).eval()
@@ -254,7 +254,9 @@ def test_integer_linear_wiring_against_the_float_form(monkeypatch, fuse):
         carried = codes_of(h)
         assert carried is not None and carried.codes.dtype == torch.uint8  # the layer hands its codes on
         assert torch.equal(Q.dequantize(carried.codes, carried.scale, carried.zero_point), h)
+        before = fake.calls["gemm"]
         y_int = qnet(x)
+        assert fake.calls["gemm"] == before + 2  # both layers took the integer route
     steps = _steps_apart(y_int, y_float_form, qnet[3].scale)
     assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
     assert _rel(y_int, model(x)) < 0.05
@@ -286,7 +288,7 @@ def test_integer_conv_wiring_against_the_float_form(monkeypatch, rank, stride, p
     float sequence on the same converted model up to isolated one-step differences."""
     from lucid_b200 import backends
 
-    abi_standin.install(monkeypatch, pose_as_cuda=True)
+    fake = abi_standin.install(monkeypatch, pose_as_cuda=True)
     conv_t = (torch.nn.Conv1d, torch.nn.Conv2d)[rank - 1]
     same = padding == "same1"
     torch.manual_seed(30 + rank + stride)
@@ -304,8 +306,39 @@ def test_integer_conv_wiring_against_the_float_form(monkeypatch, rank, stride, p
         monkeypatch.setattr(backends.quantized, "_engine", "auto")
         assert qnet[1]._int8_ok() and qnet[3]._int8_ok()
         y_int = qnet(x)
+        assert fake.calls["conv"] >= 2  # both layers took the integer route
         y = net(x)
     assert y_int.shape == y.shape
     steps = _steps_apart(y_int, y_float_form, qnet[3].scale)
     assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
     assert _rel(y_int, y) < 0.06
+
+
+@pytest.mark.parametrize("stride,pad,opad,groups", [(2, 1, 1, 1), (1, 0, 0, 2), (3, 2, 1, 1)])
+def test_integer_conv_transpose_wiring_against_the_float_form(monkeypatch, stride, pad, opad, groups):
+    """``ConvTranspose2d`` on the integer convolution (input codes laid at stride distance into a
+    frame of the zero point's code, flipped / channel-swapped filters): the frame geometry and the
+    filter re-layout are host code, checked here against the float sequence of the same module."""
+    from lucid_b200 import backends
+
+    fake = abi_standin.install(monkeypatch, pose_as_cuda=True)
+    torch.manual_seed(40 + stride)
+    net = torch.nn.Sequential(Q.QuantStub(),
+                              torch.nn.ConvTranspose2d(32, 32, 3, stride, pad, opad, groups, True),
+                              Q.DeQuantStub()).eval()
+    x = torch.randn(2, 32, 7, 9) + 0.5
+    prepared = Q.prepare(net, _minmax_qconfig())
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    assert type(qnet[1]) is nnq.ConvTranspose2d and float(qnet[0].zero_point) != 0.0
+    with torch.no_grad():
+        y_float_form = qnet(x)
+        monkeypatch.setattr(backends.quantized, "_engine", "auto")
+        y_int = qnet(x)
+        assert fake.calls["conv"] >= 1  # the integer convolution ran
+        y = net(x)
+    assert y_int.shape == y.shape
+    steps = _steps_apart(y_int, y_float_form, qnet[1].scale)
+    assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
+    assert _rel(y_int, y) < 0.05
