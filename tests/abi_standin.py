@@ -7,7 +7,8 @@ the duration of one test, ``lucid_b200._lib.load`` by an object that implements 
 entry points those workflows touch (``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``,
 ``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather, and for the Linear
 family and the convolutions ``lq_rowsum_s8`` / ``lq_quantize_dynamic`` / ``lq_gemm_s8_ws`` /
-``lq_conv2d_nhwc_s8_ex``) in NumPy on host pointers,
+``lq_conv2d_nhwc_s8_ex``, and the merges / byte tables ``lq_qmerge`` / ``lq_lut_u8`` /
+``lq_lut2_u8``) in NumPy on host pointers,
 lifts the device checks, and switches the engine to ``"reference"`` by default so that layers run
 the reference's float sequence.  The arithmetic is the
 oracle's (same operation order); nothing here is importable from the package and nothing in the
@@ -195,6 +196,47 @@ class StandIn:
         m = g.N * g.P * g.Q
         got = self._epilogue(np.ascontiguousarray(acc).reshape(m, g.K).astype(np.int64), e, m, g.K)
         _arr(out, e.out_dtype, m * g.K).reshape(m, g.K)[...] = got
+        return 0
+
+    # ---- element-wise merges and byte tables ---------------------------------------------------
+    @staticmethod
+    def _operand(p, code, sp, zp, n):
+        v = _arr(p, code, n)
+        if code in (2, 3, 4):  # codes: decoded as lq_dequantize would
+            return ((v.astype(np.float32) - _arr(zp, 0, 1)[0]) * _arr(sp, 0, 1)[0]).astype(np.float32)
+        if code != 0:
+            raise NotImplementedError("the stand-in merges f32 values and integer codes")
+        return v
+
+    def lq_qmerge(self, op, x, xcode, xs, xz, y, ycode, ys, yz, y_scalar, n, out_scale, out_zp, qmin, qmax, out_codes,
+                  ccode, out_f32, stream):
+        self.calls["merge"] += 1
+        a = self._operand(x, xcode, xs, xz, n)
+        b = np.float32(_f(y_scalar)) if _addr(y) is None else self._operand(y, ycode, ys, yz, n)
+        t = a if op == 3 else ((a * b) if op == 1 else (a + b)).astype(np.float32)
+        if op == 2:
+            t = np.maximum(t, np.float32(0))
+        S, Z = _arr(out_scale, 0, 1)[0], _arr(out_zp, 0, 1)[0]
+        q = np.clip(np.rint((t / S).astype(np.float32)) + Z, qmin, qmax)
+        if _addr(out_codes) is not None:
+            _arr(out_codes, ccode, n)[...] = q.astype(_NP[ccode])
+        if _addr(out_f32) is not None:
+            _arr(out_f32, 0, n)[...] = ((q - Z) * S).astype(np.float32)
+        return 0
+
+    def lq_lut_u8(self, codes, n, table, out, stream):
+        self.calls["lut"] += 1
+        _arr(out, 3, n)[...] = _arr(table, 3, 256)[_arr(codes, 3, n)]
+        return 0
+
+    def lq_lut2_u8(self, x, y, n, table, out_codes, out_f32, out_scale, out_zp, is_signed, stream):
+        self.calls["lut2"] += 1
+        got = _arr(table, 3, 65536)[_arr(x, 3, n).astype(np.int64) * 256 + _arr(y, 3, n)]
+        if _addr(out_codes) is not None:
+            _arr(out_codes, 3, n)[...] = got
+        if _addr(out_f32) is not None:
+            q = got.view(np.int8).astype(np.float32) if is_signed else got.astype(np.float32)
+            _arr(out_f32, 0, n)[...] = ((q - _arr(out_zp, 0, 1)[0]) * _arr(out_scale, 0, 1)[0]).astype(np.float32)
         return 0
 
     def lq_gemm_workspace_bytes(self):

@@ -342,3 +342,48 @@ def test_integer_conv_transpose_wiring_against_the_float_form(monkeypatch, strid
     steps = _steps_apart(y_int, y_float_form, qnet[1].scale)
     assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 2e-3
     assert _rel(y_int, y) < 0.05
+
+
+class _Residual(torch.nn.Module):
+    """conv -> relu -> conv, + identity, relu: the block whose merge ``FloatFunctional`` marks."""
+
+    def __init__(self):
+        super().__init__()
+        self.quant, self.dequant = Q.QuantStub(), Q.DeQuantStub()
+        self.conv1, self.relu1 = torch.nn.Conv2d(16, 16, 3, padding=1), torch.nn.ReLU()
+        self.conv2 = torch.nn.Conv2d(16, 16, 3, padding=1)
+        self.skip = nnq.FloatFunctional()
+        self.act = torch.nn.Hardswish()
+
+    def forward(self, x):
+        x = self.quant(x)
+        y = self.conv2(self.relu1(self.conv1(x)))
+        return self.dequant(self.act(self.skip.add_relu(y, x)))
+
+
+def test_residual_block_with_merge_and_activation_tables(monkeypatch):
+    """A residual block end to end under engine "auto" over the stand-in: the merge reads both
+    operands as codes (the identity straight from the stub, on another grid than the branch), the
+    activation runs through its byte table, and the result equals the float sequence of the same
+    converted model up to isolated one-step differences
+    (lucid/nn/quantized/functional_module.py:230-258, activation.py:22-60)."""
+    from lucid_b200 import backends
+
+    fake = abi_standin.install(monkeypatch, pose_as_cuda=True)
+    torch.manual_seed(50)
+    net = _Residual().eval()
+    x = torch.randn(2, 16, 9, 9) + 0.2
+    prepared = Q.prepare(Q.fuse_modules(net, [["conv1", "relu1"]]), _minmax_qconfig())
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    assert type(qnet.skip) is nnq.QFunctional and type(qnet.act) is nnq.Hardswish
+    with torch.no_grad():
+        y_float_form = qnet(x)
+        monkeypatch.setattr(backends.quantized, "_engine", "auto")
+        y_int = qnet(x)
+        y = net(x)
+    assert fake.calls["conv"] >= 2 and (fake.calls["merge"] or fake.calls["lut2"]) and fake.calls["lut"] >= 1
+    steps = _steps_apart(y_int, y_float_form, qnet.act.scale)
+    assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 5e-3
+    assert _rel(y_int, y) < 0.06
