@@ -1,18 +1,21 @@
 """A NumPy stand-in for a handful of C-ABI entry points -- TEST INFRASTRUCTURE ONLY.
 
 The package has no CPU path: without the CUDA library every call raises.  The CPU test suite
-still wants to exercise the HOST logic of the workflows (what ``prepare_qat`` swaps, what
-``convert`` builds from a trained module, which grid ends up where).  ``install`` replaces, for
-the duration of one test, ``lucid_b200._lib.load`` by an object that implements the streaming
-entry points those workflows touch (``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``,
-``lq_minmax``, ``lq_calculate_qparams``, the plain ``lq_embedding_s8`` gather, and for the Linear
-family and the convolutions ``lq_rowsum_s8`` / ``lq_quantize_dynamic`` / ``lq_gemm_s8_ws`` /
-``lq_conv2d_nhwc_s8_ex``, and the merges / byte tables ``lq_qmerge`` / ``lq_lut_u8`` /
-``lq_lut2_u8``) in NumPy on host pointers,
-lifts the device checks, and switches the engine to ``"reference"`` by default so that layers run
-the reference's float sequence.  The arithmetic is the
-oracle's (same operation order); nothing here is importable from the package and nothing in the
-package knows about it."""
+still wants to exercise the HOST logic around the kernels (what ``prepare_qat`` swaps, what
+``convert`` builds from a trained module, which scale / zero point / row sum reaches which slot
+of an epilogue).  ``install`` replaces, for the duration of one test, ``lucid_b200._lib.load`` by
+an object that implements in NumPy, on host pointers, the entry points those paths touch:
+
+* streams: ``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``, ``lq_minmax``,
+  ``lq_calculate_qparams``, ``lq_quantize_dynamic``, the plain ``lq_embedding_s8`` gather;
+* contractions: ``lq_rowsum_s8``, ``lq_gemm_s8_ws``, ``lq_conv2d_nhwc_s8_ex`` (the oracle's exact
+  convolution), with the epilogue as ``include/lucid_b200.h`` states it;
+* merges and byte tables: ``lq_qmerge``, ``lq_lut_u8``, ``lq_lut2_u8``.
+
+It also lifts the device checks and sets the engine (``"reference"`` by default: layers run the
+reference's float sequence; ``"auto"`` runs the integer routes through the stand-in).  The
+arithmetic is the oracle's (same operation order).  Nothing here is importable from the package
+and nothing in the package knows about it."""
 
 from __future__ import annotations
 
