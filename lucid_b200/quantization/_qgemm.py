@@ -18,7 +18,7 @@ _GROUPS = (32, 64, 128)
 
 def is_available() -> bool:
     """The group-wise kernels are part of the library (lucid/quantization/_qgemm.py:24-66)."""
-    return _lib.available()
+    return _lib.is_available()
 
 
 def _check(bits: int, group_size: int, in_features: int) -> None:

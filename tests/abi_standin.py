@@ -10,7 +10,8 @@ an object that implements in NumPy, on host pointers, the entry points those pat
   ``lq_calculate_qparams``, ``lq_quantize_dynamic``, the plain ``lq_embedding_s8`` gather;
 * contractions: ``lq_rowsum_s8``, ``lq_gemm_s8_ws``, ``lq_conv2d_nhwc_s8_ex`` (the oracle's exact
   convolution), with the epilogue as ``include/lucid_b200.h`` states it;
-* merges and byte tables: ``lq_qmerge``, ``lq_lut_u8``, ``lq_lut2_u8``.
+* merges and byte tables: ``lq_qmerge``, ``lq_lut_u8``, ``lq_lut2_u8``;
+* the group-wise weight-only route: ``lq_groupwise_quantize`` / ``_dequantize`` / ``_matmul``.
 
 It also lifts the device checks and sets the engine (``"reference"`` by default: layers run the
 reference's float sequence; ``"auto"`` runs the integer routes through the stand-in).  The
@@ -240,6 +241,42 @@ class StandIn:
         if _addr(out_f32) is not None:
             q = got.view(np.int8).astype(np.float32) if is_signed else got.astype(np.float32)
             _arr(out_f32, 0, n)[...] = ((q - _arr(out_zp, 0, 1)[0]) * _arr(out_scale, 0, 1)[0]).astype(np.float32)
+        return 0
+
+    # ---- group-wise weight-only codes (the oracle's restatement) ---------------------------------
+    def lq_groupwise_quantize(self, w, n, k, group, bits, packed, scales, biases, stream):
+        from oracle import lucid_oracle as O
+
+        p, s, b = O.groupwise_quantize(_arr(w, 0, n * k).reshape(n, k), group, bits)
+        _arr(packed, 5, n * k * bits // 32).view(np.uint32)[...] = p.reshape(-1)
+        _arr(scales, 0, n * (k // group))[...] = s.reshape(-1)
+        _arr(biases, 0, n * (k // group))[...] = b.reshape(-1)
+        return 0
+
+    def _gw(self, packed, scales, biases, n, k, group, bits):
+        return (_arr(packed, 5, n * k * bits // 32).view(np.uint32).reshape(n, -1),
+                _arr(scales, 0, n * (k // group)).reshape(n, -1), _arr(biases, 0, n * (k // group)).reshape(n, -1))
+
+    def lq_groupwise_dequantize(self, packed, scales, biases, n, k, group, bits, out, stream):
+        from oracle import lucid_oracle as O
+
+        _arr(out, 0, n * k).reshape(n, k)[...] = O.groupwise_dequantize(*self._gw(packed, scales, biases, n, k, group, bits),
+                                                                         group, bits)
+        return 0
+
+    def lq_groupwise_matmul(self, x, xcode, m, ldx, packed, scales, biases, n, k, group, bits, bias, relu, out, ldo, stream):
+        from oracle import lucid_oracle as O
+
+        if xcode != 0 or ldx != k or ldo != n:
+            raise NotImplementedError("the stand-in multiplies dense f32 activations")
+        self.calls["groupwise"] += 1
+        y = O.groupwise_matmul_f64(_arr(x, 0, m * k).reshape(m, k), *self._gw(packed, scales, biases, n, k, group, bits),
+                                   group, bits)
+        if _addr(bias) is not None:
+            y = y + _arr(bias, 0, n)[None, :]
+        if relu:
+            y = np.maximum(y, 0.0)
+        _arr(out, 0, m * n).reshape(m, n)[...] = y.astype(np.float32)
         return 0
 
     def lq_gemm_workspace_bytes(self):

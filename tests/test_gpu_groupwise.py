@@ -76,6 +76,10 @@ def test_module_tracks_the_float_layer_and_round_trips(bits, gate):
     assert torch.equal(relu(x), torch.relu(yq))
 
 
+def test_the_route_reports_itself_available():
+    assert _qgemm.is_available() is True
+
+
 def test_bad_arguments_raise():
     w = torch.randn(8, 96, device="cuda")
     with pytest.raises(_lib.ShapeMismatch):

@@ -387,3 +387,41 @@ def test_residual_block_with_merge_and_activation_tables(monkeypatch):
     steps = _steps_apart(y_int, y_float_form, qnet.act.scale)
     assert float(steps.max()) <= 1.0 and float((steps > 0).float().mean()) < 5e-3
     assert _rel(y_int, y) < 0.06
+
+
+def test_group_wise_engine_routes_the_linear_family(monkeypatch):
+    """``engine = "mlx_group"`` (lucid/quantization/_quantize.py:116-179, lucid/backends/__init__.py:90-96):
+    ``convert`` builds the weight-only layer for Linear / LinearReLU with the bit width of the
+    qconfig's weight observer and the first of the group sizes 64, 128, 32 that divides
+    ``in_features``; a layer none divides keeps the calibrated layer; ``quantize_dynamic`` routes by
+    its ``dtype``.  Other modules are untouched by the engine."""
+    from lucid_b200 import backends
+    from lucid_b200.quantization import _qgemm
+    from lucid_b200.quantization._quantize import _mlx_group_size
+
+    assert [_mlx_group_size(k) for k in (64, 128, 192, 96, 32, 48, 100)] == [64, 64, 64, 32, 32, None, None]
+    assert _qgemm.is_available() is False  # no CUDA device here; the call itself must work
+    fake = abi_standin.install(monkeypatch, engine="mlx_group")
+    assert backends.quantized.use_mlx() and not backends.quantized.use_int8()
+    torch.manual_seed(60)
+    net = torch.nn.Sequential(Q.QuantStub(), torch.nn.Linear(96, 128), torch.nn.ReLU(), torch.nn.Linear(128, 48),
+                              torch.nn.Linear(48, 8), Q.DeQuantStub()).eval()
+    x = torch.randn(20, 96)
+    w4 = Q.QConfig(activation=Q.MinMaxObserver,
+                   weight=Q.PerChannelMinMaxObserver.with_args(qdtype=Q.qint4, qscheme=Q.per_channel_symmetric))
+    mapping = Q.QConfigMapping().set_global(_minmax_qconfig()).set_module_name("3", w4)
+    prepared = Q.prepare(Q.fuse_modules(net, [["1", "2"]]), mapping)
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    first, second, third = qnet[1], qnet[3], qnet[4]
+    assert type(first) is nnq.QuantizedLinearMLX and (first.bits, first.group_size, first.relu) == (8, 32, True)
+    assert type(second) is nnq.QuantizedLinearMLX and (second.bits, second.group_size, second.relu) == (4, 64, False)
+    assert type(third) is nnq.Linear  # 48 input features: no group size divides them
+    assert second.packed_weight.shape == (48, 128 * 4 // 32) and second.scales.shape == (48, 2)
+    with torch.no_grad():
+        y, y_q = net(x), qnet(x)
+    assert fake.calls["groupwise"] == 2
+    assert _rel(y_q, y) < 0.25  # the 4-bit layer dominates the error
+    dyn = Q.quantize_dynamic(torch.nn.Sequential(torch.nn.Linear(64, 16), torch.nn.Linear(48, 4)).eval())
+    assert type(dyn[0]) is nnq.QuantizedLinearMLX and type(dyn[1]) is nnq.dynamic.Linear
