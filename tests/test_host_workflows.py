@@ -425,3 +425,69 @@ def test_group_wise_engine_routes_the_linear_family(monkeypatch):
     assert _rel(y_q, y) < 0.25  # the 4-bit layer dominates the error
     dyn = Q.quantize_dynamic(torch.nn.Sequential(torch.nn.Linear(64, 16), torch.nn.Linear(48, 4)).eval())
     assert type(dyn[0]) is nnq.QuantizedLinearMLX and type(dyn[1]) is nnq.dynamic.Linear
+
+
+class _CatMul(torch.nn.Module):
+    """Two branches concatenated, a 1x1 mix, and a gate: cat / mul merges and a table activation."""
+
+    def __init__(self):
+        super().__init__()
+        self.quant, self.dequant = Q.QuantStub(), Q.DeQuantStub()
+        self.a, self.b = torch.nn.Conv2d(16, 16, 1), torch.nn.Conv2d(16, 16, 3, padding=1)
+        self.join, self.gate = nnq.FloatFunctional(), nnq.FloatFunctional()
+        self.sig, self.mix = torch.nn.Sigmoid(), torch.nn.Conv2d(32, 16, 1)
+
+    def forward(self, x):
+        x = self.quant(x)
+        y = self.mix(self.join.cat([self.a(x), self.b(x)], dim=1))
+        return self.dequant(self.gate.mul(y, self.sig(y)))
+
+
+def _sweep_cases():
+    seq, stub, unstub = torch.nn.Sequential, Q.QuantStub, Q.DeQuantStub
+    return {
+        "conv1d": (seq(stub(), torch.nn.Conv1d(16, 32, 5, padding=2), torch.nn.ReLU(), torch.nn.Conv1d(32, 16, 3, stride=2),
+                       unstub()), (2, 16, 20), [["1", "2"]]),
+        "conv3d": (seq(stub(), torch.nn.Conv3d(16, 16, 3, padding=1), torch.nn.ReLU(), unstub()), (2, 16, 5, 6, 7), [["1", "2"]]),
+        "conv_transpose1d": (seq(stub(), torch.nn.ConvTranspose1d(16, 16, 3, 2), unstub()), (2, 16, 9), None),
+        "conv_transpose3d": (seq(stub(), torch.nn.ConvTranspose3d(16, 8, 3, 2), unstub()), (2, 16, 4, 4, 4), None),
+        "cat_mul_sigmoid": (_CatMul(), (2, 16, 8, 8), None),
+        "activations": (seq(stub(), torch.nn.Linear(32, 32), torch.nn.Hardswish(), torch.nn.Linear(32, 32), torch.nn.Tanh(),
+                            torch.nn.Linear(32, 32), torch.nn.ELU(), torch.nn.Linear(32, 32), torch.nn.LeakyReLU(0.1),
+                            torch.nn.Linear(32, 16), torch.nn.Hardsigmoid(), unstub()), (40, 32), None),
+        "depthwise": (seq(stub(), torch.nn.Conv2d(16, 16, 3, padding=1, groups=16), torch.nn.Conv2d(16, 32, 1), unstub()),
+                      (2, 16, 8, 8), None),
+        "reflect_padding": (seq(stub(), torch.nn.Conv2d(16, 16, 3, padding=1, padding_mode="reflect"), unstub()),
+                            (2, 16, 8, 8), None),
+    }
+
+
+@pytest.mark.parametrize("engine", ["reference", "auto"])
+@pytest.mark.parametrize("case", sorted(_sweep_cases()))
+def test_every_module_family_converts_runs_and_round_trips(monkeypatch, case, engine):
+    """fuse -> prepare -> calibrate -> convert -> state_dict round trip -> forward for each module
+    family ``convert`` maps (lucid/quantization/_quantize.py:66-113), under the float engine and
+    under the integer one (layers outside the integer kernels' reach -- depthwise, reflect padding,
+    volumes, 1-D / 3-D transposed -- take their float route there)."""
+    import warnings
+
+    from lucid_b200 import backends
+
+    abi_standin.install(monkeypatch, pose_as_cuda=True)
+    torch.manual_seed(70)
+    net, shape, fuse = _sweep_cases()[case]
+    net.eval()
+    x = torch.randn(*shape)
+    prepared = Q.prepare(Q.fuse_modules(net, fuse) if fuse else net, _minmax_qconfig())
+    with torch.no_grad():
+        prepared(x)
+    qnet = Q.convert(prepared)
+    state = qnet.state_dict()
+    assert not any(k.endswith(".weight") for k in state)  # float weights are gone
+    qnet.load_state_dict(state)
+    monkeypatch.setattr(backends.quantized, "_engine", engine)
+    with torch.no_grad(), warnings.catch_warnings():
+        warnings.simplefilter("ignore")  # layers outside the integer path say so once
+        y, y_q = net(x), qnet(x)
+    assert y_q.shape == y.shape and bool(torch.isfinite(y_q).all())
+    assert _rel(y_q, y) < 0.05
