@@ -7,7 +7,7 @@ of an epilogue).  ``install`` replaces, for the duration of one test, ``lucid_b2
 an object that implements in NumPy, on host pointers, the entry points those paths touch:
 
 * streams: ``lq_quantize``, ``lq_dequantize``, ``lq_fake_quantize``, ``lq_minmax``,
-  ``lq_calculate_qparams``, ``lq_quantize_dynamic``, the plain ``lq_embedding_s8`` gather;
+  ``lq_calculate_qparams``, ``lq_histogram_observe``, ``lq_quantize_dynamic``, the plain ``lq_embedding_s8`` gather;
 * contractions: ``lq_rowsum_s8``, ``lq_gemm_s8_ws``, ``lq_conv2d_nhwc_s8_ex`` (the oracle's exact
   convolution), with the epilogue as ``include/lucid_b200.h`` states it;
 * merges and byte tables: ``lq_qmerge``, ``lq_lut_u8``, ``lq_lut2_u8``;
@@ -99,6 +99,18 @@ class StandIn:
             _arr(mn, 0, 1)[0] = X.min()
             _arr(mx, 0, 1)[0] = X.max()
         return 0
+
+    def lq_histogram_observe(self, x, code, n, bins, min_val, max_val, hist, ws, ws_bytes, stream):
+        """One HistogramObserver batch on the state behind the pointers (the oracle's step)."""
+        from oracle import lucid_oracle as O
+
+        mn, mx, h = _arr(min_val, 0, 1), _arr(max_val, 0, 1), _arr(hist, 0, bins)
+        state = None if not np.isfinite(mn[0]) else (float(mn[0]), float(mx[0]), h.copy())
+        mn[0], mx[0], h[...] = O.histogram_observe(_arr(x, code, n), state, bins)
+        return 0
+
+    def lq_histc_workspace_bytes(self):
+        return 64
 
     def lq_minmax_workspace_bytes(self):
         return 64
@@ -301,6 +313,7 @@ def install(monkeypatch, engine: str = "reference", pose_as_cuda: bool = False) 
     monkeypatch.setattr(_lib, "check_device_status_lazily", lambda device, every=256: None)
     monkeypatch.setattr(_lib, "minmax_workspace", lambda device: torch.zeros(64, dtype=torch.uint8))
     monkeypatch.setattr(_lib, "status_word", lambda device: torch.zeros(1, dtype=torch.int32))
+    monkeypatch.setattr(_lib, "histc_workspace", lambda device: torch.zeros(64, dtype=torch.uint8))
     monkeypatch.setattr(_lib, "ieee_float32", plain_float32)
     monkeypatch.setattr(torch.cuda, "device", lambda dev: contextlib.nullcontext())
     monkeypatch.setattr(_lib, "gemm_workspace", lambda device: torch.zeros(64, dtype=torch.uint8))

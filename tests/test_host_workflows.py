@@ -491,3 +491,33 @@ def test_every_module_family_converts_runs_and_round_trips(monkeypatch, case, en
         y, y_q = net(x), qnet(x)
     assert y_q.shape == y.shape and bool(torch.isfinite(y_q).all())
     assert _rel(y_q, y) < 0.05
+
+
+def test_default_static_ptq_uses_the_histogram_observer():
+    """``prepare(model)`` with no qconfig (lucid/quantization/qconfig.py:180-192): activations get a
+    ``HistogramObserver``, weights a per-channel min/max one; after two calibration batches with
+    different ranges the grids ``convert`` bakes are the ones the oracle derives from the same
+    batches (state kept on the module, clip search on the host)."""
+    import numpy as np
+
+    from oracle import lucid_oracle as O
+
+    torch.manual_seed(80)
+    net = torch.nn.Sequential(Q.QuantStub(), torch.nn.Linear(32, 16), Q.DeQuantStub()).eval()
+    prepared = Q.prepare(net)
+    assert isinstance(prepared[0].activation_post_process, Q.HistogramObserver)
+    assert isinstance(prepared[1].activation_post_process, Q.HistogramObserver)
+    batches = [torch.randn(64, 32), torch.randn(64, 32) * 3 + 1]
+    with torch.no_grad():
+        for b in batches:
+            prepared(b)
+    qnet = Q.convert(prepared)
+    state = None
+    for b in batches:
+        state = O.histogram_observe(b.numpy(), state, 2048)
+    s, z = O.histogram_qparams(state[0], state[1], state[2], False, O.QUINT8)
+    assert float(qnet[0].scale) == float(s) and float(qnet[0].zero_point) == float(z)
+    obs = prepared[0].activation_post_process
+    assert np.array_equal(obs.histogram.numpy(), state[2]) and float(obs.histogram.sum()) == 2 * 64 * 32
+    with torch.no_grad():
+        assert _rel(qnet(batches[1]), net(batches[1])) < 0.05
