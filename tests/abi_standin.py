@@ -11,6 +11,7 @@ an object that implements in NumPy, on host pointers, the entry points those pat
 * contractions: ``lq_rowsum_s8``, ``lq_gemm_s8_ws``, ``lq_conv2d_nhwc_s8_ex`` (the oracle's exact
   convolution), with the epilogue as ``include/lucid_b200.h`` states it;
 * merges and byte tables: ``lq_qmerge``, ``lq_lut_u8``, ``lq_lut2_u8``;
+* the recurrent cell ``lq_lstm_cell_f32``;
 * the group-wise weight-only route: ``lq_groupwise_quantize`` / ``_dequantize`` / ``_matmul``.
 
 It also lifts the device checks and sets the engine (``"reference"`` by default: layers run the
@@ -289,6 +290,18 @@ class StandIn:
         if relu:
             y = np.maximum(y, 0.0)
         _arr(out, 0, m * n).reshape(m, n)[...] = y.astype(np.float32)
+        return 0
+
+    def lq_lstm_cell_f32(self, gates, ldg, c_prev, h_out, ldh, c_out, batch, hidden, stream):
+        """c = sigmoid(f) * c_prev + sigmoid(i) * tanh(g); h = sigmoid(o) * tanh(c); gate order i, f, g, o."""
+        self.calls["lstm_cell"] += 1
+        if ldg != 4 * hidden or ldh != hidden:
+            raise NotImplementedError("the stand-in reads dense gates")
+        g = _arr(gates, 0, batch * 4 * hidden).reshape(batch, 4, hidden).astype(np.float64)
+        sig = lambda v: 1.0 / (1.0 + np.exp(-v))  # noqa: E731
+        c = sig(g[:, 1]) * _arr(c_prev, 0, batch * hidden).reshape(batch, hidden) + sig(g[:, 0]) * np.tanh(g[:, 2])
+        _arr(c_out, 0, batch * hidden).reshape(batch, hidden)[...] = c.astype(np.float32)
+        _arr(h_out, 0, batch * hidden).reshape(batch, hidden)[...] = (sig(g[:, 3]) * np.tanh(c)).astype(np.float32)
         return 0
 
     def lq_gemm_workspace_bytes(self):

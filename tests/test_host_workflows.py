@@ -521,3 +521,32 @@ def test_default_static_ptq_uses_the_histogram_observer():
     assert np.array_equal(obs.histogram.numpy(), state[2]) and float(obs.histogram.sum()) == 2 * 64 * 32
     with torch.no_grad():
         assert _rel(qnet(batches[1]), net(batches[1])) < 0.05
+
+
+@pytest.mark.parametrize("layers,bidirectional,batch_first", [(1, False, False), (2, True, True)])
+def test_dynamic_lstm_host_loop_against_the_float_layer(standin, layers, bidirectional, batch_first):
+    """The weight-only LSTM (lucid/nn/quantized/dynamic/rnn.py:27-111): layer / direction / time
+    loops, state hand-over and the reversed direction are host code around the cell kernel;
+    with the decoded weights loaded into a float ``nn.LSTM`` the two must agree to rounding."""
+    torch.manual_seed(90 + layers)
+    lstm = torch.nn.LSTM(12, 16, layers, batch_first=batch_first, bidirectional=bidirectional).eval()
+    model = torch.nn.Sequential()
+    model.add_module("rnn", lstm)
+    q = Q.quantize_dynamic(model).rnn
+    assert type(q) is nnq.dynamic.LSTM and q.weight_ih_l0_int8.dtype == torch.int8
+    twin = torch.nn.LSTM(12, 16, layers, batch_first=batch_first, bidirectional=bidirectional).eval()
+    with torch.no_grad():
+        for name, p in twin.named_parameters():
+            p.copy_(q._weight(name)[1] if name.startswith("weight") else getattr(q, name))
+    x = torch.randn(5, 7, 12)  # (batch, time, ...) or (time, batch, ...): both are 3-D
+    h0 = torch.randn(layers * (2 if bidirectional else 1), 5 if batch_first else 7, 16)
+    c0 = torch.randn_like(h0)
+    with torch.no_grad():
+        y, (h, c) = q(x, (h0, c0))
+        y_t, (h_t, c_t) = twin(x, (h0, c0))
+    n_dir = 2 if bidirectional else 1
+    assert standin.calls["lstm_cell"] == layers * n_dir * (7 if batch_first else 5)
+    for got, want in ((y, y_t), (h, h_t), (c, c_t)):
+        assert got.shape == want.shape and float((got - want).abs().max()) < 1e-5
+    with torch.no_grad():  # and the float layer it came from, to the weights' 8-bit grid
+        assert _rel(y, lstm(x, (h0, c0))[0]) < 0.05
